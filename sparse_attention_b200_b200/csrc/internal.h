@@ -1,0 +1,40 @@
+// Declarations shared by the translation units of libsparse_b200.so.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <cstdint>
+
+#define SB_OK 0
+#define SB_ERR_INVALID (-1)   // rejected argument (shape, alignment, null pointer ...)
+#define SB_ERR_CUDA (-2)      // a CUDA runtime / driver call failed
+#define SB_ERR_TIMEOUT (-3)   // a kernel gave up a bounded wait (see sparse_b200_device_status)
+
+namespace sb {
+
+// Per-device state created on first use (device current at that time).
+struct DeviceCtx {
+  int device = -1;
+  int sm_count = 0;
+  int* status = nullptr;      // device word written by kernels that abort a wait
+  int qc_attr_bf16 = 0, qc_attr_f32 = 0;
+  int misc_attr[8] = {0};
+};
+DeviceCtx* device_ctx();
+
+int set_error(int code, const char* message);   // stores a thread-local message, returns code
+
+int encode_tiled(CUtensorMap* map, CUtensorMapDataType type, int rank, void* ptr, const cuuint64_t* dims,
+                 const cuuint64_t* strides, const cuuint32_t* box, const cuuint32_t* steps,
+                 CUtensorMapSwizzle swizzle, CUtensorMapL2promotion promo);
+
+struct QCentricArgs {
+  const void *q, *k, *v;
+  const int32_t* block_idx;
+  const int32_t* block_count;
+  void* out;
+  float* lse;
+  int batch, hq, hkv, sq, skv, topk, nseg, out_f32;
+};
+int launch_q_centric(const QCentricArgs& a, cudaStream_t stream);
+
+}  // namespace sb

@@ -1,0 +1,560 @@
+// Q-centric block-sparse attention forward for sm_100a (B200).
+//
+// One persistent CTA per SM walks a static list of work items. An item is two
+// query streams of 128 rows each:
+//   * pair mode  (even GQA group size): two query heads of one KV-head group at
+//     the same query block. They share one selection list, so every selected K
+//     and V tile is fetched once and used by both streams.
+//   * split mode (group size 1 or odd): two neighbouring query blocks of one
+//     head, each with its own list and its own K/V tiles.
+// Roles: warps 0-3 softmax of stream 0, warps 4-7 softmax of stream 1, warp 8
+// issues tcgen05 MMAs, warp 9 issues TMA loads. K/V tiles selected by block
+// index are gathered by TMA into a ring of 32 KiB shared-memory slots; S = QK^T
+// and O += PV accumulate in tensor memory (S0,S1,O0,O1 = 512 columns); P is
+// written back over S as packed bf16 and fed to the PV MMA straight from
+// tensor memory. The ring, the Q buffers and all barriers stay live across
+// items, so loads of the next item overlap the tail of the current one.
+//
+// Replaces the reference kernels dense14_sparse_two_q_kernel
+// (attention/q_centric/01_block_sparse.cu:181) and dense14_sparse_gqa_kernel
+// (attention/q_centric/02_gqa_block_sparse.cu:178); adds LSE output, per-row
+// block counts, 64-bit output addressing and an outer "segment" dimension used
+// by the KV-centric operator and the cross-GPU KV split.
+#include "ptx.cuh"
+#include "internal.h"
+
+namespace sb {
+namespace qc {
+
+constexpr int TILE = 128;            // rows per Q tile and per KV block
+constexpr int HEAD_DIM = 128;
+constexpr int TILE_BYTES = TILE * HEAD_DIM * 2;   // 32 KiB
+constexpr int PANEL_BYTES = TILE * 128;            // 64-column half of a tile
+constexpr int RING = 5;              // K/V ring slots
+constexpr int NUM_THREADS = 320;
+constexpr int MMA_WARP = 8;
+constexpr int LOAD_WARP = 9;
+constexpr int TMEM_COLS = 512;
+constexpr float RESCALE_LOG2 = 8.0f;   // keep a stale row max while it lags by < 2^8
+
+// shared memory map (offsets from a 1024-aligned base)
+constexpr int OFF_Q = 0;
+constexpr int OFF_RING = 2 * TILE_BYTES;
+constexpr int OFF_BAR = OFF_RING + RING * TILE_BYTES;
+// barrier indices (8 bytes each)
+constexpr int BAR_Q_FULL = 0;      // [2]
+constexpr int BAR_Q_EMPTY = 2;     // [2]
+constexpr int BAR_S_FULL = 4;      // [2]
+constexpr int BAR_P_FULL = 6;      // [2]
+constexpr int BAR_O_FULL = 8;      // [2]
+constexpr int BAR_KV_FULL = 10;    // [RING]
+constexpr int BAR_KV_EMPTY = 10 + RING;  // [RING]
+constexpr int NUM_BARS = 10 + 2 * RING;
+constexpr int OFF_MISC = OFF_BAR + NUM_BARS * 8;   // tmem base (4 B), abort flag (4 B)
+constexpr int SMEM_BYTES = OFF_MISC + 16 + 1024;   // + slack for manual 1024 alignment
+
+struct Params {
+  const int32_t* ids;      // [nseg, B, Hkv, Qt, topk]
+  const int32_t* counts;   // [nseg, B, Hkv, Qt] or nullptr (= topk everywhere)
+  void* out;               // [nseg, B, Hq, Sq, 128] bf16 or fp32
+  float* lse;              // [nseg, B, Hq, Sq] or nullptr
+  int* status;
+  int batch, hq, hkv, sq, skv, topk, nseg;
+  int group, qt, pair_mode;
+  int items_per_seg, num_items;
+  float scale_log2;
+};
+
+struct Stream {
+  bool valid;          // this stream exists (split mode, odd tile count)
+  int count;           // live list entries
+  const int32_t* list; // its selection list
+  int q_row;           // first row in the 2-D view of Q
+  int kv_row;          // first row of its KV head in the 2-D view of K/V
+  long long out_row;   // first output row (64-bit: outputs may exceed 2^31 elements)
+};
+
+__device__ __forceinline__ void decode_item(const Params& p, int item, Stream (&s)[2]) {
+  const int seg = item / p.items_per_seg;
+  const int local = item - seg * p.items_per_seg;
+  if (p.pair_mode) {
+    const int pairs = p.group >> 1;
+    const int pair = local % pairs;
+    const int t = local / pairs;
+    const int qtile = t % p.qt;
+    const int bk = t / p.qt;            // batch * Hkv + kv head
+    const int b = bk / p.hkv, kvh = bk - b * p.hkv;
+    const long long row = (static_cast<long long>(seg) * p.batch * p.hkv + bk) * p.qt + qtile;
+    const int cnt = p.counts ? p.counts[row] : p.topk;
+#pragma unroll
+    for (int q = 0; q < 2; ++q) {
+      const int head = kvh * p.group + 2 * pair + q;
+      const int bh = b * p.hq + head;
+      s[q].valid = true;
+      s[q].count = cnt;
+      s[q].list = p.ids + row * p.topk;
+      s[q].q_row = bh * p.sq + qtile * TILE;
+      s[q].kv_row = bk * p.skv;
+      s[q].out_row = (static_cast<long long>(seg) * p.batch * p.hq + bh) * p.sq + qtile * TILE;
+    }
+  } else {
+    const int qpairs = (p.qt + 1) >> 1;
+    const int qp = local % qpairs;
+    const int bh = local / qpairs;      // batch * Hq + head
+    const int b = bh / p.hq, head = bh - b * p.hq;
+    const int kvh = head / p.group;
+    const int bk = b * p.hkv + kvh;
+#pragma unroll
+    for (int q = 0; q < 2; ++q) {
+      const int qtile = 2 * qp + q;
+      const bool valid = qtile < p.qt;
+      const long long row = (static_cast<long long>(seg) * p.batch * p.hkv + bk) * p.qt + (valid ? qtile : 0);
+      s[q].valid = valid;
+      s[q].count = valid ? (p.counts ? p.counts[row] : p.topk) : 0;
+      s[q].list = p.ids + row * p.topk;
+      s[q].q_row = bh * p.sq + qtile * TILE;
+      s[q].kv_row = bk * p.skv;
+      s[q].out_row = (static_cast<long long>(seg) * p.batch * p.hq + bh) * p.sq + qtile * TILE;
+    }
+  }
+  // counts come from the caller: clamp to the list capacity
+#pragma unroll
+  for (int q = 0; q < 2; ++q) s[q].count = min(max(s[q].count, 0), p.topk);
+}
+
+// One list cursor of the load warp: 32 ids cached across the lanes.
+struct IdCursor {
+  int cached;
+  __device__ __forceinline__ int get(const int32_t* list, int count, int i, int lane) {
+    if ((i & 31) == 0) cached = (i + lane < count) ? __ldg(list + i + lane) : 0;
+    return __shfl_sync(0xffffffffu, cached, i & 31);
+  }
+};
+
+template <bool OUT_F32>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+q_centric_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
+                 const __grid_constant__ CUtensorMap v_map, const Params p) {
+  extern __shared__ unsigned char smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  unsigned char* gbase = smem_raw + (base - raw);
+  const uint32_t bar0 = base + OFF_BAR;
+  volatile int* misc = reinterpret_cast<volatile int*>(gbase + OFF_MISC);
+  auto bar = [&](int i) { return bar0 + 8u * i; };
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  Guard guard{misc + 1, p.status};
+
+  if (threadIdx.x == 0) {
+    misc[1] = 0;
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(bar(BAR_Q_FULL + i), 1);
+      mbar_init(bar(BAR_Q_EMPTY + i), 1);
+      mbar_init(bar(BAR_S_FULL + i), 1);
+      mbar_init(bar(BAR_P_FULL + i), 4);   // one arrival per softmax warp
+      mbar_init(bar(BAR_O_FULL + i), 1);
+    }
+    for (int i = 0; i < RING; ++i) {
+      mbar_init(bar(BAR_KV_FULL + i), 1);
+      mbar_init(bar(BAR_KV_EMPTY + i), 1);
+    }
+    fence_mbar_init();
+  }
+  if (warp == MMA_WARP) {
+    tmem_alloc(smem_u32(const_cast<int*>(misc)), TMEM_COLS);
+    tmem_relinquish();
+  }
+  if (warp == LOAD_WARP && lane == 0) {
+    prefetch_tmap(&q_map);
+    prefetch_tmap(&k_map);
+    prefetch_tmap(&v_map);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = static_cast<uint32_t>(misc[0]);
+  // tensor memory columns: S0 0..127, S1 128..255, O0 256..383, O1 384..511.
+  // P (bf16 pairs) overwrites columns 0..63 of its S.
+
+  if (warp == LOAD_WARP) {
+    // ------------------------------------------------------------- TMA producer
+    uint32_t fills = 0;            // tiles pushed into the ring so far
+    uint32_t qloads[2] = {0, 0};
+    bool ok = true;
+    auto push = [&](const CUtensorMap* map, int row) -> bool {
+      const uint32_t slot = fills % RING, use = fills / RING;
+      if (use > 0) {
+        bool w = mbar_wait(bar(BAR_KV_EMPTY + slot), (use - 1) & 1, guard, 0x100 + slot);
+        if (!__all_sync(0xffffffffu, w)) return false;
+      }
+      if (lane == 0) {
+        const uint32_t dst = base + OFF_RING + slot * TILE_BYTES;
+        mbar_expect_tx(bar(BAR_KV_FULL + slot), TILE_BYTES);
+        tma_load_2d(dst, map, 0, row, bar(BAR_KV_FULL + slot));
+        tma_load_2d(dst + PANEL_BYTES, map, 64, row, bar(BAR_KV_FULL + slot));
+      }
+      ++fills;
+      return true;
+    };
+    auto push_q = [&](int q, int row) -> bool {
+      if (qloads[q] > 0) {
+        bool w = mbar_wait(bar(BAR_Q_EMPTY + q), (qloads[q] - 1) & 1, guard, 0x110 + q);
+        if (!__all_sync(0xffffffffu, w)) return false;
+      }
+      if (lane == 0) {
+        const uint32_t dst = base + OFF_Q + q * TILE_BYTES;
+        mbar_expect_tx(bar(BAR_Q_FULL + q), TILE_BYTES);
+        tma_load_2d(dst, &q_map, 0, row, bar(BAR_Q_FULL + q));
+        tma_load_2d(dst + PANEL_BYTES, &q_map, 64, row, bar(BAR_Q_FULL + q));
+      }
+      ++qloads[q];
+      return true;
+    };
+    for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x) {
+      Stream s[2];
+      decode_item(p, item, s);
+      IdCursor kc[2], vc[2];
+      kc[0].cached = kc[1].cached = vc[0].cached = vc[1].cached = 0;
+      if (p.pair_mode) {
+        const int n = s[0].count;
+        if (n == 0) continue;
+        ok = push_q(0, s[0].q_row) && push_q(1, s[1].q_row);
+        if (!ok) break;
+        ok = push(&k_map, s[0].kv_row + kc[0].get(s[0].list, n, 0, lane) * TILE);
+        for (int i = 0; ok && i < n; ++i) {
+          ok = push(&v_map, s[0].kv_row + vc[0].get(s[0].list, n, i, lane) * TILE);
+          if (ok && i + 1 < n)
+            ok = push(&k_map, s[0].kv_row + kc[0].get(s[0].list, n, i + 1, lane) * TILE);
+        }
+      } else {
+        for (int q = 0; ok && q < 2; ++q)
+          if (s[q].count > 0) {
+            ok = push_q(q, s[q].q_row) &&
+                 push(&k_map, s[q].kv_row + kc[q].get(s[q].list, s[q].count, 0, lane) * TILE);
+          }
+        const int n = max(s[0].count, s[1].count);
+        for (int i = 0; ok && i < n; ++i)
+          for (int q = 0; ok && q < 2; ++q)
+            if (i < s[q].count) {
+              ok = push(&v_map, s[q].kv_row + vc[q].get(s[q].list, s[q].count, i, lane) * TILE);
+              if (ok && i + 1 < s[q].count)
+                ok = push(&k_map, s[q].kv_row + kc[q].get(s[q].list, s[q].count, i + 1, lane) * TILE);
+            }
+      }
+    }
+    if (!ok) {
+      // Let copies already in flight land before the CTA gives up its shared memory.
+      for (uint32_t f = (fills > RING ? fills - RING : 0); f < fills; ++f)
+        mbar_wait_drain(bar(BAR_KV_FULL + f % RING), (f / RING) & 1);
+      for (int q = 0; q < 2; ++q)
+        if (qloads[q] > 0) mbar_wait_drain(bar(BAR_Q_FULL + q), (qloads[q] - 1) & 1);
+    }
+  } else if (warp == MMA_WARP) {
+    // ------------------------------------------------------------- MMA issuer
+    constexpr uint32_t IDESC_QK = idesc_bf16(TILE, TILE, false);
+    constexpr uint32_t IDESC_PV = idesc_bf16(TILE, HEAD_DIM, true);
+    uint32_t taken = 0;            // ring tiles consumed so far
+    uint32_t qtaken[2] = {0, 0};
+    uint32_t pphase[2] = {0, 0};
+    bool ok = true;
+    auto acquire = [&](uint32_t& slot) -> bool {
+      slot = taken % RING;
+      bool w = mbar_wait(bar(BAR_KV_FULL + slot), (taken / RING) & 1, guard, 0x200 + slot);
+      ++taken;
+      w = __all_sync(0xffffffffu, w);
+      tc_fence_after();
+      return w;
+    };
+    auto wait_q = [&](int q) -> bool {
+      bool w = mbar_wait(bar(BAR_Q_FULL + q), qtaken[q] & 1, guard, 0x210 + q);
+      ++qtaken[q];
+      w = __all_sync(0xffffffffu, w);
+      tc_fence_after();
+      return w;
+    };
+    auto wait_p = [&](int q) -> bool {
+      bool w = mbar_wait(bar(BAR_P_FULL + q), pphase[q], guard, 0x220 + q);
+      pphase[q] ^= 1;
+      w = __all_sync(0xffffffffu, w);
+      tc_fence_after();
+      return w;
+    };
+    // S_q = Q_q K^T : 8 MMAs of K = 16 over two 64-column panels.
+    auto issue_qk = [&](int q, uint32_t slot) {
+      if (lane == 0) {
+        const uint64_t a0 = desc_sw128_kmajor(base + OFF_Q + q * TILE_BYTES);
+        const uint64_t b0 = desc_sw128_kmajor(base + OFF_RING + slot * TILE_BYTES);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint64_t step = static_cast<uint64_t>((kk >> 2) * (PANEL_BYTES >> 4) + (kk & 3) * 2);
+          mma_ss(tmem + q * TILE, a0 + step, b0 + step, IDESC_QK, kk > 0);
+        }
+      }
+    };
+    // O_q (+)= P_q V : A from tensor memory (8 columns per K = 16), B = V MN-major.
+    auto issue_pv = [&](int q, uint32_t slot, bool accumulate) {
+      if (lane == 0) {
+        const uint64_t b0 = desc_sw128_mnmajor(base + OFF_RING + slot * TILE_BYTES, PANEL_BYTES, 1024);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)
+          mma_ts(tmem + 256 + q * HEAD_DIM, tmem + q * TILE + kk * 8,
+                 b0 + static_cast<uint64_t>(kk * (2048 >> 4)), IDESC_PV, (accumulate || kk > 0) ? 1u : 0u);
+      }
+    };
+    auto commit = [&](int b) { if (lane == 0) tc_commit(bar(b)); };
+
+    for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x) {
+      Stream s[2];
+      decode_item(p, item, s);
+      uint32_t kslot = 0, vslot = 0;
+      if (p.pair_mode) {
+        const int n = s[0].count;
+        if (n == 0) continue;
+        ok = wait_q(0) && wait_q(1) && acquire(kslot);
+        if (!ok) break;
+        issue_qk(0, kslot); commit(BAR_S_FULL + 0);
+        issue_qk(1, kslot); commit(BAR_S_FULL + 1);
+        commit(BAR_KV_EMPTY + kslot);
+        if (n == 1) { commit(BAR_Q_EMPTY + 0); commit(BAR_Q_EMPTY + 1); }
+        for (int i = 0; ok && i < n; ++i) {
+          const bool more = i + 1 < n;
+          ok = acquire(vslot) && wait_p(0);
+          if (!ok) break;
+          issue_pv(0, vslot, i > 0);
+          if (more) {
+            ok = acquire(kslot);
+            if (!ok) break;
+            issue_qk(0, kslot); commit(BAR_S_FULL + 0);
+          } else {
+            commit(BAR_O_FULL + 0);
+          }
+          ok = wait_p(1);
+          if (!ok) break;
+          issue_pv(1, vslot, i > 0);
+          commit(BAR_KV_EMPTY + vslot);
+          if (more) {
+            issue_qk(1, kslot); commit(BAR_S_FULL + 1);
+            commit(BAR_KV_EMPTY + kslot);
+            if (i + 2 == n) { commit(BAR_Q_EMPTY + 0); commit(BAR_Q_EMPTY + 1); }
+          } else {
+            commit(BAR_O_FULL + 1);
+          }
+        }
+      } else {
+        for (int q = 0; ok && q < 2; ++q)
+          if (s[q].count > 0) {
+            ok = wait_q(q) && acquire(kslot);
+            if (!ok) break;
+            issue_qk(q, kslot); commit(BAR_S_FULL + q);
+            commit(BAR_KV_EMPTY + kslot);
+            if (s[q].count == 1) commit(BAR_Q_EMPTY + q);
+          }
+        const int n = max(s[0].count, s[1].count);
+        for (int i = 0; ok && i < n; ++i)
+          for (int q = 0; ok && q < 2; ++q)
+            if (i < s[q].count) {
+              ok = acquire(vslot) && wait_p(q);
+              if (!ok) break;
+              issue_pv(q, vslot, i > 0);
+              commit(BAR_KV_EMPTY + vslot);
+              if (i + 1 < s[q].count) {
+                ok = acquire(kslot);
+                if (!ok) break;
+                issue_qk(q, kslot); commit(BAR_S_FULL + q);
+                commit(BAR_KV_EMPTY + kslot);
+                if (i + 2 == s[q].count) commit(BAR_Q_EMPTY + q);
+              } else {
+                commit(BAR_O_FULL + q);
+              }
+            }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------- softmax + epilogue
+    const int q = warp >> 2;                       // stream
+    const int row_in_tile = (warp & 3) * 32 + lane;
+    const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const uint32_t t_s = tmem + lane_base + q * TILE;
+    const uint32_t t_o = tmem + lane_base + 256 + q * HEAD_DIM;
+    uint32_t sphase = 0, ophase = 0;
+    bool ok = true;
+    for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x) {
+      Stream s[2];
+      decode_item(p, item, s);
+      const Stream& me = s[q];
+      if (!me.valid) continue;
+      const long long orow = me.out_row + row_in_tile;
+      if (me.count == 0) {
+        // empty list: neutral element of the log-sum-exp merge
+        if (OUT_F32) {
+          float4* dst = reinterpret_cast<float4*>(static_cast<float*>(p.out) + orow * HEAD_DIM);
+          for (int c = 0; c < HEAD_DIM / 4; ++c) dst[c] = make_float4(0.f, 0.f, 0.f, 0.f);
+        } else {
+          uint4* dst = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.out) + orow * HEAD_DIM);
+          for (int c = 0; c < HEAD_DIM / 8; ++c) dst[c] = make_uint4(0u, 0u, 0u, 0u);
+        }
+        if (p.lse) p.lse[orow] = -INFINITY;
+        continue;
+      }
+      float row_max = 0.f, row_sum = 0.f;
+      for (int i = 0; i < me.count; ++i) {
+        bool w = mbar_wait(bar(BAR_S_FULL + q), sphase, guard, 0x300 + q);
+        sphase ^= 1;
+        ok = __all_sync(0xffffffffu, w);
+        if (!ok) break;
+        tc_fence_after();
+        uint32_t sv[4][32];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) tmem_ld32(t_s + c * 32, sv[c]);
+        tc_wait_ld();
+        float tile_max = -INFINITY;
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+          for (int j = 0; j < 32; ++j) tile_max = fmaxf(tile_max, __uint_as_float(sv[c][j]));
+        tile_max *= p.scale_log2;
+        // Lazy rescale: keep a stale row max while the true max is less than
+        // 2^RESCALE_LOG2 above it (P stays finite in bf16, the sum in fp32).
+        float factor = 1.0f;
+        if (i == 0) {
+          row_max = tile_max;
+        } else if (tile_max - row_max > RESCALE_LOG2) {
+          factor = ex2_approx(row_max - tile_max);
+          row_max = tile_max;
+          row_sum *= factor;
+        }
+        // O of this stream is idle here: the PV MMA of the previous tile was
+        // issued before the QK MMA whose commit released these scores, so it
+        // has completed, and the next PV waits for the arrival below.
+        if (i > 0 && __any_sync(0xffffffffu, factor != 1.0f)) {
+#pragma unroll 1
+          for (int c = 0; c < 4; ++c) {
+            uint32_t ov[32];
+            tmem_ld32(t_o + c * 32, ov);
+            tc_wait_ld();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) ov[j] = __float_as_uint(__uint_as_float(ov[j]) * factor);
+            tmem_st32(t_o + c * 32, ov);
+          }
+        }
+        float tile_sum = 0.f;
+        const float neg_max = -row_max;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t pk[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const float p0 = ex2_approx(fmaf(__uint_as_float(sv[c][2 * j]), p.scale_log2, neg_max));
+            const float p1 = ex2_approx(fmaf(__uint_as_float(sv[c][2 * j + 1]), p.scale_log2, neg_max));
+            tile_sum += p0 + p1;
+            pk[j] = pack_bf16x2(p0, p1);
+          }
+          tmem_st16(t_s + c * 16, pk);
+        }
+        row_sum += tile_sum;
+        tc_wait_st();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(BAR_P_FULL + q));
+      }
+      if (!ok) break;
+      {
+        bool w = mbar_wait(bar(BAR_O_FULL + q), ophase, guard, 0x310 + q);
+        ophase ^= 1;
+        ok = __all_sync(0xffffffffu, w);
+        if (!ok) break;
+        tc_fence_after();
+      }
+      const float inv = 1.0f / row_sum;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t ov[32];
+        tmem_ld32(t_o + c * 32, ov);
+        tc_wait_ld();
+        if (OUT_F32) {
+          float4* dst = reinterpret_cast<float4*>(static_cast<float*>(p.out) + orow * HEAD_DIM + c * 32);
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            dst[j] = make_float4(__uint_as_float(ov[4 * j]) * inv, __uint_as_float(ov[4 * j + 1]) * inv,
+                                 __uint_as_float(ov[4 * j + 2]) * inv, __uint_as_float(ov[4 * j + 3]) * inv);
+        } else {
+          uint4* dst = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.out) + orow * HEAD_DIM + c * 32);
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            dst[j] = make_uint4(
+                pack_bf16x2(__uint_as_float(ov[8 * j]) * inv, __uint_as_float(ov[8 * j + 1]) * inv),
+                pack_bf16x2(__uint_as_float(ov[8 * j + 2]) * inv, __uint_as_float(ov[8 * j + 3]) * inv),
+                pack_bf16x2(__uint_as_float(ov[8 * j + 4]) * inv, __uint_as_float(ov[8 * j + 5]) * inv),
+                pack_bf16x2(__uint_as_float(ov[8 * j + 6]) * inv, __uint_as_float(ov[8 * j + 7]) * inv));
+        }
+      }
+      if (p.lse) p.lse[orow] = (row_max + log2f(row_sum)) * 0.6931471805599453f;
+      tc_fence_before();
+    }
+  }
+
+  // ---------------------------------------------------------------- teardown
+  tc_fence_before();
+  __syncthreads();
+  if (warp == MMA_WARP) {
+    tc_fence_after();
+    tmem_dealloc(tmem, TMEM_COLS);
+  }
+}
+
+// ------------------------------------------------------------------ host side
+static int encode_rows_map(CUtensorMap* map, const void* ptr, uint64_t rows) {
+  const cuuint64_t dims[2] = {HEAD_DIM, rows};
+  const cuuint64_t strides[1] = {HEAD_DIM * 2};
+  const cuuint32_t box[2] = {64, TILE};
+  const cuuint32_t steps[2] = {1, 1};
+  return encode_tiled(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box,
+                      steps, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
+}
+
+}  // namespace qc
+
+int launch_q_centric(const QCentricArgs& a, cudaStream_t stream) {
+  using namespace qc;
+  DeviceCtx* ctx = device_ctx();
+  if (!ctx) return SB_ERR_CUDA;
+  const int group = a.hq / a.hkv;
+  Params p{};
+  p.ids = a.block_idx;
+  p.counts = a.block_count;
+  p.out = a.out;
+  p.lse = a.lse;
+  p.status = ctx->status;
+  p.batch = a.batch; p.hq = a.hq; p.hkv = a.hkv; p.sq = a.sq; p.skv = a.skv;
+  p.topk = a.topk; p.nseg = a.nseg;
+  p.group = group;
+  p.qt = a.sq / TILE;
+  p.pair_mode = (group % 2 == 0) ? 1 : 0;
+  p.items_per_seg = p.pair_mode ? a.batch * a.hkv * p.qt * (group / 2)
+                                : a.batch * a.hq * ((p.qt + 1) / 2);
+  p.num_items = p.items_per_seg * a.nseg;
+  p.scale_log2 = 1.4426950408889634f / sqrtf(static_cast<float>(HEAD_DIM));
+
+  CUtensorMap qm, km, vm;
+  if (encode_rows_map(&qm, a.q, static_cast<uint64_t>(a.batch) * a.hq * a.sq) ||
+      encode_rows_map(&km, a.k, static_cast<uint64_t>(a.batch) * a.hkv * a.skv) ||
+      encode_rows_map(&vm, a.v, static_cast<uint64_t>(a.batch) * a.hkv * a.skv))
+    return set_error(SB_ERR_CUDA, "cuTensorMapEncodeTiled failed for q/k/v");
+
+  auto kernel = a.out_f32 ? q_centric_kernel<true> : q_centric_kernel<false>;
+  int& configured = a.out_f32 ? ctx->qc_attr_f32 : ctx->qc_attr_bf16;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    if (e != cudaSuccess) return set_error(SB_ERR_CUDA, cudaGetErrorString(e));
+    configured = 1;
+  }
+  const int grid = p.num_items < ctx->sm_count ? p.num_items : ctx->sm_count;
+  kernel<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(qm, km, vm, p);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return set_error(SB_ERR_CUDA, cudaGetErrorString(e));
+  return SB_OK;
+}
+
+}  // namespace sb
