@@ -409,11 +409,16 @@ q_centric_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
 #pragma unroll
         for (int c = 0; c < 4; ++c) tmem_ld32(t_s + c * 32, sv[c]);
         tc_wait_ld();
-        float tile_max = -INFINITY;
+        // eight independent running maxima keep the dependency chain short
+        float mx[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) mx[j] = __uint_as_float(sv[0][j]);
 #pragma unroll
         for (int c = 0; c < 4; ++c)
 #pragma unroll
-          for (int j = 0; j < 32; ++j) tile_max = fmaxf(tile_max, __uint_as_float(sv[c][j]));
+          for (int j = (c == 0 ? 8 : 0); j < 32; ++j) mx[j & 7] = fmaxf(mx[j & 7], __uint_as_float(sv[c][j]));
+        float tile_max = fmaxf(fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])),
+                               fmaxf(fmaxf(mx[4], mx[5]), fmaxf(mx[6], mx[7])));
         tile_max *= p.scale_log2;
         // Lazy rescale: keep a stale row max while the true max is less than
         // 2^RESCALE_LOG2 above it (P stays finite in bf16, the sum in fp32).
@@ -439,7 +444,7 @@ q_centric_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
             tmem_st32(t_o + c * 32, ov);
           }
         }
-        float tile_sum = 0.f;
+        float part[4] = {0.f, 0.f, 0.f, 0.f};
         const float neg_max = -row_max;
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
@@ -448,12 +453,12 @@ q_centric_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
           for (int j = 0; j < 16; ++j) {
             const float p0 = ex2_approx(fmaf(__uint_as_float(sv[c][2 * j]), p.scale_log2, neg_max));
             const float p1 = ex2_approx(fmaf(__uint_as_float(sv[c][2 * j + 1]), p.scale_log2, neg_max));
-            tile_sum += p0 + p1;
+            part[j & 3] += p0 + p1;
             pk[j] = pack_bf16x2(p0, p1);
           }
           tmem_st16(t_s + c * 16, pk);
         }
-        row_sum += tile_sum;
+        row_sum += (part[0] + part[1]) + (part[2] + part[3]);
         tc_wait_st();
         tc_fence_before();
         __syncwarp();
