@@ -59,6 +59,87 @@ int sparse_b200_q_centric_partial(const void* q, const void* k, const void* v, c
                                   int nseg, int partial_is_f32, int batch, int hq, int hkv, int sq, int skv,
                                   int topk, void* stream);
 
+/* Log-sum-exp merge of `ranks` normalised partial outputs per row:
+ * out[row] = sum_r exp(L_r - L) O_r, out_lse[row] = L = logsumexp_r L_r, ranks
+ * accumulated in order. rank_major != 0: partial [ranks, rows, 128] and
+ * partial_lse [ranks, rows] (what sparse_b200_q_centric_partial writes);
+ * rank_major == 0: partial [rows, ranks, 128], partial_lse [rows, ranks] (the
+ * layout of kv11_launch_combine_f32 / _bf16,
+ * attention/kv_centric/optimization_round11/combine11.cu:63-72, which this
+ * replaces for any rank count). A rank with LSE = -inf is ignored. out is bf16
+ * [rows, 128]; out_lse may be NULL. Also merges the partials of a KV split
+ * across GPUs once they are in local memory. */
+int sparse_b200_combine(const void* partial, int partial_is_f32, const float* partial_lse, void* out, float* out_lse,
+                        int64_t rows, int ranks, int rank_major, void* stream);
+
+/* Scheduling metadata of the KV-centric operator: cut every selection list into
+ * nseg KV ranges of ceil(kv_blocks/nseg) blocks. seg_block_idx
+ * [nseg, B, Hkv, q_blocks, TopK], seg_block_count [nseg, B, Hkv, q_blocks];
+ * error_word gets bit 1 if an id lies outside [0, kv_blocks) (the caller zeroes
+ * it). Role of kv4_build_metadata
+ * (attention/kv_centric/optimization_round4/gpu_metadata.cu:82-108). */
+int sparse_b200_split_kv_segments(const int32_t* block_idx, const int32_t* block_count, int32_t* seg_block_idx,
+                                  int32_t* seg_block_count, int32_t* error_word, int batch, int hkv, int q_blocks,
+                                  int topk, int kv_blocks, int nseg, void* stream);
+
+/* Whole KV-centric operator = metadata + main + combine on one stream, the
+ * sequence of Prepared.run() (attention/kv_centric/optimization_round11/api11.py:85-92).
+ * KV ranges are processed outer; each (query block, KV range) yields one partial
+ * (O, LSE), merged per query. `workspace` (device, 256-byte aligned) must hold
+ * sparse_b200_kv_centric_workspace_bytes(...) bytes; nothing is allocated. */
+int64_t sparse_b200_kv_centric_workspace_bytes(int batch, int hq, int hkv, int sq, int topk, int nseg,
+                                               int partial_is_f32);
+int sparse_b200_kv_centric(const void* q, const void* k, const void* v, const int32_t* block_idx,
+                           const int32_t* block_count, void* out, float* lse, void* workspace,
+                           int64_t workspace_bytes, int nseg, int partial_is_f32, int batch, int hq, int hkv, int sq,
+                           int skv, int topk, void* stream);
+
+/* R1 / R4 block-summary indexer (indexers/r1_r4/gpu_ops.py:6-49,
+ * indexers/r1_r4/block_selectors.py:9-45), any Hkv, group size x R <= 64, any TopK.
+ * pool_blocks: x [B, H, S, 128] bf16 -> desc [B, H, S/128, R, 128] bf16, the
+ * fp32 mean of 128/R consecutive tokens summed in token order.
+ * summary_select: score[b, kvh, qb, kb] = 128^-0.5 * max over (heads of the
+ * group, R x R representatives) of the descriptor dot product (fp32, feature
+ * order); block_idx [B, Hkv, q_blocks, TopK] = top-k by (score descending, id
+ * ascending); scores [B, Hkv, q_blocks, kv_blocks] fp32 is optional (NULL).
+ * indexer_summary = pool(q), pool(k), select: the whole SummarySelector.run(). */
+int sparse_b200_pool_blocks(const void* x, void* desc, int batch, int heads, int seq, int representatives,
+                            void* stream);
+int sparse_b200_summary_select(const void* q_desc, const void* k_desc, float* scores, int32_t* block_idx, int batch,
+                               int hq, int hkv, int q_blocks, int kv_blocks, int representatives, int topk,
+                               void* stream);
+int sparse_b200_indexer_summary(const void* q, const void* k, void* q_desc, void* k_desc, float* scores,
+                                int32_t* block_idx, int batch, int hq, int hkv, int sq, int skv, int representatives,
+                                int topk, void* stream);
+
+/* NVFP4 indexer. Index vectors: 64 bytes of e2m1 codes (low nibble first) + 8
+ * e4m3 scales per 128 features (contract of prepare_fp4_inputs,
+ * indexers/fp4/fp4.py:37-60). q_codes [B*Sq, Hidx, 64], q_scales [B*Sq, Hidx, 8],
+ * k_codes [B*Skv/128, Hk, 128, 64], k_scales [B*Skv/128, Hk, 128, 8], Hk = 1 or Hidx.
+ * nvfp4_quantize: x [B, heads_out*group, S, 128] bf16 -> codes and scales of the
+ * mean over each `group` of heads; paged = 0 writes the query layout, 1 the key
+ * page layout. (No counterpart in the reference, which feeds random bytes.)
+ * fp4_scores: query_scores [Hidx, Skv/128, B*Sq] = max over the keys of a page
+ * (what fp4_indexer_block_scores returns, indexers/fp4/fp4.py:122-134) and / or
+ * tile_scores [B, Hidx, Sq/128, Skv/128] = max over the queries of a tile too.
+ * tile_topk: query_scores -> block_idx [B, H, Sq/128, TopK]
+ * (fp4_tile_topk_launch, indexers/fp4/tile_topk.cu:130-153, any TopK).
+ * row_topk: tile_scores [rows, kv_tiles] -> block_idx [rows, TopK].
+ * indexer_fp4 = fp4_scores(tile) + row_topk: fp4_indexer() of fp4.py:137-146
+ * without materialising per-query scores. */
+int sparse_b200_nvfp4_quantize(const void* x, void* packed, void* scales, int batch, int heads_out, int group,
+                               int seq, int paged, void* stream);
+int sparse_b200_fp4_scores(const void* q_codes, const void* q_scales, const void* k_codes, const void* k_scales,
+                           float* query_scores, float* tile_scores, int batch, int hidx, int hk, int len_q, int len_kv,
+                           void* stream);
+int sparse_b200_tile_topk(const float* query_scores, int32_t* block_idx, int batch, int heads, int len_q, int kv_tiles,
+                          int topk, void* stream);
+int sparse_b200_row_topk(const float* tile_scores, int32_t* block_idx, int64_t rows, int kv_tiles, int topk,
+                         void* stream);
+int sparse_b200_indexer_fp4(const void* q_codes, const void* q_scales, const void* k_codes, const void* k_scales,
+                            float* tile_scores, int32_t* block_idx, int batch, int hidx, int hk, int len_q, int len_kv,
+                            int topk, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

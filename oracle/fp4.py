@@ -60,6 +60,33 @@ def quantize_nvfp4(x):
 
 
 @torch.no_grad()
+def group_mean(x, heads_out):
+    """[B,H,S,128] -> fp32 [B,heads_out,S,128]: mean of each group of H/heads_out
+    consecutive heads, summed in head order then divided (IEEE fp32)."""
+    b, h, s, d = x.shape
+    g = h // heads_out
+    xf = x.float().reshape(b, heads_out, g, s, d)
+    acc = torch.zeros((b, heads_out, s, d), dtype=torch.float32)
+    for i in range(g):
+        acc = acc + xf[:, :, i]
+    return acc / float(g) if g > 1 else acc
+
+
+def quantize_queries(q, hidx):
+    """q [B,Hq,Sq,128] -> (codes [B*Sq,hidx,64], scales [B*Sq,hidx,8]), token-major."""
+    b, _, sq, _ = q.shape
+    m = group_mean(q, hidx).permute(0, 2, 1, 3).reshape(b * sq, hidx, 128)
+    return quantize_nvfp4(m)
+
+
+def quantize_keys(k):
+    """k [B,Hkv,Skv,128] -> paged (codes [B*Skv/128,Hkv,128,64], scales [...,8])."""
+    b, h, skv, _ = k.shape
+    paged = k.float().reshape(b, h, skv // 128, 128, 128).permute(0, 2, 1, 3, 4).reshape(b * skv // 128, h, 128, 128)
+    return quantize_nvfp4(paged)
+
+
+@torch.no_grad()
 def dequantize_nvfp4(packed, scales):
     """fp4_reference.py:4-14."""
     codes = torch.stack((packed & 15, packed >> 4), dim=-1).reshape(*packed.shape[:-1], 128).long()

@@ -128,4 +128,180 @@ int sparse_b200_q_centric_partial(const void* q, const void* k, const void* v, c
   return launch_q_centric(a, static_cast<cudaStream_t>(stream));
 }
 
+int sparse_b200_combine(const void* partial, int partial_is_f32, const float* partial_lse, void* out, float* out_lse,
+                        int64_t rows, int ranks, int rank_major, void* stream) {
+  REQUIRE(partial && partial_lse && out, "partial, partial_lse and out must be non-null device pointers");
+  REQUIRE(rows > 0 && ranks > 0, "rows and ranks must be positive");
+  REQUIRE(aligned16(partial) && aligned16(out), "partial and out must be 16-byte aligned");
+  const long long psr = rank_major ? rows * 128 : 128, psw = rank_major ? 128 : static_cast<long long>(ranks) * 128;
+  const long long lsr = rank_major ? rows : 1, lsw = rank_major ? 1 : ranks;
+  return launch_combine(partial, partial_is_f32, partial_lse, out, out_lse, rows, ranks, psr, psw, lsr, lsw,
+                        static_cast<cudaStream_t>(stream));
+}
+
+int sparse_b200_split_kv_segments(const int32_t* block_idx, const int32_t* block_count, int32_t* seg_block_idx,
+                                  int32_t* seg_block_count, int32_t* error_word, int batch, int hkv, int q_blocks,
+                                  int topk, int kv_blocks, int nseg, void* stream) {
+  REQUIRE(block_idx && seg_block_idx && seg_block_count && error_word, "null pointer");
+  REQUIRE(batch > 0 && hkv > 0 && q_blocks > 0 && topk > 0 && kv_blocks > 0, "sizes must be positive");
+  REQUIRE(nseg >= 1 && nseg <= kv_blocks, "segment count must be in [1, kv_blocks]");
+  return launch_split_segments(block_idx, block_count, seg_block_idx, seg_block_count, error_word,
+                               static_cast<long long>(batch) * hkv * q_blocks, topk, kv_blocks, nseg,
+                               static_cast<cudaStream_t>(stream));
+}
+
+static size_t align256(size_t x) { return (x + 255) & ~static_cast<size_t>(255); }
+
+int64_t sparse_b200_kv_centric_workspace_bytes(int batch, int hq, int hkv, int sq, int topk, int nseg,
+                                               int partial_is_f32) {
+  if (batch <= 0 || hq <= 0 || hkv <= 0 || sq < 128 || topk <= 0 || nseg <= 0) return SB_ERR_INVALID;
+  const size_t lists = static_cast<size_t>(batch) * hkv * (sq / 128);
+  const size_t rows = static_cast<size_t>(batch) * hq * sq;
+  size_t total = 256;                                                   // error word
+  total += align256(lists * nseg * topk * 4) + align256(lists * nseg * 4);   // segment lists and counts
+  total += align256(rows * nseg * 128 * (partial_is_f32 ? 4 : 2));      // partial O
+  total += align256(rows * nseg * 4);                                   // partial LSE
+  return static_cast<int64_t>(total);
+}
+
+int sparse_b200_kv_centric(const void* q, const void* k, const void* v, const int32_t* block_idx,
+                           const int32_t* block_count, void* out, float* lse, void* workspace,
+                           int64_t workspace_bytes, int nseg, int partial_is_f32, int batch, int hq, int hkv, int sq,
+                           int skv, int topk, void* stream) {
+  int rc = check_attention(q, k, v, block_idx, out, batch, hq, hkv, sq, skv, topk, nseg);
+  if (rc) return rc;
+  REQUIRE(workspace && (reinterpret_cast<uintptr_t>(workspace) & 255u) == 0, "workspace must be 256-byte aligned");
+  REQUIRE(nseg <= skv / 128, "more segments than KV blocks");
+  REQUIRE(workspace_bytes >= sparse_b200_kv_centric_workspace_bytes(batch, hq, hkv, sq, topk, nseg, partial_is_f32),
+          "workspace too small (see sparse_b200_kv_centric_workspace_bytes)");
+  const size_t lists = static_cast<size_t>(batch) * hkv * (sq / 128);
+  const size_t rows = static_cast<size_t>(batch) * hq * sq;
+  unsigned char* w = static_cast<unsigned char*>(workspace);
+  int32_t* err = reinterpret_cast<int32_t*>(w);
+  w += 256;
+  int32_t* seg_ids = reinterpret_cast<int32_t*>(w);
+  w += align256(lists * nseg * topk * 4);
+  int32_t* seg_counts = reinterpret_cast<int32_t*>(w);
+  w += align256(lists * nseg * 4);
+  void* partial = w;
+  w += align256(rows * nseg * 128 * (partial_is_f32 ? 4 : 2));
+  float* plse = reinterpret_cast<float*>(w);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (cudaMemsetAsync(err, 0, 4, st) != cudaSuccess) return set_error(SB_ERR_CUDA, "memset failed");
+  rc = launch_split_segments(block_idx, block_count, seg_ids, seg_counts, err, static_cast<long long>(lists), topk,
+                             skv / 128, nseg, st);
+  if (rc) return rc;
+  QCentricArgs a{q, k, v, seg_ids, seg_counts, partial, plse, batch, hq, hkv, sq, skv, topk, nseg,
+                 partial_is_f32 ? 1 : 0};
+  rc = launch_q_centric(a, st);
+  if (rc) return rc;
+  return launch_combine(partial, partial_is_f32, plse, out, lse, static_cast<long long>(rows), nseg,
+                        static_cast<long long>(rows) * 128, 128, static_cast<long long>(rows), 1, st);
+}
+
+int sparse_b200_pool_blocks(const void* x, void* desc, int batch, int heads, int seq, int representatives,
+                            void* stream) {
+  REQUIRE(x && desc, "null pointer");
+  REQUIRE(batch > 0 && heads > 0 && seq >= 128 && seq % 128 == 0, "sequence must be a positive multiple of 128");
+  REQUIRE(representatives == 1 || representatives == 2 || representatives == 4, "representatives must be 1, 2 or 4");
+  REQUIRE(aligned16(x) && aligned16(desc), "x and desc must be 16-byte aligned");
+  const long long num = static_cast<long long>(batch) * heads * (seq / 128) * representatives;
+  return launch_pool(x, desc, num, 128 / representatives, static_cast<cudaStream_t>(stream));
+}
+
+static int check_summary(int batch, int hq, int hkv, int qt, int nt, int r, int topk) {
+  REQUIRE(batch > 0 && hkv > 0 && hq >= hkv && hq % hkv == 0, "Hq must be a positive multiple of Hkv");
+  REQUIRE(qt > 0 && nt > 0, "block counts must be positive");
+  REQUIRE(r == 1 || r == 2 || r == 4, "representatives must be 1, 2 or 4");
+  REQUIRE((hq / hkv) * r <= 64, "group size x representatives must not exceed 64");
+  REQUIRE(topk > 0 && topk <= nt, "top-k must be in [1, number of KV blocks]");
+  return SB_OK;
+}
+
+int sparse_b200_summary_select(const void* q_desc, const void* k_desc, float* scores, int32_t* block_idx, int batch,
+                               int hq, int hkv, int q_blocks, int kv_blocks, int representatives, int topk,
+                               void* stream) {
+  REQUIRE(q_desc && k_desc && block_idx, "null pointer");
+  int rc = check_summary(batch, hq, hkv, q_blocks, kv_blocks, representatives, topk);
+  if (rc) return rc;
+  return launch_summary_score_topk(q_desc, k_desc, scores, block_idx, batch, hq, hkv, q_blocks, kv_blocks,
+                                   representatives, topk, static_cast<cudaStream_t>(stream));
+}
+
+int sparse_b200_indexer_summary(const void* q, const void* k, void* q_desc, void* k_desc, float* scores,
+                                int32_t* block_idx, int batch, int hq, int hkv, int sq, int skv, int representatives,
+                                int topk, void* stream) {
+  REQUIRE(q && k && q_desc && k_desc && block_idx, "null pointer");
+  REQUIRE(sq >= 128 && sq % 128 == 0 && skv >= 128 && skv % 128 == 0, "Sq and Skv must be positive multiples of 128");
+  int rc = check_summary(batch, hq, hkv, sq / 128, skv / 128, representatives, topk);
+  if (rc) return rc;
+  rc = sparse_b200_pool_blocks(q, q_desc, batch, hq, sq, representatives, stream);
+  if (rc) return rc;
+  rc = sparse_b200_pool_blocks(k, k_desc, batch, hkv, skv, representatives, stream);
+  if (rc) return rc;
+  return launch_summary_score_topk(q_desc, k_desc, scores, block_idx, batch, hq, hkv, sq / 128, skv / 128,
+                                   representatives, topk, static_cast<cudaStream_t>(stream));
+}
+
+int sparse_b200_nvfp4_quantize(const void* x, void* packed, void* scales, int batch, int heads_out, int group,
+                               int seq, int paged, void* stream) {
+  REQUIRE(x && packed && scales, "null pointer");
+  REQUIRE(batch > 0 && heads_out > 0 && group > 0 && seq > 0, "sizes must be positive");
+  REQUIRE(!paged || seq % 128 == 0, "paged output needs a sequence that is a multiple of 128");
+  REQUIRE(aligned16(x) && (reinterpret_cast<uintptr_t>(packed) & 7u) == 0, "x must be 16-byte, packed 8-byte aligned");
+  return launch_quantize(x, packed, scales, batch, heads_out, group, seq, paged, static_cast<cudaStream_t>(stream));
+}
+
+static int check_fp4(const void* qp, const void* qs, const void* kp, const void* ks, int batch, int hidx, int hk,
+                     int len_q, int len_kv) {
+  REQUIRE(qp && qs && kp && ks, "null pointer");
+  REQUIRE(batch > 0 && len_q > 0 && len_q % 128 == 0, "B must be positive and Sq a positive multiple of 128");
+  REQUIRE(len_kv >= 128 && len_kv % 128 == 0, "Skv must be a positive multiple of 128");
+  REQUIRE(hidx > 0 && (hk == 1 || hk == hidx), "key index heads must be 1 or equal to the query index heads");
+  REQUIRE((reinterpret_cast<uintptr_t>(qp) & 3u) == 0 && (reinterpret_cast<uintptr_t>(kp) & 3u) == 0,
+          "packed codes must be 4-byte aligned");
+  return SB_OK;
+}
+
+int sparse_b200_fp4_scores(const void* q_codes, const void* q_scales, const void* k_codes, const void* k_scales,
+                           float* query_scores, float* tile_scores, int batch, int hidx, int hk, int len_q, int len_kv,
+                           void* stream) {
+  int rc = check_fp4(q_codes, q_scales, k_codes, k_scales, batch, hidx, hk, len_q, len_kv);
+  if (rc) return rc;
+  REQUIRE(query_scores || tile_scores, "at least one score output is required");
+  return launch_fp4_scores(q_codes, q_scales, k_codes, k_scales, query_scores, tile_scores, batch, hidx, hk, len_q,
+                           len_kv, static_cast<cudaStream_t>(stream));
+}
+
+int sparse_b200_tile_topk(const float* query_scores, int32_t* block_idx, int batch, int heads, int len_q, int kv_tiles,
+                          int topk, void* stream) {
+  REQUIRE(query_scores && block_idx, "null pointer");
+  REQUIRE(batch > 0 && heads > 0 && len_q > 0 && len_q % 128 == 0, "len_q must be a positive multiple of 128");
+  REQUIRE(kv_tiles > 0 && topk > 0 && topk <= kv_tiles, "top-k must be in [1, kv_tiles]");
+  REQUIRE(aligned16(query_scores), "scores must be 16-byte aligned");
+  return launch_tile_max_topk(query_scores, block_idx, batch, heads, len_q, kv_tiles, topk,
+                              static_cast<cudaStream_t>(stream));
+}
+
+int sparse_b200_row_topk(const float* tile_scores, int32_t* block_idx, int64_t rows, int kv_tiles, int topk,
+                         void* stream) {
+  REQUIRE(tile_scores && block_idx, "null pointer");
+  REQUIRE(rows > 0 && kv_tiles > 0 && topk > 0 && topk <= kv_tiles, "top-k must be in [1, kv_tiles]");
+  return launch_row_topk(tile_scores, block_idx, rows, kv_tiles, topk, static_cast<cudaStream_t>(stream));
+}
+
+int sparse_b200_indexer_fp4(const void* q_codes, const void* q_scales, const void* k_codes, const void* k_scales,
+                            float* tile_scores, int32_t* block_idx, int batch, int hidx, int hk, int len_q, int len_kv,
+                            int topk, void* stream) {
+  int rc = check_fp4(q_codes, q_scales, k_codes, k_scales, batch, hidx, hk, len_q, len_kv);
+  if (rc) return rc;
+  REQUIRE(tile_scores && block_idx, "tile score workspace and block_idx are required");
+  REQUIRE(topk > 0 && topk <= len_kv / 128, "top-k must be in [1, kv_tiles]");
+  rc = launch_fp4_scores(q_codes, q_scales, k_codes, k_scales, nullptr, tile_scores, batch, hidx, hk, len_q, len_kv,
+                         static_cast<cudaStream_t>(stream));
+  if (rc) return rc;
+  return launch_row_topk(tile_scores, block_idx, static_cast<long long>(batch) * hidx * (len_q / 128), len_kv / 128,
+                         topk, static_cast<cudaStream_t>(stream));
+}
+
 }  // extern "C"

@@ -42,35 +42,38 @@ __device__ __forceinline__ uint32_t e2m1_code(float ratio) {
   return (c != 0 && ratio < 0.f) ? (c | 8u) : c;
 }
 
-// x: [outer, heads_in, inner, 128] bf16 viewed so that one output row (o, h, i)
-// averages heads h*group .. h*group+group-1. One thread per 16-feature group.
+// x: [B, H_in, S, 128] bf16. Output row (b, h, s) quantises the fp32 mean, in
+// head order, of heads h*group .. h*group+group-1 (group = 1: the head itself).
+// Row placement: token-major [(b*S + s), h] (query index vectors) or paged
+// [(b*S/128 + s/128), h, s%128] (key index pages). One thread per 16-feature group.
 __global__ void __launch_bounds__(256) quantize_kernel(const __nv_bfloat16* __restrict__ x,
                                                        uint8_t* __restrict__ packed, uint8_t* __restrict__ scales,
-                                                       long long rows_out, int group, long long head_stride,
-                                                       long long heads_out, long long inner,
-                                                       long long out_row_stride_h, long long out_row_stride_i) {
+                                                       int batch, int heads_out, int group, int seq, int paged) {
   const long long gid = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   const long long row = gid >> 3;
   const int g16 = static_cast<int>(gid & 7);
-  if (row >= rows_out) return;
-  // row enumerates (o, h, i) with i fastest
-  const long long i = row % inner;
-  const long long oh = row / inner;
-  const long long h = oh % heads_out, o = oh / heads_out;
-  const __nv_bfloat16* src = x + ((o * heads_out + h) * group) * head_stride + i * 128 + g16 * 16;
+  const long long rows = static_cast<long long>(batch) * heads_out * seq;
+  if (row >= rows) return;
+  const int s_pos = static_cast<int>(row % seq);
+  const long long bh = row / seq;
+  const int h = static_cast<int>(bh % heads_out);
+  const long long b = bh / heads_out;
+  const long long head_stride = static_cast<long long>(seq) * 128;
+  const __nv_bfloat16* src =
+      x + ((b * heads_out + h) * group) * head_stride + static_cast<long long>(s_pos) * 128 + g16 * 16;
   float v[16];
 #pragma unroll
   for (int e = 0; e < 16; ++e) v[e] = 0.f;
   for (int gh = 0; gh < group; ++gh) {
     const uint4* p = reinterpret_cast<const uint4*>(src + gh * head_stride);
-    const uint4 a = __ldg(p), b = __ldg(p + 1);
+    const uint4 a = __ldg(p), c = __ldg(p + 1);
     const __nv_bfloat162* ha = reinterpret_cast<const __nv_bfloat162*>(&a);
-    const __nv_bfloat162* hb = reinterpret_cast<const __nv_bfloat162*>(&b);
+    const __nv_bfloat162* hc = reinterpret_cast<const __nv_bfloat162*>(&c);
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
-      const float2 fa = __bfloat1622float2(ha[e]), fb = __bfloat1622float2(hb[e]);
+      const float2 fa = __bfloat1622float2(ha[e]), fc = __bfloat1622float2(hc[e]);
       v[2 * e] += fa.x; v[2 * e + 1] += fa.y;
-      v[8 + 2 * e] += fb.x; v[8 + 2 * e + 1] += fb.y;
+      v[8 + 2 * e] += fc.x; v[8 + 2 * e + 1] += fc.y;
     }
   }
   if (group > 1) {
@@ -83,26 +86,250 @@ __global__ void __launch_bounds__(256) quantize_kernel(const __nv_bfloat16* __re
   for (int e = 0; e < 16; ++e) amax = fmaxf(amax, fabsf(v[e]));
   const float want = fminf(__fdiv_rn(amax, 6.0f), 448.0f);
   const __nv_fp8_storage_t sbits = __nv_cvt_float_to_fp8(want, __NV_SATFINITE, __NV_E4M3);
-  const float s = __half2float(__half(__nv_cvt_fp8_to_halfraw(sbits, __NV_E4M3)));
+  const float sc = __half2float(__half(__nv_cvt_fp8_to_halfraw(sbits, __NV_E4M3)));
   uint32_t lo = 0, hi = 0;
-  if (s > 0.f) {
+  if (sc > 0.f) {
 #pragma unroll
-    for (int e = 0; e < 8; ++e) lo |= e2m1_code(__fdiv_rn(v[e], s)) << (4 * e);
+    for (int e = 0; e < 8; ++e) lo |= e2m1_code(__fdiv_rn(v[e], sc)) << (4 * e);
 #pragma unroll
-    for (int e = 0; e < 8; ++e) hi |= e2m1_code(__fdiv_rn(v[8 + e], s)) << (4 * e);
+    for (int e = 0; e < 8; ++e) hi |= e2m1_code(__fdiv_rn(v[8 + e], sc)) << (4 * e);
   }
-  // output row index: o, h, i with caller-given strides (queries are token-major, keys page-major)
-  const long long orow = o * (heads_out * inner) * 0 + 0;  // placeholder to keep the compiler quiet
-  (void)orow;
-  const long long out_row = (row / inner) * 0 + (o * heads_out * inner) * 0;  // unused
-  (void)out_row;
-  const long long dst_row = o * out_row_stride_h * 0 + h * out_row_stride_h + i * out_row_stride_i +
-                            o * (out_row_stride_h * heads_out > out_row_stride_i * inner
-                                     ? out_row_stride_h * heads_out
-                                     : out_row_stride_i * inner);
-  *reinterpret_cast<uint2*>(packed + dst_row * 64 + g16 * 8) = make_uint2(lo, hi);
-  scales[dst_row * 8 + g16] = sbits;
+  long long dst;
+  if (paged)
+    dst = ((b * (seq >> 7) + (s_pos >> 7)) * heads_out + h) * 128 + (s_pos & 127);
+  else
+    dst = (b * seq + s_pos) * heads_out + h;
+  *reinterpret_cast<uint2*>(packed + dst * 64 + g16 * 8) = make_uint2(lo, hi);
+  scales[dst * 8 + g16] = sbits;
+}
+
+// ---------------------------------------------------------------- scorer
+__device__ __forceinline__ float e4m3_to_float(uint8_t bits) {
+  return __half2float(__half(__nv_cvt_fp8_to_halfraw(bits, __NV_E4M3)));
+}
+// eight e2m1 codes (one 32-bit word) -> eight signed bytes 2*value, as two dp4a operands
+__device__ __forceinline__ void codes_to_int8(uint32_t w, uint32_t& lo4, uint32_t& hi4) {
+  const unsigned long long lut = 0x0C08060403020100ULL;
+  uint32_t out[2] = {0u, 0u};
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const uint32_t c = (w >> (4 * i)) & 15u;
+    int m = static_cast<int>((lut >> (8 * (c & 7u))) & 0xFFu);
+    if (c & 8u) m = -m;
+    out[i >> 2] |= (static_cast<uint32_t>(m) & 0xFFu) << (8 * (i & 3));
+  }
+  lo4 = out[0];
+  hi4 = out[1];
+}
+
+constexpr int ROW_WORDS = 36;   // 128 int8 = 32 words, padded to 36 for conflict-free 16-byte reads
+
+// One CTA: one query tile (128 queries of one index head) against `pages_per_cta`
+// key pages. Thread (ty, tx) = (tid / 16, tid % 16) owns queries ty*8..ty*8+7 and
+// keys tx, tx+16, ..., tx+112.
+__global__ void __launch_bounds__(256) fp4_score_kernel(const uint8_t* __restrict__ qp, const uint8_t* __restrict__ qs,
+                                                        const uint8_t* __restrict__ kp, const uint8_t* __restrict__ ks,
+                                                        float* __restrict__ query_scores,  // [Hidx, tiles, B*Sq] or null
+                                                        float* __restrict__ tile_scores,   // [B, Hidx, Qt, tiles] or null
+                                                        int batch, int hidx, int hk, int len_q, int tiles,
+                                                        int pages_per_cta) {
+  __shared__ uint32_t q_i8[128 * ROW_WORDS];
+  __shared__ uint32_t k_i8[128 * ROW_WORDS];
+  __shared__ float q_sc[128 * 8];
+  __shared__ float k_sc[128 * 8];
+  __shared__ float red[8];
+
+  const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+  const int qt = len_q >> 7;
+  const int qtile = blockIdx.y % qt;
+  const int bh = blockIdx.y / qt;
+  const int h = bh % hidx, b = bh / hidx;
+  const long long q_row0 = static_cast<long long>(b) * len_q + static_cast<long long>(qtile) * 128;
+
+  // stage the query tile: 128 rows x 16 words of codes, 8 scales (0.25 folded in)
+  for (int e = tid; e < 128 * 16; e += 256) {
+    const int r = e >> 4, w = e & 15;
+    const uint32_t word = *reinterpret_cast<const uint32_t*>(qp + ((q_row0 + r) * hidx + h) * 64 + w * 4);
+    uint32_t a, c;
+    codes_to_int8(word, a, c);
+    q_i8[r * ROW_WORDS + 2 * w] = a;
+    q_i8[r * ROW_WORDS + 2 * w + 1] = c;
+  }
+  for (int e = tid; e < 128 * 8; e += 256)
+    q_sc[e] = 0.25f * e4m3_to_float(qs[((q_row0 + (e >> 3)) * hidx + h) * 8 + (e & 7)]);
+
+  const int page0 = blockIdx.x * pages_per_cta;
+  for (int pg = page0; pg < min(page0 + pages_per_cta, tiles); ++pg) {
+    __syncthreads();
+    const long long page = (static_cast<long long>(b) * tiles + pg) * hk + (hk > 1 ? h : 0);
+    for (int e = tid; e < 128 * 16; e += 256) {
+      const int r = e >> 4, w = e & 15;
+      const uint32_t word = __ldg(reinterpret_cast<const uint32_t*>(kp + (page * 128 + r) * 64 + w * 4));
+      uint32_t a, c;
+      codes_to_int8(word, a, c);
+      k_i8[r * ROW_WORDS + 2 * w] = a;
+      k_i8[r * ROW_WORDS + 2 * w + 1] = c;
+    }
+    for (int e = tid; e < 128 * 8; e += 256) k_sc[e] = e4m3_to_float(ks[(page * 128 + (e >> 3)) * 8 + (e & 7)]);
+    __syncthreads();
+
+    float acc[8][8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[i][j] = 0.f;
+#pragma unroll 1
+    for (int g = 0; g < 8; ++g) {
+      uint4 qv[8], kv[8];
+      float qsc[8], ksc[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        qv[i] = *reinterpret_cast<const uint4*>(&q_i8[(ty * 8 + i) * ROW_WORDS + g * 4]);
+        qsc[i] = q_sc[(ty * 8 + i) * 8 + g];
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        kv[j] = *reinterpret_cast<const uint4*>(&k_i8[(tx + 16 * j) * ROW_WORDS + g * 4]);
+        ksc[j] = k_sc[(tx + 16 * j) * 8 + g];
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          int isum = __dp4a(static_cast<int>(qv[i].x), static_cast<int>(kv[j].x), 0);
+          isum = __dp4a(static_cast<int>(qv[i].y), static_cast<int>(kv[j].y), isum);
+          isum = __dp4a(static_cast<int>(qv[i].z), static_cast<int>(kv[j].z), isum);
+          isum = __dp4a(static_cast<int>(qv[i].w), static_cast<int>(kv[j].w), isum);
+          // exact product (<= 12 + 8 significant bits), one rounding in the add
+          acc[i][j] = fmaf(static_cast<float>(isum), qsc[i] * ksc[j], acc[i][j]);
+        }
+    }
+    // per query: max over this thread's 8 keys, then over the 16 threads of the row
+    float tile_best = -CUDART_INF_F;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      float m = acc[i][0];
+#pragma unroll
+      for (int j = 1; j < 8; ++j) m = fmaxf(m, acc[i][j]);
+#pragma unroll
+      for (int d = 1; d < 16; d <<= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, d));
+      if (query_scores && tx == 0)
+        query_scores[(static_cast<long long>(h) * tiles + pg) * (static_cast<long long>(batch) * len_q) + q_row0 +
+                     ty * 8 + i] = m;
+      tile_best = fmaxf(tile_best, m);
+    }
+    if (tile_scores) {
+      tile_best = fmaxf(tile_best, __shfl_xor_sync(0xffffffffu, tile_best, 16));
+      if ((tid & 31) == 0) red[tid >> 5] = tile_best;
+      __syncthreads();
+      if (tid == 0) {
+        float m = red[0];
+#pragma unroll
+        for (int w = 1; w < 8; ++w) m = fmaxf(m, red[w]);
+        tile_scores[((static_cast<long long>(b) * hidx + h) * qt + qtile) * tiles + pg] = m;
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------- top-k stages
+// query_scores [H, tiles, B*Sq] -> max over the 128 queries of a tile -> top-k
+// (tile_max_topk16_kernel, indexers/fp4/tile_topk.cu:38-126, any k and tile count).
+__global__ void __launch_bounds__(256) tile_max_topk_kernel(const float* __restrict__ query_scores,
+                                                            int32_t* __restrict__ ids, int batch, int heads,
+                                                            int len_q, int tiles, int topk) {
+  extern __shared__ float smem[];
+  float* scores = smem;
+  float* scratch_f = scores + tiles;
+  int* scratch_i = reinterpret_cast<int*>(scratch_f + 10);
+  const int qt = len_q >> 7;
+  const int row = blockIdx.x;                 // (b * heads + h) * qt + qtile
+  const int qtile = row % qt, bh = row / qt, h = bh % heads, b = bh / heads;
+  const long long total_q = static_cast<long long>(batch) * len_q;
+  const long long q0 = static_cast<long long>(b) * len_q + static_cast<long long>(qtile) * 128;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int t = warp; t < tiles; t += 8) {
+    const float4 v = *reinterpret_cast<const float4*>(query_scores + (static_cast<long long>(h) * tiles + t) * total_q +
+                                                      q0 + lane * 4);
+    float m = fmaxf(fmaxf(v.x, v.y), fmaxf(v.z, v.w));
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, d));
+    if (lane == 0) scores[t] = m;
+  }
+  __syncthreads();
+  block_topk(scores, tiles, topk, ids + static_cast<long long>(row) * topk, scratch_f, scratch_i);
+}
+
+// tile_scores [rows, tiles] -> top-k per row
+__global__ void __launch_bounds__(256) row_topk_kernel(const float* __restrict__ tile_scores, int32_t* __restrict__ ids,
+                                                       int tiles, int topk) {
+  extern __shared__ float smem[];
+  float* scores = smem;
+  float* scratch_f = scores + tiles;
+  int* scratch_i = reinterpret_cast<int*>(scratch_f + 10);
+  const long long row = blockIdx.x;
+  for (int t = threadIdx.x; t < tiles; t += blockDim.x) scores[t] = tile_scores[row * tiles + t];
+  __syncthreads();
+  block_topk(scores, tiles, topk, ids + row * topk, scratch_f, scratch_i);
 }
 
 }  // namespace
+
+static int check_launch() {
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? SB_OK : set_error(SB_ERR_CUDA, cudaGetErrorString(e));
+}
+
+int launch_quantize(const void* x, void* packed, void* scales, int batch, int heads_out, int group, int seq,
+                    int paged, cudaStream_t stream) {
+  const long long threads = static_cast<long long>(batch) * heads_out * seq * 8;
+  quantize_kernel<<<static_cast<unsigned>((threads + 255) / 256), 256, 0, stream>>>(
+      static_cast<const __nv_bfloat16*>(x), static_cast<uint8_t*>(packed), static_cast<uint8_t*>(scales), batch,
+      heads_out, group, seq, paged);
+  return check_launch();
+}
+
+int launch_fp4_scores(const void* qp, const void* qs, const void* kp, const void* ks, float* query_scores,
+                      float* tile_scores, int batch, int hidx, int hk, int len_q, int len_kv, cudaStream_t stream) {
+  const int tiles = len_kv / 128, qt = len_q / 128;
+  int pages_per_cta = 8;
+  while (pages_per_cta > 1 && static_cast<long long>((tiles + pages_per_cta - 1) / pages_per_cta) * batch * hidx * qt < 592)
+    pages_per_cta >>= 1;
+  dim3 grid((tiles + pages_per_cta - 1) / pages_per_cta, batch * hidx * qt);
+  fp4_score_kernel<<<grid, 256, 0, stream>>>(static_cast<const uint8_t*>(qp), static_cast<const uint8_t*>(qs),
+                                             static_cast<const uint8_t*>(kp), static_cast<const uint8_t*>(ks),
+                                             query_scores, tile_scores, batch, hidx, hk, len_q, tiles, pages_per_cta);
+  return check_launch();
+}
+
+static int topk_smem(int tiles) { return (tiles + 10) * sizeof(float) + 16 * sizeof(int); }
+
+int launch_tile_max_topk(const float* query_scores, int32_t* ids, int batch, int heads, int len_q, int tiles, int topk,
+                         cudaStream_t stream) {
+  DeviceCtx* ctx = device_ctx();
+  if (!ctx) return SB_ERR_CUDA;
+  if (topk_smem(tiles) > 200 * 1024) return set_error(SB_ERR_INVALID, "too many KV tiles for the top-k stage");
+  if (!ctx->misc_attr[5]) {
+    cudaFuncSetAttribute(tile_max_topk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    cudaFuncSetAttribute(row_topk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    ctx->misc_attr[5] = 1;
+  }
+  tile_max_topk_kernel<<<batch * heads * (len_q / 128), 256, topk_smem(tiles), stream>>>(query_scores, ids, batch, heads,
+                                                                                         len_q, tiles, topk);
+  return check_launch();
+}
+
+int launch_row_topk(const float* tile_scores, int32_t* ids, long long rows, int tiles, int topk, cudaStream_t stream) {
+  DeviceCtx* ctx = device_ctx();
+  if (!ctx) return SB_ERR_CUDA;
+  if (topk_smem(tiles) > 200 * 1024) return set_error(SB_ERR_INVALID, "too many KV tiles for the top-k stage");
+  if (!ctx->misc_attr[5]) {
+    cudaFuncSetAttribute(tile_max_topk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    cudaFuncSetAttribute(row_topk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    ctx->misc_attr[5] = 1;
+  }
+  row_topk_kernel<<<static_cast<unsigned>(rows), 256, topk_smem(tiles), stream>>>(tile_scores, ids, tiles, topk);
+  return check_launch();
+}
+
 }  // namespace sb

@@ -37,4 +37,20 @@ struct QCentricArgs {
 };
 int launch_q_centric(const QCentricArgs& a, cudaStream_t stream);
 
+int launch_combine(const void* partial, int partial_is_f32, const float* lses, void* out, float* out_lse,
+                   long long rows, int ranks, long long p_stride_rank, long long p_stride_row,
+                   long long l_stride_rank, long long l_stride_row, cudaStream_t stream);
+int launch_split_segments(const int32_t* ids, const int32_t* counts, int32_t* seg_ids, int32_t* seg_counts,
+                          int* error, long long lists, int topk, int kv_blocks, int nseg, cudaStream_t stream);
+int launch_pool(const void* x, void* desc, long long num_desc, int tokens_per_desc, cudaStream_t stream);
+int launch_summary_score_topk(const void* qd, const void* kd, float* scores, int32_t* ids, int batch, int hq, int hkv,
+                              int qt, int nt, int r, int topk, cudaStream_t stream);
+int launch_quantize(const void* x, void* packed, void* scales, int batch, int heads_out, int group, int seq,
+                    int paged, cudaStream_t stream);
+int launch_fp4_scores(const void* qp, const void* qs, const void* kp, const void* ks, float* query_scores,
+                      float* tile_scores, int batch, int hidx, int hk, int len_q, int len_kv, cudaStream_t stream);
+int launch_tile_max_topk(const float* query_scores, int32_t* ids, int batch, int heads, int len_q, int tiles, int topk,
+                         cudaStream_t stream);
+int launch_row_topk(const float* tile_scores, int32_t* ids, long long rows, int tiles, int topk, cudaStream_t stream);
+
 }  // namespace sb

@@ -412,11 +412,11 @@ q_centric_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
         // eight independent running maxima keep the dependency chain short
         float mx[8];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) mx[j] = __uint_as_float(sv[0][j]);
+        for (int j = 0; j < 8; ++j) mx[j] = -INFINITY;
 #pragma unroll
         for (int c = 0; c < 4; ++c)
 #pragma unroll
-          for (int j = (c == 0 ? 8 : 0); j < 32; ++j) mx[j & 7] = fmaxf(mx[j & 7], __uint_as_float(sv[c][j]));
+          for (int j = 0; j < 32; ++j) mx[j & 7] = fmaxf(mx[j & 7], __uint_as_float(sv[c][j]));
         float tile_max = fmaxf(fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])),
                                fmaxf(fmaxf(mx[4], mx[5]), fmaxf(mx[6], mx[7])));
         tile_max *= p.scale_log2;

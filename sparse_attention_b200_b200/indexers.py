@@ -1,0 +1,178 @@
+"""Host-side mirrors of the reference indexers, bound to the C ABI.
+
+SummarySelector   indexers/r1_r4/block_selectors.py:9-45 (prepare / score+topk / run)
+quantize_*        bf16 -> NVFP4 index vectors (no counterpart in the reference)
+fp4_block_scores  indexers/fp4/fp4.py:122-134
+tile_topk(_out)   indexers/fp4/__init__.py:24-38, indexers/fp4/wrapper.cpp:16-72
+fp4_indexer       indexers/fp4/fp4.py:137-146
+indexed_attention indexers/fp4/pipeline.py:49-65
+"""
+import ctypes
+
+import torch
+
+from . import _lib
+
+
+class SummarySelector:
+    """R1 / R4 selector for q [B,Hq,Sq,128], k [B,Hkv,Skv,128] (bf16, CUDA).
+    ids [B,Hkv,Sq/128,topk] are score-descending, ties to the lower block id."""
+
+    def __init__(self, q, k, representatives, topk=16, keep_scores=True):
+        b, hq, sq, d = q.shape
+        if d != 128 or sq % 128 or k.shape[0] != b or k.shape[3] != 128 or k.shape[2] % 128:
+            raise ValueError("D128 and complete 128-token blocks only")
+        hkv = k.shape[1]
+        if hq % hkv or representatives not in (1, 2, 4) or (hq // hkv) * representatives > 64:
+            raise ValueError("Hq must be a multiple of Hkv; R in (1,2,4); group size x R <= 64")
+        for t in (q, k):
+            if not (t.is_cuda and t.dtype == torch.bfloat16 and t.is_contiguous()):
+                raise ValueError("q and k must be contiguous bf16 CUDA tensors")
+        self.q, self.k, self.r, self.b, self.hq, self.hkv = q, k, representatives, b, hq, hkv
+        self.qt, self.nt, self.topk = sq // 128, k.shape[2] // 128, topk
+        if not 0 < topk <= self.nt:
+            raise ValueError("topk must be in [1, number of KV blocks]")
+        r = representatives
+        self.qd = torch.empty((b, hq, self.qt, r, 128), dtype=torch.bfloat16, device=q.device)
+        self.kd = torch.empty((b, hkv, self.nt, r, 128), dtype=torch.bfloat16, device=q.device)
+        self.scores = torch.empty((b, hkv, self.qt, self.nt), dtype=torch.float32, device=q.device) \
+            if keep_scores else None
+        self.ids = torch.empty((b, hkv, self.qt, topk), dtype=torch.int32, device=q.device)
+        self.name = f"mean{r}_bf16"
+
+    def prepare(self):
+        L = _lib.lib()
+        with torch.cuda.device(self.q.device):
+            st = _lib.current_stream()
+            _lib.check(L.sparse_b200_pool_blocks(_lib.ptr(self.q), _lib.ptr(self.qd), self.b, self.hq,
+                                                 self.qt * 128, self.r, st))
+            _lib.check(L.sparse_b200_pool_blocks(_lib.ptr(self.k), _lib.ptr(self.kd), self.b, self.hkv,
+                                                 self.nt * 128, self.r, st))
+
+    def score(self):
+        """Scores and top-k are one fused kernel here (the raw matrix is never stored)."""
+        with torch.cuda.device(self.q.device):
+            _lib.check(_lib.lib().sparse_b200_summary_select(
+                _lib.ptr(self.qd), _lib.ptr(self.kd), _lib.ptr(self.scores), _lib.ptr(self.ids), self.b, self.hq,
+                self.hkv, self.qt, self.nt, self.r, self.topk, _lib.current_stream()))
+
+    def topk_stage(self):
+        return self.ids
+
+    def run(self):
+        with torch.cuda.device(self.q.device):
+            _lib.check(_lib.lib().sparse_b200_indexer_summary(
+                _lib.ptr(self.q), _lib.ptr(self.k), _lib.ptr(self.qd), _lib.ptr(self.kd), _lib.ptr(self.scores),
+                _lib.ptr(self.ids), self.b, self.hq, self.hkv, self.qt * 128, self.nt * 128, self.r, self.topk,
+                _lib.current_stream()))
+        return self.ids
+
+
+# ---------------------------------------------------------------- NVFP4
+def quantize_queries(q, hidx):
+    """q [B,Hq,Sq,128] bf16 -> (codes [B*Sq,hidx,64] u8, scales [B*Sq,hidx,8] e4m3):
+    index vector h = mean over the Hq/hidx heads of group h."""
+    b, hq, sq, _ = q.shape
+    if hq % hidx:
+        raise ValueError("Hq must be a multiple of the index head count")
+    codes = torch.empty((b * sq, hidx, 64), dtype=torch.uint8, device=q.device)
+    scales = torch.empty((b * sq, hidx, 8), dtype=torch.float8_e4m3fn, device=q.device)
+    with torch.cuda.device(q.device):
+        _lib.check(_lib.lib().sparse_b200_nvfp4_quantize(_lib.ptr(q), _lib.ptr(codes), _lib.ptr(scales), b, hidx,
+                                                         hq // hidx, sq, 0, _lib.current_stream()))
+    return codes, scales
+
+
+def quantize_keys(k):
+    """k [B,Hkv,Skv,128] bf16 -> paged (codes [B*Skv/128,Hkv,128,64], scales [...,128,8])."""
+    b, hkv, skv, _ = k.shape
+    codes = torch.empty((b * skv // 128, hkv, 128, 64), dtype=torch.uint8, device=k.device)
+    scales = torch.empty((b * skv // 128, hkv, 128, 8), dtype=torch.float8_e4m3fn, device=k.device)
+    with torch.cuda.device(k.device):
+        _lib.check(_lib.lib().sparse_b200_nvfp4_quantize(_lib.ptr(k), _lib.ptr(codes), _lib.ptr(scales), b, hkv, 1,
+                                                         skv, 1, _lib.current_stream()))
+    return codes, scales
+
+
+def prepare_fp4_inputs(q_fp4, k_fp4, q_scale, k_scale, *, batch_size, len_q, len_kv):
+    """Validated bundle with the reference's keys (indexers/fp4/fp4.py:37-85). No
+    scale reordering is needed: the scorer reads the public layout directly."""
+    if batch_size <= 0 or len_q <= 0 or len_q % 128 or len_kv <= 0 or len_kv % 128:
+        raise ValueError("B must be positive; Sq and Skv positive multiples of 128")
+    if q_fp4.ndim != 3 or q_fp4.shape[0] != batch_size * len_q or q_fp4.shape[2] != 64:
+        raise ValueError("Qidx must be [B*Sq,Hidx,64]")
+    hidx = q_fp4.shape[1]
+    pages = batch_size * (len_kv // 128)
+    if k_fp4.ndim != 4 or k_fp4.shape[0] != pages or k_fp4.shape[1] not in (1, hidx) \
+            or tuple(k_fp4.shape[2:]) != (128, 64):
+        raise ValueError("Kidx must be [pages,1 or Hidx,128,64]")
+    expected = (("Qidx", q_fp4, (batch_size * len_q, hidx, 64), torch.uint8),
+                ("Kidx", k_fp4, tuple(k_fp4.shape), torch.uint8),
+                ("Q scales", q_scale, (batch_size * len_q, hidx, 8), torch.float8_e4m3fn),
+                ("K scales", k_scale, (*k_fp4.shape[:3], 8), torch.float8_e4m3fn))
+    for name, t, shape, dtype in expected:
+        if not t.is_cuda or t.device != q_fp4.device or t.dtype != dtype or tuple(t.shape) != shape \
+                or not t.is_contiguous():
+            raise ValueError(f"{name} must be contiguous {dtype} {shape} on Qidx's CUDA device")
+    return {"q": q_fp4, "k": k_fp4, "q_scale": q_scale, "k_scale": k_scale, "batch_size": batch_size,
+            "hkv": hidx, "hk": k_fp4.shape[1], "len_q": len_q, "len_kv": len_kv}
+
+
+def fp4_block_scores(inputs):
+    """fp32 [Hidx, KV_tiles, B*Sq] scores (max over the keys of each page)."""
+    b, h, lq, lkv = inputs["batch_size"], inputs["hkv"], inputs["len_q"], inputs["len_kv"]
+    scores = torch.empty((h, lkv // 128, b * lq), dtype=torch.float32, device=inputs["q"].device)
+    with torch.cuda.device(scores.device):
+        _lib.check(_lib.lib().sparse_b200_fp4_scores(
+            _lib.ptr(inputs["q"]), _lib.ptr(inputs["q_scale"]), _lib.ptr(inputs["k"]), _lib.ptr(inputs["k_scale"]),
+            _lib.ptr(scores), None, b, h, inputs["hk"], lq, lkv, _lib.current_stream()))
+    return scores
+
+
+def tile_topk_out(scores, selected, *, batch_size, len_q):
+    if not (scores.is_cuda and scores.dtype == torch.float32 and scores.is_contiguous() and scores.ndim == 3):
+        raise _lib.SparseB200Error("scores must be contiguous float32 [Hkv,KV_tiles,B*Sq] on CUDA")
+    heads, tiles, total = scores.shape
+    if batch_size <= 0 or len_q <= 0 or len_q % 128 or total != batch_size * len_q:
+        raise _lib.SparseB200Error("B*Sq must match the score matrix; Sq a positive multiple of 128")
+    topk = int(selected.shape[-1])
+    if selected.dtype != torch.int32 or not selected.is_contiguous() \
+            or tuple(selected.shape) != (batch_size, heads, len_q // 128, topk) or selected.device != scores.device:
+        raise _lib.SparseB200Error("selected must be contiguous int32 [B,Hkv,Sq/128,TopK] on the scores' device")
+    with torch.cuda.device(scores.device):
+        _lib.check(_lib.lib().sparse_b200_tile_topk(_lib.ptr(scores), _lib.ptr(selected), batch_size, heads, len_q,
+                                                    tiles, topk, _lib.current_stream()))
+    return selected
+
+
+def tile_topk(scores, *, batch_size, len_q, topk=16):
+    selected = torch.empty((batch_size, scores.shape[0], len_q // 128, topk), dtype=torch.int32,
+                           device=scores.device)
+    return tile_topk_out(scores, selected, batch_size=batch_size, len_q=len_q)
+
+
+def fp4_indexer(inputs, selected=None, topk=16, tile_scores=None):
+    """Scoring + max over the query tile + top-k; only ids (and tile scores) touch memory."""
+    b, h, lq, lkv = inputs["batch_size"], inputs["hkv"], inputs["len_q"], inputs["len_kv"]
+    dev = inputs["q"].device
+    if selected is None:
+        selected = torch.empty((b, h, lq // 128, topk), dtype=torch.int32, device=dev)
+    if tile_scores is None:
+        tile_scores = torch.empty((b, h, lq // 128, lkv // 128), dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        _lib.check(_lib.lib().sparse_b200_indexer_fp4(
+            _lib.ptr(inputs["q"]), _lib.ptr(inputs["q_scale"]), _lib.ptr(inputs["k"]), _lib.ptr(inputs["k_scale"]),
+            _lib.ptr(tile_scores), _lib.ptr(selected), b, h, inputs["hk"], lq, lkv, int(selected.shape[-1]),
+            _lib.current_stream()))
+    return selected
+
+
+def indexed_attention(q, k, v, inputs, topk=16):
+    """(O, selected): FP4 indexer then Q-centric attention on the same stream."""
+    from .q_centric import attention
+    b, hq, sq, _ = q.shape
+    if inputs["batch_size"] != b or inputs["hkv"] != k.shape[1] or inputs["len_q"] != sq \
+            or inputs["len_kv"] != k.shape[2]:
+        raise ValueError("indexer inputs must match attention shapes")
+    selected = fp4_indexer(inputs, topk=topk)
+    return attention(q, k, v, selected), selected

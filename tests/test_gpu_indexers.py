@@ -1,0 +1,181 @@
+"""R1/R4 and NVFP4 indexers through the C ABI: ids bit-exact (ties to the lower
+block id), descriptors and scores bit-exact against the oracle's fixed
+arithmetic, and the reference's own gates against its stored outputs
+(benchmarks/ch4_selectors/harness.py:22-42, 116-119)."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from oracle import inputs as gen
+from tests.golden import cases
+
+pytestmark = pytest.mark.gpu
+G = os.path.join(os.path.dirname(__file__), "golden")
+
+
+def sp():
+    import sparse_attention_b200_b200 as m
+    return m
+
+
+def margins(scores, topk):
+    s = torch.sort(scores, dim=-1, descending=True).values
+    return (s[..., :topk] - s[..., 1:topk + 1]).min().item() if scores.shape[-1] > topk else float("inf")
+
+
+@pytest.mark.parametrize("family", ["gaussian", "cancellation_stress", "zeros"])
+@pytest.mark.parametrize("r", [1, 4])
+def test_summary_selector_reference_gate(family, r):
+    m = sp()
+    fx = np.load(os.path.join(G, "selectors.npz"))
+    q, k = cases.selector_inputs(family)
+    sel = m.SummarySelector(q.cuda(), k.cuda(), r, topk=16)
+    sel.run()
+    torch.cuda.synchronize()
+    tag = f"{family}_r{r}"
+    # reference gate: ids exact, scores atol 2e-5 / rtol 3e-4
+    np.testing.assert_array_equal(sel.ids.cpu().numpy(), fx[tag + "_ids"])
+    np.testing.assert_allclose(sel.scores.cpu().numpy(), fx[tag + "_scores"], atol=2e-5, rtol=3e-4)
+    # oracle: everything bit for bit
+    qd, kd, scores, ids = oracle.summary_select(q, k, r, 16)
+    assert torch.equal(sel.qd.cpu().view(torch.int16), qd.view(torch.int16))
+    assert torch.equal(sel.kd.cpu().view(torch.int16), kd.view(torch.int16))
+    assert torch.equal(sel.scores.cpu(), scores)
+    assert torch.equal(sel.ids.cpu(), ids)
+    if family == "zeros":
+        assert torch.equal(sel.ids.cpu(), torch.arange(16, dtype=torch.int32).expand_as(ids))
+
+
+@pytest.mark.parametrize("shape", [
+    # B, Hq, Hkv, Sq, Skv, R, topk, k offset
+    (1, 8, 8, 4096, 4096, 1, 8, 0.5),        # configuration 1
+    (2, 16, 2, 1024, 8192, 4, 32, 0.5),      # group 8, R4, top-32 of 64
+    (1, 16, 1, 512, 16384, 4, 64, 0.5),      # group 16, top-64 of 128
+    (1, 4, 2, 256, 1024, 2, 8, 0.0),         # R2, top-k == all blocks
+    (1, 6, 2, 256, 2048, 4, 5, 0.0),         # group 3
+])
+def test_summary_selector_bit_exact(shape):
+    b, hq, hkv, sq, skv, r, topk, off = shape
+    m = sp()
+    q, k, _ = gen.make_qkv(b, hq, hkv, sq, skv, seed=17, k_block_offset=off)
+    sel = m.SummarySelector(q.cuda(), k.cuda(), r, topk=topk)
+    sel.prepare()
+    sel.score()
+    torch.cuda.synchronize()
+    qd, kd, scores, ids = oracle.summary_select(q, k, r, topk)
+    assert torch.equal(sel.qd.cpu().view(torch.int16), qd.view(torch.int16))
+    assert torch.equal(sel.kd.cpu().view(torch.int16), kd.view(torch.int16))
+    assert torch.equal(sel.scores.cpu(), scores), (sel.scores.cpu() - scores).abs().max()
+    assert torch.equal(sel.ids.cpu(), ids)
+    print("k-th vs (k+1)-th score margin", margins(scores, topk))
+    # the fused entry gives the same ids without storing scores
+    sel2 = m.SummarySelector(q.cuda(), k.cuda(), r, topk=topk, keep_scores=False)
+    assert torch.equal(sel2.run().cpu(), ids)
+
+
+def test_summary_selector_duplicate_scores_tie_to_lower_id():
+    """Duplicate KV blocks give exactly equal scores: the lower id must come first."""
+    m = sp()
+    q, k, _ = gen.make_qkv(1, 4, 1, 256, 2048, seed=23)
+    k = k.clone()
+    k[:, :, 5 * 128:6 * 128] = k[:, :, 2 * 128:3 * 128]
+    k[:, :, 9 * 128:10 * 128] = k[:, :, 2 * 128:3 * 128]
+    sel = m.SummarySelector(q.cuda(), k.cuda(), 4, topk=16)
+    ids = sel.run().cpu()
+    _, _, scores, ref = oracle.summary_select(q, k, 4, 16)
+    assert torch.equal(ids, ref)
+    pos = {int(v): i for i, v in enumerate(ids[0, 0, 0].tolist())}
+    assert pos[2] + 1 == pos[5] and pos[5] + 1 == pos[9]
+
+
+def test_fp4_reference_gate_and_bit_exact():
+    m = sp()
+    fx = np.load(os.path.join(G, "fp4.npz"))
+    qp, qs, kp, ks, b, lq, lkv = cases.fp4_case()
+    inputs = m.prepare_fp4_inputs(qp.cuda(), kp.cuda(), qs.cuda(), ks.cuda(), batch_size=b, len_q=lq, len_kv=lkv)
+    scores = m.fp4_block_scores(inputs)
+    ids = m.tile_topk(scores, batch_size=b, len_q=lq, topk=16)
+    torch.cuda.synchronize()
+    # reference gate: scores rtol 1e-4 / atol 1e-3, ids exact
+    np.testing.assert_allclose(scores.cpu().numpy(), fx["scores"], rtol=1e-4, atol=1e-3)
+    np.testing.assert_array_equal(ids.cpu().numpy(), fx["ids"])
+    # oracle: bit for bit
+    ref = oracle.fp4_scores(qp, qs, kp, ks, b, lq, lkv)
+    assert torch.equal(scores.cpu(), ref)
+    # fused indexer: same ids, tile scores = max over the query tile
+    tile = torch.empty((b, qp.shape[1], lq // 128, lkv // 128), device="cuda")
+    ids2 = m.fp4_indexer(inputs, topk=16, tile_scores=tile)
+    assert torch.equal(ids2.cpu(), ids.cpu())
+    assert torch.equal(tile.cpu(), oracle.fp4_tile_scores(ref, b, lq))
+    # top-k of other sizes
+    for kk in (1, 5, 16):
+        got = m.tile_topk(scores, batch_size=b, len_q=lq, topk=kk)
+        assert torch.equal(got.cpu(), oracle.fp4_select(ref, b, lq, kk))
+
+
+def test_nvfp4_quantiser_and_quantised_indexer():
+    """bf16 -> NVFP4 (parity unpinned by the reference: checked against the stated
+    rule in the oracle), then the configuration-4 flow at a small size:
+    quantise Q (group mean) and K, score, top-k, KV-centric attention."""
+    m = sp()
+    b, hq, hkv, n, topk = 1, 16, 2, 1024, 4
+    q, k, v = gen.make_qkv(b, hq, hkv, n, n, seed=41, k_block_offset=0.5)
+    q[0, 0, 0, :16] = torch.tensor([0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0, 6.0,
+                                    -0.25, -0.75, -1.25, -1.75, -2.5, -3.5, -5.0, -6.0]).to(torch.bfloat16)
+    qc, qs = m.quantize_queries(q.cuda(), hkv)
+    kc, ks = m.quantize_keys(k.cuda())
+    torch.cuda.synchronize()
+    rqc, rqs = oracle.quantize_queries(q, hkv)
+    rkc, rks = oracle.quantize_keys(k)
+    assert torch.equal(qs.cpu().view(torch.uint8), rqs.view(torch.uint8))
+    assert torch.equal(ks.cpu().view(torch.uint8), rks.view(torch.uint8))
+    assert torch.equal(qc.cpu(), rqc) and torch.equal(kc.cpu(), rkc)
+    inputs = m.prepare_fp4_inputs(qc, kc, qs, ks, batch_size=b, len_q=n, len_kv=n)
+    ids = m.fp4_indexer(inputs, topk=topk)
+    ref_scores = oracle.fp4_scores(rqc, rqs, rkc, rks, b, n, n)
+    ref_ids = oracle.fp4_select(ref_scores, b, n, topk)
+    assert torch.equal(ids.cpu(), ref_ids)
+    out, lse = m.kv_centric_attention(q.cuda(), k.cuda(), v.cuda(), ids, nseg=2)
+    ref_o, ref_l = oracle.gather_attention(q, k, v, ref_ids)
+    d = (out.float().cpu() - ref_o).abs()
+    assert d.max() <= 2e-2 and d.mean() <= 2e-3
+    assert torch.all((lse.cpu() - ref_l).abs() <= 1e-3 * ref_l.abs().clamp_min(1.0))
+    o2, sel2 = m.indexed_attention(q.cuda(), k.cuda(), v.cuda(), inputs, topk=topk)
+    assert torch.equal(sel2.cpu(), ref_ids)
+    assert (o2.float().cpu() - ref_o).abs().max() <= 2e-2
+    m.device_status()
+
+
+def test_indexer_then_attention_config1():
+    """Configuration 1 end to end: R1 picks top-8 of 32, Q-centric attention,
+    against the masked-attention oracle."""
+    m = sp()
+    q, k, v = gen.make_qkv(1, 8, 8, 4096, 4096, seed=17, k_block_offset=0.5)
+    sel = m.SummarySelector(q.cuda(), k.cuda(), 1, topk=8)
+    ids = sel.run()
+    ref_ids = oracle.summary_select(q, k, 1, 8)[3]
+    assert torch.equal(ids.cpu(), ref_ids)
+    out, lse = m.attention(q.cuda(), k.cuda(), v.cuda(), ids, return_lse=True)
+    ref_o, ref_l = oracle.masked_attention(q, k, v, ref_ids)
+    d = (out.float().cpu() - ref_o).abs()
+    assert d.max() <= 2e-2 and d.mean() <= 2e-3
+    assert torch.all((lse.cpu() - ref_l).abs() <= 1e-3 * ref_l.abs().clamp_min(1.0))
+
+
+def test_rejected_indexer_inputs():
+    m = sp()
+    q, k, _ = gen.make_qkv(1, 4, 2, 256, 512, seed=1)
+    with pytest.raises(ValueError):
+        m.SummarySelector(q.cuda(), k.cuda(), 3)
+    with pytest.raises(ValueError):
+        m.SummarySelector(q.cuda(), k.cuda(), 1, topk=5)
+    with pytest.raises(ValueError):
+        m.SummarySelector(q.float().cuda(), k.cuda(), 1, topk=2)
+    scores = torch.zeros((1, 4, 256), device="cuda")
+    with pytest.raises(RuntimeError):
+        m.tile_topk(scores, batch_size=1, len_q=256, topk=5)
+    with pytest.raises(RuntimeError):
+        m.tile_topk(scores.double(), batch_size=1, len_q=256, topk=2)
