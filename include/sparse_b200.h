@@ -140,6 +140,22 @@ int sparse_b200_indexer_fp4(const void* q_codes, const void* q_scales, const voi
                             float* tile_scores, int32_t* block_idx, int batch, int hidx, int hk, int len_q, int len_kv,
                             int topk, void* stream);
 
+/* R1 / R4 summary indexer that allocates nothing and takes no workspace: same
+ * inputs, outputs, arithmetic and results as sparse_b200_indexer_summary, with
+ * the pooled descriptors kept in an 8 MiB array built into the library. It has
+ * no counterpart in the reference. It is for callers that cannot allocate
+ * device memory where they need block ids (inside a stream capture, under a
+ * memory pool that owns the whole device, behind a plugin interface that passes
+ * only inputs and outputs). Limits: (B*Hq*Sq/128 + B*Hkv*Skv/128) * R <= 32768
+ * descriptors, group size x R <= 16, Skv/128 <= 4096; anything larger returns
+ * SPARSE_B200_ERR_INVALID. Every GPU that loads the library holds the 8 MiB
+ * until exit. All calls on a device share the array: calls that overlap on the
+ * GPU race, so keep them on one stream or order them yourself. The first call on
+ * a device resolves the array's address; make it before any stream capture. */
+int sparse_b200_indexer_summary_noalloc(const void* q, const void* k, float* scores, int32_t* block_idx, int batch,
+                                        int hq, int hkv, int sq, int skv, int representatives, int topk,
+                                        void* stream);
+
 #ifdef __cplusplus
 }
 #endif

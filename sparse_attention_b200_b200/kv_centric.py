@@ -115,8 +115,9 @@ def combine(partial, lses):
     rows = lses.numel() // ranks
     out = torch.empty((*partial.shape[:-2], 128), dtype=torch.bfloat16, device=partial.device)
     lse = torch.empty(partial.shape[:-2], dtype=torch.float32, device=partial.device)
+    partial, lses = partial.contiguous(), lses.contiguous()   # keep any copies alive across the call
     with torch.cuda.device(partial.device):
         _lib.check(_lib.lib().sparse_b200_combine(
-            _lib.ptr(partial.contiguous()), int(partial.dtype == torch.float32), _lib.ptr(lses.contiguous()),
+            _lib.ptr(partial), int(partial.dtype == torch.float32), _lib.ptr(lses),
             _lib.ptr(out), _lib.ptr(lse), ctypes.c_int64(rows), ranks, 0, _lib.current_stream()))
     return out, lse
