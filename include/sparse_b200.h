@@ -144,9 +144,9 @@ int sparse_b200_indexer_fp4(const void* q_codes, const void* q_scales, const voi
  * inputs, outputs, arithmetic and results as sparse_b200_indexer_summary, with
  * the pooled descriptors kept in an 8 MiB array built into the library. It has
  * no counterpart in the reference. It is for callers that cannot allocate
- * device memory where they need block ids (inside a stream capture, under a
- * memory pool that owns the whole device, behind a plugin interface that passes
- * only inputs and outputs). Limits: (B*Hq*Sq/128 + B*Hkv*Skv/128) * R <= 32768
+ * device memory where they need block ids (under a memory pool that owns the
+ * whole device, inside a serving loop with a fixed memory budget, behind a
+ * plugin interface that passes only inputs and outputs). Limits: (B*Hq*Sq/128 + B*Hkv*Skv/128) * R <= 32768
  * descriptors, group size x R <= 16, Skv/128 <= 4096; anything larger returns
  * SPARSE_B200_ERR_INVALID. Every GPU that loads the library holds the 8 MiB
  * until exit. All calls on a device share the array: calls that overlap on the

@@ -1,8 +1,8 @@
 // R1 / R4 summary indexer for callers that must not allocate device memory.
 //
 // Some hosts of this library cannot call cudaMalloc at the point where they
-// need block ids: code running inside a CUDA-graph capture or under a framework
-// memory pool that forbids outside allocations, a serving loop with a fixed
+// need block ids: code running under a framework memory pool that owns the
+// device and forbids outside allocations, a serving loop with a fixed
 // device-memory budget, or a plugin that is handed its inputs and outputs and
 // nothing else. The regular entry point (sparse_b200_indexer_summary) makes the
 // caller supply two descriptor workspaces; this variant keeps those pooled

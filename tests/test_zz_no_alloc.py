@@ -1,8 +1,8 @@
 """The allocation-free summary indexer against the regular entry point.
 
 Some callers of this library cannot allocate device memory at the point where
-they need block ids (a CUDA-graph capture in progress, a framework pool that
-owns the device, a plugin that only receives inputs and outputs), so
+they need block ids (a framework pool that owns the device, a serving loop with
+a fixed memory budget, a plugin that only receives inputs and outputs), so
 sparse_b200_indexer_summary_noalloc keeps its pooled descriptors in an 8 MiB
 array inside the library. The array is shared and keeps the last call's
 contents, so the check runs two different problems back to back and requires
