@@ -31,9 +31,10 @@ sys.path.insert(0, ROOT)
 
 METRIC = "sparse-attn fwd TFLOPS (selected blocks) & % BF16 tensor peak; indexer ms"
 WORKLOAD = {"name": "q_centric_mha_32k", "B": 1, "Hq": 32, "Hkv": 32, "N": 32768, "topk": 16}
-# DRAM bytes per launch of the attention kernel on this workload, from the
-# Nsight Compute capture summarised in profiles/ (None until captured).
-NCU_TRAFFIC_BYTES = None
+# DRAM bytes per launch of the attention kernel on this workload
+# (dram__bytes_read.sum + dram__bytes_write.sum, Nsight Compute capture
+# summarised in profiles/q_centric_kernel_mha_32k.md).
+NCU_TRAFFIC_BYTES = 1.090e9
 
 
 def flops(w):
@@ -102,7 +103,7 @@ class ClockSampler:
                 "sm_max_mhz": max(mx) if mx else None, "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def cpu_sample(w, budget_s=12.0, max_heads=8):
+def cpu_sample(w, budget_s=20.0, max_heads=32):
     """Oracle gather path (the reference's torch computation) on whole heads of
     the workload until the time budget is used. Returns (TFLOP/s, description)."""
     import torch

@@ -4,7 +4,8 @@ import ctypes
 import os
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "libsparse_b200.so")
+# SPARSE_B200_LIB selects another build of the same library (kernel tuning experiments).
+LIB_PATH = os.environ.get("SPARSE_B200_LIB") or os.path.join(HERE, "libsparse_b200.so")
 
 ERR_INVALID, ERR_CUDA, ERR_TIMEOUT = -1, -2, -3
 

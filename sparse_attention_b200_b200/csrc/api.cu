@@ -17,6 +17,11 @@ int set_error(int code, const char* message) {
   return code;
 }
 
+#ifdef SB_QC_TRACE
+static const size_t STATUS_BYTES = 64 + 32 * 256 * 8;   // debug builds: room for clock stamps
+#else
+static const size_t STATUS_BYTES = sizeof(int);
+#endif
 static std::mutex g_mutex;
 static DeviceCtx g_ctx[64];
 typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -44,8 +49,8 @@ DeviceCtx* device_ctx() {
     g_encode = reinterpret_cast<EncodeFn>(fn);
   }
   if (cudaDeviceGetAttribute(&c.sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
-      cudaMalloc(&c.status, sizeof(int)) != cudaSuccess ||
-      cudaMemset(c.status, 0, sizeof(int)) != cudaSuccess) {
+      cudaMalloc(&c.status, STATUS_BYTES) != cudaSuccess ||
+      cudaMemset(c.status, 0, STATUS_BYTES) != cudaSuccess) {
     set_error(SB_ERR_CUDA, "device state initialisation failed");
     return nullptr;
   }
@@ -77,6 +82,14 @@ extern "C" {
 
 const char* sparse_b200_last_error(void) { return g_error; }
 
+#ifdef SB_QC_TRACE
+int sparse_b200_debug_trace(void* host, int bytes) {
+  DeviceCtx* ctx = device_ctx();
+  if (!ctx) return SB_ERR_CUDA;
+  return cudaMemcpy(host, ctx->status + 16, bytes, cudaMemcpyDeviceToHost) == cudaSuccess ? 0 : SB_ERR_CUDA;
+}
+#endif
+
 int sparse_b200_device_status(int reset) {
   DeviceCtx* ctx = device_ctx();
   if (!ctx) return SB_ERR_CUDA;
@@ -97,7 +110,7 @@ static int check_attention(const void* q, const void* k, const void* v, const in
   REQUIRE(topk > 0, "selected_count must be positive");
   REQUIRE(topk <= skv / 128, "selected_count cannot exceed the number of KV tiles");
   REQUIRE(nseg >= 1, "segment count must be positive");
-  REQUIRE(static_cast<long long>(batch) * hq * sq < (1LL << 31) &&
+  REQUIRE(static_cast<long long>(nseg) * batch * hq * sq < (1LL << 31) &&
               static_cast<long long>(batch) * hkv * skv < (1LL << 31),
           "flattened Q / KV row counts must fit int32 (TMA row coordinates)");
   REQUIRE(static_cast<long long>(nseg) * batch * hkv * (sq / 128) * topk < (1LL << 40), "block_idx too large");

@@ -30,7 +30,14 @@ constexpr int TILE = 128;            // rows per Q tile and per KV block
 constexpr int HEAD_DIM = 128;
 constexpr int TILE_BYTES = TILE * HEAD_DIM * 2;   // 32 KiB
 constexpr int PANEL_BYTES = TILE * 128;            // 64-column half of a tile
-constexpr int RING = 5;              // K/V ring slots
+#ifndef SB_QC_RING
+#define SB_QC_RING 4
+#endif
+#ifndef SB_QC_POLY_PERIOD
+#define SB_QC_POLY_PERIOD 0
+#endif
+constexpr int RING = SB_QC_RING;     // K/V ring slots
+constexpr int POLY_PERIOD = SB_QC_POLY_PERIOD;   // one pair of exponentials in this many runs on the FMA pipe (0: none)
 constexpr int NUM_THREADS = 320;
 constexpr int MMA_WARP = 8;
 constexpr int LOAD_WARP = 9;
@@ -40,7 +47,9 @@ constexpr float RESCALE_LOG2 = 8.0f;   // keep a stale row max while it lags by 
 // shared memory map (offsets from a 1024-aligned base)
 constexpr int OFF_Q = 0;
 constexpr int OFF_RING = 2 * TILE_BYTES;
-constexpr int OFF_BAR = OFF_RING + RING * TILE_BYTES;
+constexpr int OFF_STAGE = OFF_RING + RING * TILE_BYTES;   // 8 softmax warps x 4 KiB output staging
+constexpr int STAGE_BYTES = 4096;
+constexpr int OFF_BAR = OFF_STAGE + 8 * STAGE_BYTES;
 // barrier indices (8 bytes each)
 constexpr int BAR_Q_FULL = 0;      // [2]
 constexpr int BAR_Q_EMPTY = 2;     // [2]
@@ -52,6 +61,14 @@ constexpr int BAR_KV_EMPTY = 10 + RING;  // [RING]
 constexpr int NUM_BARS = 10 + 2 * RING;
 constexpr int OFF_MISC = OFF_BAR + NUM_BARS * 8;   // tmem base (4 B), abort flag (4 B)
 constexpr int SMEM_BYTES = OFF_MISC + 16 + 1024;   // + slack for manual 1024 alignment
+
+#ifdef SB_QC_TRACE
+// Debug builds only: clock64 stamps of CTA 0 into the words after the status word.
+#define TRACE(slot, idx) do { if (blockIdx.x == 0 && lane == 0 && (idx) < 256) \
+    reinterpret_cast<long long*>(p.status + 16)[(slot) * 256 + (idx)] = clock64(); } while (0)
+#else
+#define TRACE(slot, idx) do { } while (0)
+#endif
 
 struct Params {
   const int32_t* ids;      // [nseg, B, Hkv, Qt, topk]
@@ -134,7 +151,8 @@ struct IdCursor {
 template <bool OUT_F32>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 q_centric_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
-                 const __grid_constant__ CUtensorMap v_map, const Params p) {
+                 const __grid_constant__ CUtensorMap v_map, const __grid_constant__ CUtensorMap o_map,
+                 const Params p) {
   extern __shared__ unsigned char smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
@@ -170,6 +188,7 @@ q_centric_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
     prefetch_tmap(&q_map);
     prefetch_tmap(&k_map);
     prefetch_tmap(&v_map);
+    prefetch_tmap(&o_map);
   }
   tc_fence_before();
   __syncthreads();
@@ -189,6 +208,7 @@ q_centric_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
         bool w = mbar_wait(bar(BAR_KV_EMPTY + slot), (use - 1) & 1, guard, 0x100 + slot);
         if (!__all_sync(0xffffffffu, w)) return false;
       }
+      TRACE(24, static_cast<int>(fills));
       if (lane == 0) {
         const uint32_t dst = base + OFF_RING + slot * TILE_BYTES;
         mbar_expect_tx(bar(BAR_KV_FULL + slot), TILE_BYTES);
@@ -261,7 +281,9 @@ q_centric_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
     bool ok = true;
     auto acquire = [&](uint32_t& slot) -> bool {
       slot = taken % RING;
+      TRACE(22, static_cast<int>(taken));
       bool w = mbar_wait(bar(BAR_KV_FULL + slot), (taken / RING) & 1, guard, 0x200 + slot);
+      TRACE(23, static_cast<int>(taken));
       ++taken;
       w = __all_sync(0xffffffffu, w);
       tc_fence_after();
@@ -274,11 +296,16 @@ q_centric_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
       tc_fence_after();
       return w;
     };
+    int trace_p[2] = {0, 0};
+    (void)trace_p;
     auto wait_p = [&](int q) -> bool {
+      TRACE(20 + q, trace_p[q]);
       bool w = mbar_wait(bar(BAR_P_FULL + q), pphase[q], guard, 0x220 + q);
       pphase[q] ^= 1;
       w = __all_sync(0xffffffffu, w);
       tc_fence_after();
+      TRACE(16 + q, trace_p[q]);
+      ++trace_p[q];
       return w;
     };
     // S_q = Q_q K^T : 8 MMAs of K = 16 over two 64-column panels.
@@ -380,6 +407,8 @@ q_centric_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
     const uint32_t t_o = tmem + lane_base + 256 + q * HEAD_DIM;
     uint32_t sphase = 0, ophase = 0;
     bool ok = true;
+    int trace_n = 0;
+    (void)trace_n;
     for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x) {
       Stream s[2];
       decode_item(p, item, s);
@@ -405,20 +434,22 @@ q_centric_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
         ok = __all_sync(0xffffffffu, w);
         if (!ok) break;
         tc_fence_after();
+        if ((warp & 3) == 0) TRACE(q * 8 + 0, trace_n);
         uint32_t sv[4][32];
 #pragma unroll
         for (int c = 0; c < 4; ++c) tmem_ld32(t_s + c * 32, sv[c]);
         tc_wait_ld();
-        // eight independent running maxima keep the dependency chain short
-        float mx[8];
+        if ((warp & 3) == 0) TRACE(q * 8 + 1, trace_n);
+        // four independent running maxima, three-input max: 64 instructions per row
+        float mx[4];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) mx[j] = -INFINITY;
+        for (int j = 0; j < 4; ++j) mx[j] = -INFINITY;
 #pragma unroll
         for (int c = 0; c < 4; ++c)
 #pragma unroll
-          for (int j = 0; j < 32; ++j) mx[j & 7] = fmaxf(mx[j & 7], __uint_as_float(sv[c][j]));
-        float tile_max = fmaxf(fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])),
-                               fmaxf(fmaxf(mx[4], mx[5]), fmaxf(mx[6], mx[7])));
+          for (int j = 0; j < 32; j += 2)
+            mx[(j >> 1) & 3] = max3(mx[(j >> 1) & 3], __uint_as_float(sv[c][j]), __uint_as_float(sv[c][j + 1]));
+        float tile_max = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
         tile_max *= p.scale_log2;
         // Lazy rescale: keep a stale row max while the true max is less than
         // 2^RESCALE_LOG2 above it (P stays finite in bf16, the sum in fp32).
@@ -444,25 +475,42 @@ q_centric_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
             tmem_st32(t_o + c * 32, ov);
           }
         }
-        float part[4] = {0.f, 0.f, 0.f, 0.f};
-        const float neg_max = -row_max;
+        if ((warp & 3) == 0) TRACE(q * 8 + 2, trace_n);
+        // p = 2^(s*scale - max): packed FMAs; one pair in every POLY_PERIOD goes to
+        // the FMA-pipe polynomial, the rest to the special-function unit.
+        float2 part[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
+        const float2 scale2 = make_float2(p.scale_log2, p.scale_log2);
+        const float2 neg_max2 = make_float2(-row_max, -row_max);
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           uint32_t pk[16];
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
-            const float p0 = ex2_approx(fmaf(__uint_as_float(sv[c][2 * j]), p.scale_log2, neg_max));
-            const float p1 = ex2_approx(fmaf(__uint_as_float(sv[c][2 * j + 1]), p.scale_log2, neg_max));
-            part[j & 3] += p0 + p1;
-            pk[j] = pack_bf16x2(p0, p1);
+            const float2 x = fma2(make_float2(__uint_as_float(sv[c][2 * j]), __uint_as_float(sv[c][2 * j + 1])),
+                                  scale2, neg_max2);
+            float2 e;
+            if (POLY_PERIOD > 0 && (j % (POLY_PERIOD > 0 ? POLY_PERIOD : 1)) == (POLY_PERIOD - 1)) {
+              e = exp2_poly2(x);
+            } else {
+#ifdef SB_QC_EXPERIMENT_NOEXP
+              e = x;
+#else
+              e = make_float2(ex2_approx(x.x), ex2_approx(x.y));
+#endif
+            }
+            part[j & 1] = add2(part[j & 1], e);
+            pk[j] = pack_bf16x2(e.x, e.y);
           }
           tmem_st16(t_s + c * 16, pk);
         }
-        row_sum += (part[0] + part[1]) + (part[2] + part[3]);
+        row_sum += (part[0].x + part[0].y) + (part[1].x + part[1].y);
+        if ((warp & 3) == 0) TRACE(q * 8 + 3, trace_n);
         tc_wait_st();
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(bar(BAR_P_FULL + q));
+        if ((warp & 3) == 0) TRACE(q * 8 + 4, trace_n);
+        ++trace_n;
       }
       if (!ok) break;
       {
@@ -472,27 +520,50 @@ q_centric_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
         if (!ok) break;
         tc_fence_after();
       }
+      // Epilogue: normalise this warp's 32 rows, stage them in shared memory in the
+      // 128-byte-swizzled box layout and let TMA write them out asynchronously
+      // (a direct store would scatter 16-byte pieces over 32 rows per instruction).
       const float inv = 1.0f / row_sum;
+      const uint32_t stage = base + OFF_STAGE + warp * STAGE_BYTES;
+      unsigned char* stage_g = gbase + OFF_STAGE + warp * STAGE_BYTES;
+      const int out_row32 = static_cast<int>(me.out_row) + (warp & 3) * 32;
+      constexpr int PASSES = OUT_F32 ? 4 : 2;        // 128 bytes of a row per pass
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t ov[32];
-        tmem_ld32(t_o + c * 32, ov);
-        tc_wait_ld();
+      for (int pass = 0; pass < PASSES; ++pass) {
+        if (lane == 0) bulk_wait_read0();            // the previous store has left the staging tile
+        __syncwarp();
         if (OUT_F32) {
-          float4* dst = reinterpret_cast<float4*>(static_cast<float*>(p.out) + orow * HEAD_DIM + c * 32);
+          uint32_t ov[32];
+          tmem_ld32(t_o + pass * 32, ov);
+          tc_wait_ld();
 #pragma unroll
-          for (int j = 0; j < 8; ++j)
-            dst[j] = make_float4(__uint_as_float(ov[4 * j]) * inv, __uint_as_float(ov[4 * j + 1]) * inv,
-                                 __uint_as_float(ov[4 * j + 2]) * inv, __uint_as_float(ov[4 * j + 3]) * inv);
+          for (int j = 0; j < 8; ++j) {
+            const float4 val = make_float4(__uint_as_float(ov[4 * j]) * inv, __uint_as_float(ov[4 * j + 1]) * inv,
+                                           __uint_as_float(ov[4 * j + 2]) * inv, __uint_as_float(ov[4 * j + 3]) * inv);
+            *reinterpret_cast<float4*>(stage_g + lane * 128 + ((j ^ (lane & 7)) << 4)) = val;
+          }
         } else {
-          uint4* dst = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.out) + orow * HEAD_DIM + c * 32);
 #pragma unroll
-          for (int j = 0; j < 4; ++j)
-            dst[j] = make_uint4(
-                pack_bf16x2(__uint_as_float(ov[8 * j]) * inv, __uint_as_float(ov[8 * j + 1]) * inv),
-                pack_bf16x2(__uint_as_float(ov[8 * j + 2]) * inv, __uint_as_float(ov[8 * j + 3]) * inv),
-                pack_bf16x2(__uint_as_float(ov[8 * j + 4]) * inv, __uint_as_float(ov[8 * j + 5]) * inv),
-                pack_bf16x2(__uint_as_float(ov[8 * j + 6]) * inv, __uint_as_float(ov[8 * j + 7]) * inv));
+          for (int cc = 0; cc < 2; ++cc) {
+            uint32_t ov[32];
+            tmem_ld32(t_o + pass * 64 + cc * 32, ov);
+            tc_wait_ld();
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const uint4 val = make_uint4(
+                  pack_bf16x2(__uint_as_float(ov[8 * j]) * inv, __uint_as_float(ov[8 * j + 1]) * inv),
+                  pack_bf16x2(__uint_as_float(ov[8 * j + 2]) * inv, __uint_as_float(ov[8 * j + 3]) * inv),
+                  pack_bf16x2(__uint_as_float(ov[8 * j + 4]) * inv, __uint_as_float(ov[8 * j + 5]) * inv),
+                  pack_bf16x2(__uint_as_float(ov[8 * j + 6]) * inv, __uint_as_float(ov[8 * j + 7]) * inv));
+              *reinterpret_cast<uint4*>(stage_g + lane * 128 + (((cc * 4 + j) ^ (lane & 7)) << 4)) = val;
+            }
+          }
+        }
+        fence_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          tma_store_2d(&o_map, pass * (OUT_F32 ? 32 : 64), out_row32, stage);
+          bulk_commit();
         }
       }
       if (p.lse) p.lse[orow] = (row_max + log2f(row_sum)) * 0.6931471805599453f;
@@ -501,6 +572,7 @@ q_centric_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
   }
 
   // ---------------------------------------------------------------- teardown
+  if (warp < 8 && lane == 0) bulk_wait_all();      // output stores of this warp have completed
   tc_fence_before();
   __syncthreads();
   if (warp == MMA_WARP) {
@@ -510,6 +582,16 @@ q_centric_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
 }
 
 // ------------------------------------------------------------------ host side
+// Output map: boxes of 32 rows x 128 bytes, 128-byte swizzle.
+static int encode_out_map(CUtensorMap* map, void* ptr, uint64_t rows, bool f32) {
+  const cuuint64_t dims[2] = {HEAD_DIM, rows};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(HEAD_DIM) * (f32 ? 4 : 2)};
+  const cuuint32_t box[2] = {f32 ? 32u : 64u, 32};
+  const cuuint32_t steps[2] = {1, 1};
+  return encode_tiled(map, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, ptr, dims,
+                      strides, box, steps, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE);
+}
+
 static int encode_rows_map(CUtensorMap* map, const void* ptr, uint64_t rows) {
   const cuuint64_t dims[2] = {HEAD_DIM, rows};
   const cuuint64_t strides[1] = {HEAD_DIM * 2};
@@ -542,11 +624,12 @@ int launch_q_centric(const QCentricArgs& a, cudaStream_t stream) {
   p.num_items = p.items_per_seg * a.nseg;
   p.scale_log2 = 1.4426950408889634f / sqrtf(static_cast<float>(HEAD_DIM));
 
-  CUtensorMap qm, km, vm;
+  CUtensorMap qm, km, vm, om;
   if (encode_rows_map(&qm, a.q, static_cast<uint64_t>(a.batch) * a.hq * a.sq) ||
       encode_rows_map(&km, a.k, static_cast<uint64_t>(a.batch) * a.hkv * a.skv) ||
-      encode_rows_map(&vm, a.v, static_cast<uint64_t>(a.batch) * a.hkv * a.skv))
-    return set_error(SB_ERR_CUDA, "cuTensorMapEncodeTiled failed for q/k/v");
+      encode_rows_map(&vm, a.v, static_cast<uint64_t>(a.batch) * a.hkv * a.skv) ||
+      encode_out_map(&om, a.out, static_cast<uint64_t>(a.nseg) * a.batch * a.hq * a.sq, a.out_f32 != 0))
+    return set_error(SB_ERR_CUDA, "cuTensorMapEncodeTiled failed for q/k/v/out");
 
   auto kernel = a.out_f32 ? q_centric_kernel<true> : q_centric_kernel<false>;
   int& configured = a.out_f32 ? ctx->qc_attr_f32 : ctx->qc_attr_bf16;
@@ -556,7 +639,7 @@ int launch_q_centric(const QCentricArgs& a, cudaStream_t stream) {
     configured = 1;
   }
   const int grid = p.num_items < ctx->sm_count ? p.num_items : ctx->sm_count;
-  kernel<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(qm, km, vm, p);
+  kernel<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(qm, km, vm, om, p);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return set_error(SB_ERR_CUDA, cudaGetErrorString(e));
   return SB_OK;
