@@ -4,3 +4,4 @@ from .q_centric import attention, attention_out, attention_partial_out, stage_fu
 from .kv_centric import Prepared, kv_centric_attention, combine  # noqa: F401
 from .indexers import (SummarySelector, quantize_queries, quantize_keys, prepare_fp4_inputs,  # noqa: F401
                        fp4_block_scores, tile_topk, tile_topk_out, fp4_indexer, indexed_attention)
+from . import sharding  # noqa: F401

@@ -1,0 +1,139 @@
+"""Multi-GPU sharding of the hot path: one process per GPU, torch.distributed for the plumbing.
+
+Two ways to shard, both without TMA multicast or any load from a peer's memory:
+
+* by (batch, KV-head group): groups are independent in the indexer, in the
+  attention kernel and in Combine, so ranks need no data-path collective
+  (`group_range`, `group_view`);
+* by KV range (long contexts): `kv_ranks` ranks share the same heads, each owns a
+  contiguous range of KV blocks and the K/V rows of that range. A rank filters every
+  selection list to its range, runs the same attention kernel and gets a normalised
+  partial (O_r, L_r) for EVERY query; one exchange step then moves the slice of rows
+  a rank owns from every peer into local memory (NCCL send/recv), and the local
+  Combine kernel merges them by log-sum-exp (`KVSplit`).
+
+The reference has no multi-GPU path; this module adds the one the 1 Mi-token
+configuration needs.
+"""
+import torch
+import torch.distributed as dist
+
+
+def group_range(n_groups, world, rank):
+    """Contiguous, balanced range [start, stop) of (batch, KV-head) groups for `rank`."""
+    base, extra = divmod(n_groups, world)
+    start = rank * base + min(rank, extra)
+    return start, start + base + (1 if rank < extra else 0)
+
+
+def group_view(q, k, v, ids, start, stop, counts=None):
+    """Views of the groups [start, stop): the rank's problem has batch = #groups,
+    Hq = group size, Hkv = 1. No copy: a group is contiguous in every tensor."""
+    b, hq, sq, d = q.shape
+    hkv, skv = k.shape[1:3]
+    g = hq // hkv
+    qv = q.view(b * hkv, g, sq, d)[start:stop]
+    kv = k.view(b * hkv, 1, skv, d)[start:stop]
+    vv = v.view(b * hkv, 1, skv, d)[start:stop]
+    iv = ids.view(b * hkv, 1, ids.shape[2], ids.shape[3])[start:stop]
+    cv = None if counts is None else counts.view(b * hkv, 1, counts.shape[2])[start:stop]
+    return qv, kv, vv, iv, cv
+
+
+def kv_block_range(kv_blocks, kv_ranks, kv_rank):
+    """KV blocks [lo, hi) owned by a rank: ceil(kv_blocks / kv_ranks) wide, the same
+    split the segment-metadata kernel makes."""
+    width = (kv_blocks + kv_ranks - 1) // kv_ranks
+    lo = min(kv_rank * width, kv_blocks)
+    return lo, min(lo + width, kv_blocks)
+
+
+def exchange_rows(send, group=None):
+    """send: [R, rows_per_rank, ...] (slice j goes to rank j of `group`). Returns
+    recv [R, rows_per_rank, ...] where slice i came from rank i. Point-to-point
+    send/recv, so it runs on NCCL (GPU tensors) and on gloo (CPU tensors)."""
+    world = dist.get_world_size(group)
+    me = dist.get_rank(group)
+    recv = torch.empty_like(send)
+    recv[me].copy_(send[me])
+    ops = []
+    for peer in range(world):
+        if peer == me:
+            continue
+        gp = dist.get_global_rank(group, peer) if group is not None else peer
+        ops.append(dist.P2POp(dist.isend, send[peer], gp, group))
+        ops.append(dist.P2POp(dist.irecv, recv[peer], gp, group))
+    if ops:
+        for req in dist.batch_isend_irecv(ops):
+            req.wait()
+    return recv
+
+
+def _gpu_filter(ids, counts, kv_blocks, kv_ranks, kv_rank):
+    """Lists restricted to this rank's KV range, ids rebased to the local K/V slice."""
+    from . import _lib
+    b, hkv, qb, topk = ids.shape
+    seg_ids = torch.empty((kv_ranks, b, hkv, qb, topk), dtype=torch.int32, device=ids.device)
+    seg_counts = torch.empty((kv_ranks, b, hkv, qb), dtype=torch.int32, device=ids.device)
+    err = torch.zeros(1, dtype=torch.int32, device=ids.device)
+    with torch.cuda.device(ids.device):
+        _lib.check(_lib.lib().sparse_b200_split_kv_segments(
+            _lib.ptr(ids), _lib.ptr(counts), _lib.ptr(seg_ids), _lib.ptr(seg_counts), _lib.ptr(err),
+            b, hkv, qb, topk, kv_blocks, kv_ranks, _lib.current_stream()))
+    lo, _ = kv_block_range(kv_blocks, kv_ranks, kv_rank)
+    return (seg_ids[kv_rank] - lo).clamp_(min=0), seg_counts[kv_rank]
+
+
+def _gpu_attention(q, k, v, ids, counts):
+    from .q_centric import attention_out
+    out = torch.empty_like(q)
+    lse = torch.empty(q.shape[:3], dtype=torch.float32, device=q.device)
+    attention_out(q, k, v, ids, out, counts, lse)
+    return out, lse
+
+
+def _gpu_combine(partial, lses):
+    """partial [R, rows, 128] bf16/fp32, lses [R, rows] -> (bf16 [rows,128], fp32 [rows])."""
+    from . import _lib
+    import ctypes
+    ranks, rows = lses.shape
+    out = torch.empty((rows, 128), dtype=torch.bfloat16, device=partial.device)
+    lse = torch.empty((rows,), dtype=torch.float32, device=partial.device)
+    with torch.cuda.device(partial.device):
+        _lib.check(_lib.lib().sparse_b200_combine(
+            _lib.ptr(partial), int(partial.dtype == torch.float32), _lib.ptr(lses), _lib.ptr(out), _lib.ptr(lse),
+            ctypes.c_int64(rows), ranks, 1, _lib.current_stream()))
+    return out, lse
+
+
+class KVSplit:
+    """KV-range split of one (set of) head group(s) over the ranks of `group`.
+
+    q [B,Hq,Sq,128] (same on every rank of the group), k_local / v_local
+    [B,Hkv,Skv/R,128] (this rank's KV rows), ids [B,Hkv,Sq/128,TopK] GLOBAL block ids.
+    `run` returns this rank's slice of the merged result: rows [r*rows/R, (r+1)*rows/R)
+    of the flattened [B*Hq*Sq] axis, as (O [rows/R,128] bf16, LSE [rows/R] fp32).
+    The three stage functions can be replaced (the CPU tests inject the oracle)."""
+
+    def __init__(self, group=None, filter_fn=_gpu_filter, attention_fn=_gpu_attention, combine_fn=_gpu_combine):
+        self.group = group
+        self.ranks = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.filter_fn, self.attention_fn, self.combine_fn = filter_fn, attention_fn, combine_fn
+
+    def partial(self, q, k_local, v_local, ids, kv_blocks, counts=None):
+        ids_r, counts_r = self.filter_fn(ids, counts, kv_blocks, self.ranks, self.rank)
+        return self.attention_fn(q, k_local, v_local, ids_r, counts_r)
+
+    def merge(self, o_r, l_r):
+        rows = l_r.numel()
+        if rows % self.ranks:
+            raise ValueError("B*Hq*Sq must be divisible by the number of KV ranks")
+        per = rows // self.ranks
+        o_all = exchange_rows(o_r.reshape(self.ranks, per, 128), self.group)
+        l_all = exchange_rows(l_r.reshape(self.ranks, per), self.group)
+        return self.combine_fn(o_all, l_all)
+
+    def run(self, q, k_local, v_local, ids, kv_blocks, counts=None):
+        o_r, l_r = self.partial(q, k_local, v_local, ids, kv_blocks, counts)
+        return self.merge(o_r, l_r)
