@@ -278,6 +278,178 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+# --------------------------------------------------------------------------- other configurations
+CONFIGS = {
+    # name: B, Hq, Hkv, N, topk, indexer, operator
+    "c1": dict(B=1, Hq=8, Hkv=8, N=4096, topk=8, indexer="r1", op="q_centric", k_offset=0.5),
+    "c3": dict(B=2, Hq=64, Hkv=8, N=65536, topk=32, indexer="r4", op="q_centric", k_offset=0.5),
+    "c4": dict(B=1, Hq=64, Hkv=4, N=131072, topk=64, indexer="fp4", op="kv_centric", k_offset=0.0),
+    "c5": dict(B=1, Hq=64, Hkv=8, N=1048576, topk=64, indexer="r4", op="q_centric", k_offset=0.5),
+}
+
+
+def fill_normal_bf16(t, gen, k_offset=0.0):
+    """N(0,1) in place, generated head by head (a 1 Mi-token tensor does not fit twice in fp32);
+    optionally adds a per-128-row-block offset ~ N(0, k_offset) (the K families of configurations 1, 3, 5)."""
+    import torch
+    flat = t.view(-1, t.shape[-2], t.shape[-1])
+    for h in range(flat.shape[0]):
+        rows = flat.shape[1]
+        for r0 in range(0, rows, 1 << 18):
+            r1 = min(rows, r0 + (1 << 18))
+            x = torch.randn((r1 - r0, 128), device=t.device, generator=gen)
+            if k_offset:
+                off = torch.randn(((r1 - r0) // 128, 1, 128), device=t.device, generator=gen) * k_offset
+                x = (x.view(-1, 128, 128) + off).view(-1, 128)
+            flat[h, r0:r1] = x.to(torch.bfloat16)
+
+
+def timed(fn, steps, warmup, barrier):
+    import torch
+    for _ in range(warmup):
+        fn()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    barrier()
+    return e0.elapsed_time(e1) / steps
+
+
+def run_config(args):
+    """Configurations 1, 3, 4, 5: indexer -> lists -> attention operator, stage by stage.
+    With N > 1 ranks the (batch, KV-head) groups are dealt to the ranks (strong scaling, no
+    collective); --kv-split R additionally splits the KV range R ways inside each head shard
+    and merges partial (O, LSE) over NCCL."""
+    import torch
+    import torch.distributed as dist
+    import sparse_attention_b200_b200 as sp
+    from sparse_attention_b200_b200 import sharding
+
+    cfg = CONFIGS[args.workload]
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    kvs = max(1, args.kv_split)
+    head_shards = world // kvs
+    shard, kv_rank = rank // kvs, rank % kvs
+    kv_group = None
+    if kvs > 1:
+        for s_ in range(head_shards):
+            g_ = dist.new_group(list(range(s_ * kvs, (s_ + 1) * kvs)))
+            if s_ == shard:
+                kv_group = g_
+
+    B, Hq, Hkv, N, topk = cfg["B"], cfg["Hq"], cfg["Hkv"], cfg["N"], cfg["topk"]
+    G = Hq // Hkv
+    g0, g1 = sharding.group_range(B * Hkv, head_shards, shard)
+    ng = g1 - g0                                    # this rank's problem: batch ng, Hq G, Hkv 1
+    gen = torch.Generator(device=dev).manual_seed(17 + shard)
+    q = torch.empty((ng, G, N, 128), dtype=torch.bfloat16, device=dev)
+    k = torch.empty((ng, 1, N, 128), dtype=torch.bfloat16, device=dev)
+    v = torch.empty((ng, 1, N, 128), dtype=torch.bfloat16, device=dev)
+    fill_normal_bf16(q, gen)
+    fill_normal_bf16(k, gen, cfg["k_offset"])
+    fill_normal_bf16(v, gen)
+    nb = N // 128
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    stages = {}
+    steps, warmup = args.steps, max(args.warmup, 3)
+    # ---------------- indexer
+    if cfg["indexer"] in ("r1", "r4"):
+        r = 1 if cfg["indexer"] == "r1" else 4
+        sel = sp.SummarySelector(q, k, r, topk=topk, keep_scores=False)
+        stages["indexer_pool_ms"] = timed(sel.prepare, steps, warmup, barrier)
+        stages["indexer_score_topk_ms"] = timed(sel.score, steps, warmup, barrier)
+        stages["indexer_ms"] = timed(sel.run, steps, warmup, barrier)
+        ids = sel.ids
+        pool_bytes = (q.numel() + k.numel()) * 2 * (1 + r / 128.0)
+        stages["indexer_pool_gbs"] = pool_bytes / stages["indexer_pool_ms"] / 1e6
+        stages["indexer_score_flop"] = 2.0 * ng * (G * nb * r) * (nb * r) * 128
+    else:
+        hidx = 1                                   # one index vector per (token, KV head) = mean of the group
+        qc = qs = kc = ks = None
+
+        def quant():
+            nonlocal qc, qs, kc, ks
+            qc, qs = sp.quantize_queries(q, hidx)
+            kc, ks = sp.quantize_keys(k)
+        stages["quantize_ms"] = timed(quant, steps, warmup, barrier)
+        inputs = sp.prepare_fp4_inputs(qc, kc, qs, ks, batch_size=ng, len_q=N, len_kv=N)
+        ids = torch.empty((ng, 1, nb, topk), dtype=torch.int32, device=dev)
+        tile_scores = torch.empty((ng, 1, nb, nb), dtype=torch.float32, device=dev)
+        stages["indexer_ms"] = timed(lambda: sp.fp4_indexer(inputs, ids, tile_scores=tile_scores),
+                                     min(steps, 3), 1, barrier)
+    # ---------------- attention
+    fl_local = 4.0 * ng * G * N * (topk * 128) * 128
+    if kvs > 1:
+        lo, hi = sharding.kv_block_range(nb, kvs, kv_rank)
+        k_loc = k[:, :, lo * 128:hi * 128].contiguous()
+        v_loc = v[:, :, lo * 128:hi * 128].contiguous()
+        split = sharding.KVSplit(kv_group)
+        res = {}
+
+        def attn():
+            res["o"], res["l"] = split.run(q, k_loc, v_loc, ids, nb)
+        fl_local /= kvs
+    elif cfg["op"] == "kv_centric":
+        prep = sp.Prepared(q, k, v, ids, nseg=args.segments, partial="bf16")
+        stages["kv_metadata_ms"] = timed(prep.metadata, steps, warmup, barrier)
+        stages["kv_main_ms"] = timed(prep.main, steps, warmup, barrier)
+        stages["kv_combine_ms"] = timed(prep.combine, steps, warmup, barrier)
+        rows = ng * G * N
+        comb_bytes = rows * (args.segments * (256 + 4) + 256 + 4)
+        stages["kv_combine_gbs"] = comb_bytes / stages["kv_combine_ms"] / 1e6
+        attn = prep.run
+    else:
+        out = torch.empty_like(q)
+        lse = torch.empty((ng, G, N), dtype=torch.float32, device=dev)
+
+        def attn():
+            sp.attention_out(q, k, v, ids, out, None, lse)
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    ms_attn = timed(attn, steps, warmup, barrier)
+    clocks = sampler.stop() if rank == 0 else None
+    sp.device_status()
+    t = torch.tensor([ms_attn, stages.get("indexer_ms", 0.0)], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_attn, ms_idx = t.tolist()
+    total_flops = 4.0 * B * Hq * N * (topk * 128) * 128
+    if rank == 0:
+        peak_tf, peak_gbs, peak_src = measured_peaks()
+        value = total_flops / (ms_attn * 1e-3) / 1e12
+        per_gpu = value / world
+        line = {"metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": steps,
+                "warmup": warmup, "ms_per_step": ms_attn, "higher_is_better": True, "scaling": "strong",
+                "vs_baseline": None, "dtype": "bf16", "data": "synthetic (seeded N(0,1), K block offsets per config)",
+                "config": {"workload": args.workload, **{kk: vv for kk, vv in cfg.items()}, "d": 128,
+                           "sharding": f"{head_shards} head-group shard(s) x {kvs} KV range(s)",
+                           "kv_segments": args.segments if cfg["op"] == "kv_centric" else None},
+                "pct_bf16_peak": 100.0 * per_gpu / peak_tf, "indexer_ms": ms_idx,
+                "stages_rank0": stages,
+                "roofline": {"bound": "tensor", "achieved": per_gpu, "peak": peak_tf, "unit": "TFLOP/s",
+                             "frac": per_gpu / peak_tf, "traffic": None, "peak_source": peak_src,
+                             "kernel": "q_centric_kernel", "hbm_peak_gbs": peak_gbs},
+                "clocks": clocks}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -286,9 +458,15 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--kernel-only", action="store_true",
                     help="device-resident timing only (used for profiler captures): no e2e, no CPU baseline")
+    ap.add_argument("--workload", default="c2", choices=["c2"] + sorted(CONFIGS),
+                    help="c2 (default) is the headline workload; c1/c3/c4/c5 run indexer + operator stage by stage")
+    ap.add_argument("--kv-split", type=int, default=1, help="KV ranges per head shard (c5 only, needs --gpus >= 2)")
+    ap.add_argument("--segments", type=int, default=4, help="KV-range segments of the KV-centric operator (c4)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload != "c2":
+        run_config(args)
     else:
         run_ours(args)
 

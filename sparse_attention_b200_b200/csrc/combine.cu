@@ -1,7 +1,7 @@
 // Log-sum-exp merge of partial (O, LSE): HBM-bound streaming kernel.
 //   m = max_r L_r, w_r = exp(L_r - m), O = sum_r w_r O_r / sum_r w_r,
 //   LSE = m + log(sum_r w_r)            (ranks accumulated in order 0..R-1)
-// One warp per output row, four features per lane. Partials may be fp32 or
+// Half a warp per output row, eight features per lane. Partials may be fp32 or
 // bf16 and are addressed with strides, so both the rank-major layout
 // [R, rows, 128] written by the segment kernel and the rank-inner layout
 // [rows, R, 128] of the reference are accepted.
@@ -14,73 +14,91 @@
 namespace sb {
 namespace {
 
+// eight consecutive features of one partial row as fp32
 template <typename T>
-__device__ __forceinline__ float4 load4(const T* p);
+__device__ __forceinline__ void load8(const T* p, float (&f)[8]);
 template <>
-__device__ __forceinline__ float4 load4<float>(const float* p) {
-  return __ldcs(reinterpret_cast<const float4*>(p));
+__device__ __forceinline__ void load8<float>(const float* p, float (&f)[8]) {
+  const float4 a = __ldcs(reinterpret_cast<const float4*>(p));
+  const float4 b = __ldcs(reinterpret_cast<const float4*>(p) + 1);
+  f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
 }
 template <>
-__device__ __forceinline__ float4 load4<__nv_bfloat16>(const __nv_bfloat16* p) {
-  const uint2 raw = __ldcs(reinterpret_cast<const uint2*>(p));
-  const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
-  const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
-  return make_float4(a.x, a.y, b.x, b.y);
+__device__ __forceinline__ void load8<__nv_bfloat16>(const __nv_bfloat16* p, float (&f)[8]) {
+  const uint4 raw = __ldcs(reinterpret_cast<const uint4*>(p));
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    const float2 v = __bfloat1622float2(h[e]);
+    f[2 * e] = v.x;
+    f[2 * e + 1] = v.y;
+  }
 }
 
+// Half a warp (16 lanes x 8 features) per output row. The partial rows of up to
+// four ranks are requested before the weights are known, so the two dependent
+// memory round trips (LSE, then partials) overlap; a rank of weight 0 is then
+// dropped with a select, whatever it holds.
 template <typename T>
 __global__ void __launch_bounds__(256) combine_kernel(const T* __restrict__ partial, const float* __restrict__ lses,
                                                       __nv_bfloat16* __restrict__ out, float* __restrict__ out_lse,
                                                       long long rows, int ranks, long long p_stride_rank,
                                                       long long p_stride_row, long long l_stride_rank,
                                                       long long l_stride_row) {
-  const int lane = threadIdx.x & 31;
-  const long long warps_total = static_cast<long long>(gridDim.x) * (blockDim.x >> 5);
-  for (long long row = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5); row < rows;
-       row += warps_total) {
-    float maximum = -CUDART_INF_F;
-    for (int r = lane; r < ranks; r += 32)
-      maximum = fmaxf(maximum, lses[r * l_stride_rank + row * l_stride_row]);
-#pragma unroll
-    for (int d = 16; d > 0; d >>= 1) maximum = fmaxf(maximum, __shfl_xor_sync(0xffffffffu, maximum, d));
-    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  const int sub = threadIdx.x & 15;
+  const long long halves_total = static_cast<long long>(gridDim.x) * (blockDim.x >> 4);
+  for (long long row = static_cast<long long>(blockIdx.x) * (blockDim.x >> 4) + (threadIdx.x >> 4); row < rows;
+       row += halves_total) {
+    const T* base = partial + row * p_stride_row + sub * 8;
+    const float* lbase = lses + row * l_stride_row;
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
     float denom = 0.f;
+    // Requests first, arithmetic later: the partial rows of the first four ranks and
+    // every rank's LSE (a broadcast within the half warp) are all in flight together.
+    float val[4][8];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if (j < ranks) {
+        load8<T>(base + j * p_stride_rank, val[j]);
+      } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) val[j][e] = 0.f;
+      }
+    }
+    float maximum = -CUDART_INF_F;
+    for (int r = 0; r < ranks; ++r) maximum = fmaxf(maximum, __ldg(lbase + r * l_stride_rank));
     if (maximum > -CUDART_INF_F) {
-      const T* base = partial + row * p_stride_row + lane * 4;
       for (int r0 = 0; r0 < ranks; r0 += 4) {
-        float4 val[4];
         float wgt[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          const int r = r0 + j;
-          if (r < ranks) {
-            const float l = lses[r * l_stride_rank + row * l_stride_row];
-            wgt[j] = (l > -CUDART_INF_F) ? expf(l - maximum) : 0.f;
-            // A rank with weight 0 may hold anything (even NaN): skip its load.
-            val[j] = (wgt[j] > 0.f) ? load4<T>(base + r * p_stride_rank) : make_float4(0.f, 0.f, 0.f, 0.f);
+          if (r0 + j < ranks) {
+            if (r0 > 0) load8<T>(base + (r0 + j) * p_stride_rank, val[j]);
+            wgt[j] = expf(__ldg(lbase + (r0 + j) * l_stride_rank) - maximum);   // exp(-inf) = 0
           } else {
             wgt[j] = 0.f;
-            val[j] = make_float4(0.f, 0.f, 0.f, 0.f);
           }
         }
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           denom += wgt[j];
-          acc.x = fmaf(wgt[j], val[j].x, acc.x);
-          acc.y = fmaf(wgt[j], val[j].y, acc.y);
-          acc.z = fmaf(wgt[j], val[j].z, acc.z);
-          acc.w = fmaf(wgt[j], val[j].w, acc.w);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) acc[e] = fmaf(wgt[j], wgt[j] > 0.f ? val[j][e] : 0.f, acc[e]);
         }
       }
       const float inv = 1.0f / denom;
-      acc.x *= inv; acc.y *= inv; acc.z *= inv; acc.w *= inv;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[e] *= inv;
     }
-    __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x, acc.y), hi = __floats2bfloat162_rn(acc.z, acc.w);
-    uint2 packed;
-    packed.x = *reinterpret_cast<uint32_t*>(&lo);
-    packed.y = *reinterpret_cast<uint32_t*>(&hi);
-    *reinterpret_cast<uint2*>(out + row * 128 + lane * 4) = packed;
-    if (lane == 0 && out_lse) out_lse[row] = (maximum > -CUDART_INF_F) ? maximum + logf(denom) : -CUDART_INF_F;
+    uint4 packed;
+    uint32_t* pw = reinterpret_cast<uint32_t*>(&packed);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      __nv_bfloat162 h = __floats2bfloat162_rn(acc[2 * e], acc[2 * e + 1]);
+      pw[e] = *reinterpret_cast<uint32_t*>(&h);
+    }
+    *reinterpret_cast<uint4*>(out + row * 128 + sub * 8) = packed;
+    if (sub == 0 && out_lse) out_lse[row] = (maximum > -CUDART_INF_F) ? maximum + logf(denom) : -CUDART_INF_F;
   }
 }
 
@@ -91,8 +109,8 @@ int launch_combine(const void* partial, int partial_is_f32, const float* lses, v
                    long long l_stride_rank, long long l_stride_row, cudaStream_t stream) {
   DeviceCtx* ctx = device_ctx();
   if (!ctx) return SB_ERR_CUDA;
-  const long long blocks_needed = (rows + 7) / 8;
-  const long long cap = static_cast<long long>(ctx->sm_count) * 32;
+  const long long blocks_needed = (rows + 15) / 16;
+  const long long cap = static_cast<long long>(ctx->sm_count) * 64;
   const int grid = static_cast<int>(blocks_needed < cap ? blocks_needed : cap);
   if (partial_is_f32)
     combine_kernel<float><<<grid, 256, 0, stream>>>(static_cast<const float*>(partial), lses,
