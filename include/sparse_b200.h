@@ -112,6 +112,18 @@ int sparse_b200_indexer_summary(const void* q, const void* k, void* q_desc, void
                                 int32_t* block_idx, int batch, int hq, int hkv, int sq, int skv, int representatives,
                                 int topk, void* stream);
 
+/* Same block ids as sparse_b200_indexer_summary, bit for bit, computed with a
+ * tensor-core pre-filter (tcgen05 MMA on the pooled descriptors) followed by exact
+ * re-scoring of the surviving candidates and an exact fallback per list when the
+ * pre-filter cannot be proven safe. No scores output. `aux` is a device workspace
+ * of sparse_b200_indexer_summary_aux_bytes(B, Hkv) bytes; its last int counts the
+ * lists that took the fallback. Shapes the tensor-core path does not cover run the
+ * exact kernel. Replaces descriptor_dot + reduce_topk (indexers/r1_r4/gpu_ops.py:19-49). */
+int64_t sparse_b200_indexer_summary_aux_bytes(int batch, int hkv);
+int sparse_b200_indexer_summary_fast(const void* q, const void* k, void* q_desc, void* k_desc, void* aux,
+                                     int32_t* block_idx, int batch, int hq, int hkv, int sq, int skv,
+                                     int representatives, int topk, void* stream);
+
 /* NVFP4 indexer. Index vectors: 64 bytes of e2m1 codes (low nibble first) + 8
  * e4m3 scales per 128 features (contract of prepare_fp4_inputs,
  * indexers/fp4/fp4.py:37-60). q_codes [B*Sq, Hidx, 64], q_scales [B*Sq, Hidx, 8],

@@ -256,6 +256,31 @@ int sparse_b200_indexer_summary(const void* q, const void* k, void* q_desc, void
                                    representatives, topk, static_cast<cudaStream_t>(stream));
 }
 
+int64_t sparse_b200_indexer_summary_aux_bytes(int batch, int hkv) {
+  if (batch <= 0 || hkv <= 0) return SB_ERR_INVALID;
+  return (static_cast<int64_t>(batch) * hkv + 1) * 4;
+}
+
+int sparse_b200_indexer_summary_fast(const void* q, const void* k, void* q_desc, void* k_desc, void* aux,
+                                     int32_t* block_idx, int batch, int hq, int hkv, int sq, int skv,
+                                     int representatives, int topk, void* stream) {
+  REQUIRE(q && k && q_desc && k_desc && aux && block_idx, "null pointer");
+  REQUIRE(sq >= 128 && sq % 128 == 0 && skv >= 128 && skv % 128 == 0, "Sq and Skv must be positive multiples of 128");
+  int rc = check_summary(batch, hq, hkv, sq / 128, skv / 128, representatives, topk);
+  if (rc) return rc;
+  REQUIRE((reinterpret_cast<uintptr_t>(aux) & 3u) == 0 && aligned16(q_desc) && aligned16(k_desc), "misaligned workspace");
+  rc = sparse_b200_pool_blocks(q, q_desc, batch, hq, sq, representatives, stream);
+  if (rc) return rc;
+  rc = sparse_b200_pool_blocks(k, k_desc, batch, hkv, skv, representatives, stream);
+  if (rc) return rc;
+  rc = launch_summary_select_tc(q_desc, k_desc, aux, block_idx, batch, hq, hkv, sq / 128, skv / 128, representatives,
+                                topk, static_cast<cudaStream_t>(stream));
+  if (rc == 1)      // not eligible for the tensor-core path: exact kernel, same ids
+    rc = launch_summary_score_topk(q_desc, k_desc, nullptr, block_idx, batch, hq, hkv, sq / 128, skv / 128,
+                                   representatives, topk, static_cast<cudaStream_t>(stream));
+  return rc;
+}
+
 int sparse_b200_nvfp4_quantize(const void* x, void* packed, void* scales, int batch, int heads_out, int group,
                                int seq, int paged, void* stream) {
   REQUIRE(x && packed && scales, "null pointer");

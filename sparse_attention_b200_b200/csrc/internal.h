@@ -18,6 +18,7 @@ struct DeviceCtx {
   int* status = nullptr;      // device word written by kernels that abort a wait
   int qc_attr_bf16 = 0, qc_attr_f32 = 0;
   int misc_attr[8] = {0};
+  int tc_attr = 0;
 };
 DeviceCtx* device_ctx();
 
@@ -45,6 +46,8 @@ int launch_split_segments(const int32_t* ids, const int32_t* counts, int32_t* se
 int launch_pool(const void* x, void* desc, long long num_desc, int tokens_per_desc, cudaStream_t stream);
 int launch_summary_score_topk(const void* qd, const void* kd, float* scores, int32_t* ids, int batch, int hq, int hkv,
                               int qt, int nt, int r, int topk, cudaStream_t stream);
+int launch_summary_select_tc(const void* qd, const void* kd, void* aux, int32_t* ids, int batch, int hq, int hkv,
+                             int qt, int nt, int r, int topk, cudaStream_t stream);
 int launch_quantize(const void* x, void* packed, void* scales, int batch, int heads_out, int group, int seq,
                     int paged, cudaStream_t stream);
 int launch_fp4_scores(const void* qp, const void* qs, const void* kp, const void* ks, float* query_scores,

@@ -16,10 +16,11 @@ __device__ __forceinline__ bool better(float s, int i, float bs, int bi) {
   return s > bs || (s == bs && i < bi);
 }
 
-// scores: shared memory [n]; scratch: shared memory, 2 * (blockDim.x / 32) + 2 words.
+// scores: shared memory [n]; scratch_f / scratch_i: shared memory, blockDim.x / 32 + 1 words each.
 // All threads of the block must call. ids_out may point to global memory.
-__device__ __forceinline__ void block_topk(float* scores, int n, int k, int32_t* ids_out, float* scratch_f,
-                                           int* scratch_i) {
+// vals_out (optional, may be shared memory): the scores of the winners, same order.
+__device__ __forceinline__ void block_topk_ex(float* scores, int n, int k, int32_t* ids_out, float* vals_out,
+                                              float* scratch_f, int* scratch_i) {
   const int tid = threadIdx.x, nthreads = blockDim.x;
   const int lane = tid & 31, warp = tid >> 5, nwarps = nthreads >> 5;
   float my_s = -CUDART_INF_F;
@@ -55,7 +56,7 @@ __device__ __forceinline__ void block_topk(float* scores, int n, int k, int32_t*
         const int oi = __shfl_xor_sync(0xffffffffu, bi, d);
         if (better(os, oi, bs, bi)) { bs = os; bi = oi; }
       }
-      if (lane == 0) { scratch_i[nwarps] = bi; }
+      if (lane == 0) { scratch_i[nwarps] = bi; scratch_f[nwarps] = bs; }
     }
     __syncthreads();
     const int winner = scratch_i[nwarps];
@@ -63,9 +64,17 @@ __device__ __forceinline__ void block_topk(float* scores, int n, int k, int32_t*
       scores[winner] = __int_as_float(0x7fc00000);   // NaN = retired
       dirty = true;
     }
-    if (tid == 0) ids_out[rank] = winner == INT_MAX ? 0 : winner;
+    if (tid == 0) {
+      ids_out[rank] = winner == INT_MAX ? 0 : winner;
+      if (vals_out) vals_out[rank] = scratch_f[nwarps];
+    }
     __syncthreads();
   }
+}
+
+__device__ __forceinline__ void block_topk(float* scores, int n, int k, int32_t* ids_out, float* scratch_f,
+                                           int* scratch_i) {
+  block_topk_ex(scores, n, k, ids_out, nullptr, scratch_f, scratch_i);
 }
 
 }  // namespace sb

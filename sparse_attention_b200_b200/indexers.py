@@ -38,6 +38,8 @@ class SummarySelector:
         self.scores = torch.empty((b, hkv, self.qt, self.nt), dtype=torch.float32, device=q.device) \
             if keep_scores else None
         self.ids = torch.empty((b, hkv, self.qt, topk), dtype=torch.int32, device=q.device)
+        # workspace of the tensor-core path: key abs-max per (batch, KV head) + fallback counter
+        self.aux = torch.zeros(b * hkv + 1, dtype=torch.int32, device=q.device)
         self.name = f"mean{r}_bf16"
 
     def prepare(self):
@@ -59,7 +61,22 @@ class SummarySelector:
     def topk_stage(self):
         return self.ids
 
+    def run_fast(self):
+        """Same ids through the tensor-core pre-filter + exact re-scoring (no scores output)."""
+        with torch.cuda.device(self.q.device):
+            _lib.check(_lib.lib().sparse_b200_indexer_summary_fast(
+                _lib.ptr(self.q), _lib.ptr(self.k), _lib.ptr(self.qd), _lib.ptr(self.kd), _lib.ptr(self.aux),
+                _lib.ptr(self.ids), self.b, self.hq, self.hkv, self.qt * 128, self.nt * 128, self.r, self.topk,
+                _lib.current_stream()))
+        return self.ids
+
+    def fallback_lists(self):
+        """Lists of the last run_fast() that needed the exact fallback (synchronising)."""
+        return int(self.aux[-1].item())
+
     def run(self):
+        if self.scores is None:
+            return self.run_fast()
         with torch.cuda.device(self.q.device):
             _lib.check(_lib.lib().sparse_b200_indexer_summary(
                 _lib.ptr(self.q), _lib.ptr(self.k), _lib.ptr(self.qd), _lib.ptr(self.kd), _lib.ptr(self.scores),

@@ -76,6 +76,61 @@ def test_summary_selector_bit_exact(shape):
     assert torch.equal(sel2.run().cpu(), ids)
 
 
+@pytest.mark.parametrize("shape", [
+    # B, Hq, Hkv, Sq, Skv, R, topk, k offset
+    (1, 8, 8, 4096, 4096, 1, 8, 0.5),        # configuration 1 (GR = 1, candidates = 24 of 32)
+    (2, 16, 2, 1024, 8192, 4, 32, 0.5),      # group 8, R4 (GR = 32)
+    (1, 16, 1, 512, 16384, 4, 64, 0.5),      # group 16, R4 (GR = 64), top-64 of 128
+    (1, 4, 2, 256, 1024, 2, 8, 0.0),         # GR = 4, top-k == all blocks
+    (1, 8, 2, 384, 32768, 1, 16, 0.5),       # GR = 4, 256 blocks, query-block count not a multiple of QB
+    (1, 2, 1, 256, 65536, 4, 16, 0.0),       # GR = 8, 512 blocks
+    (1, 6, 2, 256, 2048, 4, 5, 0.0),         # group 3: not eligible, exact kernel behind the same entry
+])
+def test_summary_selector_tensor_core_path_bit_exact(shape):
+    b, hq, hkv, sq, skv, r, topk, off = shape
+    m = sp()
+    q, k, _ = gen.make_qkv(b, hq, hkv, sq, skv, seed=19, k_block_offset=off)
+    sel = m.SummarySelector(q.cuda(), k.cuda(), r, topk=topk, keep_scores=False)
+    ids = sel.run_fast()
+    torch.cuda.synchronize()
+    m.device_status()
+    ref = oracle.summary_select(q, k, r, topk)[3]
+    assert torch.equal(ids.cpu(), ref)
+    print("lists that fell back to exact scoring:", sel.fallback_lists())
+
+
+def test_summary_selector_tensor_core_path_ties_and_constant_inputs():
+    """Exact ties cannot be proven safe by the pre-filter: those lists must take the
+    exact fallback and still come out with the lower block id first."""
+    m = sp()
+    q, k = cases.selector_inputs("zeros", skv=8192)      # 64 blocks > 32 candidates
+    sel = m.SummarySelector(q.cuda(), k.cuda(), 4, topk=16, keep_scores=False)
+    ids = sel.run_fast().cpu()
+    assert torch.equal(ids, torch.arange(16, dtype=torch.int32).expand_as(ids))
+    assert sel.fallback_lists() == ids.shape[0] * ids.shape[1] * ids.shape[2]
+    # constant non-zero inputs: every score equal and non-zero
+    qc = torch.full_like(q, 0.5)
+    kc = torch.full_like(k, -0.25)
+    sel = m.SummarySelector(qc.cuda(), kc.cuda(), 1, topk=16, keep_scores=False)
+    ids = sel.run_fast().cpu()
+    assert torch.equal(ids, torch.arange(16, dtype=torch.int32).expand_as(ids))
+    # duplicated KV blocks inside the top-k: equal exact scores, lower id first
+    q, k, _ = gen.make_qkv(1, 4, 1, 256, 8192, seed=23)
+    k = k.clone()
+    k[:, :, 5 * 128:6 * 128] = k[:, :, 2 * 128:3 * 128]
+    k[:, :, 9 * 128:10 * 128] = k[:, :, 2 * 128:3 * 128]
+    sel = m.SummarySelector(q.cuda(), k.cuda(), 4, topk=16, keep_scores=False)
+    assert torch.equal(sel.run_fast().cpu(), oracle.summary_select(q, k, 4, 16)[3])
+    # the reference's stress family
+    fx = np.load(os.path.join(G, "selectors.npz"))
+    for family in ("gaussian", "cancellation_stress"):
+        q, k = cases.selector_inputs(family)
+        for r in (1, 4):
+            sel = m.SummarySelector(q.cuda(), k.cuda(), r, topk=16, keep_scores=False)
+            np.testing.assert_array_equal(sel.run_fast().cpu().numpy(), fx[f"{family}_r{r}_ids"])
+    m.device_status()
+
+
 def test_summary_selector_duplicate_scores_tie_to_lower_id():
     """Duplicate KV blocks give exactly equal scores: the lower id must come first."""
     m = sp()
