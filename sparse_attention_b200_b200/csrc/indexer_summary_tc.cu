@@ -223,7 +223,8 @@ score_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant
   } else if (warp < 4) {
     // epilogue: thread = key descriptor row of the tile
     const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
-    const int rr = p.r < 32 ? p.r : 32;
+    const int r_log2 = 31 - __clz(p.r);                  // R is 1, 2 or 4
+    const int n_chunks = n_cols >> 4;
     bool ok = true;
     for (int t = 0; ok && t < num_tiles; ++t) {
       const int acc = t & 1;
@@ -233,41 +234,51 @@ score_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant
       tc_fence_after();
       const int n = ((t + rot) % num_tiles) * 128 + warp * 32 + lane;
       const bool row_ok = n < n_keys;
-      const int blk = n / p.r;
-      auto flush = [&](int tl, float val) {
-        for (int d = 1; d < rr; d <<= 1) val = fmaxf(val, __shfl_xor_sync(0xffffffffu, val, d));
-        if (row_ok && (lane % rr) == 0 && qtile0 + tl < p.qt) atomicMax(&scores[tl * p.nt + blk], f2ord(val));
-      };
+      const int blk = n >> r_log2;
       const uint32_t t_acc = tmem + lane_base + acc * 128;
-      float cur = -INFINITY;
-      for (int c = 0; c < (n_cols >> 4); ++c) {
-        uint32_t v[16];
-        tmem_ld16(t_acc + c * 16, v);
-        tc_wait_ld();
-        if (GR >= 16) {
-          float m = __uint_as_float(v[0]);
+      // all columns into registers with one wait, then hand the accumulator back at once
+      uint32_t v[8][16];
 #pragma unroll
-          for (int j = 1; j < 16; ++j) m = fmaxf(m, __uint_as_float(v[j]));
-          cur = fmaxf(cur, m);
-          if ((((c + 1) * 16) % GR) == 0) {
-            flush((c * 16) / GR, cur);
-            cur = -INFINITY;
-          }
-        } else {
-          constexpr int PER = GR >= 16 ? 1 : 16 / GR;
-          constexpr int W = GR >= 16 ? 16 : GR;
-#pragma unroll
-          for (int sg = 0; sg < PER; ++sg) {
-            float m = __uint_as_float(v[sg * W]);
-#pragma unroll
-            for (int j = 1; j < W; ++j) m = fmaxf(m, __uint_as_float(v[sg * W + j]));
-            flush(c * PER + sg, m);
-          }
-        }
-      }
+      for (int c = 0; c < 8; ++c)
+        if (c < n_chunks) tmem_ld16(t_acc + c * 16, v[c]);
+      tc_wait_ld();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(ACC_EMPTY + acc));
+      // Every (query block, KV block) pair is produced by exactly one lane group of one
+      // tile, so a plain store suffices.
+      auto flush = [&](int tl, float val) {
+        for (int d = 1; d < p.r; d <<= 1) val = fmaxf(val, __shfl_xor_sync(0xffffffffu, val, d));
+        if (row_ok && (lane & (p.r - 1)) == 0 && qtile0 + tl < p.qt) scores[tl * p.nt + blk] = f2ord(val);
+      };
+      float cur = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        if (c < n_chunks) {
+          if (GR >= 16) {
+            float m5[5];
+#pragma unroll
+            for (int j = 0; j < 5; ++j)
+              m5[j] = max3(__uint_as_float(v[c][3 * j]), __uint_as_float(v[c][3 * j + 1]), __uint_as_float(v[c][3 * j + 2]));
+            const float m = fmaxf(max3(m5[0], m5[1], m5[2]), max3(m5[3], m5[4], __uint_as_float(v[c][15])));
+            cur = fmaxf(cur, m);
+            if ((((c + 1) * 16) % GR) == 0) {
+              flush((c * 16) / GR, cur);
+              cur = -INFINITY;
+            }
+          } else {
+            constexpr int PER = GR >= 16 ? 1 : 16 / GR;
+            constexpr int W = GR >= 16 ? 16 : GR;
+#pragma unroll
+            for (int sg = 0; sg < PER; ++sg) {
+              float m = __uint_as_float(v[c][sg * W]);
+#pragma unroll
+              for (int j = 1; j < W; ++j) m = fmaxf(m, __uint_as_float(v[c][sg * W + j]));
+              flush(c * PER + sg, m);
+            }
+          }
+        }
+      }
     }
   }
   tc_fence_before();
@@ -294,12 +305,17 @@ score_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant
       const int qtile = qtile0 + tl;
       const unsigned* keys = reinterpret_cast<const unsigned*>(scores + tl * p.nt);   // ordered ints
       // query descriptors of the list as fp32 [128][MP], and the largest L1 norm among them
-      for (int e = lane; e < 128 * MP; e += 32) {
-        const int m = e % MP, d = e / MP;
+      for (int m = 0; m < MP; ++m) {        // one descriptor row per step: 256 contiguous bytes
         const int mm = m < GR ? m : 0;
         const int g = mm / p.r, rq = mm - g * p.r;
         const long long qrow = ((static_cast<long long>(b) * p.hq + kvh * group + g) * p.qt + qtile) * p.r + rq;
-        q_s[d * MP + m] = __bfloat162float(p.qd[qrow * 128 + d]);
+        const uint2 raw = __ldg(reinterpret_cast<const uint2*>(p.qd + qrow * 128) + lane);
+        const float2 f0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+        const float2 f1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+        q_s[(4 * lane + 0) * MP + m] = f0.x;
+        q_s[(4 * lane + 1) * MP + m] = f0.y;
+        q_s[(4 * lane + 2) * MP + m] = f1.x;
+        q_s[(4 * lane + 3) * MP + m] = f1.y;
       }
       __syncwarp();
       float l1 = 0.f;
