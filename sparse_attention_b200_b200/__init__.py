@@ -5,3 +5,4 @@ from .kv_centric import Prepared, kv_centric_attention, combine  # noqa: F401
 from .indexers import (SummarySelector, quantize_queries, quantize_keys, prepare_fp4_inputs,  # noqa: F401
                        fp4_block_scores, tile_topk, tile_topk_out, fp4_indexer, indexed_attention)
 from . import sharding  # noqa: F401
+from .host_io import HostPipeline  # noqa: F401

@@ -223,3 +223,20 @@ def test_partial_segments_merge_to_whole():
         d = (o - ref_o).abs()
         assert d.max() <= 2e-2 and d.mean() <= 2e-3
         assert torch.all((l - ref_l).abs() <= 1e-3 * ref_l.abs().clamp_min(1.0))
+
+
+def test_host_pipeline_matches_device_path():
+    """Pinned host buffers in and out, chunks pipelined over three streams."""
+    m = sp()
+    q, k, v = gen.make_qkv(2, 8, 4, 512, 1024, seed=91)
+    ids = gen.make_ids(2, 4, 4, 8, 3, 92, "unsorted")
+    ref_o, ref_l = oracle.gather_attention(q, k, v, ids)
+    hq_, hk_, hv_, hi_ = (t.pin_memory() for t in (q, k, v, ids))
+    ho = torch.full(q.shape, float("nan"), dtype=torch.bfloat16).pin_memory()
+    hl = torch.full(q.shape[:3], float("nan")).pin_memory()
+    pipe = m.HostPipeline(2, 8, 4, 512, 1024, 3, "cuda:0", chunks=3)
+    for _ in range(2):                      # second call reuses the staging buffers
+        ho.fill_(float("nan"))
+        pipe.run(hq_, hk_, hv_, hi_, ho, hl).synchronize()
+        check(ho, hl, ref_o, ref_l)
+    m.device_status()
