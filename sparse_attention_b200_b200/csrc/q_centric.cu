@@ -232,35 +232,64 @@ q_centric_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
       ++qloads[q];
       return true;
     };
+    // Token order (must mirror the MMA warp): the first K tile of a stream's NEXT item
+    // (and its Q tile) follows that stream's last V tile of the current item, so the
+    // next item's first QK can be issued before the current item has drained.
+    bool primed[2] = {false, false};
     for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x) {
-      Stream s[2];
+      Stream s[2], nx[2];
       decode_item(p, item, s);
-      IdCursor kc[2], vc[2];
-      kc[0].cached = kc[1].cached = vc[0].cached = vc[1].cached = 0;
+      const bool has_next = item + static_cast<int>(gridDim.x) < p.num_items;
+      if (has_next) decode_item(p, item + gridDim.x, nx);
+      IdCursor kc[2], vc[2], nc[2];
+      kc[0].cached = kc[1].cached = vc[0].cached = vc[1].cached = nc[0].cached = nc[1].cached = 0;
       if (p.pair_mode) {
         const int n = s[0].count;
+        const bool was_primed = primed[0];
+        primed[0] = primed[1] = false;
         if (n == 0) continue;
-        ok = push_q(0, s[0].q_row) && push_q(1, s[1].q_row);
-        if (!ok) break;
-        ok = push(&k_map, s[0].kv_row + kc[0].get(s[0].list, n, 0, lane) * TILE);
+        if (!was_primed) {
+          ok = push_q(0, s[0].q_row) && push_q(1, s[1].q_row) &&
+               push(&k_map, s[0].kv_row + kc[0].get(s[0].list, n, 0, lane) * TILE);
+        } else {
+          kc[0].get(s[0].list, n, 0, lane);      // keep the cursor in step
+        }
         for (int i = 0; ok && i < n; ++i) {
           ok = push(&v_map, s[0].kv_row + vc[0].get(s[0].list, n, i, lane) * TILE);
-          if (ok && i + 1 < n)
+          if (!ok) break;
+          if (i + 1 < n) {
             ok = push(&k_map, s[0].kv_row + kc[0].get(s[0].list, n, i + 1, lane) * TILE);
+          } else if (has_next && nx[0].count > 0) {
+            ok = push_q(0, nx[0].q_row) &&
+                 push(&k_map, nx[0].kv_row + nc[0].get(nx[0].list, nx[0].count, 0, lane) * TILE) &&
+                 push_q(1, nx[1].q_row);
+            primed[0] = primed[1] = true;
+          }
         }
       } else {
+        bool was_primed[2] = {primed[0], primed[1]};
+        primed[0] = primed[1] = false;
         for (int q = 0; ok && q < 2; ++q)
           if (s[q].count > 0) {
-            ok = push_q(q, s[q].q_row) &&
-                 push(&k_map, s[q].kv_row + kc[q].get(s[q].list, s[q].count, 0, lane) * TILE);
+            if (!was_primed[q])
+              ok = push_q(q, s[q].q_row) &&
+                   push(&k_map, s[q].kv_row + kc[q].get(s[q].list, s[q].count, 0, lane) * TILE);
+            else
+              kc[q].get(s[q].list, s[q].count, 0, lane);
           }
         const int n = max(s[0].count, s[1].count);
         for (int i = 0; ok && i < n; ++i)
           for (int q = 0; ok && q < 2; ++q)
             if (i < s[q].count) {
               ok = push(&v_map, s[q].kv_row + vc[q].get(s[q].list, s[q].count, i, lane) * TILE);
-              if (ok && i + 1 < s[q].count)
+              if (!ok) break;
+              if (i + 1 < s[q].count) {
                 ok = push(&k_map, s[q].kv_row + kc[q].get(s[q].list, s[q].count, i + 1, lane) * TILE);
+              } else if (has_next && nx[q].count > 0) {
+                ok = push_q(q, nx[q].q_row) &&
+                     push(&k_map, nx[q].kv_row + nc[q].get(nx[q].list, nx[q].count, 0, lane) * TILE);
+                primed[q] = true;
+              }
             }
       }
     }
@@ -332,21 +361,29 @@ q_centric_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
     };
     auto commit = [&](int b) { if (lane == 0) tc_commit(bar(b)); };
 
+    bool primed[2] = {false, false};
     for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x) {
-      Stream s[2];
+      Stream s[2], nx[2];
       decode_item(p, item, s);
+      const bool has_next = item + static_cast<int>(gridDim.x) < p.num_items;
+      if (has_next) decode_item(p, item + gridDim.x, nx);
       uint32_t kslot = 0, vslot = 0;
       if (p.pair_mode) {
         const int n = s[0].count;
+        const bool was_primed = primed[0];
+        primed[0] = primed[1] = false;
         if (n == 0) continue;
-        ok = wait_q(0) && wait_q(1) && acquire(kslot);
-        if (!ok) break;
-        issue_qk(0, kslot); commit(BAR_S_FULL + 0);
-        issue_qk(1, kslot); commit(BAR_S_FULL + 1);
-        commit(BAR_KV_EMPTY + kslot);
-        if (n == 1) { commit(BAR_Q_EMPTY + 0); commit(BAR_Q_EMPTY + 1); }
+        if (!was_primed) {
+          ok = wait_q(0) && wait_q(1) && acquire(kslot);
+          if (!ok) break;
+          issue_qk(0, kslot); commit(BAR_S_FULL + 0);
+          issue_qk(1, kslot); commit(BAR_S_FULL + 1);
+          commit(BAR_KV_EMPTY + kslot);
+          if (n == 1) { commit(BAR_Q_EMPTY + 0); commit(BAR_Q_EMPTY + 1); }
+        }
         for (int i = 0; ok && i < n; ++i) {
           const bool more = i + 1 < n;
+          const bool prime = !more && has_next && nx[0].count > 0;
           ok = acquire(vslot) && wait_p(0);
           if (!ok) break;
           issue_pv(0, vslot, i > 0);
@@ -356,6 +393,11 @@ q_centric_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
             issue_qk(0, kslot); commit(BAR_S_FULL + 0);
           } else {
             commit(BAR_O_FULL + 0);
+            if (prime) {              // first QK of the next item, stream 0
+              ok = wait_q(0) && acquire(kslot);
+              if (!ok) break;
+              issue_qk(0, kslot); commit(BAR_S_FULL + 0);
+            }
           }
           ok = wait_p(1);
           if (!ok) break;
@@ -367,11 +409,21 @@ q_centric_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
             if (i + 2 == n) { commit(BAR_Q_EMPTY + 0); commit(BAR_Q_EMPTY + 1); }
           } else {
             commit(BAR_O_FULL + 1);
+            if (prime) {              // and stream 1, same K tile
+              ok = wait_q(1);
+              if (!ok) break;
+              issue_qk(1, kslot); commit(BAR_S_FULL + 1);
+              commit(BAR_KV_EMPTY + kslot);
+              if (nx[0].count == 1) { commit(BAR_Q_EMPTY + 0); commit(BAR_Q_EMPTY + 1); }
+              primed[0] = primed[1] = true;
+            }
           }
         }
       } else {
+        bool was_primed[2] = {primed[0], primed[1]};
+        primed[0] = primed[1] = false;
         for (int q = 0; ok && q < 2; ++q)
-          if (s[q].count > 0) {
+          if (s[q].count > 0 && !was_primed[q]) {
             ok = wait_q(q) && acquire(kslot);
             if (!ok) break;
             issue_qk(q, kslot); commit(BAR_S_FULL + q);
@@ -394,6 +446,14 @@ q_centric_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
                 if (i + 2 == s[q].count) commit(BAR_Q_EMPTY + q);
               } else {
                 commit(BAR_O_FULL + q);
+                if (has_next && nx[q].count > 0) {     // first QK of this stream's next item
+                  ok = wait_q(q) && acquire(kslot);
+                  if (!ok) break;
+                  issue_qk(q, kslot); commit(BAR_S_FULL + q);
+                  commit(BAR_KV_EMPTY + kslot);
+                  if (nx[q].count == 1) commit(BAR_Q_EMPTY + q);
+                  primed[q] = true;
+                }
               }
             }
       }
