@@ -392,8 +392,11 @@ def run_config(args):
         inputs = sp.prepare_fp4_inputs(qc, kc, qs, ks, batch_size=ng, len_q=N, len_kv=N)
         ids = torch.empty((ng, 1, nb, topk), dtype=torch.int32, device=dev)
         tile_scores = torch.empty((ng, 1, nb, nb), dtype=torch.float32, device=dev)
-        stages["indexer_ms"] = timed(lambda: sp.fp4_indexer(inputs, ids, tile_scores=tile_scores),
-                                     min(steps, 3), 1, barrier)
+        stages["indexer_exact_ms"] = timed(lambda: sp.fp4_indexer(inputs, ids, tile_scores=tile_scores),
+                                           1, 1, barrier)
+        ws = sp.fp4_indexer_fast(inputs, ids)[1]
+        stages["indexer_ms"] = timed(lambda: sp.fp4_indexer_fast(inputs, ids, workspace=ws), min(steps, 3), 1, barrier)
+        stages["indexer_fallback_tiles"] = int(ws[4:8].view(torch.int32).item())
     # ---------------- attention
     fl_local = 4.0 * ng * G * N * (topk * 128) * 128
     if kvs > 1:

@@ -152,6 +152,19 @@ int sparse_b200_indexer_fp4(const void* q_codes, const void* q_scales, const voi
                             float* tile_scores, int32_t* block_idx, int batch, int hidx, int hk, int len_q, int len_kv,
                             int topk, void* stream);
 
+/* Same block ids as sparse_b200_indexer_fp4, bit for bit, with the scoring on the
+ * tensor cores: dequantised NVFP4 values are exact in bf16, so tcgen05 bf16 MMAs
+ * pre-filter the pages of every query tile, the surviving candidates are re-scored
+ * with the exact group-ordered arithmetic, and a tile whose pre-filter cannot be
+ * proven safe is scored exactly in full. `workspace` (256-byte aligned device memory
+ * of sparse_b200_indexer_fp4_workspace_bytes(...) bytes) holds the dequantised
+ * copies; the int at byte offset 4 counts the tiles that took the fallback.
+ * Role of fp4_indexer() (indexers/fp4/fp4.py:137-146). */
+int64_t sparse_b200_indexer_fp4_workspace_bytes(int batch, int hidx, int hk, int len_q, int len_kv);
+int sparse_b200_indexer_fp4_fast(const void* q_codes, const void* q_scales, const void* k_codes, const void* k_scales,
+                                 void* workspace, int64_t workspace_bytes, int32_t* block_idx, int batch, int hidx,
+                                 int hk, int len_q, int len_kv, int topk, void* stream);
+
 /* R1 / R4 summary indexer that allocates nothing and takes no workspace: same
  * inputs, outputs, arithmetic and results as sparse_b200_indexer_summary, with
  * the pooled descriptors kept in an 8 MiB array built into the library. It has

@@ -342,4 +342,40 @@ int sparse_b200_indexer_fp4(const void* q_codes, const void* q_scales, const voi
                          topk, static_cast<cudaStream_t>(stream));
 }
 
+int64_t sparse_b200_indexer_fp4_workspace_bytes(int batch, int hidx, int hk, int len_q, int len_kv) {
+  if (batch <= 0 || hidx <= 0 || hk <= 0 || len_q <= 0 || len_kv <= 0) return SB_ERR_INVALID;
+  const int64_t q = align256(static_cast<size_t>(batch) * len_q * hidx * 256);
+  const int64_t k = align256(static_cast<size_t>(batch) * len_kv * hk * 256);
+  const int64_t tile = align256(static_cast<size_t>(batch) * hidx * (len_q / 128) * (len_kv / 128) * 4);
+  return 256 + q + k + tile;
+}
+
+int sparse_b200_indexer_fp4_fast(const void* q_codes, const void* q_scales, const void* k_codes, const void* k_scales,
+                                 void* workspace, int64_t workspace_bytes, int32_t* block_idx, int batch, int hidx,
+                                 int hk, int len_q, int len_kv, int topk, void* stream) {
+  int rc = check_fp4(q_codes, q_scales, k_codes, k_scales, batch, hidx, hk, len_q, len_kv);
+  if (rc) return rc;
+  REQUIRE(workspace && block_idx && (reinterpret_cast<uintptr_t>(workspace) & 255u) == 0,
+          "workspace must be a 256-byte aligned device pointer");
+  REQUIRE(topk > 0 && topk <= len_kv / 128, "top-k must be in [1, kv_tiles]");
+  REQUIRE(workspace_bytes >= sparse_b200_indexer_fp4_workspace_bytes(batch, hidx, hk, len_q, len_kv),
+          "workspace too small (see sparse_b200_indexer_fp4_workspace_bytes)");
+  unsigned char* w = static_cast<unsigned char*>(workspace);
+  void* aux = w;
+  void* q_deq = w + 256;
+  void* k_deq = w + 256 + align256(static_cast<size_t>(batch) * len_q * hidx * 256);
+  float* tile_scores = reinterpret_cast<float*>(static_cast<unsigned char*>(k_deq) +
+                                                align256(static_cast<size_t>(batch) * len_kv * hk * 256));
+  rc = launch_fp4_indexer_tc(q_codes, q_scales, k_codes, k_scales, q_deq, k_deq, aux, block_idx, batch, hidx, hk, len_q,
+                             len_kv, topk, static_cast<cudaStream_t>(stream));
+  if (rc == 1) {   // not eligible: exact scorer + top-k, same ids
+    rc = launch_fp4_scores(q_codes, q_scales, k_codes, k_scales, nullptr, tile_scores, batch, hidx, hk, len_q, len_kv,
+                           static_cast<cudaStream_t>(stream));
+    if (rc) return rc;
+    rc = launch_row_topk(tile_scores, block_idx, static_cast<long long>(batch) * hidx * (len_q / 128), len_kv / 128,
+                         topk, static_cast<cudaStream_t>(stream));
+  }
+  return rc;
+}
+
 }  // extern "C"

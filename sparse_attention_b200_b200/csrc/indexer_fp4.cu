@@ -17,6 +17,7 @@
 // number of KV tiles; integer dot products run on dp4a.
 #include "internal.h"
 #include "topk.cuh"
+#include "fp4_exact.cuh"
 #include <cuda_bf16.h>
 #include <cuda_fp8.h>
 
@@ -104,25 +105,7 @@ __global__ void __launch_bounds__(256) quantize_kernel(const __nv_bfloat16* __re
 }
 
 // ---------------------------------------------------------------- scorer
-__device__ __forceinline__ float e4m3_to_float(uint8_t bits) {
-  return __half2float(__half(__nv_cvt_fp8_to_halfraw(bits, __NV_E4M3)));
-}
-// eight e2m1 codes (one 32-bit word) -> eight signed bytes 2*value, as two dp4a operands
-__device__ __forceinline__ void codes_to_int8(uint32_t w, uint32_t& lo4, uint32_t& hi4) {
-  const unsigned long long lut = 0x0C08060403020100ULL;
-  uint32_t out[2] = {0u, 0u};
-#pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    const uint32_t c = (w >> (4 * i)) & 15u;
-    int m = static_cast<int>((lut >> (8 * (c & 7u))) & 0xFFu);
-    if (c & 8u) m = -m;
-    out[i >> 2] |= (static_cast<uint32_t>(m) & 0xFFu) << (8 * (i & 3));
-  }
-  lo4 = out[0];
-  hi4 = out[1];
-}
-
-constexpr int ROW_WORDS = 36;   // 128 int8 = 32 words, padded to 36 for conflict-free 16-byte reads
+constexpr int ROW_WORDS = FP4_ROW_WORDS;
 
 // One CTA: one query tile (128 queries of one index head) against `pages_per_cta`
 // key pages. Thread (ty, tx) = (tid / 16, tid % 16) owns queries ty*8..ty*8+7 and

@@ -1,0 +1,469 @@
+// Tensor-core path of the NVFP4 indexer: the same block ids as the exact dp4a scorer
+// followed by tile top-k, bit for bit.
+//
+// A dequantised NVFP4 value (e2m1 code x e4m3 scale) has at most 7 significant bits
+// and is exactly representable in bf16, so bf16 tensor-core MMAs on dequantised
+// copies compute every product exactly; only their fp32 accumulation differs from
+// the fixed group-by-group order that defines a score. As in the summary indexer
+// the MMA result is therefore a PRE-FILTER: per query tile the C best pages by
+// approximate tile score are re-scored exactly, the exact top-k of those is the
+// answer when exact k-th score > C-th approximate score + delta
+// (delta = 2^-14 * max_q ||q||_1 * max|k|), and the tile falls back to exact scores
+// of every page otherwise.
+// Same role as Fp4IndexerStagedMmaSm100 + tile_max_topk16_kernel
+// (indexers/fp4/vendor_minimax_msa/src/sm100/fp4_indexer.py:483-1086,
+// indexers/fp4/tile_topk.cu:38-126).
+#include "ptx.cuh"
+#include "internal.h"
+#include "topk.cuh"
+#include "fp4_exact.cuh"
+#include <cuda_bf16.h>
+
+namespace sb {
+namespace ftc {
+
+constexpr int TILE_BYTES = 128 * 256;
+constexpr int PANEL_BYTES = 128 * 128;
+constexpr int A_STAGES = 2;
+constexpr int C_MAX = 192;
+constexpr int NUM_THREADS = 320;
+constexpr int TMA_WARP = 8, MMA_WARP = 9;
+constexpr float EPS = 6.103515625e-05f;   // 2^-14
+constexpr int MAX_TILES = 16384;           // 64 KiB of scores
+
+constexpr int OFF_A = 0;
+constexpr int OFF_B = A_STAGES * TILE_BYTES;
+constexpr int OFF_SCORES = OFF_B + TILE_BYTES;
+
+struct Params {
+  const uint8_t *qp, *qs, *kp, *ks;   // public NVFP4 layout (codes, e4m3 scales)
+  const float* k_absmax;              // [1] max |dequantised key element|
+  int32_t* ids;                       // [B, Hidx, Qt, topk]
+  int* status;
+  int* fallbacks;
+  int batch, hidx, hk, len_q, tiles, topk, cand;
+};
+
+__device__ __forceinline__ int f2ord(float f) {
+  const int i = __float_as_int(f);
+  return i >= 0 ? i : i ^ 0x7fffffff;
+}
+__device__ __forceinline__ float ord2f(int i) { return __int_as_float(i >= 0 ? i : i ^ 0x7fffffff); }
+
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%2, %3, %4}], [%5];" ::"r"(dst),
+      "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
+
+// codes + scales -> bf16 (exact). One thread per 8 features.
+__global__ void __launch_bounds__(256) dequant_kernel(const uint8_t* __restrict__ codes,
+                                                      const uint8_t* __restrict__ scales,
+                                                      __nv_bfloat16* __restrict__ out, long long rows) {
+  const long long gid = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const long long row = gid >> 4;
+  const int w = static_cast<int>(gid & 15);
+  if (row >= rows) return;
+  const uint32_t word = __ldg(reinterpret_cast<const uint32_t*>(codes + row * 64 + w * 4));
+  const float sc = 0.5f * e4m3_to_float(scales[row * 8 + (w >> 1)]);
+  const unsigned long long lut = 0x0C08060403020100ULL;
+  uint4 o;
+  uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    float f[2];
+#pragma unroll
+    for (int t = 0; t < 2; ++t) {
+      const uint32_t c = (word >> (4 * (2 * e + t))) & 15u;
+      float m = static_cast<float>((lut >> (8 * (c & 7u))) & 0xFFu);
+      f[t] = ((c & 8u) ? -m : m) * sc;
+    }
+    __nv_bfloat162 h = __floats2bfloat162_rn(f[0], f[1]);
+    ow[e] = *reinterpret_cast<uint32_t*>(&h);
+  }
+  *reinterpret_cast<uint4*>(out + row * 128 + w * 8) = o;
+}
+
+__global__ void __launch_bounds__(256) absmax_all_kernel(const __nv_bfloat16* __restrict__ x, float* __restrict__ out,
+                                                         long long n16) {
+  const uint4* src = reinterpret_cast<const uint4*>(x);
+  float m = 0.f;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n16;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const uint4 v = __ldg(src + i);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 f = __bfloat1622float2(h[e]);
+      m = fmaxf(m, fmaxf(fabsf(f.x), fabsf(f.y)));
+    }
+  }
+#pragma unroll
+  for (int d = 16; d > 0; d >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, d));
+  if ((threadIdx.x & 31) == 0) atomicMax(reinterpret_cast<int*>(out), __float_as_int(m));
+}
+
+// One CTA per (batch, index head, query tile): approximate tile scores of every key
+// page on the tensor cores, then candidate selection and exact re-scoring.
+// Warps 0-7 epilogue (lane quarter = warp & 3, column half = warp >> 2), warp 8 TMA,
+// warp 9 MMA issue.
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+fp4_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map, const Params p) {
+  extern __shared__ unsigned char smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  unsigned char* gbase = smem_raw + (base - raw);
+  int* scores = reinterpret_cast<int*>(gbase + OFF_SCORES);
+  const int score_bytes = (p.tiles * 4 + 15) & ~15;
+  unsigned char* aux = gbase + OFF_SCORES + score_bytes;
+  const uint32_t bar0 = base + OFF_SCORES + score_bytes;
+  volatile int* misc = reinterpret_cast<volatile int*>(aux + 128);   // tmem base, abort, unsafe, l1q bits
+  float* scratch_f = reinterpret_cast<float*>(aux + 192);            // [16]
+  int* scratch_i = reinterpret_cast<int*>(aux + 256);                // [16]
+  auto bar = [&](int i) { return bar0 + 8u * i; };
+  enum { A_FULL = 0, A_EMPTY = A_STAGES, B_FULL = 2 * A_STAGES, ACC_FULL = 2 * A_STAGES + 1, ACC_EMPTY = 2 * A_STAGES + 3 };
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int qt = p.len_q >> 7;
+  const int qtile = blockIdx.x % qt;
+  const int bh = blockIdx.x / qt;
+  const int h = bh % p.hidx, b = bh / p.hidx;
+  const int hk_idx = p.hk > 1 ? h : 0;
+  const long long q_row0 = static_cast<long long>(b) * p.len_q + static_cast<long long>(qtile) * 128;
+  const int num_tiles = p.tiles;
+  const int rot = static_cast<int>((static_cast<unsigned>(qtile) * 37u) % static_cast<unsigned>(num_tiles));
+  Guard guard{misc + 1, p.status};
+
+  if (threadIdx.x == 0) {
+    misc[1] = 0;
+    for (int i = 0; i < A_STAGES; ++i) {
+      mbar_init(bar(A_FULL + i), 1);
+      mbar_init(bar(A_EMPTY + i), 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(bar(ACC_FULL + i), 1);
+      mbar_init(bar(ACC_EMPTY + i), 8);
+    }
+    mbar_init(bar(B_FULL), 1);
+    fence_mbar_init();
+  }
+  if (warp == MMA_WARP) {
+    tmem_alloc(smem_u32(const_cast<int*>(misc)), 256);
+    tmem_relinquish();
+  }
+  for (int j = threadIdx.x; j < p.tiles; j += NUM_THREADS) scores[j] = static_cast<int>(0x80000000u);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = static_cast<uint32_t>(misc[0]);
+
+  if (warp == TMA_WARP) {
+    if (lane == 0) {
+      mbar_expect_tx(bar(B_FULL), TILE_BYTES);
+      tma_load_3d(base + OFF_B, &q_map, 0, h, static_cast<int>(q_row0), bar(B_FULL));
+      tma_load_3d(base + OFF_B + PANEL_BYTES, &q_map, 64, h, static_cast<int>(q_row0), bar(B_FULL));
+    }
+    bool ok = true;
+    for (int t = 0; ok && t < num_tiles; ++t) {
+      const int s = t % A_STAGES, use = t / A_STAGES;
+      if (use > 0) {
+        bool w = mbar_wait(bar(A_EMPTY + s), (use - 1) & 1, guard, 0x500 + s);
+        ok = __all_sync(0xffffffffu, w);
+        if (!ok) break;
+      }
+      if (lane == 0) {
+        const uint32_t dst = base + OFF_A + s * TILE_BYTES;
+        const int pg = (t + rot) % num_tiles;
+        const int row = ((b * p.tiles + pg) * p.hk + hk_idx) * 128;
+        mbar_expect_tx(bar(A_FULL + s), TILE_BYTES);
+        tma_load_2d(dst, &k_map, 0, row, bar(A_FULL + s));
+        tma_load_2d(dst + PANEL_BYTES, &k_map, 64, row, bar(A_FULL + s));
+      }
+    }
+    if (!ok)
+      for (int t = max(0, num_tiles - A_STAGES); t < num_tiles; ++t)
+        mbar_wait_drain(bar(A_FULL + t % A_STAGES), (t / A_STAGES) & 1);
+  } else if (warp == MMA_WARP) {
+    const uint32_t idesc = idesc_bf16(128, 128, false);
+    bool ok = true;
+    {
+      bool w = mbar_wait(bar(B_FULL), 0, guard, 0x510);
+      ok = __all_sync(0xffffffffu, w);
+      tc_fence_after();
+    }
+    for (int t = 0; ok && t < num_tiles; ++t) {
+      const int s = t % A_STAGES, acc = t & 1;
+      bool w = mbar_wait(bar(A_FULL + s), (t / A_STAGES) & 1, guard, 0x520 + s);
+      if (w && t >= 2) w = mbar_wait(bar(ACC_EMPTY + acc), ((t >> 1) - 1) & 1, guard, 0x530 + acc);
+      ok = __all_sync(0xffffffffu, w);
+      if (!ok) break;
+      tc_fence_after();
+      if (lane == 0) {
+        const uint64_t a0 = desc_sw128_kmajor(base + OFF_A + s * TILE_BYTES);
+        const uint64_t b0 = desc_sw128_kmajor(base + OFF_B);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint64_t step = static_cast<uint64_t>((kk >> 2) * (PANEL_BYTES >> 4) + (kk & 3) * 2);
+          mma_ss(tmem + acc * 128, a0 + step, b0 + step, idesc, kk > 0);
+        }
+        tc_commit(bar(A_EMPTY + s));
+        tc_commit(bar(ACC_FULL + acc));
+      }
+    }
+  } else {
+    // epilogue: thread = key row of the page, this warp's 64-column half of the query tile
+    const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const int half = warp >> 2;
+    bool ok = true;
+    for (int t = 0; ok && t < num_tiles; ++t) {
+      const int acc = t & 1;
+      bool w = mbar_wait(bar(ACC_FULL + acc), (t >> 1) & 1, guard, 0x540 + acc);
+      ok = __all_sync(0xffffffffu, w);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t t_acc = tmem + lane_base + acc * 128 + half * 64;
+      uint32_t v[4][16];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tmem_ld16(t_acc + c * 16, v[c]);
+      tc_wait_ld();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(ACC_EMPTY + acc));
+      float m4[4];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        float m5[5];
+#pragma unroll
+        for (int j = 0; j < 5; ++j)
+          m5[j] = max3(__uint_as_float(v[c][3 * j]), __uint_as_float(v[c][3 * j + 1]), __uint_as_float(v[c][3 * j + 2]));
+        m4[c] = fmaxf(max3(m5[0], m5[1], m5[2]), max3(m5[3], m5[4], __uint_as_float(v[c][15])));
+      }
+      float m = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+#pragma unroll
+      for (int d = 16; d > 0; d >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, d));
+      if (lane == 0) atomicMax(&scores[(t + rot) % num_tiles], f2ord(m));
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == MMA_WARP) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 256);
+  }
+  if (misc[1]) return;
+
+  // ------------------------------------------------------------- selection
+  uint32_t* q_i8 = reinterpret_cast<uint32_t*>(gbase + OFF_A);
+  uint32_t* k_i8 = q_i8 + 128 * FP4_ROW_WORDS;
+  float* q_sc = reinterpret_cast<float*>(k_i8 + 128 * FP4_ROW_WORDS);
+  float* k_sc = q_sc + 128 * 8;
+  int32_t* cand_ids = reinterpret_cast<int32_t*>(gbase + OFF_B);
+  int* cand_ex = reinterpret_cast<int*>(cand_ids + C_MAX);
+  const int C = p.cand;
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+  int32_t* out = p.ids + (static_cast<long long>(bh) * qt + qtile) * p.topk;
+
+  fp4_stage_rows(q_i8, q_sc, p.qp + (q_row0 * p.hidx + h) * 64, static_cast<long long>(p.hidx) * 64,
+                 p.qs + (q_row0 * p.hidx + h) * 8, static_cast<long long>(p.hidx) * 8, 0.25f);
+  if (threadIdx.x == 0) { misc[2] = 0; misc[3] = 0; }
+  for (int c = threadIdx.x; c < C_MAX; c += NUM_THREADS) cand_ex[c] = static_cast<int>(0x80000000u);
+  __syncthreads();
+  if (threadIdx.x < 128) {                 // L1 norm of one dequantised query row
+    float l1 = 0.f;
+    for (int g = 0; g < 8; ++g) {
+      int sum = 0;
+      for (int w = 0; w < 4; ++w) {
+        const uint32_t word = q_i8[threadIdx.x * FP4_ROW_WORDS + g * 4 + w];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) sum += abs(static_cast<int>(static_cast<int8_t>((word >> (8 * e)) & 0xFFu)));
+      }
+      l1 += static_cast<float>(sum) * 2.0f * q_sc[threadIdx.x * 8 + g];
+    }
+    atomicMax(const_cast<int*>(misc + 3), __float_as_int(l1 * 1.0001f));
+  }
+  float thr = 0.f;
+  if (warp == 0) {
+    // C-th largest approximate score and the candidate set (ties at the threshold in index order)
+    const unsigned* keys = reinterpret_cast<const unsigned*>(scores);
+    const unsigned lt_mask = (1u << lane) - 1u;
+    unsigned T = 0;
+    for (int bit = 31; bit >= 0; --bit) {
+      const unsigned trial = T | (1u << bit);
+      int cnt = 0;
+      for (int j = lane; j < p.tiles; j += 32) cnt += ((keys[j] ^ 0x80000000u) >= trial) ? 1 : 0;
+#pragma unroll
+      for (int d = 16; d > 0; d >>= 1) cnt += __shfl_xor_sync(0xffffffffu, cnt, d);
+      if (cnt >= C) T = trial;
+    }
+    int n_gt = 0;
+    for (int j = lane; j < p.tiles; j += 32) n_gt += ((keys[j] ^ 0x80000000u) > T) ? 1 : 0;
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) n_gt += __shfl_xor_sync(0xffffffffu, n_gt, d);
+    const int need_eq = C - n_gt;
+    int out_run = 0, eq_run = 0;
+    for (int base_j = 0; base_j < p.tiles; base_j += 32) {
+      const int j = base_j + lane;
+      const unsigned u = j < p.tiles ? (keys[j] ^ 0x80000000u) : 0u;
+      const bool is_gt = j < p.tiles && u > T;
+      const bool is_eq = j < p.tiles && u == T;
+      const unsigned eq_ballot = __ballot_sync(0xffffffffu, is_eq);
+      const bool take = is_gt || (is_eq && eq_run + __popc(eq_ballot & lt_mask) < need_eq);
+      const unsigned take_ballot = __ballot_sync(0xffffffffu, take);
+      if (take) cand_ids[out_run + __popc(take_ballot & lt_mask)] = j;
+      out_run += __popc(take_ballot);
+      eq_run += __popc(eq_ballot);
+    }
+    thr = ord2f(static_cast<int>(T ^ 0x80000000u));
+  }
+  __syncthreads();
+  // exact tile score of one page: max over the 128 x 128 dots, whole CTA
+  auto exact_page = [&](int pg) -> float {
+    const long long page = (static_cast<long long>(b) * p.tiles + pg) * p.hk + hk_idx;
+    fp4_stage_rows(k_i8, k_sc, p.kp + page * 128 * 64, 64, p.ks + page * 128 * 8, 8, 1.0f);
+    __syncthreads();
+    float m = -INFINITY;
+    if (threadIdx.x < 256) {
+      float acc[8][8];
+      fp4_block_dots(q_i8, q_sc, k_i8, k_sc, ty, tx, acc);
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) m = fmaxf(m, acc[i][j]);
+    }
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, d));
+    return m;                              // per-warp maximum; lane 0 publishes it
+  };
+  for (int c = 0; c < C; ++c) {
+    const float m = exact_page(cand_ids[c]);
+    if (lane == 0) atomicMax(&cand_ex[c], f2ord(m));
+    __syncthreads();
+  }
+  if (warp == 0) {
+    constexpr int SLOTS = C_MAX / 32;
+    float es[SLOTS];
+    int ei[SLOTS];
+#pragma unroll
+    for (int sidx = 0; sidx < SLOTS; ++sidx) {
+      const int c = lane + 32 * sidx;
+      es[sidx] = c < C ? ord2f(cand_ex[c]) : -INFINITY;
+      ei[sidx] = c < C ? cand_ids[c] : INT_MAX;
+    }
+    float kth = -INFINITY;
+    for (int rank = 0; rank < p.topk; ++rank) {
+      float bs = es[0];
+      int bi = ei[0];
+#pragma unroll
+      for (int sidx = 1; sidx < SLOTS; ++sidx)
+        if (better(es[sidx], ei[sidx], bs, bi)) { bs = es[sidx]; bi = ei[sidx]; }
+#pragma unroll
+      for (int d = 16; d > 0; d >>= 1) {
+        const float os = __shfl_xor_sync(0xffffffffu, bs, d);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, d);
+        if (better(os, oi, bs, bi)) { bs = os; bi = oi; }
+      }
+#pragma unroll
+      for (int sidx = 0; sidx < SLOTS; ++sidx)
+        if (ei[sidx] == bi) { es[sidx] = -INFINITY; ei[sidx] = INT_MAX; }
+      if (lane == 0) out[rank] = bi;
+      kth = bs;
+    }
+    const float delta = EPS * __int_as_float(misc[3]) * p.k_absmax[0];
+    const bool safe = (C >= p.tiles) || (kth > thr + delta);
+    if (lane == 0) misc[2] = safe ? 0 : 1;
+  }
+  __syncthreads();
+  if (misc[2]) {
+    float* row = reinterpret_cast<float*>(scores);
+    for (int pg = 0; pg < p.tiles; ++pg) {
+      const float m = exact_page(pg);
+      if (lane == 0) scratch_f[warp] = m;
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        float mm = scratch_f[0];
+        for (int w = 1; w < NUM_THREADS / 32; ++w) mm = fmaxf(mm, scratch_f[w]);
+        row[pg] = mm;
+      }
+      __syncthreads();
+    }
+    block_topk(row, p.tiles, p.topk, out, scratch_f, scratch_i);
+    if (threadIdx.x == 0 && p.fallbacks) atomicAdd(p.fallbacks, 1);
+  }
+}
+
+}  // namespace ftc
+
+// Returns SB_OK when the tensor-core path ran, 1 when the problem is not eligible.
+// q_deq / k_deq: bf16 workspaces of B*Sq*Hidx*128 and (B*Skv/128)*Hk*128*128 elements;
+// aux: one float (key abs-max) + one int (fallback counter).
+int launch_fp4_indexer_tc(const void* qp, const void* qs, const void* kp, const void* ks, void* q_deq, void* k_deq,
+                          void* aux, int32_t* ids, int batch, int hidx, int hk, int len_q, int len_kv, int topk,
+                          cudaStream_t stream) {
+  using namespace ftc;
+  const int tiles = len_kv / 128, qt = len_q / 128;
+  const int extra = topk / 4 > 16 ? topk / 4 : 16;
+  int cand = topk + extra;
+  if (cand > tiles) cand = tiles;
+  if (cand > C_MAX || tiles > MAX_TILES) return 1;
+  const long long q_rows = static_cast<long long>(batch) * len_q * hidx;
+  const long long k_rows = static_cast<long long>(batch) * tiles * hk * 128;
+  if (q_rows >= (1LL << 31) || k_rows >= (1LL << 31)) return 1;
+  DeviceCtx* ctx = device_ctx();
+  if (!ctx) return SB_ERR_CUDA;
+  if (cudaMemsetAsync(aux, 0, 8, stream) != cudaSuccess) return set_error(SB_ERR_CUDA, "memset failed");
+  dequant_kernel<<<static_cast<unsigned>((q_rows * 16 + 255) / 256), 256, 0, stream>>>(
+      static_cast<const uint8_t*>(qp), static_cast<const uint8_t*>(qs), static_cast<__nv_bfloat16*>(q_deq), q_rows);
+  dequant_kernel<<<static_cast<unsigned>((k_rows * 16 + 255) / 256), 256, 0, stream>>>(
+      static_cast<const uint8_t*>(kp), static_cast<const uint8_t*>(ks), static_cast<__nv_bfloat16*>(k_deq), k_rows);
+  absmax_all_kernel<<<ctx->sm_count * 4, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(k_deq),
+                                                            static_cast<float*>(aux), k_rows * 16);
+  CUtensorMap qm, km;
+  {
+    const cuuint64_t dims[3] = {128, static_cast<cuuint64_t>(hidx), static_cast<cuuint64_t>(batch) * len_q};
+    const cuuint64_t strides[2] = {256, static_cast<cuuint64_t>(hidx) * 256};
+    const cuuint32_t box[3] = {64, 1, 128};
+    const cuuint32_t steps[3] = {1, 1, 1};
+    if (encode_tiled(&qm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, q_deq, dims, strides, box, steps,
+                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B))
+      return set_error(SB_ERR_CUDA, "cuTensorMapEncodeTiled failed for the dequantised queries");
+  }
+  {
+    const cuuint64_t dims[2] = {128, static_cast<cuuint64_t>(k_rows)};
+    const cuuint64_t strides[1] = {256};
+    const cuuint32_t box[2] = {64, 128};
+    const cuuint32_t steps[2] = {1, 1};
+    if (encode_tiled(&km, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, k_deq, dims, strides, box, steps,
+                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B))
+      return set_error(SB_ERR_CUDA, "cuTensorMapEncodeTiled failed for the dequantised keys");
+  }
+  Params p{};
+  p.qp = static_cast<const uint8_t*>(qp); p.qs = static_cast<const uint8_t*>(qs);
+  p.kp = static_cast<const uint8_t*>(kp); p.ks = static_cast<const uint8_t*>(ks);
+  p.k_absmax = static_cast<const float*>(aux);
+  p.fallbacks = reinterpret_cast<int*>(aux) + 1;
+  p.ids = ids;
+  p.status = ctx->status;
+  p.batch = batch; p.hidx = hidx; p.hk = hk; p.len_q = len_q; p.tiles = tiles; p.topk = topk; p.cand = cand;
+  const size_t smem = OFF_SCORES + ((static_cast<size_t>(tiles) * 4 + 15) & ~static_cast<size_t>(15)) + 320 + 1024;
+  if (!(ctx->tc_attr & (1 << 8))) {
+    cudaError_t e = cudaFuncSetAttribute(fp4_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448);
+    if (e != cudaSuccess) return set_error(SB_ERR_CUDA, cudaGetErrorString(e));
+    ctx->tc_attr |= (1 << 8);
+  }
+  fp4_tc_kernel<<<batch * hidx * qt, NUM_THREADS, smem, stream>>>(qm, km, p);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? SB_OK : set_error(SB_ERR_CUDA, cudaGetErrorString(e));
+}
+
+}  // namespace sb

@@ -48,6 +48,9 @@ int launch_summary_score_topk(const void* qd, const void* kd, float* scores, int
                               int qt, int nt, int r, int topk, cudaStream_t stream);
 int launch_summary_select_tc(const void* qd, const void* kd, void* aux, int32_t* ids, int batch, int hq, int hkv,
                              int qt, int nt, int r, int topk, cudaStream_t stream);
+int launch_fp4_indexer_tc(const void* qp, const void* qs, const void* kp, const void* ks, void* q_deq, void* k_deq,
+                          void* aux, int32_t* ids, int batch, int hidx, int hk, int len_q, int len_kv, int topk,
+                          cudaStream_t stream);
 int launch_quantize(const void* x, void* packed, void* scales, int batch, int heads_out, int group, int seq,
                     int paged, cudaStream_t stream);
 int launch_fp4_scores(const void* qp, const void* qs, const void* kp, const void* ks, float* query_scores,

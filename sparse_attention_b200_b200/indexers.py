@@ -184,6 +184,26 @@ def fp4_indexer(inputs, selected=None, topk=16, tile_scores=None):
     return selected
 
 
+def fp4_indexer_fast(inputs, selected=None, topk=16, workspace=None):
+    """Same ids as fp4_indexer through the tensor-core pre-filter + exact re-scoring.
+    Returns (selected, workspace); workspace[1] (int32 view) counts fallback tiles."""
+    b, h, lq, lkv = inputs["batch_size"], inputs["hkv"], inputs["len_q"], inputs["len_kv"]
+    dev = inputs["q"].device
+    L = _lib.lib()
+    L.sparse_b200_indexer_fp4_workspace_bytes.restype = ctypes.c_int64
+    need = L.sparse_b200_indexer_fp4_workspace_bytes(b, h, inputs["hk"], lq, lkv)
+    if workspace is None:
+        workspace = torch.empty(need, dtype=torch.uint8, device=dev)
+    if selected is None:
+        selected = torch.empty((b, h, lq // 128, topk), dtype=torch.int32, device=dev)
+    with torch.cuda.device(dev):
+        _lib.check(L.sparse_b200_indexer_fp4_fast(
+            _lib.ptr(inputs["q"]), _lib.ptr(inputs["q_scale"]), _lib.ptr(inputs["k"]), _lib.ptr(inputs["k_scale"]),
+            _lib.ptr(workspace), ctypes.c_int64(workspace.numel()), _lib.ptr(selected), b, h, inputs["hk"], lq, lkv,
+            int(selected.shape[-1]), _lib.current_stream()))
+    return selected, workspace
+
+
 def indexed_attention(q, k, v, inputs, topk=16):
     """(O, selected): FP4 indexer then Q-centric attention on the same stream."""
     from .q_centric import attention

@@ -204,6 +204,46 @@ def test_nvfp4_quantiser_and_quantised_indexer():
     m.device_status()
 
 
+def test_fp4_tensor_core_path_bit_exact():
+    """Tensor-core pre-filter + exact re-scoring must give the ids of the exact scorer."""
+    m = sp()
+    # random codes (the reference's synthetic family), one shared key head, 16 pages: all pages are candidates
+    qp, qs, kp, ks, b, lq, lkv = cases.fp4_case()
+    inputs = m.prepare_fp4_inputs(qp.cuda(), kp.cuda(), qs.cuda(), ks.cuda(), batch_size=b, len_q=lq, len_kv=lkv)
+    ids, _ = m.fp4_indexer_fast(inputs, topk=16)
+    fx = np.load(os.path.join(G, "fp4.npz"))
+    np.testing.assert_array_equal(ids.cpu().numpy(), fx["ids"])
+    # more pages than candidates, per-head key pages, top-4 and top-24
+    for (hidx, hk, lq, lkv, topk, seed) in [(2, 2, 256, 8192, 4, 5), (1, 1, 384, 16384, 24, 6)]:
+        g = torch.Generator().manual_seed(seed)
+        pages = lkv // 128
+        qp = torch.randint(256, (lq, hidx, 64), dtype=torch.uint8, generator=g)
+        kp = torch.randint(256, (pages, hk, 128, 64), dtype=torch.uint8, generator=g)
+        choices = torch.tensor([0.25, 0.375, 0.5, 0.75, 1.0, 1.5, 2.0])
+        qs = choices[torch.randint(7, (lq, hidx, 8), generator=g)].to(torch.float8_e4m3fn)
+        ks = choices[torch.randint(7, (pages, hk, 128, 8), generator=g)].to(torch.float8_e4m3fn)
+        inputs = m.prepare_fp4_inputs(qp.cuda(), kp.cuda(), qs.cuda(), ks.cuda(), batch_size=1, len_q=lq, len_kv=lkv)
+        ids, ws = m.fp4_indexer_fast(inputs, topk=topk)
+        torch.cuda.synchronize()
+        m.device_status()
+        ref = oracle.fp4_select(oracle.fp4_scores(qp, qs, kp, ks, 1, lq, lkv), 1, lq, topk)
+        assert torch.equal(ids.cpu(), ref)
+        assert torch.equal(ids.cpu(), m.fp4_indexer(inputs, topk=topk).cpu())
+        print("fallback tiles:", int(ws[4:8].view(torch.int32).item()))
+    # quantised real data (configuration-4 flow) and exact ties (all-zero keys): lower id first
+    q, k, _ = gen.make_qkv(1, 16, 2, 512, 8192, seed=43, k_block_offset=0.5)
+    qc, qsc = m.quantize_queries(q.cuda(), 2)
+    kc, ksc = m.quantize_keys(k.cuda())
+    inputs = m.prepare_fp4_inputs(qc, kc, qsc, ksc, batch_size=1, len_q=512, len_kv=8192)
+    ids, _ = m.fp4_indexer_fast(inputs, topk=8)
+    assert torch.equal(ids.cpu(), m.fp4_indexer(inputs, topk=8).cpu())
+    kc.zero_()
+    ids, ws = m.fp4_indexer_fast(inputs, topk=8)
+    assert torch.equal(ids.cpu(), torch.arange(8, dtype=torch.int32).expand_as(ids.cpu()))
+    assert int(ws[4:8].view(torch.int32).item()) == ids.shape[1] * ids.shape[2]
+    m.device_status()
+
+
 def test_indexer_then_attention_config1():
     """Configuration 1 end to end: R1 picks top-8 of 32, Q-centric attention,
     against the masked-attention oracle."""
