@@ -328,7 +328,10 @@ def run_config(args):
     import sparse_attention_b200_b200 as sp
     from sparse_attention_b200_b200 import sharding
 
-    cfg = CONFIGS[args.workload]
+    cfg = dict(CONFIGS[args.workload])
+    if args.n:                       # shorter sequence of the same configuration (profiler captures)
+        cfg["N"] = args.n
+        cfg["topk"] = min(cfg["topk"], args.n // 128)
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -467,6 +470,7 @@ def main():
     ap.add_argument("--workload", default="c2", choices=["c2"] + sorted(CONFIGS),
                     help="c2 (default) is the headline workload; c1/c3/c4/c5 run indexer + operator stage by stage")
     ap.add_argument("--kv-split", type=int, default=1, help="KV ranges per head shard (c5 only, needs --gpus >= 2)")
+    ap.add_argument("--n", type=int, default=0, help="override the token count of c1/c3/c4/c5 (small profiler cases)")
     ap.add_argument("--segments", type=int, default=4, help="KV-range segments of the KV-centric operator (c4)")
     args = ap.parse_args()
     if args.impl == "reference":
