@@ -318,6 +318,45 @@ def timed(fn, steps, warmup, barrier):
     return e0.elapsed_time(e1) / steps
 
 
+def run_kv_token(args):
+    """The reference's own KV-centric benchmark shape (B8, Hq16, Hkv1, Sq = Skv = 4096, TopK 16,
+    per-TOKEN independent lists; benchmarks/ch5_kv_centric/round11_final/RESULTS_RU.md:9-13)
+    through the per-token operator: metadata, main, combine."""
+    import torch
+    import sparse_attention_b200_b200 as sp
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    B, Hq, Hkv, S, topk = 8, 16, 1, args.n or 4096, 16
+    gen = torch.Generator(device=dev).manual_seed(17)
+    q = torch.randn((B, Hq, S, 128), device=dev, generator=gen).to(torch.bfloat16)
+    k = torch.randn((B, Hkv, S, 128), device=dev, generator=gen).to(torch.bfloat16)
+    v = torch.randn((B, Hkv, S, 128), device=dev, generator=gen).to(torch.bfloat16)
+    selected = torch.rand((B * Hkv * S, S // 128), device=dev, generator=gen).argsort(-1)[:, :topk] \
+        .int().reshape(B, Hkv, S, topk).contiguous()
+    prep = sp.PreparedTokens(q, k, v, selected)
+
+    def barrier():
+        torch.cuda.synchronize()
+    stages = {"metadata_ms": timed(prep.metadata, args.steps, 3, barrier),
+              "main_ms": timed(prep.main, args.steps, 3, barrier),
+              "combine_ms": timed(prep.combine, args.steps, 3, barrier)}
+    ms = timed(prep.run, args.steps, 3, barrier)
+    sp.device_status()
+    fl = 4.0 * B * Hq * S * (topk * 128) * 128
+    peak_tf, peak_gbs, peak_src = measured_peaks()
+    value = fl / (ms * 1e-3) / 1e12
+    print(json.dumps({"metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": 1, "steps": args.steps,
+                      "warmup": 3, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+                      "dtype": "bf16", "data": "synthetic (seeded N(0,1), independent per-token lists)",
+                      "config": {"workload": "kv_token_reference_shape", "B": B, "Hq": Hq, "Hkv": Hkv, "Sq": S, "Skv": S,
+                                 "topk": topk}, "stages_rank0": stages,
+                      "reference_published": {"ms": 1.503, "tflops": 365.8, "variant": "tma16_bf16",
+                                              "source": "benchmarks/ch5_kv_centric/round11_final/RESULTS_RU.md:12"},
+                      "roofline": {"bound": "tensor", "achieved": value, "peak": peak_tf, "unit": "TFLOP/s",
+                                   "frac": value / peak_tf, "traffic": None, "peak_source": peak_src,
+                                   "kernel": "kv_token_kernel + combine_kernel"}}), flush=True)
+
+
 def run_config(args):
     """Configurations 1, 3, 4, 5: indexer -> lists -> attention operator, stage by stage.
     With N > 1 ranks the (batch, KV-head) groups are dealt to the ranks (strong scaling, no
@@ -467,7 +506,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--kernel-only", action="store_true",
                     help="device-resident timing only (used for profiler captures): no e2e, no CPU baseline")
-    ap.add_argument("--workload", default="c2", choices=["c2"] + sorted(CONFIGS),
+    ap.add_argument("--workload", default="c2", choices=["c2", "kvtoken"] + sorted(CONFIGS),
                     help="c2 (default) is the headline workload; c1/c3/c4/c5 run indexer + operator stage by stage")
     ap.add_argument("--kv-split", type=int, default=1, help="KV ranges per head shard (c5 only, needs --gpus >= 2)")
     ap.add_argument("--n", type=int, default=0, help="override the token count of c1/c3/c4/c5 (small profiler cases)")
@@ -475,6 +514,8 @@ def main():
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload == "kvtoken":
+        run_kv_token(args)
     elif args.workload != "c2":
         run_config(args)
     else:

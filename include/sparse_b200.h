@@ -94,6 +94,29 @@ int sparse_b200_kv_centric(const void* q, const void* k, const void* v, const in
                            int64_t workspace_bytes, int nseg, int partial_is_f32, int batch, int hq, int hkv, int sq,
                            int skv, int topk, void* stream);
 
+/* KV-centric operator for per-TOKEN selection lists, the reference's own KV-centric
+ * contract with a free TopK: selected [B, Hkv, Sq, TopK] int32 (any Sq >= 1).
+ * kv_token_metadata builds the reverse index on the GPU: rows = (b*Hkv + kvh)*kv_blocks
+ * + block; row_ptr [rows+1], query_ids / ranks [B*Hkv*Sq*TopK] (edge order inside a row
+ * is arbitrary), task_ptr [rows+1] (task_ptr[rows] = task count), tasks [max_tasks, 4] =
+ * (group, block, first edge, edge count <= 128/group_size); counts and cursors are
+ * scratch of rows+1 ints; error_word bit 1 = id out of range. Replaces
+ * kv4_build_metadata (attention/kv_centric/optimization_round4/gpu_metadata.cu:82-108).
+ * kv_token_main gathers the queries of every task, runs QK / softmax over the one
+ * block / PV on the tensor cores and scatters normalised partials [B, Hq, Sq, TopK, 128]
+ * bf16 and partial_lse [B, Hq, Sq, TopK]; q is [B, Hq, Sq, 128]. Replaces kv11_launch
+ * (attention/kv_centric/optimization_round11/tma11_kernel.cu:439-452). Merge with
+ * sparse_b200_combine(partial, 0, partial_lse, out, lse, B*Hq*Sq, TopK, rank_major = 0). */
+int64_t sparse_b200_kv_token_max_tasks(int batch, int hkv, int sq, int topk, int kv_blocks, int group_size);
+int sparse_b200_kv_token_metadata(const int32_t* selected, int32_t* counts, int32_t* cursors, int32_t* row_ptr,
+                                  int32_t* query_ids, int32_t* ranks, int32_t* task_ptr, int32_t* tasks,
+                                  int32_t* error_word, int batch, int hkv, int sq, int topk, int kv_blocks,
+                                  int group_size, void* stream);
+int sparse_b200_kv_token_main(const void* q, const void* k, const void* v, const int32_t* tasks,
+                              const int32_t* task_ptr, const int32_t* query_ids, const int32_t* ranks, void* partial,
+                              float* partial_lse, int batch, int hq, int hkv, int sq, int skv, int topk,
+                              void* stream);
+
 /* R1 / R4 block-summary indexer (indexers/r1_r4/gpu_ops.py:6-49,
  * indexers/r1_r4/block_selectors.py:9-45), any Hkv, group size x R <= 64, any TopK.
  * pool_blocks: x [B, H, S, 128] bf16 -> desc [B, H, S/128, R, 128] bf16, the

@@ -342,6 +342,50 @@ int sparse_b200_indexer_fp4(const void* q_codes, const void* q_scales, const voi
                          topk, static_cast<cudaStream_t>(stream));
 }
 
+int64_t sparse_b200_kv_token_max_tasks(int batch, int hkv, int sq, int topk, int kv_blocks, int group_size) {
+  if (batch <= 0 || hkv <= 0 || sq <= 0 || topk <= 0 || kv_blocks <= 0 || group_size <= 0 || group_size > 128)
+    return SB_ERR_INVALID;
+  const int64_t edges = static_cast<int64_t>(batch) * hkv * sq * topk;
+  const int64_t rows = static_cast<int64_t>(batch) * hkv * kv_blocks;
+  const int64_t cap = 128 / group_size;
+  const int64_t bound = (edges + cap - 1) / cap + rows;
+  return bound < edges ? bound : edges;
+}
+
+int sparse_b200_kv_token_metadata(const int32_t* selected, int32_t* counts, int32_t* cursors, int32_t* row_ptr,
+                                  int32_t* query_ids, int32_t* ranks, int32_t* task_ptr, int32_t* tasks,
+                                  int32_t* error_word, int batch, int hkv, int sq, int topk, int kv_blocks,
+                                  int group_size, void* stream) {
+  REQUIRE(selected && counts && cursors && row_ptr && query_ids && ranks && task_ptr && tasks && error_word,
+          "null pointer");
+  REQUIRE(batch > 0 && hkv > 0 && sq > 0 && topk > 0 && kv_blocks > 0, "sizes must be positive");
+  REQUIRE(group_size == 1 || group_size == 2 || group_size == 4 || group_size == 8 || group_size == 16,
+          "supported ratios Hq/Hkv are 1, 2, 4, 8, and 16");
+  REQUIRE(static_cast<long long>(batch) * hkv * sq * topk < (1LL << 31) &&
+              static_cast<long long>(batch) * hkv * kv_blocks < (1LL << 31) - 1,
+          "metadata is limited to signed int32 offsets");
+  REQUIRE((reinterpret_cast<uintptr_t>(tasks) & 15u) == 0, "tasks must be 16-byte aligned");
+  return launch_token_metadata(selected, counts, cursors, row_ptr, query_ids, ranks, task_ptr, tasks, error_word,
+                               batch * hkv, sq, topk, kv_blocks, group_size, static_cast<cudaStream_t>(stream));
+}
+
+int sparse_b200_kv_token_main(const void* q, const void* k, const void* v, const int32_t* tasks,
+                              const int32_t* task_ptr, const int32_t* query_ids, const int32_t* ranks, void* partial,
+                              float* partial_lse, int batch, int hq, int hkv, int sq, int skv, int topk,
+                              void* stream) {
+  REQUIRE(q && k && v && tasks && task_ptr && query_ids && ranks && partial && partial_lse, "null pointer");
+  REQUIRE(batch > 0 && hkv > 0 && hq >= hkv && hq % hkv == 0, "Hq must be a positive multiple of Hkv");
+  const int g = hq / hkv;
+  REQUIRE(g == 1 || g == 2 || g == 4 || g == 8 || g == 16, "supported ratios Hq/Hkv are 1, 2, 4, 8, and 16");
+  REQUIRE(sq > 0 && skv >= 128 && skv % 128 == 0 && topk > 0 && topk <= skv / 128,
+          "Skv must be a positive multiple of 128 and TopK at most the number of KV blocks");
+  REQUIRE(static_cast<long long>(batch) * hkv * skv < (1LL << 31), "flattened KV rows must fit int32");
+  REQUIRE(aligned16(q) && aligned16(k) && aligned16(v) && aligned16(partial) && aligned16(tasks), "misaligned pointer");
+  const long long rows = static_cast<long long>(batch) * hkv * (skv / 128);
+  return launch_kv_token_main(q, k, v, tasks, task_ptr + rows, query_ids, ranks, partial, partial_lse, batch, hq, hkv,
+                              sq, skv, topk, static_cast<cudaStream_t>(stream));
+}
+
 int64_t sparse_b200_indexer_fp4_workspace_bytes(int batch, int hidx, int hk, int len_q, int len_kv) {
   if (batch <= 0 || hidx <= 0 || hk <= 0 || len_q <= 0 || len_kv <= 0) return SB_ERR_INVALID;
   const int64_t q = align256(static_cast<size_t>(batch) * len_q * hidx * 256);

@@ -51,6 +51,12 @@ int launch_summary_select_tc(const void* qd, const void* kd, void* aux, int32_t*
 int launch_fp4_indexer_tc(const void* qp, const void* qs, const void* kp, const void* ks, void* q_deq, void* k_deq,
                           void* aux, int32_t* ids, int batch, int hidx, int hk, int len_q, int len_kv, int topk,
                           cudaStream_t stream);
+int launch_token_metadata(const int32_t* selected, int32_t* counts, int32_t* cursors, int32_t* row_ptr,
+                          int32_t* qids, int32_t* ranks, int32_t* task_ptr, int32_t* tasks, int32_t* error,
+                          int groups, int sq, int topk, int kv_blocks, int group_size, cudaStream_t stream);
+int launch_kv_token_main(const void* q, const void* k, const void* v, const int32_t* tasks, const int32_t* task_count,
+                         const int32_t* qids, const int32_t* ranks, void* partial, float* lses, int batch, int hq,
+                         int hkv, int sq, int skv, int topk, cudaStream_t stream);
 int launch_quantize(const void* x, void* packed, void* scales, int batch, int heads_out, int group, int seq,
                     int paged, cudaStream_t stream);
 int launch_fp4_scores(const void* qp, const void* qs, const void* kp, const void* ks, float* query_scores,

@@ -1,0 +1,128 @@
+// Per-TOKEN selection lists -> reverse index for the KV-centric token kernel.
+//
+// selected [B, Hkv, Sq, TopK] int32 holds, for every query token and KV-head group,
+// the KV blocks it attends to. The reverse index lists, for every row
+// (group = b*Hkv + kvh, block), the (query, rank) edges that chose the block:
+//   row_ptr [rows + 1], query_ids [E], ranks [E]   (E = B*Hkv*Sq*TopK edges)
+// and cuts every row into tasks of at most 128 / group_size queries:
+//   task_ptr [rows + 1] (task_ptr[rows] = number of tasks), tasks [T, 4] =
+//   (group, block, first edge, edge count).
+// Same structure as the reference's build (kv4_build_metadata,
+// attention/kv_centric/optimization_round4/gpu_metadata.cu:82-108; CPU statement
+// attention/kv_centric/metadata.py:43-72), for any TopK and block count, with its own
+// scans instead of a library call. Edge order inside a row is arbitrary (atomics).
+// error word: bit 1 = an id outside [0, kv_blocks).
+#include "internal.h"
+
+namespace sb {
+namespace {
+
+__global__ void __launch_bounds__(256) count_edges_kernel(const int32_t* __restrict__ selected, int32_t* counts,
+                                                          int32_t* error, long long edges, long long group_edges,
+                                                          int kv_blocks) {
+  for (long long e = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; e < edges;
+       e += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int key = selected[e];
+    if (static_cast<unsigned>(key) < static_cast<unsigned>(kv_blocks))
+      atomicAdd(counts + (e / group_edges) * kv_blocks + key, 1);
+    else
+      atomicOr(error, 1);
+  }
+}
+
+// Exclusive scan of n + 1 values by one CTA of 1024 threads (n is at most a few 10^5 rows).
+// With `capacity` > 0 the scanned values are ceil(in / capacity) (tasks per row).
+__global__ void __launch_bounds__(1024) scan_kernel(const int32_t* __restrict__ in, int32_t* __restrict__ out, int n,
+                                                    int capacity) {
+  __shared__ int warp_sums[32];
+  __shared__ int carry;
+  if (threadIdx.x == 0) carry = 0;
+  __syncthreads();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int base = 0; base <= n; base += 1024) {
+    const int i = base + threadIdx.x;
+    int v = 0;
+    if (i < n) v = capacity > 0 ? (in[i] + capacity - 1) / capacity : in[i];
+    int incl = v;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      const int o = __shfl_up_sync(0xffffffffu, incl, d);
+      if (lane >= d) incl += o;
+    }
+    if (lane == 31) warp_sums[warp] = incl;
+    __syncthreads();
+    if (warp == 0) {
+      int w = warp_sums[lane];
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        const int o = __shfl_up_sync(0xffffffffu, w, d);
+        if (lane >= d) w += o;
+      }
+      warp_sums[lane] = w;
+    }
+    __syncthreads();
+    const int prefix = carry + (warp > 0 ? warp_sums[warp - 1] : 0) + incl - v;
+    if (i <= n) out[i] = prefix;
+    __syncthreads();
+    if (threadIdx.x == 1023) carry = prefix + v;
+    __syncthreads();
+  }
+}
+
+__global__ void __launch_bounds__(256) scatter_edges_kernel(const int32_t* __restrict__ selected,
+                                                            const int32_t* __restrict__ row_ptr, int32_t* cursors,
+                                                            int32_t* __restrict__ qids, int32_t* __restrict__ ranks,
+                                                            long long edges, long long group_edges, int kv_blocks,
+                                                            int topk) {
+  for (long long e = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; e < edges;
+       e += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int key = selected[e];
+    if (static_cast<unsigned>(key) >= static_cast<unsigned>(kv_blocks)) continue;
+    const long long row = (e / group_edges) * kv_blocks + key;
+    const int dst = row_ptr[row] + atomicAdd(cursors + row, 1);
+    const long long in_group = e % group_edges;
+    qids[dst] = static_cast<int32_t>(in_group / topk);
+    ranks[dst] = static_cast<int32_t>(in_group % topk);
+  }
+}
+
+__global__ void __launch_bounds__(128) make_tasks_kernel(const int32_t* __restrict__ row_ptr,
+                                                         const int32_t* __restrict__ task_ptr,
+                                                         int32_t* __restrict__ tasks, int rows, int kv_blocks,
+                                                         int capacity) {
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    const int start = row_ptr[row], end = row_ptr[row + 1];
+    for (int task = task_ptr[row] + threadIdx.x; task < task_ptr[row + 1]; task += blockDim.x) {
+      const int begin = start + (task - task_ptr[row]) * capacity;
+      const int4 value = {row / kv_blocks, row % kv_blocks, begin, min(capacity, end - begin)};
+      *reinterpret_cast<int4*>(tasks + static_cast<long long>(task) * 4) = value;
+    }
+  }
+}
+
+}  // namespace
+
+// counts / cursors [rows + 1], row_ptr / task_ptr [rows + 1], qids / ranks [E], tasks [max_tasks, 4].
+int launch_token_metadata(const int32_t* selected, int32_t* counts, int32_t* cursors, int32_t* row_ptr,
+                          int32_t* qids, int32_t* ranks, int32_t* task_ptr, int32_t* tasks, int32_t* error,
+                          int groups, int sq, int topk, int kv_blocks, int group_size, cudaStream_t stream) {
+  const int rows = groups * kv_blocks;
+  const long long group_edges = static_cast<long long>(sq) * topk;
+  const long long edges = group_edges * groups;
+  const int capacity = 128 / group_size;
+  if (cudaMemsetAsync(counts, 0, static_cast<size_t>(rows + 1) * 4, stream) != cudaSuccess ||
+      cudaMemsetAsync(cursors, 0, static_cast<size_t>(rows + 1) * 4, stream) != cudaSuccess ||
+      cudaMemsetAsync(error, 0, 4, stream) != cudaSuccess)
+    return set_error(SB_ERR_CUDA, "memset failed");
+  const int grid = static_cast<int>(edges / 256 + 1 < 4096 ? edges / 256 + 1 : 4096);
+  count_edges_kernel<<<grid, 256, 0, stream>>>(selected, counts, error, edges, group_edges, kv_blocks);
+  scan_kernel<<<1, 1024, 0, stream>>>(counts, row_ptr, rows, 0);
+  scatter_edges_kernel<<<grid, 256, 0, stream>>>(selected, row_ptr, cursors, qids, ranks, edges, group_edges, kv_blocks,
+                                                 topk);
+  scan_kernel<<<1, 1024, 0, stream>>>(counts, task_ptr, rows, capacity);
+  make_tasks_kernel<<<rows < 4096 ? rows : 4096, 128, 0, stream>>>(row_ptr, task_ptr, tasks, rows, kv_blocks, capacity);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? SB_OK : set_error(SB_ERR_CUDA, cudaGetErrorString(e));
+}
+
+}  // namespace sb

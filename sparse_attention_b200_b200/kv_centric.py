@@ -83,6 +83,96 @@ class Prepared:
         return {"segments": self.nseg, "edges": int(self.seg_counts.sum().item())}
 
 
+class PreparedTokens:
+    """Per-TOKEN selections, the reference's own contract (api11.py:50-92, gpu_plan.py:19-45):
+    q [B,Hq,Sq,128], k/v [B,Hkv,Skv,128] bf16, selected [B,Hkv,Sq,TopK] int32 (CUDA), any TopK.
+    metadata() builds the reverse index and the task list on the GPU, main() writes one
+    normalised partial per (query, head, rank), combine() merges the TopK partials."""
+
+    def __init__(self, q, k, v, selected):
+        import ctypes
+        if not (q.is_cuda and q.dtype == torch.bfloat16 and q.is_contiguous() and q.dim() == 4 and q.shape[3] == 128):
+            raise _lib.SparseB200Error("q must be contiguous bf16 [B,Hq,Sq,128] on CUDA")
+        for t in (k, v):
+            if not (t.is_cuda and t.dtype == torch.bfloat16 and t.is_contiguous() and t.dim() == 4
+                    and t.shape[3] == 128 and t.device == q.device):
+                raise _lib.SparseB200Error("k and v must be contiguous bf16 [B,Hkv,Skv,128] on q's device")
+        b, hq, sq, d = q.shape
+        hkv, skv = k.shape[1:3]
+        if k.shape != v.shape or k.shape[0] != b or hq % hkv or skv % 128:
+            raise _lib.SparseB200Error("QKV/GQA geometry")
+        if selected.dtype != torch.int32 or not selected.is_contiguous() or selected.device != q.device \
+                or selected.dim() != 4 or tuple(selected.shape[:3]) != (b, hkv, sq):
+            raise _lib.SparseB200Error("selected must be contiguous int32 [B,Hkv,Sq,TopK] on q's device")
+        self.q, self.k, self.v, self.selected = q, k, v, selected
+        self.b, self.hq, self.hkv, self.sq, self.skv = b, hq, hkv, sq, skv
+        self.g, self.topk, self.kv_blocks = hq // hkv, int(selected.shape[3]), skv // 128
+        self.rows = b * hkv * self.kv_blocks
+        self.edges = selected.numel()
+        L = _lib.lib()
+        L.sparse_b200_kv_token_max_tasks.restype = ctypes.c_int64
+        self.max_tasks = int(L.sparse_b200_kv_token_max_tasks(b, hkv, sq, self.topk, self.kv_blocks, self.g))
+        if self.max_tasks <= 0:
+            raise _lib.SparseB200Error("invalid routing geometry")
+        dev = q.device
+
+        def ints(n):
+            return torch.empty(n, device=dev, dtype=torch.int32)
+        self.counts, self.cursors = ints(self.rows + 1), ints(self.rows + 1)
+        self.row_ptr, self.task_ptr = ints(self.rows + 1), ints(self.rows + 1)
+        self.qids, self.ranks = ints(self.edges), ints(self.edges)
+        self.tasks = torch.zeros((self.max_tasks, 4), device=dev, dtype=torch.int32)
+        self.error = ints(1)
+        self.partial = torch.empty((b, hq, sq, self.topk, d), device=dev, dtype=torch.bfloat16)
+        self.lses = torch.empty((b, hq, sq, self.topk), device=dev, dtype=torch.float32)
+        self.out = torch.empty((b, hq, sq, d), device=dev, dtype=torch.bfloat16)
+        self.out_lse = torch.empty((b, hq, sq), device=dev, dtype=torch.float32)
+
+    def poison(self):
+        for t in (self.partial, self.lses, self.out, self.out_lse):
+            t.fill_(float("nan"))
+
+    def metadata(self):
+        with torch.cuda.device(self.q.device):
+            _lib.check(_lib.lib().sparse_b200_kv_token_metadata(
+                _lib.ptr(self.selected), _lib.ptr(self.counts), _lib.ptr(self.cursors), _lib.ptr(self.row_ptr),
+                _lib.ptr(self.qids), _lib.ptr(self.ranks), _lib.ptr(self.task_ptr), _lib.ptr(self.tasks),
+                _lib.ptr(self.error), self.b, self.hkv, self.sq, self.topk, self.kv_blocks, self.g,
+                _lib.current_stream()))
+
+    def main(self):
+        with torch.cuda.device(self.q.device):
+            _lib.check(_lib.lib().sparse_b200_kv_token_main(
+                _lib.ptr(self.q), _lib.ptr(self.k), _lib.ptr(self.v), _lib.ptr(self.tasks), _lib.ptr(self.task_ptr),
+                _lib.ptr(self.qids), _lib.ptr(self.ranks), _lib.ptr(self.partial), _lib.ptr(self.lses),
+                self.b, self.hq, self.hkv, self.sq, self.skv, self.topk, _lib.current_stream()))
+
+    def combine(self):
+        import ctypes
+        with torch.cuda.device(self.q.device):
+            _lib.check(_lib.lib().sparse_b200_combine(
+                _lib.ptr(self.partial), 0, _lib.ptr(self.lses), _lib.ptr(self.out), _lib.ptr(self.out_lse),
+                ctypes.c_int64(self.out_lse.numel()), self.topk, 0, _lib.current_stream()))
+
+    def core(self):
+        self.main()
+        self.combine()
+
+    def run(self):
+        self.metadata()
+        self.core()
+        return self.out, self.out_lse
+
+    def plan(self):
+        """Host copy of the device plan (synchronising; tests compare it with the CPU builder)."""
+        status = int(self.error.item())
+        if status:
+            raise ValueError(f"GPU selected validation failed: flag={status} (1 = id out of range)")
+        ntasks = int(self.task_ptr[-1].item())
+        return {"row_ptr": self.row_ptr.cpu(), "query_ids": self.qids.cpu(), "ranks": self.ranks.cpu(),
+                "tasks": self.tasks[:ntasks].cpu()}
+
+
 def kv_centric_attention(q, k, v, selected, counts=None, nseg=None, partial="bf16", workspace=None):
     """One call through the fused C entry (metadata + main + combine, caller workspace)."""
     _validate(q, k, v, selected, None, counts)
