@@ -75,8 +75,13 @@ kv_token_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant
   const uint32_t idesc_pv = idesc_bf16(128, 128, true);
   const int rows_per_chunk = 128 >> p.group_log2;      // queries per task
 
-  uint32_t phase = 0;
-  for (int t = blockIdx.x; t < total; t += gridDim.x) {
+  // Each CTA takes a contiguous range of the task list: tasks are ordered by (group,
+  // block), so consecutive tasks mostly share their K/V block and skip the reload.
+  const int per_cta = (total + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x);
+  const int t_begin = blockIdx.x * per_cta, t_end = min(total, t_begin + per_cta);
+  uint32_t phase = 0, kv_phase = 0;
+  int loaded_group = -1, loaded_block = -1;
+  for (int t = t_begin; t < t_end; ++t) {
     const int4 task = *reinterpret_cast<const int4*>(p.tasks + static_cast<long long>(t) * 4);
     const int group = task.x, block = task.y, start = task.z, count = task.w;
     const bool valid = group >= 0 && group < p.batch * p.hkv && block >= 0 && block < p.skv / 128 && start >= 0 &&
@@ -84,8 +89,11 @@ kv_token_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant
     if (!valid) continue;                                   // block-uniform
     const int b = group / p.hkv, kvh = group - b * p.hkv;
     bool ok = true;
+    const bool reload = group != loaded_group || block != loaded_block;
+    loaded_group = group;
+    loaded_block = block;
     if (warp == ISSUE_WARP) {
-      if (lane == 0) {
+      if (reload && lane == 0) {
         const int kv_row = group * p.skv + block * 128;
         mbar_expect_tx(bar(KV_FULL), 2 * TILE_BYTES);
         tma_load_2d(base + OFF_K, &k_map, 0, kv_row, bar(KV_FULL));
@@ -119,7 +127,11 @@ kv_token_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant
     const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
     float row_max = 0.f, row_sum = 1.f;
     if (warp == ISSUE_WARP) {
-      bool w = mbar_wait(bar(KV_FULL), phase, guard, 0x600);
+      bool w = true;
+      if (reload) {
+        w = mbar_wait(bar(KV_FULL), kv_phase, guard, 0x600);
+        kv_phase ^= 1;
+      }
       ok = __all_sync(0xffffffffu, w);
       tc_fence_after();
       if (ok && lane == 0) {
