@@ -147,6 +147,14 @@ int sparse_b200_indexer_summary_fast(const void* q, const void* k, void* q_desc,
                                      int32_t* block_idx, int batch, int hq, int hkv, int sq, int skv,
                                      int representatives, int topk, void* stream);
 
+/* Indexer -> attention on one stream with no host synchronisation: R1/R4 indexer (tensor-core
+ * path) writes block_idx, the Q-centric kernel consumes it. The shape of indexed_attention()
+ * (indexers/fp4/pipeline.py:49-65) for the summary indexers; capturable in a CUDA graph after
+ * one eager call. Workspaces as in sparse_b200_indexer_summary_fast. */
+int sparse_b200_indexed_attention_summary(const void* q, const void* k, const void* v, void* q_desc, void* k_desc,
+                                          void* aux, int32_t* block_idx, void* out, float* lse, int batch, int hq,
+                                          int hkv, int sq, int skv, int representatives, int topk, void* stream);
+
 /* NVFP4 indexer. Index vectors: 64 bytes of e2m1 codes (low nibble first) + 8
  * e4m3 scales per 128 features (contract of prepare_fp4_inputs,
  * indexers/fp4/fp4.py:37-60). q_codes [B*Sq, Hidx, 64], q_scales [B*Sq, Hidx, 8],

@@ -281,6 +281,16 @@ int sparse_b200_indexer_summary_fast(const void* q, const void* k, void* q_desc,
   return rc;
 }
 
+int sparse_b200_indexed_attention_summary(const void* q, const void* k, const void* v, void* q_desc, void* k_desc,
+                                          void* aux, int32_t* block_idx, void* out, float* lse, int batch, int hq,
+                                          int hkv, int sq, int skv, int representatives, int topk, void* stream) {
+  int rc = sparse_b200_indexer_summary_fast(q, k, q_desc, k_desc, aux, block_idx, batch, hq, hkv, sq, skv,
+                                            representatives, topk, stream);
+  if (rc) return rc;
+  // same stream: the ids written by the indexer are ready for the attention kernel
+  return sparse_b200_q_centric(q, k, v, block_idx, nullptr, out, lse, batch, hq, hkv, sq, skv, topk, stream);
+}
+
 int sparse_b200_nvfp4_quantize(const void* x, void* packed, void* scales, int batch, int heads_out, int group,
                                int seq, int paged, void* stream) {
   REQUIRE(x && packed && scales, "null pointer");

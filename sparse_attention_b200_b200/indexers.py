@@ -85,6 +85,17 @@ class SummarySelector:
         return self.ids
 
 
+def summary_indexed_attention_out(selector, v, out, lse=None):
+    """selector.run_fast() + attention on the current stream as ONE C call; ids land in selector.ids."""
+    s = selector
+    with torch.cuda.device(s.q.device):
+        _lib.check(_lib.lib().sparse_b200_indexed_attention_summary(
+            _lib.ptr(s.q), _lib.ptr(s.k), _lib.ptr(v), _lib.ptr(s.qd), _lib.ptr(s.kd), _lib.ptr(s.aux),
+            _lib.ptr(s.ids), _lib.ptr(out), _lib.ptr(lse), s.b, s.hq, s.hkv, s.qt * 128, s.nt * 128, s.r, s.topk,
+            _lib.current_stream()))
+    return out
+
+
 # ---------------------------------------------------------------- NVFP4
 def quantize_queries(q, hidx):
     """q [B,Hq,Sq,128] bf16 -> (codes [B*Sq,hidx,64] u8, scales [B*Sq,hidx,8] e4m3):

@@ -260,6 +260,40 @@ def test_indexer_then_attention_config1():
     assert torch.all((lse.cpu() - ref_l).abs() <= 1e-3 * ref_l.abs().clamp_min(1.0))
 
 
+def test_indexer_attention_pipeline_in_a_cuda_graph():
+    """Indexer -> attention as one call, captured once and replayed after the inputs changed:
+    new exact ids and a correct output must come out of the replay (the reference's gate,
+    benchmarks/ch4_selectors/harness.py:105-111)."""
+    m = sp()
+    q, k, v = gen.make_qkv(1, 16, 2, 1024, 8192, seed=61, k_block_offset=0.5)
+    qc, kc, vc = q.cuda(), k.cuda(), v.cuda()
+    sel = m.SummarySelector(qc, kc, 4, topk=16, keep_scores=False)
+    out = torch.empty_like(qc)
+    lse = torch.empty(qc.shape[:3], device="cuda")
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        m.summary_indexed_attention_out(sel, vc, out, lse)           # eager call first
+    stream.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=stream):
+        m.summary_indexed_attention_out(sel, vc, out, lse)
+    torch.cuda.synchronize()
+    for shift in (0, 128, 384):
+        with torch.cuda.stream(stream):
+            qc.copy_(q.cuda().roll(shift, dims=2))
+            sel.ids.fill_(-1)
+            out.fill_(float("nan"))
+            graph.replay()
+        stream.synchronize()
+        ref_ids = oracle.summary_select(qc.cpu(), k, 4, 16)[3]
+        assert torch.equal(sel.ids.cpu(), ref_ids)
+        ref_o, ref_l = oracle.gather_attention(qc.cpu(), k, v, ref_ids)
+        d = (out.float().cpu() - ref_o).abs()
+        assert d.max() <= 2e-2 and d.mean() <= 2e-3
+        assert torch.all((lse.cpu() - ref_l).abs() <= 1e-3 * ref_l.abs().clamp_min(1.0))
+    m.device_status()
+
+
 def test_rejected_indexer_inputs():
     m = sp()
     q, k, _ = gen.make_qkv(1, 4, 2, 256, 512, seed=1)
