@@ -357,6 +357,72 @@ def run_kv_token(args):
                                    "kernel": "kv_token_kernel + combine_kernel"}}), flush=True)
 
 
+REFCMP_SHAPES = [
+    # (name, B, Hq, Hkv, Sq, Skv, topk): the reference's own benchmark shapes
+    # (benchmarks/ch4_q_centric sweep: B2, Hq16, Hkv1, Sq4096, TopK16, Skv 2048..16384), GQA 4:1,
+    # and this repository's headline MHA configuration.
+    ("ref_gqa16_skv2048", 2, 16, 1, 4096, 2048, 16),
+    ("ref_gqa16_skv4096", 2, 16, 1, 4096, 4096, 16),
+    ("ref_gqa16_skv8192", 2, 16, 1, 4096, 8192, 16),
+    ("ref_gqa16_skv16384", 2, 16, 1, 4096, 16384, 16),
+    ("gqa4_32k", 1, 32, 8, 32768, 32768, 16),
+    ("mha_32k", 1, 32, 32, 32768, 32768, 16),
+]
+
+
+def run_refcmp(args):
+    """Same-box comparator: the reference's own Q-centric kernels (p02 = Q-position pairing,
+    variant 1; p03 = head pairing, variant 2; attention/q_centric/progression.py:40-58), compiled
+    unmodified by baseline/build_reference_kernels.py into the git-ignored baseline/_ref/, timed
+    next to this repository's kernel with one protocol: same tensors, same lists, CUDA events
+    around back-to-back launches, arms interleaved in rounds and the best round kept per arm.
+    Prints one JSON line per shape; when the reference library is absent, one `unavailable` line."""
+    import torch
+    import sparse_attention_b200_b200 as sp
+    lib = os.path.join(os.path.dirname(os.path.abspath(__file__)), "baseline", "_ref", "xomtention_progression.so")
+    if not os.path.exists(lib):
+        print(json.dumps({"workload": "refcmp", "unavailable": "baseline/_ref/xomtention_progression.so not built "
+                          "(python baseline/build_reference_kernels.py)"}), flush=True)
+        return
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    torch.ops.load_library(lib)
+    ref_out = torch.ops.xomtention_progression.attention_out
+
+    def barrier():
+        torch.cuda.synchronize()
+    for name, B, Hq, Hkv, Sq, Skv, topk in REFCMP_SHAPES:
+        gen = torch.Generator(device=dev).manual_seed(23)
+        q = torch.randn((B, Hq, Sq, 128), device=dev, generator=gen).to(torch.bfloat16)
+        k = torch.randn((B, Hkv, Skv, 128), device=dev, generator=gen).to(torch.bfloat16)
+        v = torch.randn((B, Hkv, Skv, 128), device=dev, generator=gen).to(torch.bfloat16)
+        # the reference's "independent" pattern: a fresh random subset per list, ascending
+        # (attention/q_centric/progression_validation.py:21-41)
+        ids = torch.rand((B * Hkv * (Sq // 128), Skv // 128), device=dev, generator=gen).argsort(-1)[:, :topk] \
+            .sort(-1).values.int().reshape(B, Hkv, Sq // 128, topk).contiguous()
+        outs = {"ours": torch.empty_like(q), "p02": torch.empty_like(q), "p03": torch.empty_like(q)}
+        arms = {"ours": lambda: sp.attention_out(q, k, v, ids, outs["ours"]),
+                "p02": lambda: ref_out(q, k, v, ids, outs["p02"], 1)}
+        if Hq // Hkv >= 2:
+            arms["p03"] = lambda: ref_out(q, k, v, ids, outs["p03"], 2)
+        best = {a: float("inf") for a in arms}
+        for rnd in range(3):
+            for a, fn in arms.items():
+                best[a] = min(best[a], timed(fn, args.steps, 3, barrier))
+        sp.device_status()
+        fl = 4.0 * B * Hq * Sq * (topk * 128) * 128
+        diff = {a: (outs[a].float() - outs["ours"].float()).abs().max().item() for a in arms if a != "ours"}
+        ref_best = min(v_ for a, v_ in best.items() if a != "ours")
+        print(json.dumps({"workload": "refcmp", "shape": {"name": name, "B": B, "Hq": Hq, "Hkv": Hkv, "Sq": Sq,
+                                                          "Skv": Skv, "topk": topk},
+                          "us": {a: round(t * 1e3, 2) for a, t in best.items()},
+                          "tflops": {a: round(fl / (t * 1e-3) / 1e12, 1) for a, t in best.items()},
+                          "ours_over_best_reference": round(ref_best / best["ours"], 4),
+                          "max_abs_diff_vs_ours": diff, "steps": args.steps, "rounds": 3,
+                          "protocol": "back-to-back launches, no L2 flush, best of 3 interleaved rounds"}), flush=True)
+        del q, k, v, ids, outs
+
+
 def run_config(args):
     """Configurations 1, 3, 4, 5: indexer -> lists -> attention operator, stage by stage.
     With N > 1 ranks the (batch, KV-head) groups are dealt to the ranks (strong scaling, no
@@ -506,7 +572,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--kernel-only", action="store_true",
                     help="device-resident timing only (used for profiler captures): no e2e, no CPU baseline")
-    ap.add_argument("--workload", default="c2", choices=["c2", "kvtoken"] + sorted(CONFIGS),
+    ap.add_argument("--workload", default="c2", choices=["c2", "kvtoken", "refcmp"] + sorted(CONFIGS),
                     help="c2 (default) is the headline workload; c1/c3/c4/c5 run indexer + operator stage by stage")
     ap.add_argument("--kv-split", type=int, default=1, help="KV ranges per head shard (c5 only, needs --gpus >= 2)")
     ap.add_argument("--n", type=int, default=0, help="override the token count of c1/c3/c4/c5 (small profiler cases)")
@@ -516,6 +582,8 @@ def main():
         run_reference(args)
     elif args.workload == "kvtoken":
         run_kv_token(args)
+    elif args.workload == "refcmp":
+        run_refcmp(args)
     elif args.workload != "c2":
         run_config(args)
     else:

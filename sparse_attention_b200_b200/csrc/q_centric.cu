@@ -7,8 +7,9 @@
 //     and V tile is fetched once and used by both streams.
 //   * split mode (group size 1 or odd): two neighbouring query blocks of one
 //     head, each with its own list and its own K/V tiles.
-// Roles: warps 0-3 softmax of stream 0, warps 4-7 softmax of stream 1, warp 8
-// issues tcgen05 MMAs, warp 9 issues TMA loads. K/V tiles selected by block
+// Roles: warps 0-3 softmax of stream 0, warps 4-7 softmax of stream 1, one thread
+// of warp 8 issues tcgen05 MMAs (waits, issue and commits in a single thread keep
+// the P-ready -> MMA-issue latency short), warp 9 issues TMA loads. K/V tiles selected by block
 // index are gathered by TMA into a ring of 32 KiB shared-memory slots; S = QK^T
 // and O += PV accumulate in tensor memory (S0,S1,O0,O1 = 512 columns); P is
 // written back over S as packed bf16 and fed to the PV MMA straight from
@@ -301,7 +302,8 @@ q_centric_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
         if (qloads[q] > 0) mbar_wait_drain(bar(BAR_Q_FULL + q), (qloads[q] - 1) & 1);
     }
   } else if (warp == MMA_WARP) {
-    // ------------------------------------------------------------- MMA issuer
+    // ------------------------------------------------------------- MMA issuer (one thread)
+    if (lane == 0) {
     constexpr uint32_t IDESC_QK = idesc_bf16(TILE, TILE, false);
     constexpr uint32_t IDESC_PV = idesc_bf16(TILE, HEAD_DIM, true);
     uint32_t taken = 0;            // ring tiles consumed so far
@@ -314,14 +316,12 @@ q_centric_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
       bool w = mbar_wait(bar(BAR_KV_FULL + slot), (taken / RING) & 1, guard, 0x200 + slot);
       TRACE(23, static_cast<int>(taken));
       ++taken;
-      w = __all_sync(0xffffffffu, w);
       tc_fence_after();
       return w;
     };
     auto wait_q = [&](int q) -> bool {
       bool w = mbar_wait(bar(BAR_Q_FULL + q), qtaken[q] & 1, guard, 0x210 + q);
       ++qtaken[q];
-      w = __all_sync(0xffffffffu, w);
       tc_fence_after();
       return w;
     };
@@ -331,7 +331,6 @@ q_centric_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
       TRACE(20 + q, trace_p[q]);
       bool w = mbar_wait(bar(BAR_P_FULL + q), pphase[q], guard, 0x220 + q);
       pphase[q] ^= 1;
-      w = __all_sync(0xffffffffu, w);
       tc_fence_after();
       TRACE(16 + q, trace_p[q]);
       ++trace_p[q];
@@ -339,7 +338,7 @@ q_centric_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
     };
     // S_q = Q_q K^T : 8 MMAs of K = 16 over two 64-column panels.
     auto issue_qk = [&](int q, uint32_t slot) {
-      if (lane == 0) {
+      {
         const uint64_t a0 = desc_sw128_kmajor(base + OFF_Q + q * TILE_BYTES);
         const uint64_t b0 = desc_sw128_kmajor(base + OFF_RING + slot * TILE_BYTES);
 #pragma unroll
@@ -350,16 +349,22 @@ q_centric_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
       }
     };
     // O_q (+)= P_q V : A from tensor memory (8 columns per K = 16), B = V MN-major.
-    auto issue_pv = [&](int q, uint32_t slot, bool accumulate) {
-      if (lane == 0) {
+    auto issue_pv_part = [&](int q, uint32_t slot, bool accumulate, int k0, int k1) {
+      {
         const uint64_t b0 = desc_sw128_mnmajor(base + OFF_RING + slot * TILE_BYTES, PANEL_BYTES, 1024);
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)
-          mma_ts(tmem + 256 + q * HEAD_DIM, tmem + q * TILE + kk * 8,
-                 b0 + static_cast<uint64_t>(kk * (2048 >> 4)), IDESC_PV, (accumulate || kk > 0) ? 1u : 0u);
+          if (kk >= k0 && kk < k1)
+            mma_ts(tmem + 256 + q * HEAD_DIM, tmem + q * TILE + kk * 8,
+                   b0 + static_cast<uint64_t>(kk * (2048 >> 4)), IDESC_PV, (accumulate || kk > 0) ? 1u : 0u);
       }
     };
-    auto commit = [&](int b) { if (lane == 0) tc_commit(bar(b)); };
+    auto pv = [&](int q, uint32_t slot, bool accumulate) -> bool {
+      if (!wait_p(q)) return false;
+      issue_pv_part(q, slot, accumulate, 0, 8);
+      return true;
+    };
+    auto commit = [&](int b) { tc_commit(bar(b)); };
 
     bool primed[2] = {false, false};
     for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x) {
@@ -384,9 +389,8 @@ q_centric_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
         for (int i = 0; ok && i < n; ++i) {
           const bool more = i + 1 < n;
           const bool prime = !more && has_next && nx[0].count > 0;
-          ok = acquire(vslot) && wait_p(0);
+          ok = acquire(vslot) && pv(0, vslot, i > 0);
           if (!ok) break;
-          issue_pv(0, vslot, i > 0);
           if (more) {
             ok = acquire(kslot);
             if (!ok) break;
@@ -399,9 +403,8 @@ q_centric_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
               issue_qk(0, kslot); commit(BAR_S_FULL + 0);
             }
           }
-          ok = wait_p(1);
+          ok = pv(1, vslot, i > 0);
           if (!ok) break;
-          issue_pv(1, vslot, i > 0);
           commit(BAR_KV_EMPTY + vslot);
           if (more) {
             issue_qk(1, kslot); commit(BAR_S_FULL + 1);
@@ -434,9 +437,8 @@ q_centric_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
         for (int i = 0; ok && i < n; ++i)
           for (int q = 0; ok && q < 2; ++q)
             if (i < s[q].count) {
-              ok = acquire(vslot) && wait_p(q);
+              ok = acquire(vslot) && pv(q, vslot, i > 0);
               if (!ok) break;
-              issue_pv(q, vslot, i > 0);
               commit(BAR_KV_EMPTY + vslot);
               if (i + 1 < s[q].count) {
                 ok = acquire(kslot);
@@ -458,6 +460,8 @@ q_centric_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
             }
       }
     }
+    }
+    __syncwarp();
   } else {
     // ------------------------------------------------------------- softmax + epilogue
     const int q = warp >> 2;                       // stream
