@@ -7,14 +7,18 @@
 //     and V tile is fetched once and used by both streams.
 //   * split mode (group size 1 or odd): two neighbouring query blocks of one
 //     head, each with its own list and its own K/V tiles.
-// Roles: warps 0-3 softmax of stream 0, warps 4-7 softmax of stream 1, one thread
-// of warp 8 issues tcgen05 MMAs (waits, issue and commits in a single thread keep
-// the P-ready -> MMA-issue latency short), warp 9 issues TMA loads. K/V tiles selected by block
-// index are gathered by TMA into a ring of 32 KiB shared-memory slots; S = QK^T
-// and O += PV accumulate in tensor memory (S0,S1,O0,O1 = 512 columns); P is
-// written back over S as packed bf16 and fed to the PV MMA straight from
-// tensor memory. The ring, the Q buffers and all barriers stay live across
-// items, so loads of the next item overlap the tail of the current one.
+// Roles (four warpgroups, 512 threads): warps 0-3 softmax of stream 0, warps 4-7
+// softmax of stream 1, warps 8-11 epilogue (read O out of tensor memory, normalise,
+// TMA-store; the softmax warps go straight on to the next item), one thread of warp 12
+// issues tcgen05 MMAs (waits, issue and commits in a single thread keep the
+// P-ready -> MMA-issue latency short), warp 13 issues TMA loads. After the setup
+// barrier setmaxnreg moves registers from the last two warpgroups to the softmax warps.
+// K/V tiles selected by block index are gathered by TMA into a ring of 32 KiB
+// shared-memory slots; S = QK^T and O += PV accumulate in tensor memory
+// (S0,S1,O0,O1 = 512 columns); P is written back over S as packed bf16 and fed to the
+// PV MMA straight from tensor memory. The ring, the Q buffers and all barriers stay
+// live across items: the first QK of a stream's next item is issued right after its
+// last PV, and loads of the next item overlap the tail of the current one.
 //
 // Replaces the reference kernels dense14_sparse_two_q_kernel
 // (attention/q_centric/01_block_sparse.cu:181) and dense14_sparse_gqa_kernel
@@ -39,29 +43,40 @@ constexpr int PANEL_BYTES = TILE * 128;            // 64-column half of a tile
 #endif
 constexpr int RING = SB_QC_RING;     // K/V ring slots
 constexpr int POLY_PERIOD = SB_QC_POLY_PERIOD;   // one pair of exponentials in this many runs on the FMA pipe (0: none)
-constexpr int NUM_THREADS = 320;
-constexpr int MMA_WARP = 8;
-constexpr int LOAD_WARP = 9;
+constexpr int NUM_THREADS = 512;     // four warpgroups: softmax 0, softmax 1, epilogue, {MMA, TMA, 2 idle}
+constexpr int EPI_WARP0 = 8;         // warps 8..11: warp w serves tensor-memory lanes 32 * (w % 4) ..
+constexpr int MMA_WARP = 12;
+constexpr int LOAD_WARP = 13;
+// register budgets per thread after the setup barrier (setmaxnreg); 128 * (2 * 176 + 64 + 96) = 65536
+constexpr int SOFTMAX_REGS = 176;
+constexpr int EPI_REGS = 64;
+constexpr int CTRL_REGS = 96;        // MMA issuer, TMA producer, idle warps
 constexpr int TMEM_COLS = 512;
 constexpr float RESCALE_LOG2 = 8.0f;   // keep a stale row max while it lags by < 2^8
 
 // shared memory map (offsets from a 1024-aligned base)
 constexpr int OFF_Q = 0;
 constexpr int OFF_RING = 2 * TILE_BYTES;
-constexpr int OFF_STAGE = OFF_RING + RING * TILE_BYTES;   // 8 softmax warps x 4 KiB output staging
-constexpr int STAGE_BYTES = 4096;
-constexpr int OFF_BAR = OFF_STAGE + 8 * STAGE_BYTES;
+constexpr int OFF_STAGE = OFF_RING + RING * TILE_BYTES;   // 4 epilogue warps x 8 KiB output staging
+constexpr int STAGE_BYTES = 8192;
+constexpr int OFF_STATS = OFF_STAGE + 4 * STAGE_BYTES;    // [2 streams][128 rows] 1 / row sum
+constexpr int OFF_BAR = OFF_STATS + 2 * TILE * 4;
 // barrier indices (8 bytes each)
 constexpr int BAR_Q_FULL = 0;      // [2]
 constexpr int BAR_Q_EMPTY = 2;     // [2]
 constexpr int BAR_S_FULL = 4;      // [2]
 constexpr int BAR_P_FULL = 6;      // [2]
 constexpr int BAR_O_FULL = 8;      // [2]
-constexpr int BAR_KV_FULL = 10;    // [RING]
-constexpr int BAR_KV_EMPTY = 10 + RING;  // [RING]
-constexpr int NUM_BARS = 10 + 2 * RING;
-constexpr int OFF_MISC = OFF_BAR + NUM_BARS * 8;   // tmem base (4 B), abort flag (4 B)
-constexpr int SMEM_BYTES = OFF_MISC + 16 + 1024;   // + slack for manual 1024 alignment
+constexpr int BAR_STATS_FULL = 10; // [2] softmax -> epilogue: 1 / row sum of the item is in shared memory
+constexpr int BAR_O_EMPTY = 12;    // [2] epilogue -> MMA: O has been read out of tensor memory
+constexpr int BAR_STATS_EMPTY = 14; // [2] epilogue -> softmax: the previous item's 1 / row sum has been read
+constexpr int BAR_KV_FULL = 16;    // [RING]
+constexpr int BAR_KV_EMPTY = 16 + RING;  // [RING]
+constexpr int NUM_BARS = 16 + 2 * RING;
+constexpr int OFF_MISC = OFF_BAR + NUM_BARS * 8;   // tmem base (4 B), abort flag (4 B), 8 B unused, then one
+                                                   // hand-over counter per softmax warp (8 x 4 B)
+constexpr int SMEM_BYTES = OFF_MISC + 48 + 1024;   // + slack for manual 1024 alignment
+static_assert(SMEM_BYTES <= 227 * 1024, "shared memory map exceeds the per-CTA limit");
 
 #ifdef SB_QC_TRACE
 // Debug builds only: clock64 stamps of CTA 0 into the words after the status word.
@@ -140,6 +155,36 @@ __device__ __forceinline__ void decode_item(const Params& p, int item, Stream (&
   for (int q = 0; q < 2; ++q) s[q].count = min(max(s[q].count, 0), p.topk);
 }
 
+// Live list lengths of the two streams of an item: all the MMA issuer needs to know
+// (it keeps few registers so that its wait -> issue path stays free of spills).
+__device__ __forceinline__ void item_counts(const Params& p, int item, int (&cnt)[2]) {
+  const int seg = item / p.items_per_seg;
+  const int local = item - seg * p.items_per_seg;
+  if (p.pair_mode) {
+    int c = p.topk;
+    if (p.counts) {
+      const int t = local / (p.group >> 1);          // (batch * Hkv + kv head) * Qt + query tile
+      c = p.counts[static_cast<long long>(seg) * p.batch * p.hkv * p.qt + t];
+    }
+    cnt[0] = cnt[1] = min(max(c, 0), p.topk);
+  } else {
+    const int qpairs = (p.qt + 1) >> 1;
+    const int bh = local / qpairs;
+    const int qp = local - bh * qpairs;
+#pragma unroll
+    for (int q = 0; q < 2; ++q) {
+      const int qtile = 2 * qp + q;
+      int c = qtile < p.qt ? p.topk : 0;
+      if (p.counts && qtile < p.qt) {
+        const int b = bh / p.hq, head = bh - b * p.hq;
+        const int bk = b * p.hkv + head / p.group;
+        c = p.counts[(static_cast<long long>(seg) * p.batch * p.hkv + bk) * p.qt + qtile];
+      }
+      cnt[q] = min(max(c, 0), p.topk);
+    }
+  }
+}
+
 // One list cursor of the load warp: 32 ids cached across the lanes.
 struct IdCursor {
   int cached;
@@ -174,6 +219,9 @@ q_centric_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
       mbar_init(bar(BAR_S_FULL + i), 1);
       mbar_init(bar(BAR_P_FULL + i), 4);   // one arrival per softmax warp
       mbar_init(bar(BAR_O_FULL + i), 1);
+      mbar_init(bar(BAR_STATS_FULL + i), 4);
+      mbar_init(bar(BAR_O_EMPTY + i), 4);
+      mbar_init(bar(BAR_STATS_EMPTY + i), 4);
     }
     for (int i = 0; i < RING; ++i) {
       mbar_init(bar(BAR_KV_FULL + i), 1);
@@ -195,9 +243,13 @@ q_centric_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = static_cast<uint32_t>(misc[0]);
+  float* stats = reinterpret_cast<float*>(gbase + OFF_STATS);
   // tensor memory columns: S0 0..127, S1 128..255, O0 256..383, O1 384..511.
   // P (bf16 pairs) overwrites columns 0..63 of its S.
 
+  if (warp >= MMA_WARP) {
+  // fourth warpgroup: MMA issuer, TMA producer and two idle warps share one register budget
+  setmaxnreg_dec<CTRL_REGS>();
   if (warp == LOAD_WARP) {
     // ------------------------------------------------------------- TMA producer
     uint32_t fills = 0;            // tiles pushed into the ring so far
@@ -359,22 +411,30 @@ q_centric_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
                    b0 + static_cast<uint64_t>(kk * (2048 >> 4)), IDESC_PV, (accumulate || kk > 0) ? 1u : 0u);
       }
     };
+    uint32_t o_done[2] = {0, 0};   // items of each stream whose O went to the epilogue warps
     auto pv = [&](int q, uint32_t slot, bool accumulate) -> bool {
       if (!wait_p(q)) return false;
+      if (!accumulate && o_done[q] > 0) {
+        // the first PV of an item overwrites O: the previous item's O must have been read out
+        if (!mbar_wait(bar(BAR_O_EMPTY + q), (o_done[q] - 1) & 1, guard, 0x240 + q)) return false;
+        tc_fence_after();
+      }
       issue_pv_part(q, slot, accumulate, 0, 8);
       return true;
     };
+    auto commit_o = [&](int q) { tc_commit(bar(BAR_O_FULL + q)); ++o_done[q]; };
     auto commit = [&](int b) { tc_commit(bar(b)); };
 
     bool primed[2] = {false, false};
+    int cnt[2] = {0, 0}, ncnt[2] = {0, 0};
+    if (static_cast<int>(blockIdx.x) < p.num_items) item_counts(p, blockIdx.x, ncnt);
     for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x) {
-      Stream s[2], nx[2];
-      decode_item(p, item, s);
+      cnt[0] = ncnt[0]; cnt[1] = ncnt[1];
       const bool has_next = item + static_cast<int>(gridDim.x) < p.num_items;
-      if (has_next) decode_item(p, item + gridDim.x, nx);
+      if (has_next) item_counts(p, item + gridDim.x, ncnt);
       uint32_t kslot = 0, vslot = 0;
       if (p.pair_mode) {
-        const int n = s[0].count;
+        const int n = cnt[0];
         const bool was_primed = primed[0];
         primed[0] = primed[1] = false;
         if (n == 0) continue;
@@ -388,7 +448,7 @@ q_centric_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
         }
         for (int i = 0; ok && i < n; ++i) {
           const bool more = i + 1 < n;
-          const bool prime = !more && has_next && nx[0].count > 0;
+          const bool prime = !more && has_next && ncnt[0] > 0;
           ok = acquire(vslot) && pv(0, vslot, i > 0);
           if (!ok) break;
           if (more) {
@@ -396,7 +456,7 @@ q_centric_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
             if (!ok) break;
             issue_qk(0, kslot); commit(BAR_S_FULL + 0);
           } else {
-            commit(BAR_O_FULL + 0);
+            commit_o(0);
             if (prime) {              // first QK of the next item, stream 0
               ok = wait_q(0) && acquire(kslot);
               if (!ok) break;
@@ -411,13 +471,13 @@ q_centric_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
             commit(BAR_KV_EMPTY + kslot);
             if (i + 2 == n) { commit(BAR_Q_EMPTY + 0); commit(BAR_Q_EMPTY + 1); }
           } else {
-            commit(BAR_O_FULL + 1);
+            commit_o(1);
             if (prime) {              // and stream 1, same K tile
               ok = wait_q(1);
               if (!ok) break;
               issue_qk(1, kslot); commit(BAR_S_FULL + 1);
               commit(BAR_KV_EMPTY + kslot);
-              if (nx[0].count == 1) { commit(BAR_Q_EMPTY + 0); commit(BAR_Q_EMPTY + 1); }
+              if (ncnt[0] == 1) { commit(BAR_Q_EMPTY + 0); commit(BAR_Q_EMPTY + 1); }
               primed[0] = primed[1] = true;
             }
           }
@@ -426,34 +486,34 @@ q_centric_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
         bool was_primed[2] = {primed[0], primed[1]};
         primed[0] = primed[1] = false;
         for (int q = 0; ok && q < 2; ++q)
-          if (s[q].count > 0 && !was_primed[q]) {
+          if (cnt[q] > 0 && !was_primed[q]) {
             ok = wait_q(q) && acquire(kslot);
             if (!ok) break;
             issue_qk(q, kslot); commit(BAR_S_FULL + q);
             commit(BAR_KV_EMPTY + kslot);
-            if (s[q].count == 1) commit(BAR_Q_EMPTY + q);
+            if (cnt[q] == 1) commit(BAR_Q_EMPTY + q);
           }
-        const int n = max(s[0].count, s[1].count);
+        const int n = max(cnt[0], cnt[1]);
         for (int i = 0; ok && i < n; ++i)
           for (int q = 0; ok && q < 2; ++q)
-            if (i < s[q].count) {
+            if (i < cnt[q]) {
               ok = acquire(vslot) && pv(q, vslot, i > 0);
               if (!ok) break;
               commit(BAR_KV_EMPTY + vslot);
-              if (i + 1 < s[q].count) {
+              if (i + 1 < cnt[q]) {
                 ok = acquire(kslot);
                 if (!ok) break;
                 issue_qk(q, kslot); commit(BAR_S_FULL + q);
                 commit(BAR_KV_EMPTY + kslot);
-                if (i + 2 == s[q].count) commit(BAR_Q_EMPTY + q);
+                if (i + 2 == cnt[q]) commit(BAR_Q_EMPTY + q);
               } else {
-                commit(BAR_O_FULL + q);
-                if (has_next && nx[q].count > 0) {     // first QK of this stream's next item
+                commit_o(q);
+                if (has_next && ncnt[q] > 0) {     // first QK of this stream's next item
                   ok = wait_q(q) && acquire(kslot);
                   if (!ok) break;
                   issue_qk(q, kslot); commit(BAR_S_FULL + q);
                   commit(BAR_KV_EMPTY + kslot);
-                  if (nx[q].count == 1) commit(BAR_Q_EMPTY + q);
+                  if (ncnt[q] == 1) commit(BAR_Q_EMPTY + q);
                   primed[q] = true;
                 }
               }
@@ -462,14 +522,21 @@ q_centric_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
     }
     }
     __syncwarp();
-  } else {
-    // ------------------------------------------------------------- softmax + epilogue
+  }
+  } else if (warp < EPI_WARP0) {
+    // ------------------------------------------------------------- softmax
+    setmaxnreg_inc<SOFTMAX_REGS>();
     const int q = warp >> 2;                       // stream
     const int row_in_tile = (warp & 3) * 32 + lane;
     const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const uint32_t t_s = tmem + lane_base + q * TILE;
     const uint32_t t_o = tmem + lane_base + 256 + q * HEAD_DIM;
-    uint32_t sphase = 0, ophase = 0;
+    uint32_t sphase = 0;
+    // items of this stream handed to the epilogue warps so far: kept in shared memory, it is
+    // touched once per item and would otherwise occupy a register across the softmax loop
+    volatile int* handed_ptr = misc + 4 + warp;
+    if (lane == 0) *handed_ptr = 0;
+    __syncwarp();
     bool ok = true;
     int trace_n = 0;
     (void)trace_n;
@@ -577,40 +644,92 @@ q_centric_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
         ++trace_n;
       }
       if (!ok) break;
-      {
-        bool w = mbar_wait(bar(BAR_O_FULL + q), ophase, guard, 0x310 + q);
-        ophase ^= 1;
+      // Hand the row statistics to the epilogue warps and go on to the next item. A list of
+      // one block ends before its PV has been issued, so nothing else orders this write
+      // after the epilogue of the stream's previous item: wait for its release.
+      const int handed = *handed_ptr;
+      if (handed > 0) {
+        bool w = mbar_wait(bar(BAR_STATS_EMPTY + q), (handed - 1) & 1, guard, 0x320 + q);
+        ok = __all_sync(0xffffffffu, w);
+        if (!ok) break;
+      }
+      __syncwarp();
+      if (lane == 0) *handed_ptr = handed + 1;
+      stats[q * TILE + row_in_tile] = 1.0f / row_sum;
+      if (p.lse) p.lse[orow] = (row_max + log2f(row_sum)) * 0.6931471805599453f;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(BAR_STATS_FULL + q));
+    }
+  } else {
+    // ------------------------------------------------------------- epilogue warps
+    setmaxnreg_dec<EPI_REGS>();
+    // Warp w reads tensor-memory lanes 32 * (w % 4) .. + 31 of O0 and O1: normalise, stage
+    // in shared memory in the 128-byte-swizzled box layout, let TMA write the rows out.
+    const int quarter = warp & 3;
+    const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
+    const uint32_t stage = base + OFF_STAGE + quarter * STAGE_BYTES;
+    unsigned char* stage_g = gbase + OFF_STAGE + quarter * STAGE_BYTES;
+    uint32_t done[2] = {0, 0};
+    bool ok = true;
+    for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x) {
+      Stream s[2];
+      decode_item(p, item, s);
+#pragma unroll 1
+      for (int q = 0; ok && q < 2; ++q) {
+        const Stream& me = s[q];
+        if (!me.valid || me.count == 0) continue;
+        const uint32_t t_o = tmem + lane_base + 256 + q * HEAD_DIM;
+        bool w = mbar_wait(bar(BAR_STATS_FULL + q), done[q] & 1, guard, 0x400 + q);
+        w = mbar_wait(bar(BAR_O_FULL + q), done[q] & 1, guard, 0x410 + q) && w;
+        ++done[q];
         ok = __all_sync(0xffffffffu, w);
         if (!ok) break;
         tc_fence_after();
-      }
-      // Epilogue: normalise this warp's 32 rows, stage them in shared memory in the
-      // 128-byte-swizzled box layout and let TMA write them out asynchronously
-      // (a direct store would scatter 16-byte pieces over 32 rows per instruction).
-      const float inv = 1.0f / row_sum;
-      const uint32_t stage = base + OFF_STAGE + warp * STAGE_BYTES;
-      unsigned char* stage_g = gbase + OFF_STAGE + warp * STAGE_BYTES;
-      const int out_row32 = static_cast<int>(me.out_row) + (warp & 3) * 32;
-      constexpr int PASSES = OUT_F32 ? 4 : 2;        // 128 bytes of a row per pass
-#pragma unroll 1
-      for (int pass = 0; pass < PASSES; ++pass) {
-        if (lane == 0) bulk_wait_read0();            // the previous store has left the staging tile
+        if (quarter == 0) TRACE(q * 8 + 5, static_cast<int>(done[q]));
+        const float inv = stats[q * TILE + quarter * 32 + lane];
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(BAR_STATS_EMPTY + q));
+        const int out_row32 = static_cast<int>(me.out_row) + quarter * 32;
+        if (lane == 0) bulk_wait_read0();            // earlier stores have left the staging tile
         __syncwarp();
         if (OUT_F32) {
-          uint32_t ov[32];
-          tmem_ld32(t_o + pass * 32, ov);
-          tc_wait_ld();
+          // 512 bytes per row: two rounds of two 128-byte boxes
+#pragma unroll 1
+          for (int half = 0; half < 2; ++half) {
+            if (half == 1) {
+              if (lane == 0) bulk_wait_read0();
+              __syncwarp();
+            }
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const float4 val = make_float4(__uint_as_float(ov[4 * j]) * inv, __uint_as_float(ov[4 * j + 1]) * inv,
-                                           __uint_as_float(ov[4 * j + 2]) * inv, __uint_as_float(ov[4 * j + 3]) * inv);
-            *reinterpret_cast<float4*>(stage_g + lane * 128 + ((j ^ (lane & 7)) << 4)) = val;
+            for (int cc = 0; cc < 2; ++cc) {
+              uint32_t ov[32];
+              tmem_ld32(t_o + half * 64 + cc * 32, ov);
+              tc_wait_ld();
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                const float4 val = make_float4(__uint_as_float(ov[4 * j]) * inv, __uint_as_float(ov[4 * j + 1]) * inv,
+                                               __uint_as_float(ov[4 * j + 2]) * inv, __uint_as_float(ov[4 * j + 3]) * inv);
+                *reinterpret_cast<float4*>(stage_g + cc * 4096 + lane * 128 + ((j ^ (lane & 7)) << 4)) = val;
+              }
+            }
+            if (half == 1) {
+              tc_fence_before();
+              __syncwarp();
+              if (lane == 0) mbar_arrive(bar(BAR_O_EMPTY + q));
+            }
+            fence_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              tma_store_2d(&o_map, half * 64, out_row32, stage);
+              tma_store_2d(&o_map, half * 64 + 32, out_row32, stage + 4096);
+              bulk_commit();
+            }
           }
         } else {
 #pragma unroll
-          for (int cc = 0; cc < 2; ++cc) {
+          for (int cc = 0; cc < 4; ++cc) {
             uint32_t ov[32];
-            tmem_ld32(t_o + pass * 64 + cc * 32, ov);
+            tmem_ld32(t_o + cc * 32, ov);
             tc_wait_ld();
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
@@ -619,24 +738,28 @@ q_centric_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
                   pack_bf16x2(__uint_as_float(ov[8 * j + 2]) * inv, __uint_as_float(ov[8 * j + 3]) * inv),
                   pack_bf16x2(__uint_as_float(ov[8 * j + 4]) * inv, __uint_as_float(ov[8 * j + 5]) * inv),
                   pack_bf16x2(__uint_as_float(ov[8 * j + 6]) * inv, __uint_as_float(ov[8 * j + 7]) * inv));
-              *reinterpret_cast<uint4*>(stage_g + lane * 128 + (((cc * 4 + j) ^ (lane & 7)) << 4)) = val;
+              *reinterpret_cast<uint4*>(stage_g + (cc >> 1) * 4096 + lane * 128 +
+                                        ((((cc & 1) * 4 + j) ^ (lane & 7)) << 4)) = val;
             }
           }
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar(BAR_O_EMPTY + q));
+          fence_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_2d(&o_map, 0, out_row32, stage);
+            tma_store_2d(&o_map, 64, out_row32, stage + 4096);
+            bulk_commit();
+          }
         }
-        fence_async_smem();
-        __syncwarp();
-        if (lane == 0) {
-          tma_store_2d(&o_map, pass * (OUT_F32 ? 32 : 64), out_row32, stage);
-          bulk_commit();
-        }
+        if (quarter == 0) TRACE(q * 8 + 6, static_cast<int>(done[q]));
       }
-      if (p.lse) p.lse[orow] = (row_max + log2f(row_sum)) * 0.6931471805599453f;
-      tc_fence_before();
     }
+    if (lane == 0) bulk_wait_all();      // output stores of this warp have completed
   }
 
   // ---------------------------------------------------------------- teardown
-  if (warp < 8 && lane == 0) bulk_wait_all();      // output stores of this warp have completed
   tc_fence_before();
   __syncthreads();
   if (warp == MMA_WARP) {

@@ -174,3 +174,28 @@ def test_counts_and_out_of_range_flag():
     p.metadata()
     with pytest.raises(ValueError):
         p.audit()
+
+
+@pytest.mark.parametrize("hq,hkv,partial", [(32, 32, "f32"), (32, 32, "bf16"), (16, 4, "f32")])
+def test_many_items_per_cta_with_short_segment_lists(hq, hkv, partial):
+    """More work items than SMs and segment lists of 0, 1, 2 ... blocks in a row: every
+    persistent CTA walks several items whose streams end after different tile counts
+    (a one-block list ends before its PV has been issued). Split + merge must equal the
+    unsplit kernel and no bounded wait may give up."""
+    m = sp()
+    b, n, topk = 1, 4096, 16
+    g = torch.Generator(device="cuda").manual_seed(17)
+    q = torch.randn((b, hq, n, 128), device="cuda", generator=g).to(torch.bfloat16)
+    k = torch.randn((b, hkv, n, 128), device="cuda", generator=g).to(torch.bfloat16)
+    v = torch.randn((b, hkv, n, 128), device="cuda", generator=g).to(torch.bfloat16)
+    nb = n // 128
+    ids = torch.rand((b * hkv * nb, nb), device="cuda", generator=g).argsort(-1)[:, :topk].sort(-1).values \
+        .int().reshape(b, hkv, nb, topk).contiguous()
+    out, lse = m.attention(q, k, v, ids, return_lse=True)
+    torch.cuda.synchronize()
+    m.device_status()
+    o2, l2 = m.kv_centric_attention(q, k, v, ids, nseg=4, partial=partial)
+    torch.cuda.synchronize()
+    m.device_status()
+    assert (o2.float() - out.float()).abs().max().item() <= 2e-2
+    assert torch.all((l2 - lse).abs() <= 1e-3 * lse.abs().clamp_min(1.0))
