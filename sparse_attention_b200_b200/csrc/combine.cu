@@ -1,7 +1,8 @@
 // Log-sum-exp merge of partial (O, LSE): HBM-bound streaming kernel.
 //   m = max_r L_r, w_r = exp(L_r - m), O = sum_r w_r O_r / sum_r w_r,
 //   LSE = m + log(sum_r w_r)            (ranks accumulated in order 0..R-1)
-// Half a warp per output row, eight features per lane. Partials may be fp32 or
+// Half a warp per output row, eight features per lane, a whole batch of ranks in
+// flight per lane. Partials may be fp32 or
 // bf16 and are addressed with strides, so both the rank-major layout
 // [R, rows, 128] written by the segment kernel and the rank-inner layout
 // [rows, R, 128] of the reference are accepted.
@@ -14,91 +15,109 @@
 namespace sb {
 namespace {
 
-// eight consecutive features of one partial row as fp32
+// eight consecutive features of one partial row, kept raw until the weights are known
 template <typename T>
-__device__ __forceinline__ void load8(const T* p, float (&f)[8]);
+struct Raw8;
 template <>
-__device__ __forceinline__ void load8<float>(const float* p, float (&f)[8]) {
-  const float4 a = __ldcs(reinterpret_cast<const float4*>(p));
-  const float4 b = __ldcs(reinterpret_cast<const float4*>(p) + 1);
-  f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
-}
-template <>
-__device__ __forceinline__ void load8<__nv_bfloat16>(const __nv_bfloat16* p, float (&f)[8]) {
-  const uint4 raw = __ldcs(reinterpret_cast<const uint4*>(p));
-  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
-#pragma unroll
-  for (int e = 0; e < 4; ++e) {
-    const float2 v = __bfloat1622float2(h[e]);
-    f[2 * e] = v.x;
-    f[2 * e + 1] = v.y;
+struct Raw8<float> {
+  float4 a, b;
+  __device__ __forceinline__ void load(const float* p) {
+    a = __ldcs(reinterpret_cast<const float4*>(p));
+    b = __ldcs(reinterpret_cast<const float4*>(p) + 1);
   }
-}
+  __device__ __forceinline__ void unpack(float (&f)[8]) const {
+    f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+  }
+  static constexpr int BATCH = 8;      // ranks in flight per lane (64 registers)
+};
+template <>
+struct Raw8<__nv_bfloat16> {
+  uint4 raw;
+  __device__ __forceinline__ void load(const __nv_bfloat16* p) { raw = __ldcs(reinterpret_cast<const uint4*>(p)); }
+  __device__ __forceinline__ void unpack(float (&f)[8]) const {
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 v = __bfloat1622float2(h[e]);
+      f[2 * e] = v.x;
+      f[2 * e + 1] = v.y;
+    }
+  }
+  static constexpr int BATCH = 16;
+};
 
-// Half a warp (16 lanes x 8 features) per output row. The partial rows of up to
-// four ranks are requested before the weights are known, so the two dependent
-// memory round trips (LSE, then partials) overlap; a rank of weight 0 is then
-// dropped with a select, whatever it holds.
+// Half a warp (16 lanes x 8 features) per output row. The raw partial rows of a whole
+// batch of ranks (16 for bf16, 8 for fp32) are requested first; the LSEs of the row are
+// fetched one rank per lane (coalesced) and reduced with shuffles while those loads are
+// in flight, so a row costs one memory round trip per batch instead of several dependent
+// ones. A rank of weight 0 is dropped with a select, whatever it holds.
 template <typename T>
 __global__ void __launch_bounds__(256) combine_kernel(const T* __restrict__ partial, const float* __restrict__ lses,
                                                       __nv_bfloat16* __restrict__ out, float* __restrict__ out_lse,
                                                       long long rows, int ranks, long long p_stride_rank,
                                                       long long p_stride_row, long long l_stride_rank,
                                                       long long l_stride_row) {
+  constexpr int BATCH = Raw8<T>::BATCH;
   const int sub = threadIdx.x & 15;
+  const unsigned half_mask = 0xffffu << (threadIdx.x & 16);
   const long long halves_total = static_cast<long long>(gridDim.x) * (blockDim.x >> 4);
-  for (long long row = static_cast<long long>(blockIdx.x) * (blockDim.x >> 4) + (threadIdx.x >> 4); row < rows;
-       row += halves_total) {
+  const long long first = static_cast<long long>(blockIdx.x) * (blockDim.x >> 4) + (threadIdx.x >> 4);
+  // every lane of a warp runs the same number of iterations (the shuffles need both halves)
+  const long long iters = (rows + halves_total - 1) / halves_total;
+  for (long long it = 0; it < iters; ++it) {
+    const long long row_raw = first + it * halves_total;
+    const bool live = row_raw < rows;
+    const long long row = live ? row_raw : rows - 1;
     const T* base = partial + row * p_stride_row + sub * 8;
     const float* lbase = lses + row * l_stride_row;
     float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
     float denom = 0.f;
-    // Requests first, arithmetic later: the partial rows of the first four ranks and
-    // every rank's LSE (a broadcast within the half warp) are all in flight together.
-    float val[4][8];
+    Raw8<T> val[BATCH];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      if (j < ranks) {
-        load8<T>(base + j * p_stride_rank, val[j]);
-      } else {
-#pragma unroll
-        for (int e = 0; e < 8; ++e) val[j][e] = 0.f;
-      }
-    }
+    for (int j = 0; j < BATCH; ++j)
+      if (j < ranks) val[j].load(base + j * p_stride_rank);
+    // row maximum of the LSEs: lane `sub` takes ranks sub, sub + 16, ...
     float maximum = -CUDART_INF_F;
-    for (int r = 0; r < ranks; ++r) maximum = fmaxf(maximum, __ldg(lbase + r * l_stride_rank));
-    if (maximum > -CUDART_INF_F) {
-      for (int r0 = 0; r0 < ranks; r0 += 4) {
-        float wgt[4];
+    for (int r = sub; r < ranks; r += 16) maximum = fmaxf(maximum, __ldg(lbase + r * l_stride_rank));
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          if (r0 + j < ranks) {
-            if (r0 > 0) load8<T>(base + (r0 + j) * p_stride_rank, val[j]);
-            wgt[j] = expf(__ldg(lbase + (r0 + j) * l_stride_rank) - maximum);   // exp(-inf) = 0
-          } else {
-            wgt[j] = 0.f;
-          }
+    for (int d = 8; d >= 1; d >>= 1) maximum = fmaxf(maximum, __shfl_xor_sync(0xffffffffu, maximum, d));
+    if (maximum > -CUDART_INF_F) {            // uniform within the half warp
+      for (int r0 = 0; r0 < ranks; r0 += BATCH) {
+        if (r0 > 0) {
+#pragma unroll
+          for (int j = 0; j < BATCH; ++j)
+            if (r0 + j < ranks) val[j].load(base + (r0 + j) * p_stride_rank);
         }
+        // weight of rank r0 + (sub % BATCH) in this lane (ranks of a batch sit in lanes 0..BATCH-1)
+        float mine = 0.f;
+        if (sub < BATCH && r0 + sub < ranks) mine = expf(__ldg(lbase + (r0 + sub) * l_stride_rank) - maximum);
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          denom += wgt[j];
+        for (int j = 0; j < BATCH; ++j) {
+          const float w = __shfl_sync(half_mask, mine, (threadIdx.x & 16) + j);   // exp(-inf) = 0
+          if (r0 + j < ranks) {
+            float f[8];
+            val[j].unpack(f);
+            denom += w;
 #pragma unroll
-          for (int e = 0; e < 8; ++e) acc[e] = fmaf(wgt[j], wgt[j] > 0.f ? val[j][e] : 0.f, acc[e]);
+            for (int e = 0; e < 8; ++e) acc[e] = fmaf(w, w > 0.f ? f[e] : 0.f, acc[e]);
+          }
         }
       }
       const float inv = 1.0f / denom;
 #pragma unroll
       for (int e = 0; e < 8; ++e) acc[e] *= inv;
     }
-    uint4 packed;
-    uint32_t* pw = reinterpret_cast<uint32_t*>(&packed);
+    if (live) {
+      uint4 packed;
+      uint32_t* pw = reinterpret_cast<uint32_t*>(&packed);
 #pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      __nv_bfloat162 h = __floats2bfloat162_rn(acc[2 * e], acc[2 * e + 1]);
-      pw[e] = *reinterpret_cast<uint32_t*>(&h);
+      for (int e = 0; e < 4; ++e) {
+        __nv_bfloat162 h = __floats2bfloat162_rn(acc[2 * e], acc[2 * e + 1]);
+        pw[e] = *reinterpret_cast<uint32_t*>(&h);
+      }
+      *reinterpret_cast<uint4*>(out + row * 128 + sub * 8) = packed;
+      if (sub == 0 && out_lse) out_lse[row] = (maximum > -CUDART_INF_F) ? maximum + logf(denom) : -CUDART_INF_F;
     }
-    *reinterpret_cast<uint4*>(out + row * 128 + sub * 8) = packed;
-    if (sub == 0 && out_lse) out_lse[row] = (maximum > -CUDART_INF_F) ? maximum + logf(denom) : -CUDART_INF_F;
   }
 }
 

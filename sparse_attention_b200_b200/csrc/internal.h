@@ -57,6 +57,9 @@ int launch_token_metadata(const int32_t* selected, int32_t* counts, int32_t* cur
 int launch_kv_token_main(const void* q, const void* k, const void* v, const int32_t* tasks, const int32_t* task_count,
                          const int32_t* qids, const int32_t* ranks, void* partial, float* lses, int batch, int hq,
                          int hkv, int sq, int skv, int topk, cudaStream_t stream);
+int launch_kv_token_pipe(const void* q, const void* k, const void* v, const int32_t* tasks, const int32_t* task_count,
+                         const int32_t* qids, const int32_t* ranks, void* partial, float* lses, int batch, int hq,
+                         int hkv, int sq, int skv, int topk, cudaStream_t stream);
 int launch_quantize(const void* x, void* packed, void* scales, int batch, int heads_out, int group, int seq,
                     int paged, cudaStream_t stream);
 int launch_fp4_scores(const void* qp, const void* qs, const void* kp, const void* ks, float* query_scores,

@@ -251,9 +251,14 @@ int launch_kv_token_main(const void* q, const void* k, const void* v, const int3
                          const int32_t* qids, const int32_t* ranks, void* partial, float* lses, int batch, int hq,
                          int hkv, int sq, int skv, int topk, cudaStream_t stream) {
   using namespace kvt;
+  const int group = hq / hkv;
+  // groups of 8 or 16 heads take the pipelined kernel (kv_token_pipe.cu); this one serves
+  // the smaller groups, whose Q rows cannot be fetched as 1024-byte-aligned TMA boxes
+  if (group == 8 || group == 16)
+    return launch_kv_token_pipe(q, k, v, tasks, task_count, qids, ranks, partial, lses, batch, hq, hkv, sq, skv, topk,
+                                stream);
   DeviceCtx* ctx = device_ctx();
   if (!ctx) return SB_ERR_CUDA;
-  const int group = hq / hkv;
   Params p{};
   p.q = static_cast<const __nv_bfloat16*>(q);
   p.tasks = tasks; p.task_count = task_count; p.qids = qids; p.ranks = ranks;

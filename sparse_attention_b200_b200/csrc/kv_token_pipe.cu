@@ -1,0 +1,477 @@
+// KV-centric attention for per-TOKEN selection lists, pipelined variant for GQA groups of
+// 8 or 16 query heads per KV head (the reference's KV-centric contract is Hq16 / Hkv1).
+//
+// A task = (KV-head group, KV block, up to 128/G queries that selected the block); its
+// 128-row Q tile is the G heads of each of those queries. One persistent CTA per SM walks
+// a contiguous range of the task list (tasks are ordered by (group, block), so a CTA
+// reloads K/V two or three times in all) and keeps TWO tasks in flight, one per stream:
+//   warp 13      TMA producer: K/V block into one of two 64 KiB buffers when the block
+//                changes; per query one 3-D box {64 columns, 1 token, G heads} of Q per
+//                64-column panel, straight into the 128-byte-swizzled operand tile
+//   warp 12      one thread issues QK(j), then PV(j-1) of the other stream (tcgen05, TMEM)
+//   warps 0-3 / 4-7   softmax of stream 0 / 1 over the single block, P (bf16) back into S,
+//                1/row-sum to shared memory, LSE to global memory
+//   warps 8-11   epilogue: O out of tensor memory, normalise, stage, and one 4-D TMA store
+//                {64 columns, 1 rank, 1 token, G heads} per query and panel into the partial
+//                slot (query, rank) the selection list gave the block
+// Same computation as kv_tma11_ops::main_kernel
+// (attention/kv_centric/optimization_round11/tma11_kernel.cu:97-390) for any TopK, with q
+// head-major [B,Hq,Sq,128], partials [B,Hq,Sq,TopK,128] bf16 and LSE [B,Hq,Sq,TopK].
+// Rows of a tile beyond the task's query count keep whatever the buffer held: every row
+// of S, P and O depends on its own Q row only, and those rows are never stored.
+#include "ptx.cuh"
+#include "internal.h"
+
+namespace sb {
+namespace kvp {
+
+constexpr int TILE_BYTES = 128 * 256;
+constexpr int PANEL_BYTES = 128 * 128;
+constexpr int NUM_THREADS = 512;
+constexpr int EPI_WARP0 = 8;
+constexpr int MMA_WARP = 12;
+constexpr int LOAD_WARP = 13;
+// register budgets per thread after the setup barrier: 128 * (2 * 176 + 64 + 96) = 65536
+constexpr int SOFTMAX_REGS = 176;
+constexpr int EPI_REGS = 64;
+constexpr int CTRL_REGS = 96;
+
+constexpr int OFF_Q = 0;                               // [2 streams] Q tiles
+constexpr int OFF_KV = 2 * TILE_BYTES;                 // [2 buffers] K tile, V tile
+constexpr int OFF_STAGE = OFF_KV + 4 * TILE_BYTES;     // 4 epilogue warps x 8 KiB
+constexpr int STAGE_BYTES = 8192;
+constexpr int OFF_STATS = OFF_STAGE + 4 * STAGE_BYTES; // [2 streams][128 rows] 1 / row sum
+constexpr int OFF_BAR = OFF_STATS + 2 * 128 * 4;
+enum {
+  Q_FULL = 0, Q_EMPTY = 2, S_FULL = 4, P_FULL = 6, O_FULL = 8, O_EMPTY = 10, STATS_FULL = 12, STATS_EMPTY = 14,
+  KV_FULL = 16, KV_EMPTY = 18, NUM_BARS = 20
+};
+constexpr int OFF_MISC = OFF_BAR + NUM_BARS * 8;       // tmem base, abort flag
+constexpr int SMEM_BYTES = OFF_MISC + 16 + 1024;       // + slack for manual 1024 alignment
+static_assert(SMEM_BYTES <= 227 * 1024, "shared memory map exceeds the per-CTA limit");
+
+struct Params {
+  const int32_t* tasks;         // [T, 4] (group, block, first edge, count)
+  const int32_t* task_count;    // number of tasks (device memory)
+  const int32_t* qids;
+  const int32_t* ranks;
+  float* lses;                  // [B, Hq, Sq, TopK]
+  int* status;
+  int batch, hq, hkv, sq, skv, topk, group, group_log2, edges;
+  float scale_log2;
+};
+
+struct Task {
+  int group, block, start, count;
+  bool valid;
+};
+
+__device__ __forceinline__ Task read_task(const Params& p, int t) {
+  const int4 raw = *reinterpret_cast<const int4*>(p.tasks + static_cast<long long>(t) * 4);
+  Task k;
+  k.group = raw.x; k.block = raw.y; k.start = raw.z; k.count = raw.w;
+  k.valid = k.group >= 0 && k.group < p.batch * p.hkv && k.block >= 0 && k.block < p.skv / 128 && k.start >= 0 &&
+            k.count > 0 && k.count <= (128 >> p.group_log2) && static_cast<long long>(k.start) + k.count <= p.edges;
+  return k;
+}
+
+// 3-D tile load {x, y, z}
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int x, int y, int z, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%2, %3, %4}], [%5];" ::"r"(dst),
+      "l"(map), "r"(x), "r"(y), "r"(z), "r"(bar)
+      : "memory");
+}
+// 4-D tile store {x, y, z, w}; no coordinate may be negative
+__device__ __forceinline__ void tma_store_4d(const CUtensorMap* map, int x, int y, int z, int w, uint32_t src) {
+  asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%1, %2, %3, %4}], [%5];" ::"l"(map),
+               "r"(x), "r"(y), "r"(z), "r"(w), "r"(src)
+               : "memory");
+}
+
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+kv_token_pipe_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
+                     const __grid_constant__ CUtensorMap v_map, const __grid_constant__ CUtensorMap o_map,
+                     const Params p) {
+  extern __shared__ unsigned char smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  unsigned char* gbase = smem_raw + (base - raw);
+  const uint32_t bar0 = base + OFF_BAR;
+  volatile int* misc = reinterpret_cast<volatile int*>(gbase + OFF_MISC);
+  float* stats = reinterpret_cast<float*>(gbase + OFF_STATS);
+  auto bar = [&](int i) { return bar0 + 8u * i; };
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  Guard guard{misc + 1, p.status};
+
+  if (threadIdx.x == 0) {
+    misc[1] = 0;
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(bar(Q_FULL + i), 1);
+      mbar_init(bar(Q_EMPTY + i), 1);
+      mbar_init(bar(S_FULL + i), 1);
+      mbar_init(bar(P_FULL + i), 4);
+      mbar_init(bar(O_FULL + i), 1);
+      mbar_init(bar(O_EMPTY + i), 4);
+      mbar_init(bar(STATS_FULL + i), 4);
+      mbar_init(bar(STATS_EMPTY + i), 4);
+      mbar_init(bar(KV_FULL + i), 1);
+      mbar_init(bar(KV_EMPTY + i), 1);
+    }
+    fence_mbar_init();
+  }
+  if (warp == MMA_WARP) {
+    tmem_alloc(smem_u32(const_cast<int*>(misc)), 512);
+    tmem_relinquish();
+  }
+  if (warp == LOAD_WARP && lane == 0) {
+    prefetch_tmap(&q_map);
+    prefetch_tmap(&k_map);
+    prefetch_tmap(&v_map);
+    prefetch_tmap(&o_map);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = static_cast<uint32_t>(misc[0]);
+  // tensor memory columns: S0 0..127, S1 128..255, O0 256..383, O1 384..511; P over S.
+
+  const int total = *p.task_count;
+  const int per_cta = (total + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x);
+  const int t_begin = blockIdx.x * per_cta, t_end = min(total, t_begin + per_cta);
+  const int G = p.group;
+
+  if (warp >= MMA_WARP) {
+  setmaxnreg_dec<CTRL_REGS>();
+  if (warp == LOAD_WARP) {
+    // ------------------------------------------------------------- TMA producer
+    uint32_t n = 0;                 // valid tasks so far
+    int loads = 0;                  // K/V block loads so far
+    int cur_group = -1, cur_block = -1;
+    bool ok = true;
+    for (int t = t_begin; ok && t < t_end; ++t) {
+      const Task k = read_task(p, t);
+      if (!k.valid) continue;
+      const uint32_t s = n & 1, u = n >> 1;
+      ++n;
+      if (k.group != cur_group || k.block != cur_block) {
+        cur_group = k.group; cur_block = k.block;
+        const int buf = loads & 1, use = loads >> 1;
+        ++loads;
+        if (use > 0) {
+          bool w = mbar_wait(bar(KV_EMPTY + buf), (use - 1) & 1, guard, 0x700 + buf);
+          ok = __all_sync(0xffffffffu, w);
+          if (!ok) break;
+        }
+        if (lane == 0) {
+          const int kv_row = k.group * p.skv + k.block * 128;
+          const uint32_t dst = base + OFF_KV + buf * 2 * TILE_BYTES;
+          mbar_expect_tx(bar(KV_FULL + buf), 2 * TILE_BYTES);
+          tma_load_2d(dst, &k_map, 0, kv_row, bar(KV_FULL + buf));
+          tma_load_2d(dst + PANEL_BYTES, &k_map, 64, kv_row, bar(KV_FULL + buf));
+          tma_load_2d(dst + TILE_BYTES, &v_map, 0, kv_row, bar(KV_FULL + buf));
+          tma_load_2d(dst + TILE_BYTES + PANEL_BYTES, &v_map, 64, kv_row, bar(KV_FULL + buf));
+        }
+      }
+      if (u > 0) {
+        bool w = mbar_wait(bar(Q_EMPTY + s), (u - 1) & 1, guard, 0x710 + s);
+        ok = __all_sync(0xffffffffu, w);
+        if (!ok) break;
+      }
+      // lane tl fetches query tl of the task
+      int qi = -1;
+      if (lane < k.count) {
+        qi = p.qids[k.start + lane];
+        if (qi < 0 || qi >= p.sq) qi = -1;
+      }
+      const unsigned live = __ballot_sync(0xffffffffu, qi >= 0);
+      if (lane == 0) mbar_expect_tx(bar(Q_FULL + s), static_cast<uint32_t>(__popc(live)) * G * 256u);
+      __syncwarp();
+      if (qi >= 0) {
+        const int b = k.group / p.hkv, kvh = k.group - b * p.hkv;
+        const uint32_t dst = base + OFF_Q + s * TILE_BYTES + lane * G * 128;
+        tma_load_3d(dst, &q_map, 0, qi, b * p.hq + kvh * G, bar(Q_FULL + s));
+        tma_load_3d(dst + PANEL_BYTES, &q_map, 64, qi, b * p.hq + kvh * G, bar(Q_FULL + s));
+      }
+    }
+    if (!ok) {
+      // let copies in flight land before the CTA gives up its shared memory
+      for (int i = 0; i < 2; ++i) {
+        if (n > static_cast<uint32_t>(i)) mbar_wait_drain(bar(Q_FULL + ((n - 1 - i) & 1)), ((n - 1 - i) >> 1) & 1);
+        if (loads > i) mbar_wait_drain(bar(KV_FULL + ((loads - 1 - i) & 1)), ((loads - 1 - i) >> 1) & 1);
+      }
+    }
+  } else if (warp == MMA_WARP) {
+    // ------------------------------------------------------------- MMA issuer (one thread)
+    if (lane == 0) {
+      constexpr uint32_t IDESC_QK = idesc_bf16(128, 128, false);
+      constexpr uint32_t IDESC_PV = idesc_bf16(128, 128, true);
+      uint32_t n = 0;
+      int loads = 0, cur_group = -1, cur_block = -1, buf = 0, prev_buf = 0;
+      bool ok = true;
+      // O_{s} = P_{s} V of the task numbered m (stream m & 1) out of buffer vb
+      auto issue_pv = [&](uint32_t m, int vb) -> bool {
+        const uint32_t s = m & 1, u = m >> 1;
+        if (!mbar_wait(bar(P_FULL + s), u & 1, guard, 0x720 + s)) return false;
+        if (u > 0 && !mbar_wait(bar(O_EMPTY + s), (u - 1) & 1, guard, 0x730 + s)) return false;
+        tc_fence_after();
+        const uint64_t b0 = desc_sw128_mnmajor(base + OFF_KV + vb * 2 * TILE_BYTES + TILE_BYTES, PANEL_BYTES, 1024);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)
+          mma_ts(tmem + 256 + s * 128, tmem + s * 128 + kk * 8, b0 + static_cast<uint64_t>(kk * (2048 >> 4)),
+                 IDESC_PV, kk > 0 ? 1u : 0u);
+        tc_commit(bar(O_FULL + s));
+        return true;
+      };
+      for (int t = t_begin; ok && t < t_end; ++t) {
+        const Task k = read_task(p, t);
+        if (!k.valid) continue;
+        const uint32_t s = n & 1, u = n >> 1;
+        const bool change = k.group != cur_group || k.block != cur_block;
+        if (change) {
+          cur_group = k.group; cur_block = k.block;
+          buf = loads & 1;
+          ok = mbar_wait(bar(KV_FULL + buf), (loads >> 1) & 1, guard, 0x740 + buf);
+          ++loads;
+          if (!ok) break;
+        }
+        ok = mbar_wait(bar(Q_FULL + s), u & 1, guard, 0x750 + s);
+        if (!ok) break;
+        tc_fence_after();
+        {
+          const uint64_t a0 = desc_sw128_kmajor(base + OFF_Q + s * TILE_BYTES);
+          const uint64_t b0 = desc_sw128_kmajor(base + OFF_KV + buf * 2 * TILE_BYTES);
+#pragma unroll
+          for (int kk = 0; kk < 8; ++kk) {
+            const uint64_t step = static_cast<uint64_t>((kk >> 2) * (PANEL_BYTES >> 4) + (kk & 3) * 2);
+            mma_ss(tmem + s * 128, a0 + step, b0 + step, IDESC_QK, kk > 0);
+          }
+        }
+        tc_commit(bar(S_FULL + s));
+        tc_commit(bar(Q_EMPTY + s));
+        if (n > 0) {
+          ok = issue_pv(n - 1, prev_buf);
+          if (!ok) break;
+          if (change) tc_commit(bar(KV_EMPTY + prev_buf));   // that was the last MMA on the old block
+        }
+        prev_buf = buf;
+        ++n;
+      }
+      if (ok && n > 0) issue_pv(n - 1, prev_buf);
+    }
+    __syncwarp();
+  }
+  } else if (warp < EPI_WARP0) {
+    // ------------------------------------------------------------- softmax
+    setmaxnreg_inc<SOFTMAX_REGS>();
+    const uint32_t s = warp >> 2;
+    const int row = (warp & 3) * 32 + lane;
+    const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const uint32_t t_s = tmem + lane_base + s * 128;
+    uint32_t n = 0;
+    bool ok = true;
+    for (int t = t_begin; ok && t < t_end; ++t) {
+      const Task k = read_task(p, t);
+      if (!k.valid) continue;
+      const uint32_t mine = (n & 1) == s, u = n >> 1;
+      ++n;
+      if (!mine) continue;
+      // where this row's LSE goes (fetched before the scores are ready)
+      long long lse_at = -1;
+      {
+        const int tl = row >> p.group_log2, g = row & (G - 1);
+        if (tl < k.count) {
+          const int qi = p.qids[k.start + tl], rank = p.ranks[k.start + tl];
+          if (qi >= 0 && qi < p.sq && rank >= 0 && rank < p.topk) {
+            const int b = k.group / p.hkv, kvh = k.group - b * p.hkv;
+            lse_at = ((static_cast<long long>(b) * p.hq + kvh * G + g) * p.sq + qi) * p.topk + rank;
+          }
+        }
+      }
+      bool w = mbar_wait(bar(S_FULL + s), u & 1, guard, 0x760 + s);
+      ok = __all_sync(0xffffffffu, w);
+      if (!ok) break;
+      tc_fence_after();
+      uint32_t sv[4][32];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tmem_ld32(t_s + c * 32, sv[c]);
+      tc_wait_ld();
+      float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+      for (int c = 0; c < 4; ++c)
+#pragma unroll
+        for (int j = 0; j < 32; j += 2)
+          mx[(j >> 1) & 3] = max3(mx[(j >> 1) & 3], __uint_as_float(sv[c][j]), __uint_as_float(sv[c][j + 1]));
+      const float row_max = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * p.scale_log2;
+      float2 part[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
+      const float2 scale2 = make_float2(p.scale_log2, p.scale_log2), neg2 = make_float2(-row_max, -row_max);
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t pk[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const float2 x =
+              fma2(make_float2(__uint_as_float(sv[c][2 * j]), __uint_as_float(sv[c][2 * j + 1])), scale2, neg2);
+          const float2 e = make_float2(ex2_approx(x.x), ex2_approx(x.y));
+          part[j & 1] = add2(part[j & 1], e);
+          pk[j] = pack_bf16x2(e.x, e.y);
+        }
+        tmem_st16(t_s + c * 16, pk);
+      }
+      const float row_sum = (part[0].x + part[0].y) + (part[1].x + part[1].y);
+      tc_wait_st();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(P_FULL + s));
+      // 1 / row sum to the epilogue warps (after they released the previous task's)
+      if (u > 0) {
+        bool w2 = mbar_wait(bar(STATS_EMPTY + s), (u - 1) & 1, guard, 0x770 + s);
+        ok = __all_sync(0xffffffffu, w2);
+        if (!ok) break;
+      }
+      stats[s * 128 + row] = 1.0f / row_sum;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(STATS_FULL + s));
+      if (lse_at >= 0) p.lses[lse_at] = (row_max + log2f(row_sum)) * 0.6931471805599453f;
+    }
+  } else {
+    // ------------------------------------------------------------- epilogue warps
+    setmaxnreg_dec<EPI_REGS>();
+    const int quarter = warp & 3;
+    const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
+    const uint32_t stage = base + OFF_STAGE + quarter * STAGE_BYTES;
+    unsigned char* stage_g = gbase + OFF_STAGE + quarter * STAGE_BYTES;
+    const int per_warp = 32 >> p.group_log2;       // queries whose heads this warp holds
+    uint32_t n = 0;
+    bool ok = true;
+    for (int t = t_begin; ok && t < t_end; ++t) {
+      const Task k = read_task(p, t);
+      if (!k.valid) continue;
+      const uint32_t s = n & 1, u = n >> 1;
+      ++n;
+      // lane l < per_warp owns query quarter * per_warp + l of the task
+      int qi = -1, rank = -1;
+      {
+        const int tl = quarter * per_warp + lane;
+        if (lane < per_warp && tl < k.count) {
+          qi = p.qids[k.start + tl];
+          rank = p.ranks[k.start + tl];
+          if (qi < 0 || qi >= p.sq || rank < 0 || rank >= p.topk) qi = rank = -1;
+        }
+      }
+      bool w = mbar_wait(bar(STATS_FULL + s), u & 1, guard, 0x780 + s);
+      w = mbar_wait(bar(O_FULL + s), u & 1, guard, 0x790 + s) && w;
+      ok = __all_sync(0xffffffffu, w);
+      if (!ok) break;
+      tc_fence_after();
+      const float inv = stats[s * 128 + quarter * 32 + lane];
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(STATS_EMPTY + s));
+      bulk_wait_read0();                             // this lane's earlier stores have left the staging tile
+      __syncwarp();
+      const uint32_t t_o = tmem + lane_base + 256 + s * 128;
+#pragma unroll
+      for (int cc = 0; cc < 4; ++cc) {
+        uint32_t ov[32];
+        tmem_ld32(t_o + cc * 32, ov);
+        tc_wait_ld();
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const uint4 val = make_uint4(
+              pack_bf16x2(__uint_as_float(ov[8 * j]) * inv, __uint_as_float(ov[8 * j + 1]) * inv),
+              pack_bf16x2(__uint_as_float(ov[8 * j + 2]) * inv, __uint_as_float(ov[8 * j + 3]) * inv),
+              pack_bf16x2(__uint_as_float(ov[8 * j + 4]) * inv, __uint_as_float(ov[8 * j + 5]) * inv),
+              pack_bf16x2(__uint_as_float(ov[8 * j + 6]) * inv, __uint_as_float(ov[8 * j + 7]) * inv));
+          *reinterpret_cast<uint4*>(stage_g + (cc >> 1) * 4096 + lane * 128 +
+                                    ((((cc & 1) * 4 + j) ^ (lane & 7)) << 4)) = val;
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(O_EMPTY + s));
+      fence_async_smem();
+      __syncwarp();
+      if (qi >= 0) {
+        const int b = k.group / p.hkv, kvh = k.group - b * p.hkv;
+        const uint32_t src = stage + lane * G * 128;
+        tma_store_4d(&o_map, 0, rank, qi, b * p.hq + kvh * G, src);
+        tma_store_4d(&o_map, 64, rank, qi, b * p.hq + kvh * G, src + 4096);
+        bulk_commit();
+      }
+    }
+    bulk_wait_all();                                 // output stores of this lane have completed
+  }
+
+  // ---------------------------------------------------------------- teardown
+  tc_fence_before();
+  __syncthreads();
+  if (warp == MMA_WARP) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
+}  // namespace kvp
+
+// Pipelined main stage for Hq / Hkv of 8 or 16 (same arguments as launch_kv_token_main).
+int launch_kv_token_pipe(const void* q, const void* k, const void* v, const int32_t* tasks, const int32_t* task_count,
+                         const int32_t* qids, const int32_t* ranks, void* partial, float* lses, int batch, int hq,
+                         int hkv, int sq, int skv, int topk, cudaStream_t stream) {
+  using namespace kvp;
+  DeviceCtx* ctx = device_ctx();
+  if (!ctx) return SB_ERR_CUDA;
+  const int group = hq / hkv;
+  Params p{};
+  p.tasks = tasks; p.task_count = task_count; p.qids = qids; p.ranks = ranks;
+  p.lses = lses;
+  p.status = ctx->status;
+  p.batch = batch; p.hq = hq; p.hkv = hkv; p.sq = sq; p.skv = skv; p.topk = topk; p.group = group;
+  p.group_log2 = 0;
+  while ((1 << p.group_log2) < group) ++p.group_log2;
+  p.edges = static_cast<int>(static_cast<long long>(batch) * hkv * sq * topk);
+  p.scale_log2 = 1.4426950408889634f / sqrtf(128.0f);
+
+  CUtensorMap qm, km, vm, om;
+  const cuuint32_t ones[4] = {1, 1, 1, 1};
+  {
+    const cuuint64_t dims[2] = {128, static_cast<cuuint64_t>(batch) * hkv * skv};
+    const cuuint64_t strides[1] = {256};
+    const cuuint32_t box[2] = {64, 128};
+    if (encode_tiled(&km, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(k), dims, strides, box, ones,
+                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B) ||
+        encode_tiled(&vm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(v), dims, strides, box, ones,
+                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B))
+      return set_error(SB_ERR_CUDA, "cuTensorMapEncodeTiled failed for k/v");
+  }
+  {
+    // q [B*Hq, Sq, 128]: one box = the G heads of a KV group at one token, 64 columns
+    const cuuint64_t dims[3] = {128, static_cast<cuuint64_t>(sq), static_cast<cuuint64_t>(batch) * hq};
+    const cuuint64_t strides[2] = {256, static_cast<cuuint64_t>(sq) * 256};
+    const cuuint32_t box[3] = {64, 1, static_cast<cuuint32_t>(group)};
+    if (encode_tiled(&qm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(q), dims, strides, box, ones,
+                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B))
+      return set_error(SB_ERR_CUDA, "cuTensorMapEncodeTiled failed for q");
+  }
+  {
+    // partial [B*Hq, Sq, TopK, 128]: one box = the G heads of a KV group at one (token, rank)
+    const cuuint64_t dims[4] = {128, static_cast<cuuint64_t>(topk), static_cast<cuuint64_t>(sq),
+                                static_cast<cuuint64_t>(batch) * hq};
+    const cuuint64_t strides[3] = {256, static_cast<cuuint64_t>(topk) * 256,
+                                   static_cast<cuuint64_t>(sq) * topk * 256};
+    const cuuint32_t box[4] = {64, 1, 1, static_cast<cuuint32_t>(group)};
+    if (encode_tiled(&om, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, partial, dims, strides, box, ones,
+                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE))
+      return set_error(SB_ERR_CUDA, "cuTensorMapEncodeTiled failed for the partial outputs");
+  }
+  if (!(ctx->tc_attr & (1 << 10))) {
+    cudaError_t e = cudaFuncSetAttribute(kv_token_pipe_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    if (e != cudaSuccess) return set_error(SB_ERR_CUDA, cudaGetErrorString(e));
+    ctx->tc_attr |= (1 << 10);
+  }
+  kv_token_pipe_kernel<<<ctx->sm_count, NUM_THREADS, SMEM_BYTES, stream>>>(qm, km, vm, om, p);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? SB_OK : set_error(SB_ERR_CUDA, cudaGetErrorString(e));
+}
+
+}  // namespace sb
