@@ -5,9 +5,11 @@
 // 128-row Q tile is the G heads of each of those queries. One persistent CTA per SM walks
 // a contiguous range of the task list (tasks are ordered by (group, block), so a CTA
 // reloads K/V two or three times in all) and keeps TWO tasks in flight, one per stream:
-//   warp 13      TMA producer: K/V block into one of two 64 KiB buffers when the block
-//                changes; per query one 3-D box {64 columns, 1 token, G heads} of Q per
-//                64-column panel, straight into the 128-byte-swizzled operand tile
+//   warp 13      TMA producer: the K/V block when it changes (the pipeline drains there,
+//                two or three times per CTA); per query one 3-D box {64 columns, 1 token,
+//                G heads} of Q per 64-column panel, straight into the 128-byte-swizzled
+//                operand tile of a four-slot ring (Q rows mostly come from HBM: four
+//                tasks of loads in flight cover that latency)
 //   warp 12      one thread issues QK(j), then PV(j-1) of the other stream (tcgen05, TMEM)
 //   warps 0-3 / 4-7   softmax of stream 0 / 1 over the single block, P (bf16) back into S,
 //                1/row-sum to shared memory, LSE to global memory
@@ -36,15 +38,16 @@ constexpr int SOFTMAX_REGS = 176;
 constexpr int EPI_REGS = 64;
 constexpr int CTRL_REGS = 96;
 
-constexpr int OFF_Q = 0;                               // [2 streams] Q tiles
-constexpr int OFF_KV = 2 * TILE_BYTES;                 // [2 buffers] K tile, V tile
-constexpr int OFF_STAGE = OFF_KV + 4 * TILE_BYTES;     // 4 epilogue warps x 8 KiB
+constexpr int QRING = 4;
+constexpr int OFF_Q = 0;                               // [QRING] Q tiles
+constexpr int OFF_KV = QRING * TILE_BYTES;             // K tile, V tile
+constexpr int OFF_STAGE = OFF_KV + 2 * TILE_BYTES;     // 4 epilogue warps x 8 KiB
 constexpr int STAGE_BYTES = 8192;
 constexpr int OFF_STATS = OFF_STAGE + 4 * STAGE_BYTES; // [2 streams][128 rows] 1 / row sum
 constexpr int OFF_BAR = OFF_STATS + 2 * 128 * 4;
 enum {
-  Q_FULL = 0, Q_EMPTY = 2, S_FULL = 4, P_FULL = 6, O_FULL = 8, O_EMPTY = 10, STATS_FULL = 12, STATS_EMPTY = 14,
-  KV_FULL = 16, KV_EMPTY = 18, NUM_BARS = 20
+  S_FULL = 0, P_FULL = 2, O_FULL = 4, O_EMPTY = 6, STATS_FULL = 8, STATS_EMPTY = 10, KV_FULL = 12, KV_EMPTY = 13,
+  Q_FULL = 14, Q_EMPTY = 14 + QRING, NUM_BARS = 14 + 2 * QRING
 };
 constexpr int OFF_MISC = OFF_BAR + NUM_BARS * 8;       // tmem base, abort flag
 constexpr int SMEM_BYTES = OFF_MISC + 16 + 1024;       // + slack for manual 1024 alignment
@@ -107,17 +110,19 @@ kv_token_pipe_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_con
 
   if (threadIdx.x == 0) {
     misc[1] = 0;
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < QRING; ++i) {
       mbar_init(bar(Q_FULL + i), 1);
       mbar_init(bar(Q_EMPTY + i), 1);
+    }
+    mbar_init(bar(KV_FULL), 1);
+    mbar_init(bar(KV_EMPTY), 1);
+    for (int i = 0; i < 2; ++i) {
       mbar_init(bar(S_FULL + i), 1);
       mbar_init(bar(P_FULL + i), 4);
       mbar_init(bar(O_FULL + i), 1);
       mbar_init(bar(O_EMPTY + i), 4);
       mbar_init(bar(STATS_FULL + i), 4);
       mbar_init(bar(STATS_EMPTY + i), 4);
-      mbar_init(bar(KV_FULL + i), 1);
-      mbar_init(bar(KV_EMPTY + i), 1);
     }
     fence_mbar_init();
   }
@@ -150,57 +155,65 @@ kv_token_pipe_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_con
     int loads = 0;                  // K/V block loads so far
     int cur_group = -1, cur_block = -1;
     bool ok = true;
-    for (int t = t_begin; ok && t < t_end; ++t) {
-      const Task k = read_task(p, t);
-      if (!k.valid) continue;
-      const uint32_t s = n & 1, u = n >> 1;
-      ++n;
-      if (k.group != cur_group || k.block != cur_block) {
-        cur_group = k.group; cur_block = k.block;
-        const int buf = loads & 1, use = loads >> 1;
-        ++loads;
-        if (use > 0) {
-          bool w = mbar_wait(bar(KV_EMPTY + buf), (use - 1) & 1, guard, 0x700 + buf);
-          ok = __all_sync(0xffffffffu, w);
-          if (!ok) break;
-        }
-        if (lane == 0) {
-          const int kv_row = k.group * p.skv + k.block * 128;
-          const uint32_t dst = base + OFF_KV + buf * 2 * TILE_BYTES;
-          mbar_expect_tx(bar(KV_FULL + buf), 2 * TILE_BYTES);
-          tma_load_2d(dst, &k_map, 0, kv_row, bar(KV_FULL + buf));
-          tma_load_2d(dst + PANEL_BYTES, &k_map, 64, kv_row, bar(KV_FULL + buf));
-          tma_load_2d(dst + TILE_BYTES, &v_map, 0, kv_row, bar(KV_FULL + buf));
-          tma_load_2d(dst + TILE_BYTES + PANEL_BYTES, &v_map, 64, kv_row, bar(KV_FULL + buf));
-        }
-      }
-      if (u > 0) {
-        bool w = mbar_wait(bar(Q_EMPTY + s), (u - 1) & 1, guard, 0x710 + s);
-        ok = __all_sync(0xffffffffu, w);
-        if (!ok) break;
-      }
-      // lane tl fetches query tl of the task
+    // the query ids of a task are fetched one task ahead
+    auto fetch_qi = [&](const Task& k) -> int {
       int qi = -1;
-      if (lane < k.count) {
+      if (k.valid && lane < k.count) {
         qi = p.qids[k.start + lane];
         if (qi < 0 || qi >= p.sq) qi = -1;
       }
-      const unsigned live = __ballot_sync(0xffffffffu, qi >= 0);
-      if (lane == 0) mbar_expect_tx(bar(Q_FULL + s), static_cast<uint32_t>(__popc(live)) * G * 256u);
+      return qi;
+    };
+    Task k = t_begin < t_end ? read_task(p, t_begin) : Task{0, 0, 0, 0, false};
+    int qi = fetch_qi(k);
+    for (int t = t_begin; ok && t < t_end; ++t) {
+      const Task cur = k;
+      const int cur_qi = qi;
+      if (t + 1 < t_end) {
+        k = read_task(p, t + 1);
+        qi = fetch_qi(k);
+      }
+      if (!cur.valid) continue;
+      const uint32_t slot = n % QRING, use = n / QRING;
+      ++n;
+      if (cur.group != cur_group || cur.block != cur_block) {
+        cur_group = cur.group; cur_block = cur.block;
+        if (loads > 0) {
+          bool w = mbar_wait(bar(KV_EMPTY), (loads - 1) & 1, guard, 0x700);
+          ok = __all_sync(0xffffffffu, w);
+          if (!ok) break;
+        }
+        ++loads;
+        if (lane == 0) {
+          const int kv_row = cur.group * p.skv + cur.block * 128;
+          const uint32_t dst = base + OFF_KV;
+          mbar_expect_tx(bar(KV_FULL), 2 * TILE_BYTES);
+          tma_load_2d(dst, &k_map, 0, kv_row, bar(KV_FULL));
+          tma_load_2d(dst + PANEL_BYTES, &k_map, 64, kv_row, bar(KV_FULL));
+          tma_load_2d(dst + TILE_BYTES, &v_map, 0, kv_row, bar(KV_FULL));
+          tma_load_2d(dst + TILE_BYTES + PANEL_BYTES, &v_map, 64, kv_row, bar(KV_FULL));
+        }
+      }
+      if (use > 0) {
+        bool w = mbar_wait(bar(Q_EMPTY + slot), (use - 1) & 1, guard, 0x710 + slot);
+        ok = __all_sync(0xffffffffu, w);
+        if (!ok) break;
+      }
+      const unsigned live = __ballot_sync(0xffffffffu, cur_qi >= 0);
+      if (lane == 0) mbar_expect_tx(bar(Q_FULL + slot), static_cast<uint32_t>(__popc(live)) * G * 256u);
       __syncwarp();
-      if (qi >= 0) {
-        const int b = k.group / p.hkv, kvh = k.group - b * p.hkv;
-        const uint32_t dst = base + OFF_Q + s * TILE_BYTES + lane * G * 128;
-        tma_load_3d(dst, &q_map, 0, qi, b * p.hq + kvh * G, bar(Q_FULL + s));
-        tma_load_3d(dst + PANEL_BYTES, &q_map, 64, qi, b * p.hq + kvh * G, bar(Q_FULL + s));
+      if (cur_qi >= 0) {
+        const int b = cur.group / p.hkv, kvh = cur.group - b * p.hkv;
+        const uint32_t dst = base + OFF_Q + slot * TILE_BYTES + lane * G * 128;
+        tma_load_3d(dst, &q_map, 0, cur_qi, b * p.hq + kvh * G, bar(Q_FULL + slot));
+        tma_load_3d(dst + PANEL_BYTES, &q_map, 64, cur_qi, b * p.hq + kvh * G, bar(Q_FULL + slot));
       }
     }
     if (!ok) {
       // let copies in flight land before the CTA gives up its shared memory
-      for (int i = 0; i < 2; ++i) {
-        if (n > static_cast<uint32_t>(i)) mbar_wait_drain(bar(Q_FULL + ((n - 1 - i) & 1)), ((n - 1 - i) >> 1) & 1);
-        if (loads > i) mbar_wait_drain(bar(KV_FULL + ((loads - 1 - i) & 1)), ((loads - 1 - i) >> 1) & 1);
-      }
+      for (uint32_t i = 0; i < QRING; ++i)
+        if (n > i) mbar_wait_drain(bar(Q_FULL + ((n - 1 - i) % QRING)), ((n - 1 - i) / QRING) & 1);
+      if (loads > 0) mbar_wait_drain(bar(KV_FULL), (loads - 1) & 1);
     }
   } else if (warp == MMA_WARP) {
     // ------------------------------------------------------------- MMA issuer (one thread)
@@ -208,15 +221,16 @@ kv_token_pipe_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_con
       constexpr uint32_t IDESC_QK = idesc_bf16(128, 128, false);
       constexpr uint32_t IDESC_PV = idesc_bf16(128, 128, true);
       uint32_t n = 0;
-      int loads = 0, cur_group = -1, cur_block = -1, buf = 0, prev_buf = 0;
+      int loads = 0, cur_group = -1, cur_block = -1;
       bool ok = true;
-      // O_{s} = P_{s} V of the task numbered m (stream m & 1) out of buffer vb
-      auto issue_pv = [&](uint32_t m, int vb) -> bool {
+      bool pv_pending = false;      // the PV of task n - 1 has not been issued yet
+      // O_{s} = P_{s} V of the task numbered m (stream m & 1)
+      auto issue_pv = [&](uint32_t m) -> bool {
         const uint32_t s = m & 1, u = m >> 1;
         if (!mbar_wait(bar(P_FULL + s), u & 1, guard, 0x720 + s)) return false;
         if (u > 0 && !mbar_wait(bar(O_EMPTY + s), (u - 1) & 1, guard, 0x730 + s)) return false;
         tc_fence_after();
-        const uint64_t b0 = desc_sw128_mnmajor(base + OFF_KV + vb * 2 * TILE_BYTES + TILE_BYTES, PANEL_BYTES, 1024);
+        const uint64_t b0 = desc_sw128_mnmajor(base + OFF_KV + TILE_BYTES, PANEL_BYTES, 1024);
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)
           mma_ts(tmem + 256 + s * 128, tmem + s * 128 + kk * 8, b0 + static_cast<uint64_t>(kk * (2048 >> 4)),
@@ -224,24 +238,31 @@ kv_token_pipe_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_con
         tc_commit(bar(O_FULL + s));
         return true;
       };
+      Task k = t_begin < t_end ? read_task(p, t_begin) : Task{0, 0, 0, 0, false};
       for (int t = t_begin; ok && t < t_end; ++t) {
-        const Task k = read_task(p, t);
-        if (!k.valid) continue;
-        const uint32_t s = n & 1, u = n >> 1;
-        const bool change = k.group != cur_group || k.block != cur_block;
-        if (change) {
-          cur_group = k.group; cur_block = k.block;
-          buf = loads & 1;
-          ok = mbar_wait(bar(KV_FULL + buf), (loads >> 1) & 1, guard, 0x740 + buf);
+        const Task cur = k;
+        if (t + 1 < t_end) k = read_task(p, t + 1);     // fetched one task ahead of its use
+        if (!cur.valid) continue;
+        const uint32_t s = n & 1, slot = n % QRING, use = n / QRING;
+        if (cur.group != cur_group || cur.block != cur_block) {
+          cur_group = cur.group; cur_block = cur.block;
+          // the old block is done with once the last PV on it has completed
+          if (pv_pending) {
+            ok = issue_pv(n - 1);
+            pv_pending = false;
+            if (!ok) break;
+          }
+          if (loads > 0) tc_commit(bar(KV_EMPTY));
+          ok = mbar_wait(bar(KV_FULL), loads & 1, guard, 0x740);
           ++loads;
           if (!ok) break;
         }
-        ok = mbar_wait(bar(Q_FULL + s), u & 1, guard, 0x750 + s);
+        ok = mbar_wait(bar(Q_FULL + slot), use & 1, guard, 0x750 + slot);
         if (!ok) break;
         tc_fence_after();
         {
-          const uint64_t a0 = desc_sw128_kmajor(base + OFF_Q + s * TILE_BYTES);
-          const uint64_t b0 = desc_sw128_kmajor(base + OFF_KV + buf * 2 * TILE_BYTES);
+          const uint64_t a0 = desc_sw128_kmajor(base + OFF_Q + slot * TILE_BYTES);
+          const uint64_t b0 = desc_sw128_kmajor(base + OFF_KV);
 #pragma unroll
           for (int kk = 0; kk < 8; ++kk) {
             const uint64_t step = static_cast<uint64_t>((kk >> 2) * (PANEL_BYTES >> 4) + (kk & 3) * 2);
@@ -249,16 +270,15 @@ kv_token_pipe_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_con
           }
         }
         tc_commit(bar(S_FULL + s));
-        tc_commit(bar(Q_EMPTY + s));
-        if (n > 0) {
-          ok = issue_pv(n - 1, prev_buf);
+        tc_commit(bar(Q_EMPTY + slot));
+        if (pv_pending) {
+          ok = issue_pv(n - 1);
           if (!ok) break;
-          if (change) tc_commit(bar(KV_EMPTY + prev_buf));   // that was the last MMA on the old block
         }
-        prev_buf = buf;
+        pv_pending = true;
         ++n;
       }
-      if (ok && n > 0) issue_pv(n - 1, prev_buf);
+      if (ok && pv_pending) issue_pv(n - 1);
     }
     __syncwarp();
   }
