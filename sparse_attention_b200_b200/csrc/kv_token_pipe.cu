@@ -21,6 +21,7 @@
 // head-major [B,Hq,Sq,128], partials [B,Hq,Sq,TopK,128] bf16 and LSE [B,Hq,Sq,TopK].
 // Rows of a tile beyond the task's query count keep whatever the buffer held: every row
 // of S, P and O depends on its own Q row only, and those rows are never stored.
+#include <algorithm>
 #include "ptx.cuh"
 #include "internal.h"
 
@@ -61,7 +62,23 @@ struct Params {
   float* lses;                  // [B, Hq, Sq, TopK]
   int* status;
   int batch, hq, hkv, sq, skv, topk, group, group_log2, edges;
+  int phases;                   // upper bound on the number of passes over the task list (see Walk)
   float scale_log2;
+};
+
+// Order in which a CTA visits tasks. The task list (sorted by KV-head group, then block) is
+// cut into `phases` equal segments; within a segment every CTA takes a contiguous share,
+// and the CTAs go through the segments together. At any time the whole GPU then gathers Q
+// rows of a few groups only, so they come from L2 instead of HBM (one contiguous share of
+// the whole list per CTA spreads the gathers over all of Q), at the price of one more
+// K/V reload per CTA and segment.
+struct Walk {
+  int total, seg, per, count;   // tasks, tasks per segment, tasks per CTA and segment, slots to visit
+  __device__ __forceinline__ int task(int i) const {      // -1: nothing in this slot
+    const int ph = i / per, j = static_cast<int>(blockIdx.x) * per + (i - ph * per);
+    const long long t = static_cast<long long>(ph) * seg + j;
+    return (j < seg && t < total) ? static_cast<int>(t) : -1;
+  }
 };
 
 struct Task {
@@ -69,7 +86,9 @@ struct Task {
   bool valid;
 };
 
-__device__ __forceinline__ Task read_task(const Params& p, int t) {
+__device__ __forceinline__ Task read_task(const Params& p, const Walk& walk, int i) {
+  const int t = i < walk.count ? walk.task(i) : -1;
+  if (t < 0) return Task{0, 0, 0, 0, false};
   const int4 raw = *reinterpret_cast<const int4*>(p.tasks + static_cast<long long>(t) * 4);
   Task k;
   k.group = raw.x; k.block = raw.y; k.start = raw.z; k.count = raw.w;
@@ -142,9 +161,16 @@ kv_token_pipe_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_con
   const uint32_t tmem = static_cast<uint32_t>(misc[0]);
   // tensor memory columns: S0 0..127, S1 128..255, O0 256..383, O1 384..511; P over S.
 
-  const int total = *p.task_count;
-  const int per_cta = (total + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x);
-  const int t_begin = blockIdx.x * per_cta, t_end = min(total, t_begin + per_cta);
+  Walk walk;
+  walk.total = *p.task_count;
+  {
+    const int grid = static_cast<int>(gridDim.x);
+    const int phases = max(1, min(p.phases, walk.total / (grid * 16)));   // at least 16 tasks per CTA and segment
+    walk.seg = (walk.total + phases - 1) / phases;
+    walk.per = max(1, (walk.seg + grid - 1) / grid);
+    walk.count = phases * walk.per;
+  }
+  const int t_begin = 0, t_end = walk.count;
   const int G = p.group;
 
   if (warp >= MMA_WARP) {
@@ -164,15 +190,13 @@ kv_token_pipe_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_con
       }
       return qi;
     };
-    Task k = t_begin < t_end ? read_task(p, t_begin) : Task{0, 0, 0, 0, false};
+    Task k = read_task(p, walk, t_begin);
     int qi = fetch_qi(k);
     for (int t = t_begin; ok && t < t_end; ++t) {
       const Task cur = k;
       const int cur_qi = qi;
-      if (t + 1 < t_end) {
-        k = read_task(p, t + 1);
-        qi = fetch_qi(k);
-      }
+      k = read_task(p, walk, t + 1);
+      qi = fetch_qi(k);
       if (!cur.valid) continue;
       const uint32_t slot = n % QRING, use = n / QRING;
       ++n;
@@ -238,10 +262,10 @@ kv_token_pipe_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_con
         tc_commit(bar(O_FULL + s));
         return true;
       };
-      Task k = t_begin < t_end ? read_task(p, t_begin) : Task{0, 0, 0, 0, false};
+      Task k = read_task(p, walk, t_begin);
       for (int t = t_begin; ok && t < t_end; ++t) {
         const Task cur = k;
-        if (t + 1 < t_end) k = read_task(p, t + 1);     // fetched one task ahead of its use
+        k = read_task(p, walk, t + 1);                        // fetched one task ahead of its use
         if (!cur.valid) continue;
         const uint32_t s = n & 1, slot = n % QRING, use = n / QRING;
         if (cur.group != cur_group || cur.block != cur_block) {
@@ -292,7 +316,7 @@ kv_token_pipe_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_con
     uint32_t n = 0;
     bool ok = true;
     for (int t = t_begin; ok && t < t_end; ++t) {
-      const Task k = read_task(p, t);
+      const Task k = read_task(p, walk, t);
       if (!k.valid) continue;
       const uint32_t mine = (n & 1) == s, u = n >> 1;
       ++n;
@@ -366,7 +390,7 @@ kv_token_pipe_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_con
     uint32_t n = 0;
     bool ok = true;
     for (int t = t_begin; ok && t < t_end; ++t) {
-      const Task k = read_task(p, t);
+      const Task k = read_task(p, walk, t);
       if (!k.valid) continue;
       const uint32_t s = n & 1, u = n >> 1;
       ++n;
@@ -451,6 +475,9 @@ int launch_kv_token_pipe(const void* q, const void* k, const void* v, const int3
   while ((1 << p.group_log2) < group) ++p.group_log2;
   p.edges = static_cast<int>(static_cast<long long>(batch) * hkv * sq * topk);
   p.scale_log2 = 1.4426950408889634f / sqrtf(128.0f);
+  // one segment per 24 MB of Q: the Q rows a segment gathers then stay within L2
+  const long long q_bytes = static_cast<long long>(batch) * hq * sq * 256;
+  p.phases = static_cast<int>(std::min<long long>(64, (q_bytes + (24LL << 20) - 1) / (24LL << 20)));
 
   CUtensorMap qm, km, vm, om;
   const cuuint32_t ones[4] = {1, 1, 1, 1};
