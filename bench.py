@@ -423,6 +423,98 @@ def run_refcmp(args):
         del q, k, v, ids, outs
 
 
+# The reference's published selector benchmark (benchmarks/ch4_selectors/RESULTS.md:7-15), microseconds:
+# Skv -> selector -> (selector only, selector -> p03 pipeline)
+REFSEL_PUBLISHED = {4096: {"R1": (20.73, 155.72), "R4": (47.84, 175.00), "FP4": (17.66, 154.67)},
+                    8192: {"R1": (22.01, 154.33), "R4": (53.55, 178.44), "FP4": (28.92, 162.50)},
+                    16384: {"R1": (22.09, 154.50), "R4": (60.73, 187.04), "FP4": (48.38, 180.43)}}
+
+
+def graph_time_us(fn, replays=20):
+    """Median-free protocol of the reference's selector benchmark: capture one call in a CUDA
+    graph, replay it back to back, CUDA events around the replays; best of three rounds."""
+    import torch
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(3):
+            fn()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        fn()
+    best = float("inf")
+    for _ in range(3):
+        graph.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(replays):
+            graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        best = min(best, e0.elapsed_time(e1) / replays * 1e3)
+    return best
+
+
+def run_refsel(args):
+    """This repository's selectors on the reference's own selector benchmark shapes (B2, Hq16, Hkv1,
+    Sq 4096, Skv 4096 / 8192 / 16384, TopK 16; benchmarks/ch4_selectors/RESULTS.md): selector alone
+    and selector -> attention as one CUDA graph, next to the reference's published microseconds.
+    FP4 starts, as there, from prepared quantised inputs (quantisation excluded)."""
+    import torch
+    import sparse_attention_b200_b200 as sp
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    B, Hq, Hkv, Sq, topk = 2, 16, 1, 4096, 16
+    for Skv in (4096, 8192, 16384):
+        gen = torch.Generator(device=dev).manual_seed(29)
+        q = torch.randn((B, Hq, Sq, 128), device=dev, generator=gen).to(torch.bfloat16)
+        k = (torch.randn((B, Hkv, Skv, 128), device=dev, generator=gen)
+             + 0.5 * torch.randn((B, Hkv, Skv // 128, 1, 128), device=dev, generator=gen)
+             .expand(B, Hkv, Skv // 128, 128, 128).reshape(B, Hkv, Skv, 128)).to(torch.bfloat16)
+        v = torch.randn((B, Hkv, Skv, 128), device=dev, generator=gen).to(torch.bfloat16)
+        out = torch.empty_like(q)
+        row = {"workload": "refsel", "shape": {"B": B, "Hq": Hq, "Hkv": Hkv, "Sq": Sq, "Skv": Skv, "topk": topk},
+               "us": {}, "reference_published_us": {}, "protocol": "CUDA-graph replays, best of 3 rounds x 20"}
+        for name, r in (("R1", 1), ("R4", 4)):
+            sel = sp.SummarySelector(q, k, r, topk=topk, keep_scores=False)
+            exact = sp.SummarySelector(q, k, r, topk=topk, keep_scores=True)
+            t_sel = graph_time_us(sel.run_fast)
+            t_exact = graph_time_us(exact.run)
+            t_pipe = graph_time_us(lambda: sp.summary_indexed_attention_out(sel, v, out))
+            torch.cuda.synchronize()
+            assert torch.equal(sel.ids, exact.ids)
+            row["us"][name] = {"selector": round(t_sel, 2), "selector_exact_kernels": round(t_exact, 2),
+                               "selector_to_attention": round(t_pipe, 2), "fallback_lists": sel.fallback_lists()}
+            pub = REFSEL_PUBLISHED[Skv][name]
+            row["reference_published_us"][name] = {"selector": pub[0], "selector_to_p03": pub[1]}
+        qc, qs = sp.quantize_queries(q, Hkv)
+        kc, ks = sp.quantize_keys(k)
+        inputs = sp.prepare_fp4_inputs(qc, kc, qs, ks, batch_size=B, len_q=Sq, len_kv=Skv)
+        ids_fast, ws = sp.fp4_indexer_fast(inputs, topk=topk)
+        ids_exact = sp.fp4_indexer(inputs, topk=topk)
+        tile_scores = torch.empty((B, Hkv, Sq // 128, Skv // 128), dtype=torch.float32, device=dev)
+        t_sel = graph_time_us(lambda: sp.fp4_indexer_fast(inputs, selected=ids_fast, workspace=ws))
+        t_exact = graph_time_us(lambda: sp.fp4_indexer(inputs, selected=ids_exact, tile_scores=tile_scores))
+
+        def fp4_pipe():
+            sp.fp4_indexer_fast(inputs, selected=ids_fast, workspace=ws)
+            sp.attention_out(q, k, v, ids_fast, out)
+        t_pipe = graph_time_us(fp4_pipe)
+        torch.cuda.synchronize()
+        assert torch.equal(ids_fast, ids_exact)
+        row["us"]["FP4"] = {"selector": round(t_sel, 2), "selector_exact_kernels": round(t_exact, 2),
+                            "selector_to_attention": round(t_pipe, 2)}
+        pub = REFSEL_PUBLISHED[Skv]["FP4"]
+        row["reference_published_us"]["FP4"] = {"selector": pub[0], "selector_to_p03": pub[1]}
+        row["us"]["attention_only"] = round(graph_time_us(lambda: sp.attention_out(q, k, v, ids_fast, out)), 2)
+        sp.device_status()
+        print(json.dumps(row), flush=True)
+        del q, k, v, out
+
+
 def run_config(args):
     """Configurations 1, 3, 4, 5: indexer -> lists -> attention operator, stage by stage.
     With N > 1 ranks the (batch, KV-head) groups are dealt to the ranks (strong scaling, no
@@ -572,7 +664,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--kernel-only", action="store_true",
                     help="device-resident timing only (used for profiler captures): no e2e, no CPU baseline")
-    ap.add_argument("--workload", default="c2", choices=["c2", "kvtoken", "refcmp"] + sorted(CONFIGS),
+    ap.add_argument("--workload", default="c2", choices=["c2", "kvtoken", "refcmp", "refsel"] + sorted(CONFIGS),
                     help="c2 (default) is the headline workload; c1/c3/c4/c5 run indexer + operator stage by stage")
     ap.add_argument("--kv-split", type=int, default=1, help="KV ranges per head shard (c5 only, needs --gpus >= 2)")
     ap.add_argument("--n", type=int, default=0, help="override the token count of c1/c3/c4/c5 (small profiler cases)")
@@ -584,6 +676,8 @@ def main():
         run_kv_token(args)
     elif args.workload == "refcmp":
         run_refcmp(args)
+    elif args.workload == "refsel":
+        run_refsel(args)
     elif args.workload != "c2":
         run_config(args)
     else:

@@ -219,6 +219,8 @@ int sparse_b200_pool_blocks(const void* x, void* desc, int batch, int heads, int
   REQUIRE(representatives == 1 || representatives == 2 || representatives == 4, "representatives must be 1, 2 or 4");
   REQUIRE(aligned16(x) && aligned16(desc), "x and desc must be 16-byte aligned");
   const long long num = static_cast<long long>(batch) * heads * (seq / 128) * representatives;
+  if (pool_small_eligible(num))
+    return launch_pool_small(x, desc, num, 128 / representatives, static_cast<cudaStream_t>(stream));
   return launch_pool(x, desc, num, 128 / representatives, static_cast<cudaStream_t>(stream));
 }
 
@@ -252,6 +254,9 @@ int sparse_b200_indexer_summary(const void* q, const void* k, void* q_desc, void
   if (rc) return rc;
   rc = sparse_b200_pool_blocks(k, k_desc, batch, hkv, skv, representatives, stream);
   if (rc) return rc;
+  rc = launch_summary_small(q_desc, k_desc, scores, block_idx, nullptr, batch, hq, hkv, sq / 128, skv / 128,
+                            representatives, topk, static_cast<cudaStream_t>(stream));
+  if (rc != 1) return rc;            // small problem: cluster kernel, same ids and scores
   return launch_summary_score_topk(q_desc, k_desc, scores, block_idx, batch, hq, hkv, sq / 128, skv / 128,
                                    representatives, topk, static_cast<cudaStream_t>(stream));
 }
@@ -273,6 +278,11 @@ int sparse_b200_indexer_summary_fast(const void* q, const void* k, void* q_desc,
   if (rc) return rc;
   rc = sparse_b200_pool_blocks(k, k_desc, batch, hkv, skv, representatives, stream);
   if (rc) return rc;
+  // small problems: the exact cluster kernel fills the GPU better than the tensor-core pre-filter
+  rc = launch_summary_small(q_desc, k_desc, nullptr, block_idx,
+                            static_cast<int32_t*>(aux) + static_cast<long long>(batch) * hkv, batch, hq, hkv,
+                            sq / 128, skv / 128, representatives, topk, static_cast<cudaStream_t>(stream));
+  if (rc != 1) return rc;
   rc = launch_summary_select_tc(q_desc, k_desc, aux, block_idx, batch, hq, hkv, sq / 128, skv / 128, representatives,
                                 topk, static_cast<cudaStream_t>(stream));
   if (rc == 1)      // not eligible for the tensor-core path: exact kernel, same ids

@@ -19,6 +19,7 @@ struct DeviceCtx {
   int qc_attr_bf16 = 0, qc_attr_f32 = 0;
   int misc_attr[8] = {0};
   int tc_attr = 0;
+  int small_attr = 0;
 };
 DeviceCtx* device_ctx();
 
@@ -44,6 +45,12 @@ int launch_combine(const void* partial, int partial_is_f32, const float* lses, v
 int launch_split_segments(const int32_t* ids, const int32_t* counts, int32_t* seg_ids, int32_t* seg_counts,
                           int* error, long long lists, int topk, int kv_blocks, int nseg, cudaStream_t stream);
 int launch_pool(const void* x, void* desc, long long num_desc, int tokens_per_desc, cudaStream_t stream);
+// small problems (indexer_summary_small.cu)
+bool pool_small_eligible(long long num_desc);
+int launch_pool_small(const void* x, void* desc, long long num_desc, int tokens_per_desc, cudaStream_t stream);
+// returns 1 when the problem is not small; fallback_counter (may be null) is reset to 0
+int launch_summary_small(const void* qd, const void* kd, float* scores, int32_t* ids, int32_t* fallback_counter,
+                         int batch, int hq, int hkv, int qt, int nt, int r, int topk, cudaStream_t stream);
 int launch_summary_score_topk(const void* qd, const void* kd, float* scores, int32_t* ids, int batch, int hq, int hkv,
                               int qt, int nt, int r, int topk, cudaStream_t stream);
 int launch_summary_select_tc(const void* qd, const void* kd, void* aux, int32_t* ids, int batch, int hq, int hkv,

@@ -30,6 +30,77 @@ __global__ void __launch_bounds__(256) count_edges_kernel(const int32_t* __restr
   }
 }
 
+// Shared-memory variants for up to SMEM_BINS KV blocks: a CTA takes a contiguous span of edges
+// (one KV-head group, or a few), histograms it in shared memory and touches global memory once
+// per (CTA, non-empty bin) instead of once per edge: with 256 rows and half a million edges the
+// per-edge atomics of the plain kernels serialise on a few hundred addresses.
+constexpr int SMEM_BINS = 2048;
+constexpr int EDGES_PER_CTA = 4096;
+
+__global__ void __launch_bounds__(256) count_edges_smem_kernel(const int32_t* __restrict__ selected, int32_t* counts,
+                                                               int32_t* error, long long edges,
+                                                               long long group_edges, int kv_blocks) {
+  __shared__ int hist[SMEM_BINS];
+  const long long e0 = static_cast<long long>(blockIdx.x) * EDGES_PER_CTA;
+  const long long e1 = min(edges, e0 + EDGES_PER_CTA);
+  for (long long seg = e0; seg < e1;) {
+    const long long g = seg / group_edges;
+    const long long seg_end = min(e1, (g + 1) * group_edges);
+    for (int i = threadIdx.x; i < kv_blocks; i += blockDim.x) hist[i] = 0;
+    __syncthreads();
+    for (long long e = seg + threadIdx.x; e < seg_end; e += blockDim.x) {
+      const int key = selected[e];
+      if (static_cast<unsigned>(key) < static_cast<unsigned>(kv_blocks))
+        atomicAdd(&hist[key], 1);
+      else
+        atomicOr(error, 1);
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < kv_blocks; i += blockDim.x)
+      if (hist[i] > 0) atomicAdd(counts + g * kv_blocks + i, hist[i]);
+    __syncthreads();
+    seg = seg_end;
+  }
+}
+
+__global__ void __launch_bounds__(256) scatter_edges_smem_kernel(const int32_t* __restrict__ selected,
+                                                                 const int32_t* __restrict__ row_ptr, int32_t* cursors,
+                                                                 int32_t* __restrict__ qids, int32_t* __restrict__ ranks,
+                                                                 long long edges, long long group_edges, int kv_blocks,
+                                                                 int topk) {
+  __shared__ int hist[SMEM_BINS];      // edges of this span per bin, then the running local cursor
+  __shared__ int first[SMEM_BINS];     // first slot of this CTA's edges inside the row
+  const long long e0 = static_cast<long long>(blockIdx.x) * EDGES_PER_CTA;
+  const long long e1 = min(edges, e0 + EDGES_PER_CTA);
+  for (long long seg = e0; seg < e1;) {
+    const long long g = seg / group_edges;
+    const long long seg_end = min(e1, (g + 1) * group_edges);
+    for (int i = threadIdx.x; i < kv_blocks; i += blockDim.x) hist[i] = 0;
+    __syncthreads();
+    for (long long e = seg + threadIdx.x; e < seg_end; e += blockDim.x) {
+      const int key = selected[e];
+      if (static_cast<unsigned>(key) < static_cast<unsigned>(kv_blocks)) atomicAdd(&hist[key], 1);
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < kv_blocks; i += blockDim.x) {
+      const int c = hist[i];
+      if (c > 0) first[i] = row_ptr[g * kv_blocks + i] + atomicAdd(cursors + g * kv_blocks + i, c);
+      hist[i] = 0;
+    }
+    __syncthreads();
+    for (long long e = seg + threadIdx.x; e < seg_end; e += blockDim.x) {
+      const int key = selected[e];
+      if (static_cast<unsigned>(key) >= static_cast<unsigned>(kv_blocks)) continue;
+      const int dst = first[key] + atomicAdd(&hist[key], 1);
+      const long long in_group = e - g * group_edges;
+      qids[dst] = static_cast<int32_t>(in_group / topk);
+      ranks[dst] = static_cast<int32_t>(in_group % topk);
+    }
+    __syncthreads();
+    seg = seg_end;
+  }
+}
+
 // Exclusive scan of n + 1 values by one CTA of 1024 threads (n is at most a few 10^5 rows).
 // With `capacity` > 0 the scanned values are ceil(in / capacity) (tasks per row).
 __global__ void __launch_bounds__(1024) scan_kernel(const int32_t* __restrict__ in, int32_t* __restrict__ out, int n,
@@ -115,10 +186,19 @@ int launch_token_metadata(const int32_t* selected, int32_t* counts, int32_t* cur
       cudaMemsetAsync(error, 0, 4, stream) != cudaSuccess)
     return set_error(SB_ERR_CUDA, "memset failed");
   const int grid = static_cast<int>(edges / 256 + 1 < 4096 ? edges / 256 + 1 : 4096);
-  count_edges_kernel<<<grid, 256, 0, stream>>>(selected, counts, error, edges, group_edges, kv_blocks);
+  const bool in_smem = kv_blocks <= SMEM_BINS && (edges + EDGES_PER_CTA - 1) / EDGES_PER_CTA < (1LL << 30);
+  const int span_grid = static_cast<int>((edges + EDGES_PER_CTA - 1) / EDGES_PER_CTA);
+  if (in_smem)
+    count_edges_smem_kernel<<<span_grid, 256, 0, stream>>>(selected, counts, error, edges, group_edges, kv_blocks);
+  else
+    count_edges_kernel<<<grid, 256, 0, stream>>>(selected, counts, error, edges, group_edges, kv_blocks);
   scan_kernel<<<1, 1024, 0, stream>>>(counts, row_ptr, rows, 0);
-  scatter_edges_kernel<<<grid, 256, 0, stream>>>(selected, row_ptr, cursors, qids, ranks, edges, group_edges, kv_blocks,
-                                                 topk);
+  if (in_smem)
+    scatter_edges_smem_kernel<<<span_grid, 256, 0, stream>>>(selected, row_ptr, cursors, qids, ranks, edges,
+                                                             group_edges, kv_blocks, topk);
+  else
+    scatter_edges_kernel<<<grid, 256, 0, stream>>>(selected, row_ptr, cursors, qids, ranks, edges, group_edges,
+                                                   kv_blocks, topk);
   scan_kernel<<<1, 1024, 0, stream>>>(counts, task_ptr, rows, capacity);
   make_tasks_kernel<<<rows < 4096 ? rows : 4096, 128, 0, stream>>>(row_ptr, task_ptr, tasks, rows, kv_blocks, capacity);
   cudaError_t e = cudaGetLastError();

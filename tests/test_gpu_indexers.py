@@ -103,11 +103,20 @@ def test_summary_selector_tensor_core_path_ties_and_constant_inputs():
     """Exact ties cannot be proven safe by the pre-filter: those lists must take the
     exact fallback and still come out with the lower block id first."""
     m = sp()
-    q, k = cases.selector_inputs("zeros", skv=8192)      # 64 blocks > 32 candidates
+    # 160 lists (more than one per SM, so the tensor-core path is taken, not the small-problem
+    # cluster kernel) of 64 blocks > 32 candidates
+    q = torch.zeros((1, 4, 160 * 128, 128), dtype=torch.bfloat16)
+    k = torch.zeros((1, 1, 8192, 128), dtype=torch.bfloat16)
     sel = m.SummarySelector(q.cuda(), k.cuda(), 4, topk=16, keep_scores=False)
     ids = sel.run_fast().cpu()
     assert torch.equal(ids, torch.arange(16, dtype=torch.int32).expand_as(ids))
     assert sel.fallback_lists() == ids.shape[0] * ids.shape[1] * ids.shape[2]
+    # the same ties through the small-problem kernel (exact everywhere: no fallback is counted)
+    q, k = cases.selector_inputs("zeros", skv=8192)
+    sel = m.SummarySelector(q.cuda(), k.cuda(), 4, topk=16, keep_scores=False)
+    ids = sel.run_fast().cpu()
+    assert torch.equal(ids, torch.arange(16, dtype=torch.int32).expand_as(ids))
+    assert sel.fallback_lists() == 0
     # constant non-zero inputs: every score equal and non-zero
     qc = torch.full_like(q, 0.5)
     kc = torch.full_like(k, -0.25)
