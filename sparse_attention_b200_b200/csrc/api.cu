@@ -224,6 +224,21 @@ int sparse_b200_pool_blocks(const void* x, void* desc, int batch, int heads, int
   return launch_pool(x, desc, num, 128 / representatives, static_cast<cudaStream_t>(stream));
 }
 
+// Query and key descriptors: one launch when both tensors are small, else one launch each.
+static int pool_both(const void* q, void* q_desc, const void* k, void* k_desc, int batch, int hq, int hkv, int sq,
+                     int skv, int r, void* stream) {
+  const long long nq = static_cast<long long>(batch) * hq * (sq / 128) * r;
+  const long long nk = static_cast<long long>(batch) * hkv * (skv / 128) * r;
+  if (pool_small_eligible(nq + nk)) {
+    if (!(aligned16(q) && aligned16(k) && aligned16(q_desc) && aligned16(k_desc)))
+      return set_error(SB_ERR_INVALID, "x and desc must be 16-byte aligned");
+    return launch_pool_small_pair(q, q_desc, nq, k, k_desc, nk, 128 / r, static_cast<cudaStream_t>(stream));
+  }
+  int rc = sparse_b200_pool_blocks(q, q_desc, batch, hq, sq, r, stream);
+  if (rc) return rc;
+  return sparse_b200_pool_blocks(k, k_desc, batch, hkv, skv, r, stream);
+}
+
 static int check_summary(int batch, int hq, int hkv, int qt, int nt, int r, int topk) {
   REQUIRE(batch > 0 && hkv > 0 && hq >= hkv && hq % hkv == 0, "Hq must be a positive multiple of Hkv");
   REQUIRE(qt > 0 && nt > 0, "block counts must be positive");
@@ -250,9 +265,7 @@ int sparse_b200_indexer_summary(const void* q, const void* k, void* q_desc, void
   REQUIRE(sq >= 128 && sq % 128 == 0 && skv >= 128 && skv % 128 == 0, "Sq and Skv must be positive multiples of 128");
   int rc = check_summary(batch, hq, hkv, sq / 128, skv / 128, representatives, topk);
   if (rc) return rc;
-  rc = sparse_b200_pool_blocks(q, q_desc, batch, hq, sq, representatives, stream);
-  if (rc) return rc;
-  rc = sparse_b200_pool_blocks(k, k_desc, batch, hkv, skv, representatives, stream);
+  rc = pool_both(q, q_desc, k, k_desc, batch, hq, hkv, sq, skv, representatives, stream);
   if (rc) return rc;
   rc = launch_summary_small(q_desc, k_desc, scores, block_idx, nullptr, batch, hq, hkv, sq / 128, skv / 128,
                             representatives, topk, static_cast<cudaStream_t>(stream));
@@ -274,9 +287,7 @@ int sparse_b200_indexer_summary_fast(const void* q, const void* k, void* q_desc,
   int rc = check_summary(batch, hq, hkv, sq / 128, skv / 128, representatives, topk);
   if (rc) return rc;
   REQUIRE((reinterpret_cast<uintptr_t>(aux) & 3u) == 0 && aligned16(q_desc) && aligned16(k_desc), "misaligned workspace");
-  rc = sparse_b200_pool_blocks(q, q_desc, batch, hq, sq, representatives, stream);
-  if (rc) return rc;
-  rc = sparse_b200_pool_blocks(k, k_desc, batch, hkv, skv, representatives, stream);
+  rc = pool_both(q, q_desc, k, k_desc, batch, hq, hkv, sq, skv, representatives, stream);
   if (rc) return rc;
   // small problems: the exact cluster kernel fills the GPU better than the tensor-core pre-filter
   rc = launch_summary_small(q_desc, k_desc, nullptr, block_idx,

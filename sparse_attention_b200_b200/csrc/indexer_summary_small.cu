@@ -27,10 +27,18 @@ namespace {
 namespace cg = cooperative_groups;
 
 // ---------------------------------------------------------------- pooling
+// Descriptors 0 .. first - 1 come from x, the rest from x2 (queries and keys in one launch).
 __global__ void __launch_bounds__(256) pool_small_kernel(const __nv_bfloat16* __restrict__ x,
-                                                         __nv_bfloat16* __restrict__ desc, int n) {
+                                                         __nv_bfloat16* __restrict__ desc, long long first,
+                                                         const __nv_bfloat16* __restrict__ x2,
+                                                         __nv_bfloat16* __restrict__ desc2, int n) {
   extern __shared__ uint4 tile[];                 // n token rows x 16 uint4
-  const long long vec = blockIdx.x;
+  long long vec = blockIdx.x;
+  if (vec >= first) {
+    vec -= first;
+    x = x2;
+    desc = desc2;
+  }
   const uint4* src = reinterpret_cast<const uint4*>(x + vec * n * 128);
   for (int i = threadIdx.x; i < n * 16; i += blockDim.x) tile[i] = __ldcs(src + i);
   __syncthreads();
@@ -211,8 +219,16 @@ bool pool_small_eligible(long long num_desc) {
 }
 
 int launch_pool_small(const void* x, void* desc, long long num_desc, int tokens_per_desc, cudaStream_t stream) {
-  pool_small_kernel<<<static_cast<unsigned>(num_desc), 256, static_cast<size_t>(tokens_per_desc) * 256, stream>>>(
-      static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(desc), tokens_per_desc);
+  return launch_pool_small_pair(x, desc, num_desc, nullptr, nullptr, 0, tokens_per_desc, stream);
+}
+
+// Two tensors in one launch (x2 may be null with num_desc2 = 0).
+int launch_pool_small_pair(const void* x, void* desc, long long num_desc, const void* x2, void* desc2,
+                           long long num_desc2, int tokens_per_desc, cudaStream_t stream) {
+  pool_small_kernel<<<static_cast<unsigned>(num_desc + num_desc2), 256, static_cast<size_t>(tokens_per_desc) * 256,
+                      stream>>>(static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(desc), num_desc,
+                                static_cast<const __nv_bfloat16*>(x2), static_cast<__nv_bfloat16*>(desc2),
+                                tokens_per_desc);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? SB_OK : set_error(SB_ERR_CUDA, cudaGetErrorString(e));
 }

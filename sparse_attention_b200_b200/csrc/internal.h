@@ -48,6 +48,8 @@ int launch_pool(const void* x, void* desc, long long num_desc, int tokens_per_de
 // small problems (indexer_summary_small.cu)
 bool pool_small_eligible(long long num_desc);
 int launch_pool_small(const void* x, void* desc, long long num_desc, int tokens_per_desc, cudaStream_t stream);
+int launch_pool_small_pair(const void* x, void* desc, long long num_desc, const void* x2, void* desc2,
+                           long long num_desc2, int tokens_per_desc, cudaStream_t stream);
 // returns 1 when the problem is not small; fallback_counter (may be null) is reset to 0
 int launch_summary_small(const void* qd, const void* kd, float* scores, int32_t* ids, int32_t* fallback_counter,
                          int batch, int hq, int hkv, int qt, int nt, int r, int topk, cudaStream_t stream);
