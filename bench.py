@@ -34,7 +34,7 @@ WORKLOAD = {"name": "q_centric_mha_32k", "B": 1, "Hq": 32, "Hkv": 32, "N": 32768
 # DRAM bytes per launch of the attention kernel on this workload
 # (dram__bytes_read.sum + dram__bytes_write.sum, Nsight Compute capture
 # summarised in profiles/q_centric_kernel_mha_32k.md).
-NCU_TRAFFIC_BYTES = 1.090e9
+NCU_TRAFFIC_BYTES = 1.145e9
 
 
 def flops(w):
