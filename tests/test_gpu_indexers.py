@@ -140,6 +140,40 @@ def test_summary_selector_tensor_core_path_ties_and_constant_inputs():
     m.device_status()
 
 
+@pytest.mark.parametrize("b,hkv,g,sq,skv,r,topk", [
+    (2, 1, 16, 4096, 16384, 1, 16),      # the reference's selector benchmark shape: 16 query descriptors per list
+    (2, 1, 16, 4096, 4096, 4, 16),       # 64 query descriptors, 4 key representatives per block
+    (1, 2, 8, 1024, 2048 + 128, 2, 8),   # 16 descriptors, a block count that is no multiple of the chunk
+    (1, 1, 1, 512, 8192, 1, 32),         # MHA: padded query descriptors
+    (1, 4, 4, 256, 1024, 4, 8),
+])
+def test_small_problem_selector_equals_the_exact_kernels(b, hkv, g, sq, skv, r, topk):
+    """The cluster kernel for small problems (taken by run() and run_fast()) against the
+    staged exact kernels (prepare() + score()): descriptors, scores and ids bit for bit,
+    and ids against the CPU oracle."""
+    m = sp()
+    q, k, _ = gen.make_qkv(b, hkv * g, hkv, sq, skv, seed=31, k_block_offset=0.5)
+    qc, kc = q.cuda(), k.cuda()
+    staged = m.SummarySelector(qc, kc, r, topk=topk, keep_scores=True)
+    staged.prepare()
+    staged.score()
+    fused = m.SummarySelector(qc, kc, r, topk=topk, keep_scores=True)
+    fused.run()
+    fast = m.SummarySelector(qc, kc, r, topk=topk, keep_scores=False)
+    fast.aux.fill_(7)
+    fast.run_fast()
+    torch.cuda.synchronize()
+    m.device_status()
+    assert torch.equal(fused.kd.view(torch.int16), staged.kd.view(torch.int16))
+    assert torch.equal(fused.qd.view(torch.int16), staged.qd.view(torch.int16))
+    assert torch.equal(fused.scores, staged.scores)
+    assert torch.equal(fused.ids, staged.ids)
+    assert torch.equal(fast.ids, staged.ids)
+    assert fast.fallback_lists() == 0
+    ref = oracle.summary_select(q, k, r, topk)[3]
+    assert torch.equal(staged.ids.cpu(), ref)
+
+
 def test_summary_selector_duplicate_scores_tie_to_lower_id():
     """Duplicate KV blocks give exactly equal scores: the lower id must come first."""
     m = sp()
