@@ -280,52 +280,6 @@ __device__ __forceinline__ float2 add2(float2 a, float2 b) {
       : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
   return d;
 }
-__device__ __forceinline__ float2 sub2(float2 a, float2 b) {
-  float2 d;
-  asm("{\n\t"
-      ".reg .b64 ra, rb, rd;\n\t"
-      "mov.b64 ra, {%2, %3};\n\t"
-      "mov.b64 rb, {%4, %5};\n\t"
-      "sub.rn.f32x2 rd, ra, rb;\n\t"
-      "mov.b64 {%0, %1}, rd;\n\t"
-      "}"
-      : "=f"(d.x), "=f"(d.y)
-      : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
-  return d;
-}
-// a + b rounded toward minus infinity
-__device__ __forceinline__ float2 add2_rm(float2 a, float2 b) {
-  float2 d;
-  asm("{\n\t"
-      ".reg .b64 ra, rb, rd;\n\t"
-      "mov.b64 ra, {%2, %3};\n\t"
-      "mov.b64 rb, {%4, %5};\n\t"
-      "add.rm.f32x2 rd, ra, rb;\n\t"
-      "mov.b64 {%0, %1}, rd;\n\t"
-      "}"
-      : "=f"(d.x), "=f"(d.y)
-      : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
-  return d;
-}
-// 2^x for a pair on the FMA pipe (no special-function unit): x = n + f with
-// n = floor(x) taken from the mantissa of x + 1.5*2^23 (rounded down), 2^f from a
-// cubic fitted on [0,1) (max relative error 8.6e-5, far below bf16 resolution),
-// and n added into the exponent field. Inputs are clamped at -126.
-__device__ __forceinline__ float2 exp2_poly2(float2 x) {
-  const float magic = 12582912.0f;
-  x.x = fmaxf(x.x, -126.0f);
-  x.y = fmaxf(x.y, -126.0f);
-  const float2 t = add2_rm(x, make_float2(magic, magic));
-  const float2 n = sub2(t, make_float2(magic, magic));
-  const float2 f = sub2(x, n);
-  float2 p = fma2(make_float2(0.07706618f, 0.07706618f), f, make_float2(0.22764593f, 0.22764593f));
-  p = fma2(p, f, make_float2(0.6951166f, 0.6951166f));
-  p = fma2(p, f, make_float2(1.0f, 1.0f));
-  float2 r;
-  r.x = __uint_as_float(__float_as_uint(p.x) + (__float_as_uint(t.x) << 23));
-  r.y = __uint_as_float(__float_as_uint(p.y) + (__float_as_uint(t.y) << 23));
-  return r;
-}
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);

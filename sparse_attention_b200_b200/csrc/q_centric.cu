@@ -38,11 +38,7 @@ constexpr int PANEL_BYTES = TILE * 128;            // 64-column half of a tile
 #ifndef SB_QC_RING
 #define SB_QC_RING 4
 #endif
-#ifndef SB_QC_POLY_PERIOD
-#define SB_QC_POLY_PERIOD 0
-#endif
 constexpr int RING = SB_QC_RING;     // K/V ring slots
-constexpr int POLY_PERIOD = SB_QC_POLY_PERIOD;   // one pair of exponentials in this many runs on the FMA pipe (0: none)
 constexpr int NUM_THREADS = 512;     // four warpgroups: softmax 0, softmax 1, epilogue, {MMA, TMA, 2 idle}
 constexpr int EPI_WARP0 = 8;         // warps 8..11: warp w serves tensor-memory lanes 32 * (w % 4) ..
 constexpr int MMA_WARP = 12;
@@ -625,8 +621,9 @@ q_centric_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
           }
         }
         if ((warp & 3) == 0) TRACE(q * 8 + 2, trace_n);
-        // p = 2^(s*scale - max): packed FMAs; one pair in every POLY_PERIOD goes to
-        // the FMA-pipe polynomial, the rest to the special-function unit.
+        // p = 2^(s*scale - max): packed FMAs, exponentials on the special-function unit (moving a
+        // share of them to an FMA-pipe polynomial was measured slower: the softmax warps are
+        // issue-bound there).
         float2 part[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
         const float2 scale2 = make_float2(p.scale_log2, p.scale_log2);
         const float2 neg_max2 = make_float2(-row_max, -row_max);
@@ -637,16 +634,7 @@ q_centric_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
           for (int j = 0; j < 16; ++j) {
             const float2 x = fma2(make_float2(__uint_as_float(sv[c][2 * j]), __uint_as_float(sv[c][2 * j + 1])),
                                   scale2, neg_max2);
-            float2 e;
-            if (POLY_PERIOD > 0 && (j % (POLY_PERIOD > 0 ? POLY_PERIOD : 1)) == (POLY_PERIOD - 1)) {
-              e = exp2_poly2(x);
-            } else {
-#ifdef SB_QC_EXPERIMENT_NOEXP
-              e = x;
-#else
-              e = make_float2(ex2_approx(x.x), ex2_approx(x.y));
-#endif
-            }
+            const float2 e = make_float2(ex2_approx(x.x), ex2_approx(x.y));
             part[j & 1] = add2(part[j & 1], e);
             pk[j] = pack_bf16x2(e.x, e.y);
           }
