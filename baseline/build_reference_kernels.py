@@ -1,9 +1,18 @@
-"""Compile the reference's own Q-centric kernels (p02 / p03) from sources copied, unmodified,
-into the git-ignored baseline/_ref/q_centric/ (nvcc cross-compiles without a GPU), with the
-flags of attention/q_centric/progression.py:29-36. The resulting shared library registers
-torch.ops.xomtention_progression.{attention, attention_out}; `bench.py --workload refcmp`
-times it next to this repository's kernel on the same box. The only added file is a stub for
-the archived p01 launcher, which the published tree does not contain."""
+"""Compile the reference's own kernels from sources copied, unmodified, into the git-ignored
+baseline/_ref/ (nvcc cross-compiles without a GPU):
+
+* q_centric/  -> xomtention_progression.so (p02 / p03), flags of attention/q_centric/progression.py:29-36;
+  registers torch.ops.xomtention_progression.{attention, attention_out}; timed by
+  `bench.py --workload refcmp`. The only added file is a stub for the archived p01 launcher, which
+  the published tree does not contain.
+* kv_centric/ -> the round-11 KV-centric extension, built by the reference's own
+  optimization_round11/api11.py:load_extension (torch.ops.xomtention_kvopt11); timed by
+  `bench.py --workload kvtoken`.
+* r1_r4/ holds the reference's Triton selectors (compiled by Triton at run time); timed by
+  `bench.py --workload refsel`.
+
+Copy the reference's attention/q_centric sources, attention/kv_centric and indexers/r1_r4 into
+baseline/_ref/ first; nothing under baseline/_ref/ is committed."""
 import os
 import sys
 
@@ -31,7 +40,24 @@ def build():
     print(LIB)
 
 
+def build_kv_centric():
+    root = os.path.join(HERE, "_ref", "kv_centric", "optimization_round11")
+    if not os.path.isdir(root):
+        print("baseline/_ref/kv_centric absent: skipped")
+        return
+    os.environ["MAX_JOBS"] = os.environ.get("MAX_JOBS", "8")
+    os.environ.setdefault("TORCH_CUDA_ARCH_LIST", "10.0a")
+    sys.path.insert(0, root)
+    import api11
+    try:
+        api11.load_extension()
+    except OSError as e:   # the load step needs libcuda; the compile has finished by then
+        print("built; not loaded here:", e)
+    print(os.path.join(root, "build"))
+
+
 if __name__ == "__main__":
     if not os.path.isdir(SRC):
         sys.exit("copy the reference's attention/q_centric sources into baseline/_ref/q_centric first")
     build()
+    build_kv_centric()

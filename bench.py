@@ -378,6 +378,36 @@ def timed(fn, steps, warmup, barrier):
     return e0.elapsed_time(e1) / steps
 
 
+def reference_kv_centric(q, k, v, selected, ours, steps, barrier):
+    """The reference's own round-11 KV-centric operator (variant tma16_bf16: token-major Q, bf16
+    partials; attention/kv_centric/optimization_round11/api11.py:50-92), prebuilt unmodified by
+    baseline/build_reference_kernels.py in the git-ignored baseline/_ref/, timed on the same tensors
+    with the same protocol. Its Q layout [B,Sq,Hq,D] is made once outside the timing, as in the
+    reference's benchmark. Returns None when it is not built here."""
+    import torch
+    root = os.path.join(os.path.dirname(os.path.abspath(__file__)), "baseline", "_ref", "kv_centric",
+                        "optimization_round11")
+    lib = os.path.join(root, "build", "xomtention_kvopt11.so")
+    if not os.path.exists(lib) or tuple(selected.shape[1:]) != (1, q.shape[2], 16) or q.shape[1] != 16:
+        return None
+    sys.path.insert(0, root)
+    import api11
+    torch.ops.load_library(lib)
+    api11._OPS = torch.ops.xomtention_kvopt11
+    api11.old_plan.load_extension = lambda: api11._OPS
+    q_tm = q.permute(0, 2, 1, 3).contiguous()
+    ref = api11.Prepared(q_tm, k, v, selected, variant=api11.VARIANTS["tma16_bf16"])
+    stages = {"metadata_ms": timed(ref.metadata, steps, 3, barrier), "main_ms": timed(ref.main, steps, 3, barrier),
+              "combine_ms": timed(ref.combine, steps, 3, barrier)}
+    rounds = []
+    for _ in range(3):                      # interleaved with ours: same thermal state for both
+        rounds.append((timed(ref.run, steps, 3, barrier), timed(ours.run, steps, 3, barrier)))
+    diff = (ref.out.float() - ours.out.float()).abs().max().item()
+    lse_diff = (ref.out_lse - ours.out_lse).abs().max().item()
+    return {"variant": "tma16_bf16", "ms": min(r[0] for r in rounds), "ours_ms_interleaved": min(r[1] for r in rounds),
+            "stages": stages, "max_abs_diff_out": diff, "max_abs_diff_lse": lse_diff}
+
+
 def run_kv_token(args):
     """The reference's own KV-centric benchmark shape (B8, Hq16, Hkv1, Sq = Skv = 4096, TopK 16,
     per-TOKEN independent lists; benchmarks/ch5_kv_centric/round11_final/RESULTS_RU.md:9-13)
@@ -402,6 +432,7 @@ def run_kv_token(args):
               "combine_ms": timed(prep.combine, args.steps, 3, barrier)}
     ms = timed(prep.run, args.steps, 3, barrier)
     sp.device_status()
+    same_box = reference_kv_centric(q, k, v, selected, prep, args.steps, barrier)
     fl = 4.0 * B * Hq * S * (topk * 128) * 128
     peak_tf, peak_gbs, peak_src = measured_peaks()
     value = fl / (ms * 1e-3) / 1e12
@@ -412,6 +443,7 @@ def run_kv_token(args):
                                  "topk": topk}, "stages_rank0": stages,
                       "reference_published": {"ms": 1.503, "tflops": 365.8, "variant": "tma16_bf16",
                                               "source": "benchmarks/ch5_kv_centric/round11_final/RESULTS_RU.md:12"},
+                      "reference_same_box": same_box,
                       "roofline": {"bound": "tensor", "achieved": value, "peak": peak_tf, "unit": "TFLOP/s",
                                    "frac": value / peak_tf, "traffic": None, "peak_source": peak_src,
                                    "kernel": "kv_token_kernel + combine_kernel"}}), flush=True)
@@ -528,6 +560,17 @@ def run_refsel(args):
     torch.cuda.set_device(0)
     dev = torch.device("cuda", 0)
     B, Hq, Hkv, Sq, topk = 2, 16, 1, 4096, 16
+    # the reference's own Triton selectors (indexers/r1_r4/block_selectors.py:9-55), copied unmodified
+    # into the git-ignored baseline/_ref/r1_r4, when present: same tensors, same protocol
+    ref_sel = None
+    ref_dir = os.path.join(os.path.dirname(os.path.abspath(__file__)), "baseline", "_ref", "r1_r4")
+    if os.path.isdir(ref_dir):
+        try:
+            sys.path.insert(0, ref_dir)
+            import block_selectors as ref_sel
+        except Exception as e:          # Triton missing or unusable on this box
+            print(json.dumps({"workload": "refsel", "reference_same_box": f"unavailable: {e}"}), flush=True)
+            ref_sel = None
     for Skv in (4096, 8192, 16384):
         gen = torch.Generator(device=dev).manual_seed(29)
         q = torch.randn((B, Hq, Sq, 128), device=dev, generator=gen).to(torch.bfloat16)
@@ -550,6 +593,13 @@ def run_refsel(args):
                                "selector_to_attention": round(t_pipe, 2), "fallback_lists": sel.fallback_lists()}
             pub = REFSEL_PUBLISHED[Skv][name]
             row["reference_published_us"][name] = {"selector": pub[0], "selector_to_p03": pub[1]}
+            if ref_sel is not None:
+                rs = ref_sel.SummarySelector(q, k, r)
+                t_ref = graph_time_us(rs.run)
+                torch.cuda.synchronize()
+                same = (rs.ids == sel.ids).all(-1).float().mean().item()
+                row.setdefault("reference_same_box_us", {})[name] = {"selector": round(t_ref, 2),
+                                                                      "lists_with_identical_ids": round(same, 4)}
         qc, qs = sp.quantize_queries(q, Hkv)
         kc, ks = sp.quantize_keys(k)
         inputs = sp.prepare_fp4_inputs(qc, kc, qs, ks, batch_size=B, len_q=Sq, len_kv=Skv)

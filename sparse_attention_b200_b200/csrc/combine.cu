@@ -1,7 +1,7 @@
 // Log-sum-exp merge of partial (O, LSE): HBM-bound streaming kernel.
 //   m = max_r L_r, w_r = exp(L_r - m), O = sum_r w_r O_r / sum_r w_r,
 //   LSE = m + log(sum_r w_r)            (ranks accumulated in order 0..R-1)
-// Half a warp per output row, eight features per lane, a whole batch of ranks in
+// One warp per output row, four features per lane, a whole batch of ranks in
 // flight per lane. Partials may be fp32 or
 // bf16 and are addressed with strides, so both the rank-major layout
 // [R, rows, 128] written by the segment kernel and the rank-inner layout
@@ -15,110 +15,107 @@
 namespace sb {
 namespace {
 
-// eight consecutive features of one partial row, kept raw until the weights are known
+// four consecutive features of one partial row, kept raw until the weights are known
 template <typename T>
-struct Raw8;
+struct Raw4;
 template <>
-struct Raw8<float> {
-  float4 a, b;
-  __device__ __forceinline__ void load(const float* p) {
-    a = __ldcs(reinterpret_cast<const float4*>(p));
-    b = __ldcs(reinterpret_cast<const float4*>(p) + 1);
-  }
-  __device__ __forceinline__ void unpack(float (&f)[8]) const {
-    f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
-  }
-  static constexpr int BATCH = 8;      // ranks in flight per lane (64 registers)
+struct Raw4<float> {
+  float4 v;
+  __device__ __forceinline__ void load(const float* p) { v = __ldcs(reinterpret_cast<const float4*>(p)); }
+  __device__ __forceinline__ void unpack(float (&f)[4]) const { f[0] = v.x; f[1] = v.y; f[2] = v.z; f[3] = v.w; }
 };
 template <>
-struct Raw8<__nv_bfloat16> {
-  uint4 raw;
-  __device__ __forceinline__ void load(const __nv_bfloat16* p) { raw = __ldcs(reinterpret_cast<const uint4*>(p)); }
-  __device__ __forceinline__ void unpack(float (&f)[8]) const {
+struct Raw4<__nv_bfloat16> {
+  uint2 raw;
+  __device__ __forceinline__ void load(const __nv_bfloat16* p) { raw = __ldcs(reinterpret_cast<const uint2*>(p)); }
+  __device__ __forceinline__ void unpack(float (&f)[4]) const {
     const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
-#pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      const float2 v = __bfloat1622float2(h[e]);
-      f[2 * e] = v.x;
-      f[2 * e + 1] = v.y;
-    }
+    const float2 a = __bfloat1622float2(h[0]), b = __bfloat1622float2(h[1]);
+    f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y;
   }
-  static constexpr int BATCH = 16;
 };
 
-// Half a warp (16 lanes x 8 features) per output row. The raw partial rows of a whole
-// batch of ranks (16 for bf16, 8 for fp32) are requested first; the LSEs of the row are
-// fetched one rank per lane (coalesced) and reduced with shuffles while those loads are
-// in flight, so a row costs one memory round trip per batch instead of several dependent
-// ones. A rank of weight 0 is dropped with a select, whatever it holds.
-template <typename T>
-__global__ void __launch_bounds__(256) combine_kernel(const T* __restrict__ partial, const float* __restrict__ lses,
+// One warp per output row (RPW rows at a time when there are few ranks), four features per
+// lane, four warps per block and no persistent loop: registers stay low (16 (row, rank) pieces
+// of raw data per lane = 32-64 registers), so an SM keeps 32-64 rows x R ranks of loads in
+// flight, which is what a streaming kernel with two dependent round trips (LSEs, partial rows)
+// needs to approach HBM bandwidth. The raw partial rows are requested first; the LSEs of a row
+// are fetched one rank per lane and reduced with shuffles while those loads fly. A rank of
+// weight 0 is dropped with a select, whatever it holds.
+template <typename T, int RPW>
+__global__ void __launch_bounds__(128) combine_kernel(const T* __restrict__ partial, const float* __restrict__ lses,
                                                       __nv_bfloat16* __restrict__ out, float* __restrict__ out_lse,
                                                       long long rows, int ranks, long long p_stride_rank,
                                                       long long p_stride_row, long long l_stride_rank,
                                                       long long l_stride_row) {
-  constexpr int BATCH = Raw8<T>::BATCH;
-  const int sub = threadIdx.x & 15;
-  const unsigned half_mask = 0xffffu << (threadIdx.x & 16);
-  const long long halves_total = static_cast<long long>(gridDim.x) * (blockDim.x >> 4);
-  const long long first = static_cast<long long>(blockIdx.x) * (blockDim.x >> 4) + (threadIdx.x >> 4);
-  // every lane of a warp runs the same number of iterations (the shuffles need both halves)
-  const long long iters = (rows + halves_total - 1) / halves_total;
-  for (long long it = 0; it < iters; ++it) {
-    const long long row_raw = first + it * halves_total;
-    const bool live = row_raw < rows;
-    const long long row = live ? row_raw : rows - 1;
-    const T* base = partial + row * p_stride_row + sub * 8;
+  constexpr int CB = 16 / RPW;                   // ranks per batch
+  const int lane = threadIdx.x & 31;
+  const long long row0 = (static_cast<long long>(blockIdx.x) * 4 + (threadIdx.x >> 5)) * RPW;
+  if (row0 >= rows) return;                      // whole warps leave together
+  Raw4<T> val[RPW][CB];
+#pragma unroll
+  for (int rr = 0; rr < RPW; ++rr) {
+    const long long row = min(row0 + rr, rows - 1);
+#pragma unroll
+    for (int j = 0; j < CB; ++j)
+      if (j < ranks) val[rr][j].load(partial + row * p_stride_row + lane * 4 + j * p_stride_rank);
+  }
+#pragma unroll
+  for (int rr = 0; rr < RPW; ++rr) {
+    const bool live = row0 + rr < rows;
+    const long long row = live ? row0 + rr : rows - 1;
+    const T* base = partial + row * p_stride_row + lane * 4;
     const float* lbase = lses + row * l_stride_row;
-    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-    float denom = 0.f;
-    Raw8<T> val[BATCH];
-#pragma unroll
-    for (int j = 0; j < BATCH; ++j)
-      if (j < ranks) val[j].load(base + j * p_stride_rank);
-    // row maximum of the LSEs: lane `sub` takes ranks sub, sub + 16, ...
+    // row maximum of the LSEs: lane l takes ranks l, l + 32, ...
     float maximum = -CUDART_INF_F;
-    for (int r = sub; r < ranks; r += 16) maximum = fmaxf(maximum, __ldg(lbase + r * l_stride_rank));
+    for (int r = lane; r < ranks; r += 32) maximum = fmaxf(maximum, __ldg(lbase + r * l_stride_rank));
 #pragma unroll
-    for (int d = 8; d >= 1; d >>= 1) maximum = fmaxf(maximum, __shfl_xor_sync(0xffffffffu, maximum, d));
-    if (maximum > -CUDART_INF_F) {            // uniform within the half warp
-      for (int r0 = 0; r0 < ranks; r0 += BATCH) {
+    for (int d = 16; d >= 1; d >>= 1) maximum = fmaxf(maximum, __shfl_xor_sync(0xffffffffu, maximum, d));
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    float denom = 0.f;
+    if (maximum > -CUDART_INF_F) {               // uniform within the warp
+      for (int r0 = 0; r0 < ranks; r0 += CB) {
         if (r0 > 0) {
 #pragma unroll
-          for (int j = 0; j < BATCH; ++j)
-            if (r0 + j < ranks) val[j].load(base + (r0 + j) * p_stride_rank);
+          for (int j = 0; j < CB; ++j)
+            if (r0 + j < ranks) val[rr][j].load(base + (r0 + j) * p_stride_rank);
         }
-        // weight of rank r0 + (sub % BATCH) in this lane (ranks of a batch sit in lanes 0..BATCH-1)
+        // weight of rank r0 + lane in lane `lane` (the ranks of a batch sit in lanes 0..CB-1)
         float mine = 0.f;
-        if (sub < BATCH && r0 + sub < ranks) mine = expf(__ldg(lbase + (r0 + sub) * l_stride_rank) - maximum);
+        if (lane < CB && r0 + lane < ranks) mine = expf(__ldg(lbase + (r0 + lane) * l_stride_rank) - maximum);
 #pragma unroll
-        for (int j = 0; j < BATCH; ++j) {
-          const float w = __shfl_sync(half_mask, mine, (threadIdx.x & 16) + j);   // exp(-inf) = 0
+        for (int j = 0; j < CB; ++j) {
+          const float w = __shfl_sync(0xffffffffu, mine, j);   // exp(-inf) = 0
           if (r0 + j < ranks) {
-            float f[8];
-            val[j].unpack(f);
+            float f[4];
+            val[rr][j].unpack(f);
             denom += w;
 #pragma unroll
-            for (int e = 0; e < 8; ++e) acc[e] = fmaf(w, w > 0.f ? f[e] : 0.f, acc[e]);
+            for (int e = 0; e < 4; ++e) acc[e] = fmaf(w, w > 0.f ? f[e] : 0.f, acc[e]);
           }
         }
       }
       const float inv = 1.0f / denom;
 #pragma unroll
-      for (int e = 0; e < 8; ++e) acc[e] *= inv;
+      for (int e = 0; e < 4; ++e) acc[e] *= inv;
     }
     if (live) {
-      uint4 packed;
-      uint32_t* pw = reinterpret_cast<uint32_t*>(&packed);
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        __nv_bfloat162 h = __floats2bfloat162_rn(acc[2 * e], acc[2 * e + 1]);
-        pw[e] = *reinterpret_cast<uint32_t*>(&h);
-      }
-      *reinterpret_cast<uint4*>(out + row * 128 + sub * 8) = packed;
-      if (sub == 0 && out_lse) out_lse[row] = (maximum > -CUDART_INF_F) ? maximum + logf(denom) : -CUDART_INF_F;
+      uint2 packed;
+      __nv_bfloat162 h0 = __floats2bfloat162_rn(acc[0], acc[1]), h1 = __floats2bfloat162_rn(acc[2], acc[3]);
+      packed.x = *reinterpret_cast<uint32_t*>(&h0);
+      packed.y = *reinterpret_cast<uint32_t*>(&h1);
+      *reinterpret_cast<uint2*>(out + row * 128 + lane * 4) = packed;
+      if (lane == 0 && out_lse) out_lse[row] = (maximum > -CUDART_INF_F) ? maximum + logf(denom) : -CUDART_INF_F;
     }
   }
+}
+
+template <typename T, int RPW>
+static void combine_launch(const void* partial, const float* lses, void* out, float* out_lse, long long rows, int ranks,
+                           long long psr, long long psw, long long lsr, long long lsw, cudaStream_t stream) {
+  const long long blocks = (rows + 4 * RPW - 1) / (4 * RPW);
+  combine_kernel<T, RPW><<<static_cast<unsigned>(blocks), 128, 0, stream>>>(
+      static_cast<const T*>(partial), lses, static_cast<__nv_bfloat16*>(out), out_lse, rows, ranks, psr, psw, lsr, lsw);
 }
 
 }  // namespace
@@ -128,18 +125,17 @@ int launch_combine(const void* partial, int partial_is_f32, const float* lses, v
                    long long l_stride_rank, long long l_stride_row, cudaStream_t stream) {
   DeviceCtx* ctx = device_ctx();
   if (!ctx) return SB_ERR_CUDA;
-  const long long blocks_needed = (rows + 15) / 16;
-  const long long cap = static_cast<long long>(ctx->sm_count) * 64;
-  const int grid = static_cast<int>(blocks_needed < cap ? blocks_needed : cap);
-  if (partial_is_f32)
-    combine_kernel<float><<<grid, 256, 0, stream>>>(static_cast<const float*>(partial), lses,
-                                                    static_cast<__nv_bfloat16*>(out), out_lse, rows, ranks,
-                                                    p_stride_rank, p_stride_row, l_stride_rank, l_stride_row);
-  else
-    combine_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(partial), lses,
-                                                            static_cast<__nv_bfloat16*>(out), out_lse, rows, ranks,
-                                                            p_stride_rank, p_stride_row, l_stride_rank,
-                                                            l_stride_row);
+  if ((rows + 3) / 4 > 0x7fffffffLL) return set_error(SB_ERR_INVALID, "too many rows for one combine launch");
+  // few ranks: several rows per warp, so that every lane still has 16 loads in flight
+  if (partial_is_f32) {
+    if (ranks <= 4) combine_launch<float, 4>(partial, lses, out, out_lse, rows, ranks, p_stride_rank, p_stride_row, l_stride_rank, l_stride_row, stream);
+    else if (ranks <= 8) combine_launch<float, 2>(partial, lses, out, out_lse, rows, ranks, p_stride_rank, p_stride_row, l_stride_rank, l_stride_row, stream);
+    else combine_launch<float, 1>(partial, lses, out, out_lse, rows, ranks, p_stride_rank, p_stride_row, l_stride_rank, l_stride_row, stream);
+  } else {
+    if (ranks <= 4) combine_launch<__nv_bfloat16, 4>(partial, lses, out, out_lse, rows, ranks, p_stride_rank, p_stride_row, l_stride_rank, l_stride_row, stream);
+    else if (ranks <= 8) combine_launch<__nv_bfloat16, 2>(partial, lses, out, out_lse, rows, ranks, p_stride_rank, p_stride_row, l_stride_rank, l_stride_row, stream);
+    else combine_launch<__nv_bfloat16, 1>(partial, lses, out, out_lse, rows, ranks, p_stride_rank, p_stride_row, l_stride_rank, l_stride_row, stream);
+  }
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? SB_OK : set_error(SB_ERR_CUDA, cudaGetErrorString(e));
 }
