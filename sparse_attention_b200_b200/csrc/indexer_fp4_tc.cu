@@ -416,6 +416,10 @@ int launch_fp4_indexer_tc(const void* qp, const void* qs, const void* kp, const 
   int cand = topk + extra;
   if (cand > tiles) cand = tiles;
   if (cand > C_MAX || tiles > MAX_TILES) return 1;
+  // Every candidate is re-scored exactly: when half the pages or more would be candidates the
+  // pre-filter saves less than it costs (measured at 32 and 64 pages with top-16) and the exact
+  // scorer is taken instead.
+  if (2 * cand >= tiles) return 1;
   const long long q_rows = static_cast<long long>(batch) * len_q * hidx;
   const long long k_rows = static_cast<long long>(batch) * tiles * hk * 128;
   if (q_rows >= (1LL << 31) || k_rows >= (1LL << 31)) return 1;
