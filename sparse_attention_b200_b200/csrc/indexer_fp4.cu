@@ -16,6 +16,7 @@
 // tile_max_topk16_kernel (indexers/fp4/tile_topk.cu:38-126), any top-k and any
 // number of KV tiles; integer dot products run on dp4a.
 #include "internal.h"
+#include <cstdlib>
 #include "topk.cuh"
 #include "fp4_exact.cuh"
 #include <cuda_bf16.h>
@@ -179,12 +180,15 @@ __global__ void __launch_bounds__(256) fp4_score_kernel(const uint8_t* __restric
       for (int i = 0; i < 8; ++i)
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-          int isum = __dp4a(static_cast<int>(qv[i].x), static_cast<int>(kv[j].x), 0);
+          // The integer sum is accumulated on top of the bit pattern of 1.5 * 2^23: the result
+          // IS the float 12582912 + sum (|sum| <= 2304), and one exact subtraction gives
+          // float(sum) without an int-to-float conversion (a quarter-rate instruction).
+          int isum = __dp4a(static_cast<int>(qv[i].x), static_cast<int>(kv[j].x), 0x4B400000);
           isum = __dp4a(static_cast<int>(qv[i].y), static_cast<int>(kv[j].y), isum);
           isum = __dp4a(static_cast<int>(qv[i].z), static_cast<int>(kv[j].z), isum);
           isum = __dp4a(static_cast<int>(qv[i].w), static_cast<int>(kv[j].w), isum);
           // exact product (<= 12 + 8 significant bits), one rounding in the add
-          acc[i][j] = fmaf(static_cast<float>(isum), qsc[i] * ksc[j], acc[i][j]);
+          acc[i][j] = fmaf(__int_as_float(isum) - 12582912.0f, qsc[i] * ksc[j], acc[i][j]);
         }
     }
     // per query: max over this thread's 8 keys, then over the 16 threads of the row
@@ -204,6 +208,124 @@ __global__ void __launch_bounds__(256) fp4_score_kernel(const uint8_t* __restric
     if (tile_scores) {
       tile_best = fmaxf(tile_best, __shfl_xor_sync(0xffffffffu, tile_best, 16));
       if ((tid & 31) == 0) red[tid >> 5] = tile_best;
+      __syncthreads();
+      if (tid == 0) {
+        float m = red[0];
+#pragma unroll
+        for (int w = 1; w < 8; ++w) m = fmaxf(m, red[w]);
+        tile_scores[((static_cast<long long>(b) * hidx + h) * qt + qtile) * tiles + pg] = m;
+      }
+    }
+  }
+}
+
+// The same scores with the integer group sums on the tensor cores: one
+// mma.sync.m16n8k16 (s8 x s8 -> s32) is exactly one 16-element scale group of a 16 x 8 patch
+// of (query, key) pairs, and integer accumulation is exact, so every score is bit-identical
+// with fp4_score_kernel: acc = fma(float(group sum), qs * ks, acc) in group order. The
+// accumulator starts at the bit pattern of 1.5 * 2^23, which makes the result the float
+// 12582912 + sum; one exact subtraction replaces the int-to-float conversion.
+// Warp w owns queries 16 w .. 16 w + 15 against the 128 keys of the page (16 n-tiles).
+__device__ __forceinline__ void mma_s8_16816(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t b0, int c) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.s32.s8.s8.s32 {%0, %1, %2, %3}, {%4, %5}, {%6}, {%7, %8, %9, %10};"
+               : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+               : "r"(a0), "r"(a1), "r"(b0), "r"(c), "r"(c), "r"(c), "r"(c));
+}
+
+__global__ void __launch_bounds__(256) fp4_score_mma_kernel(const uint8_t* __restrict__ qp, const uint8_t* __restrict__ qs,
+                                                            const uint8_t* __restrict__ kp, const uint8_t* __restrict__ ks,
+                                                            float* __restrict__ query_scores,  // [Hidx, tiles, B*Sq] or null
+                                                            float* __restrict__ tile_scores,   // [B, Hidx, Qt, tiles] or null
+                                                            int batch, int hidx, int hk, int len_q, int tiles,
+                                                            int pages_per_cta) {
+  __shared__ uint32_t q_i8[128 * ROW_WORDS];
+  __shared__ uint32_t k_i8[128 * ROW_WORDS];
+  __shared__ float q_sc[128 * 8];
+  __shared__ __align__(8) float k_sc[8 * 128];     // [group][key]
+  __shared__ float red[8];
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int gid = lane >> 2, tig = lane & 3;
+  const int m0 = warp * 16;
+  const int qt = len_q >> 7;
+  const int qtile = blockIdx.y % qt;
+  const int bh = blockIdx.y / qt;
+  const int h = bh % hidx, b = bh / hidx;
+  const long long q_row0 = static_cast<long long>(b) * len_q + static_cast<long long>(qtile) * 128;
+
+  for (int e = tid; e < 128 * 16; e += 256) {
+    const int r = e >> 4, w = e & 15;
+    const uint32_t word = *reinterpret_cast<const uint32_t*>(qp + ((q_row0 + r) * hidx + h) * 64 + w * 4);
+    uint32_t a, c;
+    codes_to_int8(word, a, c);
+    q_i8[r * ROW_WORDS + 2 * w] = a;
+    q_i8[r * ROW_WORDS + 2 * w + 1] = c;
+  }
+  for (int e = tid; e < 128 * 8; e += 256)
+    q_sc[e] = 0.25f * e4m3_to_float(qs[((q_row0 + (e >> 3)) * hidx + h) * 8 + (e & 7)]);
+
+  const int page0 = blockIdx.x * pages_per_cta;
+  for (int pg = page0; pg < min(page0 + pages_per_cta, tiles); ++pg) {
+    __syncthreads();
+    const long long page = (static_cast<long long>(b) * tiles + pg) * hk + (hk > 1 ? h : 0);
+    for (int e = tid; e < 128 * 16; e += 256) {
+      const int r = e >> 4, w = e & 15;
+      const uint32_t word = __ldg(reinterpret_cast<const uint32_t*>(kp + (page * 128 + r) * 64 + w * 4));
+      uint32_t a, c;
+      codes_to_int8(word, a, c);
+      k_i8[r * ROW_WORDS + 2 * w] = a;
+      k_i8[r * ROW_WORDS + 2 * w + 1] = c;
+    }
+    for (int e = tid; e < 128 * 8; e += 256)
+      k_sc[(e & 7) * 128 + (e >> 3)] = e4m3_to_float(ks[(page * 128 + (e >> 3)) * 8 + (e & 7)]);
+    __syncthreads();
+
+    float acc[16][4];
+#pragma unroll
+    for (int n = 0; n < 16; ++n)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) acc[n][i] = 0.f;
+#pragma unroll 1
+    for (int g = 0; g < 8; ++g) {
+      const uint32_t a0 = q_i8[(m0 + gid) * ROW_WORDS + g * 4 + tig];
+      const uint32_t a1 = q_i8[(m0 + 8 + gid) * ROW_WORDS + g * 4 + tig];
+      const float qs0 = q_sc[(m0 + gid) * 8 + g], qs1 = q_sc[(m0 + 8 + gid) * 8 + g];
+#pragma unroll
+      for (int n = 0; n < 16; ++n) {
+        const uint32_t b0 = k_i8[(n * 8 + gid) * ROW_WORDS + g * 4 + tig];
+        const float2 kk = *reinterpret_cast<const float2*>(&k_sc[g * 128 + n * 8 + tig * 2]);
+        int d[4];
+        mma_s8_16816(d, a0, a1, b0, 0x4B400000);
+        // exact products (<= 12 + 8 significant bits), one rounding in each add
+        acc[n][0] = fmaf(__int_as_float(d[0]) - 12582912.0f, qs0 * kk.x, acc[n][0]);
+        acc[n][1] = fmaf(__int_as_float(d[1]) - 12582912.0f, qs0 * kk.y, acc[n][1]);
+        acc[n][2] = fmaf(__int_as_float(d[2]) - 12582912.0f, qs1 * kk.x, acc[n][2]);
+        acc[n][3] = fmaf(__int_as_float(d[3]) - 12582912.0f, qs1 * kk.y, acc[n][3]);
+      }
+    }
+    // per query: max over the thread's 32 keys of each of its two rows, then over the quad
+    float r0 = -CUDART_INF_F, r1 = -CUDART_INF_F;
+#pragma unroll
+    for (int n = 0; n < 16; ++n) {
+      r0 = fmaxf(r0, fmaxf(acc[n][0], acc[n][1]));
+      r1 = fmaxf(r1, fmaxf(acc[n][2], acc[n][3]));
+    }
+#pragma unroll
+    for (int dlt = 1; dlt < 4; dlt <<= 1) {
+      r0 = fmaxf(r0, __shfl_xor_sync(0xffffffffu, r0, dlt));
+      r1 = fmaxf(r1, __shfl_xor_sync(0xffffffffu, r1, dlt));
+    }
+    if (query_scores && tig == 0) {
+      float* dst = query_scores + (static_cast<long long>(h) * tiles + pg) * (static_cast<long long>(batch) * len_q) +
+                   q_row0 + m0 + gid;
+      dst[0] = r0;
+      dst[8] = r1;
+    }
+    if (tile_scores) {
+      float tile_best = fmaxf(r0, r1);
+#pragma unroll
+      for (int dlt = 4; dlt < 32; dlt <<= 1) tile_best = fmaxf(tile_best, __shfl_xor_sync(0xffffffffu, tile_best, dlt));
+      if (lane == 0) red[warp] = tile_best;
       __syncthreads();
       if (tid == 0) {
         float m = red[0];
@@ -279,9 +401,17 @@ int launch_fp4_scores(const void* qp, const void* qs, const void* kp, const void
   while (pages_per_cta > 1 && static_cast<long long>((tiles + pages_per_cta - 1) / pages_per_cta) * batch * hidx * qt < 592)
     pages_per_cta >>= 1;
   dim3 grid((tiles + pages_per_cta - 1) / pages_per_cta, batch * hidx * qt);
-  fp4_score_kernel<<<grid, 256, 0, stream>>>(static_cast<const uint8_t*>(qp), static_cast<const uint8_t*>(qs),
-                                             static_cast<const uint8_t*>(kp), static_cast<const uint8_t*>(ks),
-                                             query_scores, tile_scores, batch, hidx, hk, len_q, tiles, pages_per_cta);
+  // integer group sums on the tensor cores (bit-identical scores); SB_FP4_DP4A=1 keeps the dp4a kernel
+  static const bool use_dp4a = [] { const char* e = getenv("SB_FP4_DP4A"); return e && e[0] == '1'; }();
+  if (use_dp4a)
+    fp4_score_kernel<<<grid, 256, 0, stream>>>(static_cast<const uint8_t*>(qp), static_cast<const uint8_t*>(qs),
+                                               static_cast<const uint8_t*>(kp), static_cast<const uint8_t*>(ks),
+                                               query_scores, tile_scores, batch, hidx, hk, len_q, tiles, pages_per_cta);
+  else
+    fp4_score_mma_kernel<<<grid, 256, 0, stream>>>(static_cast<const uint8_t*>(qp), static_cast<const uint8_t*>(qs),
+                                                   static_cast<const uint8_t*>(kp), static_cast<const uint8_t*>(ks),
+                                                   query_scores, tile_scores, batch, hidx, hk, len_q, tiles,
+                                                   pages_per_cta);
   return check_launch();
 }
 

@@ -2,6 +2,7 @@
 block id), descriptors and scores bit-exact against the oracle's fixed
 arithmetic, and the reference's own gates against its stored outputs
 (benchmarks/ch4_selectors/harness.py:22-42, 116-119)."""
+import ctypes
 import os
 
 import numpy as np
@@ -256,8 +257,9 @@ def test_fp4_tensor_core_path_bit_exact():
     ids, _ = m.fp4_indexer_fast(inputs, topk=16)
     fx = np.load(os.path.join(G, "fp4.npz"))
     np.testing.assert_array_equal(ids.cpu().numpy(), fx["ids"])
-    # more pages than candidates, per-head key pages, top-4 and top-24
-    for (hidx, hk, lq, lkv, topk, seed) in [(2, 2, 256, 8192, 4, 5), (1, 1, 384, 16384, 24, 6)]:
+    # eight times more pages than candidates (the tensor-core path is taken only then), per-head
+    # key pages, top-4 and top-24
+    for (hidx, hk, lq, lkv, topk, seed) in [(2, 2, 256, 32768, 4, 5), (1, 1, 256, 49152, 24, 6)]:
         g = torch.Generator().manual_seed(seed)
         pages = lkv // 128
         qp = torch.randint(256, (lq, hidx, 64), dtype=torch.uint8, generator=g)
@@ -266,18 +268,23 @@ def test_fp4_tensor_core_path_bit_exact():
         qs = choices[torch.randint(7, (lq, hidx, 8), generator=g)].to(torch.float8_e4m3fn)
         ks = choices[torch.randint(7, (pages, hk, 128, 8), generator=g)].to(torch.float8_e4m3fn)
         inputs = m.prepare_fp4_inputs(qp.cuda(), kp.cuda(), qs.cuda(), ks.cuda(), batch_size=1, len_q=lq, len_kv=lkv)
-        ids, ws = m.fp4_indexer_fast(inputs, topk=topk)
+        fn = m.lib().sparse_b200_indexer_fp4_workspace_bytes
+        fn.restype = ctypes.c_int64
+        need = fn(1, hidx, hk, lq, lkv)
+        ws = torch.zeros(need, dtype=torch.uint8, device="cuda")
+        ids, ws = m.fp4_indexer_fast(inputs, topk=topk, workspace=ws)
         torch.cuda.synchronize()
         m.device_status()
+        assert ws[:4].view(torch.float32).item() > 0       # the key abs-max only the tensor-core path writes
         ref = oracle.fp4_select(oracle.fp4_scores(qp, qs, kp, ks, 1, lq, lkv), 1, lq, topk)
         assert torch.equal(ids.cpu(), ref)
         assert torch.equal(ids.cpu(), m.fp4_indexer(inputs, topk=topk).cpu())
         print("fallback tiles:", int(ws[4:8].view(torch.int32).item()))
     # quantised real data (configuration-4 flow) and exact ties (all-zero keys): lower id first
-    q, k, _ = gen.make_qkv(1, 16, 2, 512, 8192, seed=43, k_block_offset=0.5)
+    q, k, _ = gen.make_qkv(1, 16, 2, 256, 32768, seed=43, k_block_offset=0.5)
     qc, qsc = m.quantize_queries(q.cuda(), 2)
     kc, ksc = m.quantize_keys(k.cuda())
-    inputs = m.prepare_fp4_inputs(qc, kc, qsc, ksc, batch_size=1, len_q=512, len_kv=8192)
+    inputs = m.prepare_fp4_inputs(qc, kc, qsc, ksc, batch_size=1, len_q=256, len_kv=32768)
     ids, _ = m.fp4_indexer_fast(inputs, topk=8)
     assert torch.equal(ids.cpu(), m.fp4_indexer(inputs, topk=8).cpu())
     kc.zero_()
