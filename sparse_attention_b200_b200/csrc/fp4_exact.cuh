@@ -48,42 +48,44 @@ __device__ __forceinline__ void fp4_stage_rows(uint32_t* rows_i8, float* rows_sc
     rows_sc[e] = fold * e4m3_to_float(scales[(e >> 3) * scale_pitch + (e & 7)]);
 }
 
-// The 8 x 8 dots of thread (ty, tx); q scales must carry the 0.25 factor.
-__device__ __forceinline__ void fp4_block_dots(const uint32_t* q_i8, const float* q_sc, const uint32_t* k_i8,
-                                               const float* k_sc, int ty, int tx, float (&acc)[8][8]) {
+// Maximum over the 16 x 128 (query, key) scores of one warp: queries 16 * warp .. + 15 of the staged
+// query tile against the 128 staged keys, with the integer group sums on the tensor cores
+// (mma.sync m16n8k16, s8 x s8 -> s32, one scale group per instruction). Same arithmetic as
+// fp4_block_dots: acc = fma(float(group sum), qs * ks, acc) in group order, so the scores are
+// bit-identical; the accumulator starts at the bit pattern of 1.5 * 2^23 and one exact
+// subtraction turns the result into float(group sum). Returns this thread's partial maximum.
+__device__ __forceinline__ float fp4_block_max_mma(const uint32_t* q_i8, const float* q_sc, const uint32_t* k_i8,
+                                                   const float* k_sc, int warp, int lane) {
+  const int gid = lane >> 2, tig = lane & 3, m0 = warp * 16;
+  float acc[16][4];
 #pragma unroll
-  for (int i = 0; i < 8; ++i)
+  for (int n = 0; n < 16; ++n)
 #pragma unroll
-    for (int j = 0; j < 8; ++j) acc[i][j] = 0.f;
+    for (int i = 0; i < 4; ++i) acc[n][i] = 0.f;
 #pragma unroll 1
   for (int g = 0; g < 8; ++g) {
-    uint4 qv[8], kv[8];
-    float qsc[8], ksc[8];
+    const uint32_t a0 = q_i8[(m0 + gid) * FP4_ROW_WORDS + g * 4 + tig];
+    const uint32_t a1 = q_i8[(m0 + 8 + gid) * FP4_ROW_WORDS + g * 4 + tig];
+    const float qs0 = q_sc[(m0 + gid) * 8 + g], qs1 = q_sc[(m0 + 8 + gid) * 8 + g];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      qv[i] = *reinterpret_cast<const uint4*>(&q_i8[(ty * 8 + i) * FP4_ROW_WORDS + g * 4]);
-      qsc[i] = q_sc[(ty * 8 + i) * 8 + g];
+    for (int n = 0; n < 16; ++n) {
+      const uint32_t b0 = k_i8[(n * 8 + gid) * FP4_ROW_WORDS + g * 4 + tig];
+      const float k0 = k_sc[(n * 8 + tig * 2) * 8 + g], k1 = k_sc[(n * 8 + tig * 2 + 1) * 8 + g];
+      int d0, d1, d2, d3;
+      asm volatile(
+          "mma.sync.aligned.m16n8k16.row.col.s32.s8.s8.s32 {%0, %1, %2, %3}, {%4, %5}, {%6}, {%7, %7, %7, %7};"
+          : "=r"(d0), "=r"(d1), "=r"(d2), "=r"(d3)
+          : "r"(a0), "r"(a1), "r"(b0), "r"(0x4B400000));
+      acc[n][0] = fmaf(__int_as_float(d0) - 12582912.0f, qs0 * k0, acc[n][0]);
+      acc[n][1] = fmaf(__int_as_float(d1) - 12582912.0f, qs0 * k1, acc[n][1]);
+      acc[n][2] = fmaf(__int_as_float(d2) - 12582912.0f, qs1 * k0, acc[n][2]);
+      acc[n][3] = fmaf(__int_as_float(d3) - 12582912.0f, qs1 * k1, acc[n][3]);
     }
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      kv[j] = *reinterpret_cast<const uint4*>(&k_i8[(tx + 16 * j) * FP4_ROW_WORDS + g * 4]);
-      ksc[j] = k_sc[(tx + 16 * j) * 8 + g];
-    }
-#pragma unroll
-    for (int i = 0; i < 8; ++i)
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        // The integer sum is accumulated on top of the bit pattern of 1.5 * 2^23: the result
-        // IS the float 12582912 + sum (|sum| <= 2304), and one exact subtraction gives
-        // float(sum) without an int-to-float conversion (a quarter-rate instruction).
-        int isum = __dp4a(static_cast<int>(qv[i].x), static_cast<int>(kv[j].x), 0x4B400000);
-        isum = __dp4a(static_cast<int>(qv[i].y), static_cast<int>(kv[j].y), isum);
-        isum = __dp4a(static_cast<int>(qv[i].z), static_cast<int>(kv[j].z), isum);
-        isum = __dp4a(static_cast<int>(qv[i].w), static_cast<int>(kv[j].w), isum);
-        // exact product (<= 12 + 8 significant bits), one rounding in the add
-        acc[i][j] = fmaf(__int_as_float(isum) - 12582912.0f, qsc[i] * ksc[j], acc[i][j]);
-      }
   }
+  float m = -INFINITY;
+#pragma unroll
+  for (int n = 0; n < 16; ++n) m = fmaxf(m, fmaxf(fmaxf(acc[n][0], acc[n][1]), fmaxf(acc[n][2], acc[n][3])));
+  return m;
 }
 
 }  // namespace sb

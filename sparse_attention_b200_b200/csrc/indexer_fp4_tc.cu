@@ -271,7 +271,7 @@ fp4_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
   int32_t* cand_ids = reinterpret_cast<int32_t*>(gbase + OFF_B);
   int* cand_ex = reinterpret_cast<int*>(cand_ids + C_MAX);
   const int C = p.cand;
-  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+
   int32_t* out = p.ids + (static_cast<long long>(bh) * qt + qtile) * p.topk;
 
   fp4_stage_rows(q_i8, q_sc, p.qp + (q_row0 * p.hidx + h) * 64, static_cast<long long>(p.hidx) * 64,
@@ -333,14 +333,7 @@ fp4_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
     fp4_stage_rows(k_i8, k_sc, p.kp + page * 128 * 64, 64, p.ks + page * 128 * 8, 8, 1.0f);
     __syncthreads();
     float m = -INFINITY;
-    if (threadIdx.x < 256) {
-      float acc[8][8];
-      fp4_block_dots(q_i8, q_sc, k_i8, k_sc, ty, tx, acc);
-#pragma unroll
-      for (int i = 0; i < 8; ++i)
-#pragma unroll
-        for (int j = 0; j < 8; ++j) m = fmaxf(m, acc[i][j]);
-    }
+    if (threadIdx.x < 256) m = fp4_block_max_mma(q_i8, q_sc, k_i8, k_sc, warp, lane);
 #pragma unroll
     for (int d = 16; d > 0; d >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, d));
     return m;                              // per-warp maximum; lane 0 publishes it
