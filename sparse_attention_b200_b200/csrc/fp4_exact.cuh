@@ -48,6 +48,37 @@ __device__ __forceinline__ void fp4_stage_rows(uint32_t* rows_i8, float* rows_sc
     rows_sc[e] = fold * e4m3_to_float(scales[(e >> 3) * scale_pitch + (e & 7)]);
 }
 
+// Two fp32 lanes per instruction (round-to-nearest each lane, bit-identical with the scalar forms).
+__device__ __forceinline__ unsigned long long f32x2_pack(float lo, float hi) {
+  unsigned long long r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ unsigned long long f32x2_pack_bits(int lo, int hi) {
+  unsigned long long r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo), "r"(hi));
+  return r;
+}
+__device__ __forceinline__ void f32x2_unpack(unsigned long long v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ unsigned long long f32x2_mul(unsigned long long a, unsigned long long b) {
+  unsigned long long r;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ unsigned long long f32x2_sub(unsigned long long a, unsigned long long b) {
+  unsigned long long r;
+  asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ unsigned long long f32x2_fma(unsigned long long a, unsigned long long b,
+                                                        unsigned long long c) {
+  unsigned long long r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+
 // Maximum over the 16 x 128 (query, key) scores of one warp: queries 16 * warp .. + 15 of the staged
 // query tile against the 128 staged keys, with the integer group sums on the tensor cores
 // (mma.sync m16n8k16, s8 x s8 -> s32, one scale group per instruction). Same arithmetic as
@@ -57,34 +88,42 @@ __device__ __forceinline__ void fp4_stage_rows(uint32_t* rows_i8, float* rows_sc
 __device__ __forceinline__ float fp4_block_max_mma(const uint32_t* q_i8, const float* q_sc, const uint32_t* k_i8,
                                                    const float* k_sc, int warp, int lane) {
   const int gid = lane >> 2, tig = lane & 3, m0 = warp * 16;
-  float acc[16][4];
-#pragma unroll
-  for (int n = 0; n < 16; ++n)
-#pragma unroll
-    for (int i = 0; i < 4; ++i) acc[n][i] = 0.f;
+  const unsigned long long magic2 = f32x2_pack(12582912.0f, 12582912.0f);
+  float m = -INFINITY;
 #pragma unroll 1
-  for (int g = 0; g < 8; ++g) {
-    const uint32_t a0 = q_i8[(m0 + gid) * FP4_ROW_WORDS + g * 4 + tig];
-    const uint32_t a1 = q_i8[(m0 + 8 + gid) * FP4_ROW_WORDS + g * 4 + tig];
-    const float qs0 = q_sc[(m0 + gid) * 8 + g], qs1 = q_sc[(m0 + 8 + gid) * 8 + g];
+  for (int half = 0; half < 2; ++half) {         // 64 keys at a time: 32 accumulators per thread
+    unsigned long long acc[8][2];
 #pragma unroll
-    for (int n = 0; n < 16; ++n) {
-      const uint32_t b0 = k_i8[(n * 8 + gid) * FP4_ROW_WORDS + g * 4 + tig];
-      const float k0 = k_sc[(n * 8 + tig * 2) * 8 + g], k1 = k_sc[(n * 8 + tig * 2 + 1) * 8 + g];
-      int d0, d1, d2, d3;
-      asm volatile(
-          "mma.sync.aligned.m16n8k16.row.col.s32.s8.s8.s32 {%0, %1, %2, %3}, {%4, %5}, {%6}, {%7, %7, %7, %7};"
-          : "=r"(d0), "=r"(d1), "=r"(d2), "=r"(d3)
-          : "r"(a0), "r"(a1), "r"(b0), "r"(0x4B400000));
-      acc[n][0] = fmaf(__int_as_float(d0) - 12582912.0f, qs0 * k0, acc[n][0]);
-      acc[n][1] = fmaf(__int_as_float(d1) - 12582912.0f, qs0 * k1, acc[n][1]);
-      acc[n][2] = fmaf(__int_as_float(d2) - 12582912.0f, qs1 * k0, acc[n][2]);
-      acc[n][3] = fmaf(__int_as_float(d3) - 12582912.0f, qs1 * k1, acc[n][3]);
+    for (int n = 0; n < 8; ++n) acc[n][0] = acc[n][1] = 0ull;
+#pragma unroll 1
+    for (int g = 0; g < 8; ++g) {
+      const uint32_t a0 = q_i8[(m0 + gid) * FP4_ROW_WORDS + g * 4 + tig];
+      const uint32_t a1 = q_i8[(m0 + 8 + gid) * FP4_ROW_WORDS + g * 4 + tig];
+      const float qs0 = q_sc[(m0 + gid) * 8 + g], qs1 = q_sc[(m0 + 8 + gid) * 8 + g];
+      const unsigned long long q0 = f32x2_pack(qs0, qs0), q1 = f32x2_pack(qs1, qs1);
+#pragma unroll
+      for (int n = 0; n < 8; ++n) {
+        const int key0 = half * 64 + n * 8;
+        const uint32_t b0 = k_i8[(key0 + gid) * FP4_ROW_WORDS + g * 4 + tig];
+        const unsigned long long kk =
+            f32x2_pack(k_sc[(key0 + tig * 2) * 8 + g], k_sc[(key0 + tig * 2 + 1) * 8 + g]);
+        int d0, d1, d2, d3;
+        asm volatile(
+            "mma.sync.aligned.m16n8k16.row.col.s32.s8.s8.s32 {%0, %1, %2, %3}, {%4, %5}, {%6}, {%7, %7, %7, %7};"
+            : "=r"(d0), "=r"(d1), "=r"(d2), "=r"(d3)
+            : "r"(a0), "r"(a1), "r"(b0), "r"(0x4B400000));
+        acc[n][0] = f32x2_fma(f32x2_sub(f32x2_pack_bits(d0, d1), magic2), f32x2_mul(q0, kk), acc[n][0]);
+        acc[n][1] = f32x2_fma(f32x2_sub(f32x2_pack_bits(d2, d3), magic2), f32x2_mul(q1, kk), acc[n][1]);
+      }
+    }
+#pragma unroll
+    for (int n = 0; n < 8; ++n) {
+      float x0, x1, x2, x3;
+      f32x2_unpack(acc[n][0], x0, x1);
+      f32x2_unpack(acc[n][1], x2, x3);
+      m = fmaxf(m, fmaxf(fmaxf(x0, x1), fmaxf(x2, x3)));
     }
   }
-  float m = -INFINITY;
-#pragma unroll
-  for (int n = 0; n < 16; ++n) m = fmaxf(m, fmaxf(fmaxf(acc[n][0], acc[n][1]), fmaxf(acc[n][2], acc[n][3])));
   return m;
 }
 

@@ -232,7 +232,7 @@ __device__ __forceinline__ void mma_s8_16816(int (&d)[4], uint32_t a0, uint32_t 
                : "r"(a0), "r"(a1), "r"(b0), "r"(c), "r"(c), "r"(c), "r"(c));
 }
 
-__global__ void __launch_bounds__(256) fp4_score_mma_kernel(const uint8_t* __restrict__ qp, const uint8_t* __restrict__ qs,
+__global__ void __launch_bounds__(256, 3) fp4_score_mma_kernel(const uint8_t* __restrict__ qp, const uint8_t* __restrict__ qs,
                                                             const uint8_t* __restrict__ kp, const uint8_t* __restrict__ ks,
                                                             float* __restrict__ query_scores,  // [Hidx, tiles, B*Sq] or null
                                                             float* __restrict__ tile_scores,   // [B, Hidx, Qt, tiles] or null
@@ -280,36 +280,43 @@ __global__ void __launch_bounds__(256) fp4_score_mma_kernel(const uint8_t* __res
       k_sc[(e & 7) * 128 + (e >> 3)] = e4m3_to_float(ks[(page * 128 + (e >> 3)) * 8 + (e & 7)]);
     __syncthreads();
 
-    float acc[16][4];
-#pragma unroll
-    for (int n = 0; n < 16; ++n)
-#pragma unroll
-      for (int i = 0; i < 4; ++i) acc[n][i] = 0.f;
+    // two passes of 64 keys: 32 accumulators per thread instead of 64 keep three CTAs on an SM
+    float r0 = -CUDART_INF_F, r1 = -CUDART_INF_F;
+    const unsigned long long magic2 = f32x2_pack(12582912.0f, 12582912.0f);
 #pragma unroll 1
-    for (int g = 0; g < 8; ++g) {
-      const uint32_t a0 = q_i8[(m0 + gid) * ROW_WORDS + g * 4 + tig];
-      const uint32_t a1 = q_i8[(m0 + 8 + gid) * ROW_WORDS + g * 4 + tig];
-      const float qs0 = q_sc[(m0 + gid) * 8 + g], qs1 = q_sc[(m0 + 8 + gid) * 8 + g];
+    for (int half = 0; half < 2; ++half) {
+      unsigned long long acc[8][2];               // (row gid: two keys), (row gid + 8: two keys) per n-tile
 #pragma unroll
-      for (int n = 0; n < 16; ++n) {
-        const uint32_t b0 = k_i8[(n * 8 + gid) * ROW_WORDS + g * 4 + tig];
-        const float2 kk = *reinterpret_cast<const float2*>(&k_sc[g * 128 + n * 8 + tig * 2]);
-        int d[4];
-        mma_s8_16816(d, a0, a1, b0, 0x4B400000);
-        // exact products (<= 12 + 8 significant bits), one rounding in each add
-        acc[n][0] = fmaf(__int_as_float(d[0]) - 12582912.0f, qs0 * kk.x, acc[n][0]);
-        acc[n][1] = fmaf(__int_as_float(d[1]) - 12582912.0f, qs0 * kk.y, acc[n][1]);
-        acc[n][2] = fmaf(__int_as_float(d[2]) - 12582912.0f, qs1 * kk.x, acc[n][2]);
-        acc[n][3] = fmaf(__int_as_float(d[3]) - 12582912.0f, qs1 * kk.y, acc[n][3]);
+      for (int n = 0; n < 8; ++n) acc[n][0] = acc[n][1] = 0ull;
+#pragma unroll 1
+      for (int g = 0; g < 8; ++g) {
+        const uint32_t a0 = q_i8[(m0 + gid) * ROW_WORDS + g * 4 + tig];
+        const uint32_t a1 = q_i8[(m0 + 8 + gid) * ROW_WORDS + g * 4 + tig];
+        const float qs0 = q_sc[(m0 + gid) * 8 + g], qs1 = q_sc[(m0 + 8 + gid) * 8 + g];
+        const unsigned long long q0 = f32x2_pack(qs0, qs0), q1 = f32x2_pack(qs1, qs1);
+#pragma unroll
+        for (int n = 0; n < 8; ++n) {
+          const int key0 = half * 64 + n * 8;
+          const uint32_t b0 = k_i8[(key0 + gid) * ROW_WORDS + g * 4 + tig];
+          const unsigned long long kk = *reinterpret_cast<const unsigned long long*>(&k_sc[g * 128 + key0 + tig * 2]);
+          int d[4];
+          mma_s8_16816(d, a0, a1, b0, 0x4B400000);
+          // exact products (<= 12 + 8 significant bits), one rounding in each add; two lanes per instruction
+          acc[n][0] = f32x2_fma(f32x2_sub(f32x2_pack_bits(d[0], d[1]), magic2), f32x2_mul(q0, kk), acc[n][0]);
+          acc[n][1] = f32x2_fma(f32x2_sub(f32x2_pack_bits(d[2], d[3]), magic2), f32x2_mul(q1, kk), acc[n][1]);
+        }
+      }
+      // per query: max over the thread's keys of each of its two rows
+#pragma unroll
+      for (int n = 0; n < 8; ++n) {
+        float x0, x1, x2, x3;
+        f32x2_unpack(acc[n][0], x0, x1);
+        f32x2_unpack(acc[n][1], x2, x3);
+        r0 = fmaxf(r0, fmaxf(x0, x1));
+        r1 = fmaxf(r1, fmaxf(x2, x3));
       }
     }
-    // per query: max over the thread's 32 keys of each of its two rows, then over the quad
-    float r0 = -CUDART_INF_F, r1 = -CUDART_INF_F;
-#pragma unroll
-    for (int n = 0; n < 16; ++n) {
-      r0 = fmaxf(r0, fmaxf(acc[n][0], acc[n][1]));
-      r1 = fmaxf(r1, fmaxf(acc[n][2], acc[n][3]));
-    }
+    // ... then over the quad
 #pragma unroll
     for (int dlt = 1; dlt < 4; dlt <<= 1) {
       r0 = fmaxf(r0, __shfl_xor_sync(0xffffffffu, r0, dlt));
