@@ -83,7 +83,7 @@ class ClockSampler:
                     mask = nvml.nvmlDeviceGetCurrentClocksEventReasons(handle)
                 except Exception:
                     mask = nvml.nvmlDeviceGetCurrentClocksThrottleReasons(handle)
-                self.samples.append((float(sm), int(mask)))
+                self.samples.append((float(sm), int(mask), time.time()))
             except Exception:
                 pass
             time.sleep(0.002)
@@ -112,19 +112,33 @@ class ClockSampler:
         except OSError:
             self.proc = None
 
-    def stop(self):
+    def stop(self, window=None):
+        """window = (t0, t1) host times of the timed region: its samples are reported; the samples
+        of the whole sampling period (timed region + probe loop) are summarised beside them."""
         if self.thread is not None:
             self.stop_flag = True
             self.thread.join(timeout=2)
-            sm = [x[0] for x in self.samples]
-            reasons = set()
-            for _, mask in self.samples:
-                for bit, name in self.REASONS:
-                    if mask & bit:
-                        reasons.add(name)
-            busy = [x for x in sm if x >= 0.5 * max(sm)] if sm else []
-            return {"sm_mhz": statistics.median(busy) if busy else None, "sm_max_mhz": self.max_mhz,
-                    "reasons": sorted(reasons), "samples": len(sm), "source": "nvml, 2 ms period"}
+
+            def summary(samples):
+                sm = [x[0] for x in samples]
+                reasons = set()
+                for _, mask, _t in samples:
+                    for bit, name in self.REASONS:
+                        if mask & bit:
+                            reasons.add(name)
+                busy = [x for x in sm if x >= 0.5 * max(sm)] if sm else []
+                return (statistics.median(busy) if busy else None), sorted(reasons), len(sm)
+            inside = [x for x in self.samples if window and window[0] <= x[2] <= window[1]]
+            all_mhz, all_reasons, all_n = summary(self.samples)
+            if inside:
+                mhz, reasons, n = summary(inside)
+            else:
+                mhz, reasons, n = all_mhz, all_reasons, all_n
+            return {"sm_mhz": mhz, "sm_max_mhz": self.max_mhz, "reasons": reasons, "samples": n,
+                    "source": "nvml, 2 ms period",
+                    "window": "timed region" if inside else "timed region + 0.3 s of the same launches",
+                    "probe": {"sm_mhz": all_mhz, "reasons": all_reasons, "samples": all_n,
+                              "what": "timed region + 0.3 s of the same launches (sustained load)"}}
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.proc.terminate()
@@ -278,11 +292,13 @@ def run_ours(args):
         sampler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
+    t_region0 = time.time()
     e0.record()
     for _ in range(args.steps):
         step()
     e1.record()
     barrier()
+    t_region1 = time.time()
     ms_total = e0.elapsed_time(e1)
     sp.device_status()
     # An NVML query takes longer than one launch, so a short timed region yields one or two
@@ -293,9 +309,7 @@ def run_ours(args):
             step()
         torch.cuda.synchronize()
     barrier()
-    clocks = sampler.stop() if rank == 0 else None
-    if clocks is not None:
-        clocks["window"] = "timed region + 0.3 s of the same launches"
+    clocks = sampler.stop((t_region0, t_region1)) if rank == 0 else None
 
     e2e_ms, e2e_steps, h2d, d2h = float("nan"), 0, 0, 0
     if not args.kernel_only:
