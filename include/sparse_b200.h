@@ -175,6 +175,20 @@ int sparse_b200_nvfp4_quantize(const void* x, void* packed, void* scales, int ba
 int sparse_b200_fp4_scores(const void* q_codes, const void* q_scales, const void* k_codes, const void* k_scales,
                            float* query_scores, float* tile_scores, int batch, int hidx, int hk, int len_q, int len_kv,
                            void* stream);
+/* Ragged batches over a paged key cache, optionally causal: the contract of
+ * fp4_indexer_block_scores (indexers/fp4/vendor_minimax_msa/fp4_indexer_interface.py:745-811).
+ * q_codes [total_q, Hq, 64], q_scales [total_q, Hq, 8]; k_codes [total_pages, Hk, 128, 64],
+ * k_scales [total_pages, Hk, 128, 8]; cu_seqlens_q / cu_seqlens_k / cu_page_offsets [B + 1] and
+ * kv_indices [sum of pages] int32 device arrays; qo_offset [B] int32 or NULL (causal only: key j
+ * is visible to query i when j <= i + offset, offset = k_len - q_len unless given).
+ * query_scores [Hq, ceil(max_seqlen_k / 128), total_q] fp32 is written completely: -inf where a
+ * query sees no key of a page. Query head h reads key head h / (Hq / Hk). Same exact arithmetic
+ * as sparse_b200_fp4_scores. */
+int sparse_b200_fp4_scores_varlen(const void* q_codes, const void* q_scales, const void* k_codes, const void* k_scales,
+                                  const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k,
+                                  const int32_t* cu_page_offsets, const int32_t* kv_indices, const int32_t* qo_offset,
+                                  float* query_scores, int batch, int hq, int hk, int total_q, int total_pages,
+                                  int max_seqlen_q, int max_seqlen_k, int causal, void* stream);
 int sparse_b200_tile_topk(const float* query_scores, int32_t* block_idx, int batch, int heads, int len_q, int kv_tiles,
                           int topk, void* stream);
 int sparse_b200_row_topk(const float* tile_scores, int32_t* block_idx, int64_t rows, int kv_tiles, int topk,

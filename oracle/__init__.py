@@ -20,7 +20,7 @@ from .attention import (masked_attention, gather_attention, combine_partials,
                         expand_block_ids, filter_ids_to_range)
 from .selectors import (pool_descriptors, summary_scores, summary_select,
                         stable_topk)
-from .fp4 import (quantize_nvfp4, quantize_queries, quantize_keys, group_mean, dequantize_nvfp4, fp4_scores, fp4_tile_scores,
+from .fp4 import (quantize_nvfp4, quantize_queries, quantize_keys, group_mean, dequantize_nvfp4, fp4_scores, fp4_scores_varlen, fp4_tile_scores,
                   fp4_select, E2M1_VALUES)
 from .metadata import build_reverse_plan, validate_reverse_plan, split_kv_segments
 from . import inputs

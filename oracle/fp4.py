@@ -138,6 +138,48 @@ def fp4_scores(qp, qs, kp, ks, batch_size, len_q, len_kv):
     return out
 
 
+def fp4_scores_varlen(qp, qs, kp, ks, cu_seqlens_q, cu_seqlens_k, cu_page_offsets, kv_indices, max_seqlen_k,
+                      causal=False, qo_offset=None):
+    """Ragged batch over a paged key cache, optionally causal (PARITY UNPINNED: the vendored scorer
+    is GPU-only; this restates its documented contract, indexers/fp4/vendor_minimax_msa/
+    fp4_indexer_interface.py:745-811, with the canonical arithmetic of _canonical_dots).
+    qp [total_q,Hq,64], qs [total_q,Hq,8], kp [total_pages,Hk,128,64], ks [total_pages,Hk,128,8];
+    request b: queries cu_seqlens_q[b]..cu_seqlens_q[b+1], k_len keys in logical pages
+    kv_indices[cu_page_offsets[b] + t]; query head h reads key head h // (Hq // Hk); causal: key j is
+    visible to query i when j <= i + offset, offset = k_len - q_len unless qo_offset[b] is given
+    (src/sm100/fp4_indexer.py:525-529). Returns fp32 [Hq, ceil(max_seqlen_k/128), total_q] = max over
+    the visible keys of each page, -inf where there is none."""
+    total_q, hq = qp.shape[0], qp.shape[1]
+    hk = kp.shape[1]
+    tiles = (int(max_seqlen_k) + 127) // 128
+    out = torch.full((hq, tiles, total_q), -float("inf"), dtype=torch.float32)
+    batch = len(cu_seqlens_q) - 1
+    for b in range(batch):
+        q0, q1 = int(cu_seqlens_q[b]), int(cu_seqlens_q[b + 1])
+        k_len = int(cu_seqlens_k[b + 1]) - int(cu_seqlens_k[b])
+        q_len = q1 - q0
+        if q_len <= 0 or k_len <= 0:
+            continue
+        pages = (k_len + 127) // 128
+        phys = [int(kv_indices[int(cu_page_offsets[b]) + t]) for t in range(pages)]
+        offset = (int(qo_offset[b]) if qo_offset is not None else k_len - q_len) if causal else None
+        qi = torch.arange(q_len)[:, None]
+        kj = torch.arange(pages * 128)[None, :]
+        visible = kj < k_len
+        if causal:
+            visible = visible & (kj <= qi + offset)
+        else:
+            visible = visible.expand(q_len, -1)
+        for h in range(hq):
+            kh = h // (hq // hk)
+            keys_p = torch.stack([kp[i, kh] for i in phys]).reshape(pages * 128, 64)
+            keys_s = torch.stack([ks[i, kh] for i in phys]).reshape(pages * 128, 8)
+            dots = _canonical_dots(qp[q0:q1, h], qs[q0:q1, h], keys_p, keys_s)
+            dots = torch.where(visible, dots, torch.tensor(-float("inf")))
+            out[h, :pages, q0:q1] = dots.reshape(q_len, pages, 128).amax(-1).T
+    return out
+
+
 def fp4_tile_scores(scores, batch_size, len_q):
     """indexers/fp4/reference.py:8-13: max over the 128 queries of a tile ->
     [B, Hidx, Sq/128, Skv/128]."""

@@ -157,6 +157,44 @@ def fp4_block_scores(inputs):
     return scores
 
 
+def fp4_block_scores_varlen(q_fp4, k_fp4, q_scale, k_scale, cu_seqlens_q, cu_seqlens_k, cu_page_offsets, *,
+                            max_seqlen_q, max_seqlen_k, kv_indices, causal=False, qo_offset=None):
+    """Ragged batch over a paged key cache, optionally causal: fp32 [Hq, ceil(max_seqlen_k/128), total_q]
+    (max over the visible keys of each page, -inf where none), the public-layout form of
+    fp4_indexer_block_scores (indexers/fp4/vendor_minimax_msa/fp4_indexer_interface.py:745-811)."""
+    if q_fp4.ndim != 3 or q_fp4.shape[2] != 64 or k_fp4.ndim != 4 or tuple(k_fp4.shape[2:]) != (128, 64):
+        raise ValueError("q_fp4 must be [total_q,Hq,64] and k_fp4 [total_pages,Hk,128,64]")
+    total_q, hq = int(q_fp4.shape[0]), int(q_fp4.shape[1])
+    total_pages, hk = int(k_fp4.shape[0]), int(k_fp4.shape[1])
+    if hq % hk:
+        raise ValueError("num_qo_heads must be divisible by num_kv_heads")
+    if qo_offset is not None and not causal:
+        raise ValueError("qo_offset is only valid when causal=True")
+    batch = int(cu_seqlens_q.numel()) - 1
+    dev = q_fp4.device
+    checks = (("q_fp4", q_fp4, torch.uint8, None), ("k_fp4", k_fp4, torch.uint8, None),
+              ("q_scale", q_scale, torch.float8_e4m3fn, (total_q, hq, 8)),
+              ("k_scale", k_scale, torch.float8_e4m3fn, (total_pages, hk, 128, 8)),
+              ("cu_seqlens_q", cu_seqlens_q, torch.int32, (batch + 1,)),
+              ("cu_seqlens_k", cu_seqlens_k, torch.int32, (batch + 1,)),
+              ("cu_page_offsets", cu_page_offsets, torch.int32, (batch + 1,)),
+              ("kv_indices", kv_indices, torch.int32, None)) + \
+        ((("qo_offset", qo_offset, torch.int32, (batch,)),) if qo_offset is not None else ())
+    for name, t, dtype, shape in checks:
+        if not t.is_cuda or t.device != dev or t.dtype != dtype or not t.is_contiguous() \
+                or (shape is not None and tuple(t.shape) != shape):
+            raise ValueError(f"{name} must be a contiguous {dtype} CUDA tensor" + (f" of shape {shape}" if shape else ""))
+    tiles = (int(max_seqlen_k) + 127) // 128
+    scores = torch.empty((hq, tiles, total_q), dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        _lib.check(_lib.lib().sparse_b200_fp4_scores_varlen(
+            _lib.ptr(q_fp4), _lib.ptr(q_scale), _lib.ptr(k_fp4), _lib.ptr(k_scale), _lib.ptr(cu_seqlens_q),
+            _lib.ptr(cu_seqlens_k), _lib.ptr(cu_page_offsets), _lib.ptr(kv_indices), _lib.ptr(qo_offset),
+            _lib.ptr(scores), batch, hq, hk, total_q, total_pages, int(max_seqlen_q), int(max_seqlen_k),
+            int(bool(causal)), _lib.current_stream()))
+    return scores
+
+
 def tile_topk_out(scores, selected, *, batch_size, len_q):
     if not (scores.is_cuda and scores.dtype == torch.float32 and scores.is_contiguous() and scores.ndim == 3):
         raise _lib.SparseB200Error("scores must be contiguous float32 [Hkv,KV_tiles,B*Sq] on CUDA")

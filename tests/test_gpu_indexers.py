@@ -294,6 +294,53 @@ def test_fp4_tensor_core_path_bit_exact():
     m.device_status()
 
 
+def _varlen_case(seed, hq, hk, q_lens, k_lens, shuffle_pages=True):
+    g = torch.Generator().manual_seed(seed)
+    total_q = sum(q_lens)
+    pages_per = [(k + 127) // 128 for k in k_lens]
+    total_pages = sum(pages_per) + 3                       # a few pages nobody owns
+    qp = torch.randint(256, (total_q, hq, 64), dtype=torch.uint8, generator=g)
+    kp = torch.randint(256, (total_pages, hk, 128, 64), dtype=torch.uint8, generator=g)
+    choices = torch.tensor([0.25, 0.375, 0.5, 0.75, 1.0, 1.5, 2.0])
+    qs = choices[torch.randint(7, (total_q, hq, 8), generator=g)].to(torch.float8_e4m3fn)
+    ks = choices[torch.randint(7, (total_pages, hk, 128, 8), generator=g)].to(torch.float8_e4m3fn)
+    perm = torch.randperm(total_pages, generator=g) if shuffle_pages else torch.arange(total_pages)
+    kv_indices = perm[:sum(pages_per)].to(torch.int32)
+    cu = lambda xs: torch.tensor([0] + list(np.cumsum(xs)), dtype=torch.int32)
+    return qp, qs, kp, ks, cu(q_lens), cu(k_lens), cu(pages_per), kv_indices
+
+
+@pytest.mark.parametrize("causal", [False, True])
+def test_fp4_scores_ragged_paged_causal(causal):
+    """Ragged requests over a shuffled page table (lengths that are no multiples of 128, a request
+    with more queries than keys, GQA 4:1, a single-token decode request), optionally causal, with
+    and without an explicit causal offset: bit-exact against the oracle, -inf outside."""
+    m = sp()
+    q_lens, k_lens = [200, 128, 1, 300, 77], [1000, 128, 517, 260, 64]
+    qp, qs, kp, ks, cu_q, cu_k, cu_p, kv_idx = _varlen_case(11, 4, 1, q_lens, k_lens)
+    offsets = [None] + ([torch.tensor([800, 0, 516, -50, 10], dtype=torch.int32)] if causal else [])
+    for qo in offsets:
+        ref = oracle.fp4_scores_varlen(qp, qs, kp, ks, cu_q, cu_k, cu_p, kv_idx, max(k_lens), causal=causal,
+                                       qo_offset=qo)
+        out = m.fp4_block_scores_varlen(qp.cuda(), kp.cuda(), qs.cuda(), ks.cuda(), cu_q.cuda(), cu_k.cuda(),
+                                        cu_p.cuda(), max_seqlen_q=max(q_lens), max_seqlen_k=max(k_lens),
+                                        kv_indices=kv_idx.cuda(), causal=causal,
+                                        qo_offset=None if qo is None else qo.cuda())
+        torch.cuda.synchronize()
+        m.device_status()
+        assert out.shape == ref.shape
+        assert torch.equal(out.cpu(), ref)
+    # a dense, unshuffled batch equals the dense scorer bit for bit
+    qp, qs, kp, ks, cu_q, cu_k, cu_p, kv_idx = _varlen_case(12, 2, 2, [256, 256], [512, 512], shuffle_pages=False)
+    if not causal:
+        kp, ks = kp[:8].contiguous(), ks[:8].contiguous()
+        inputs = m.prepare_fp4_inputs(qp.cuda(), kp.cuda(), qs.cuda(), ks.cuda(), batch_size=2, len_q=256, len_kv=512)
+        dense = m.fp4_block_scores(inputs)
+        ragged = m.fp4_block_scores_varlen(qp.cuda(), kp.cuda(), qs.cuda(), ks.cuda(), cu_q.cuda(), cu_k.cuda(),
+                                           cu_p.cuda(), max_seqlen_q=256, max_seqlen_k=512, kv_indices=kv_idx.cuda())
+        assert torch.equal(dense, ragged)
+
+
 def test_indexer_then_attention_config1():
     """Configuration 1 end to end: R1 picks top-8 of 32, Q-centric attention,
     against the masked-attention oracle."""
