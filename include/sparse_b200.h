@@ -116,6 +116,14 @@ int sparse_b200_kv_token_main(const void* q, const void* k, const void* v, const
                               const int32_t* task_ptr, const int32_t* query_ids, const int32_t* ranks, void* partial,
                               float* partial_lse, int batch, int hq, int hkv, int sq, int skv, int topk,
                               void* stream);
+/* The same with q in the token-major layout [B, Sq, Hq, 128] of the reference's TMA variants
+ * (main_tm_out, attention/kv_centric/optimization_round11/api11.py:1-7,85-87): the heads of a
+ * token are one dense block, which the gather fetches faster. Hq / Hkv of 8 or 16 only. The
+ * partials keep the head-major layout [B, Hq, Sq, TopK, 128]. */
+int sparse_b200_kv_token_main_tm(const void* q_token_major, const void* k, const void* v, const int32_t* tasks,
+                                 const int32_t* task_ptr, const int32_t* query_ids, const int32_t* ranks,
+                                 void* partial, float* partial_lse, int batch, int hq, int hkv, int sq, int skv,
+                                 int topk, void* stream);
 
 /* R1 / R4 block-summary indexer (indexers/r1_r4/gpu_ops.py:6-49,
  * indexers/r1_r4/block_selectors.py:9-45), any Hkv, group size x R <= 64, any TopK.

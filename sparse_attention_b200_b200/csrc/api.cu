@@ -436,6 +436,25 @@ int sparse_b200_kv_token_main(const void* q, const void* k, const void* v, const
                               sq, skv, topk, static_cast<cudaStream_t>(stream));
 }
 
+int sparse_b200_kv_token_main_tm(const void* q_token_major, const void* k, const void* v, const int32_t* tasks,
+                                 const int32_t* task_ptr, const int32_t* query_ids, const int32_t* ranks,
+                                 void* partial, float* partial_lse, int batch, int hq, int hkv, int sq, int skv,
+                                 int topk, void* stream) {
+  REQUIRE(q_token_major && k && v && tasks && task_ptr && query_ids && ranks && partial && partial_lse, "null pointer");
+  REQUIRE(batch > 0 && hkv > 0 && hq >= hkv && hq % hkv == 0, "Hq must be a positive multiple of Hkv");
+  const int g = hq / hkv;
+  REQUIRE(g == 8 || g == 16, "the token-major layout is supported for Hq/Hkv of 8 and 16");
+  REQUIRE(sq > 0 && skv >= 128 && skv % 128 == 0 && topk > 0 && topk <= skv / 128,
+          "Skv must be a positive multiple of 128 and TopK at most the number of KV blocks");
+  REQUIRE(static_cast<long long>(batch) * hkv * skv < (1LL << 31) && static_cast<long long>(batch) * sq < (1LL << 31),
+          "flattened KV rows and tokens must fit int32");
+  REQUIRE(aligned16(q_token_major) && aligned16(k) && aligned16(v) && aligned16(partial) && aligned16(tasks),
+          "misaligned pointer");
+  const long long rows = static_cast<long long>(batch) * hkv * (skv / 128);
+  return launch_kv_token_pipe(q_token_major, k, v, tasks, task_ptr + rows, query_ids, ranks, partial, partial_lse, batch,
+                              hq, hkv, sq, skv, topk, 1, static_cast<cudaStream_t>(stream));
+}
+
 int64_t sparse_b200_indexer_fp4_workspace_bytes(int batch, int hidx, int hk, int len_q, int len_kv) {
   if (batch <= 0 || hidx <= 0 || hk <= 0 || len_q <= 0 || len_kv <= 0) return SB_ERR_INVALID;
   const int64_t q = align256(static_cast<size_t>(batch) * len_q * hidx * 256);

@@ -68,7 +68,7 @@ int launch_kv_token_main(const void* q, const void* k, const void* v, const int3
                          int hkv, int sq, int skv, int topk, cudaStream_t stream);
 int launch_kv_token_pipe(const void* q, const void* k, const void* v, const int32_t* tasks, const int32_t* task_count,
                          const int32_t* qids, const int32_t* ranks, void* partial, float* lses, int batch, int hq,
-                         int hkv, int sq, int skv, int topk, cudaStream_t stream);
+                         int hkv, int sq, int skv, int topk, int q_token_major, cudaStream_t stream);
 int launch_quantize(const void* x, void* packed, void* scales, int batch, int heads_out, int group, int seq,
                     int paged, cudaStream_t stream);
 int launch_fp4_scores_varlen(const void* qp, const void* qs, const void* kp, const void* ks, const int32_t* cu_q,

@@ -256,7 +256,7 @@ int launch_kv_token_main(const void* q, const void* k, const void* v, const int3
   // the smaller groups, whose Q rows cannot be fetched as 1024-byte-aligned TMA boxes
   if (group == 8 || group == 16)
     return launch_kv_token_pipe(q, k, v, tasks, task_count, qids, ranks, partial, lses, batch, hq, hkv, sq, skv, topk,
-                                stream);
+                                0, stream);
   DeviceCtx* ctx = device_ctx();
   if (!ctx) return SB_ERR_CUDA;
   Params p{};

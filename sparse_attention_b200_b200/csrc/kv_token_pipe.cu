@@ -63,6 +63,7 @@ struct Params {
   int* status;
   int batch, hq, hkv, sq, skv, topk, group, group_log2, edges;
   int phases;                   // upper bound on the number of passes over the task list (see Walk)
+  int q_token_major;            // q is [B, Sq, Hq, 128]: the G heads of a token are one dense box
   float scale_log2;
 };
 
@@ -229,8 +230,11 @@ kv_token_pipe_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_con
       if (cur_qi >= 0) {
         const int b = cur.group / p.hkv, kvh = cur.group - b * p.hkv;
         const uint32_t dst = base + OFF_Q + slot * TILE_BYTES + lane * G * 128;
-        tma_load_3d(dst, &q_map, 0, cur_qi, b * p.hq + kvh * G, bar(Q_FULL + slot));
-        tma_load_3d(dst + PANEL_BYTES, &q_map, 64, cur_qi, b * p.hq + kvh * G, bar(Q_FULL + slot));
+        // head-major q: {column, token, batch * Hq + head}; token-major q: {column, head, batch * Sq + token}
+        const int y = p.q_token_major ? kvh * G : cur_qi;
+        const int z = p.q_token_major ? b * p.sq + cur_qi : b * p.hq + kvh * G;
+        tma_load_3d(dst, &q_map, 0, y, z, bar(Q_FULL + slot));
+        tma_load_3d(dst + PANEL_BYTES, &q_map, 64, y, z, bar(Q_FULL + slot));
       }
     }
     if (!ok) {
@@ -458,10 +462,11 @@ kv_token_pipe_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_con
 
 }  // namespace kvp
 
-// Pipelined main stage for Hq / Hkv of 8 or 16 (same arguments as launch_kv_token_main).
+// Pipelined main stage for Hq / Hkv of 8 or 16 (arguments of launch_kv_token_main; q_token_major:
+// q is [B, Sq, Hq, 128] instead of [B, Hq, Sq, 128]).
 int launch_kv_token_pipe(const void* q, const void* k, const void* v, const int32_t* tasks, const int32_t* task_count,
                          const int32_t* qids, const int32_t* ranks, void* partial, float* lses, int batch, int hq,
-                         int hkv, int sq, int skv, int topk, cudaStream_t stream) {
+                         int hkv, int sq, int skv, int topk, int q_token_major, cudaStream_t stream) {
   using namespace kvp;
   DeviceCtx* ctx = device_ctx();
   if (!ctx) return SB_ERR_CUDA;
@@ -475,6 +480,7 @@ int launch_kv_token_pipe(const void* q, const void* k, const void* v, const int3
   while ((1 << p.group_log2) < group) ++p.group_log2;
   p.edges = static_cast<int>(static_cast<long long>(batch) * hkv * sq * topk);
   p.scale_log2 = 1.4426950408889634f / sqrtf(128.0f);
+  p.q_token_major = q_token_major;
   // one segment per 24 MB of Q: the Q rows a segment gathers then stay within L2
   const long long q_bytes = static_cast<long long>(batch) * hq * sq * 256;
   p.phases = static_cast<int>(std::min<long long>(64, (q_bytes + (24LL << 20) - 1) / (24LL << 20)));
@@ -492,10 +498,17 @@ int launch_kv_token_pipe(const void* q, const void* k, const void* v, const int3
       return set_error(SB_ERR_CUDA, "cuTensorMapEncodeTiled failed for k/v");
   }
   {
-    // q [B*Hq, Sq, 128]: one box = the G heads of a KV group at one token, 64 columns
-    const cuuint64_t dims[3] = {128, static_cast<cuuint64_t>(sq), static_cast<cuuint64_t>(batch) * hq};
-    const cuuint64_t strides[2] = {256, static_cast<cuuint64_t>(sq) * 256};
-    const cuuint32_t box[3] = {64, 1, static_cast<cuuint32_t>(group)};
+    // one box = the G heads of a KV group at one token, 64 columns.
+    // head-major q [B*Hq, Sq, 128]: rows Sq * 256 bytes apart; token-major q [B*Sq, Hq, 128]: one dense
+    // block of G * 256 bytes (the layout of the reference's TMA variants, api11.py:1-7).
+    cuuint64_t dims[3] = {128, static_cast<cuuint64_t>(sq), static_cast<cuuint64_t>(batch) * hq};
+    cuuint64_t strides[2] = {256, static_cast<cuuint64_t>(sq) * 256};
+    cuuint32_t box[3] = {64, 1, static_cast<cuuint32_t>(group)};
+    if (q_token_major) {
+      dims[1] = static_cast<cuuint64_t>(hq); dims[2] = static_cast<cuuint64_t>(batch) * sq;
+      strides[1] = static_cast<cuuint64_t>(hq) * 256;
+      box[1] = static_cast<cuuint32_t>(group); box[2] = 1;
+    }
     if (encode_tiled(&qm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(q), dims, strides, box, ones,
                      CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B))
       return set_error(SB_ERR_CUDA, "cuTensorMapEncodeTiled failed for q");

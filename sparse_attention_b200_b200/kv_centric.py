@@ -87,12 +87,18 @@ class PreparedTokens:
     """Per-TOKEN selections, the reference's own contract (api11.py:50-92, gpu_plan.py:19-45):
     q [B,Hq,Sq,128], k/v [B,Hkv,Skv,128] bf16, selected [B,Hkv,Sq,TopK] int32 (CUDA), any TopK.
     metadata() builds the reverse index and the task list on the GPU, main() writes one
-    normalised partial per (query, head, rank), combine() merges the TopK partials."""
+    normalised partial per (query, head, rank), combine() merges the TopK partials.
+    q_token_major=True: q is [B,Sq,Hq,128], the layout of the reference's TMA variants (groups of
+    8 or 16 heads only); outputs stay head-major."""
 
-    def __init__(self, q, k, v, selected):
+    def __init__(self, q, k, v, selected, q_token_major=False):
         import ctypes
         if not (q.is_cuda and q.dtype == torch.bfloat16 and q.is_contiguous() and q.dim() == 4 and q.shape[3] == 128):
-            raise _lib.SparseB200Error("q must be contiguous bf16 [B,Hq,Sq,128] on CUDA")
+            raise _lib.SparseB200Error("q must be contiguous bf16 [B,Hq,Sq,128] (or [B,Sq,Hq,128]) on CUDA")
+        self.q_token_major = bool(q_token_major)
+        q_arg = q
+        if self.q_token_major:
+            q = q.permute(0, 2, 1, 3)          # a head-major VIEW for the shape checks below; q_arg is what runs
         for t in (k, v):
             if not (t.is_cuda and t.dtype == torch.bfloat16 and t.is_contiguous() and t.dim() == 4
                     and t.shape[3] == 128 and t.device == q.device):
@@ -104,7 +110,9 @@ class PreparedTokens:
         if selected.dtype != torch.int32 or not selected.is_contiguous() or selected.device != q.device \
                 or selected.dim() != 4 or tuple(selected.shape[:3]) != (b, hkv, sq):
             raise _lib.SparseB200Error("selected must be contiguous int32 [B,Hkv,Sq,TopK] on q's device")
-        self.q, self.k, self.v, self.selected = q, k, v, selected
+        if self.q_token_major and hq // hkv not in (8, 16):
+            raise _lib.SparseB200Error("the token-major layout needs Hq/Hkv of 8 or 16")
+        self.q, self.k, self.v, self.selected = q_arg, k, v, selected
         self.b, self.hq, self.hkv, self.sq, self.skv = b, hq, hkv, sq, skv
         self.g, self.topk, self.kv_blocks = hq // hkv, int(selected.shape[3]), skv // 128
         self.rows = b * hkv * self.kv_blocks
@@ -142,7 +150,8 @@ class PreparedTokens:
 
     def main(self):
         with torch.cuda.device(self.q.device):
-            _lib.check(_lib.lib().sparse_b200_kv_token_main(
+            fn = _lib.lib().sparse_b200_kv_token_main_tm if self.q_token_major else _lib.lib().sparse_b200_kv_token_main
+            _lib.check(fn(
                 _lib.ptr(self.q), _lib.ptr(self.k), _lib.ptr(self.v), _lib.ptr(self.tasks), _lib.ptr(self.task_ptr),
                 _lib.ptr(self.qids), _lib.ptr(self.ranks), _lib.ptr(self.partial), _lib.ptr(self.lses),
                 self.b, self.hq, self.hkv, self.sq, self.skv, self.topk, _lib.current_stream()))

@@ -163,3 +163,29 @@ def test_token_operator_repeat_reorder_and_block_equivalence():
     with pytest.raises(ValueError):
         p3.plan()
     m.device_status()
+
+
+@pytest.mark.parametrize("g", [8, 16])
+def test_token_major_q_gives_identical_results(g):
+    """q handed over as [B,Sq,Hq,128] (the layout of the reference's TMA variants) must give
+    bit-identical partials, LSEs and outputs to the head-major call."""
+    import sparse_attention_b200_b200 as m
+    gen = torch.Generator().manual_seed(91)
+    b, hkv, sq, skv, topk = 2, 2, 300, 4096, 16
+    q = torch.randn((b, hkv * g, sq, 128), generator=gen).to(torch.bfloat16).cuda()
+    k = torch.randn((b, hkv, skv, 128), generator=gen).to(torch.bfloat16).cuda()
+    v = torch.randn((b, hkv, skv, 128), generator=gen).to(torch.bfloat16).cuda()
+    selected = make_selected(b, hkv, sq, skv // 128, topk, "independent", 5).cuda()
+    head_major = m.PreparedTokens(q, k, v, selected)
+    head_major.run()
+    token_major = m.PreparedTokens(q.permute(0, 2, 1, 3).contiguous(), k, v, selected, q_token_major=True)
+    token_major.poison()
+    token_major.run()
+    torch.cuda.synchronize()
+    m.device_status()
+    assert torch.equal(token_major.partial.view(torch.int16), head_major.partial.view(torch.int16))
+    assert torch.equal(token_major.lses, head_major.lses)
+    assert torch.equal(token_major.out.view(torch.int16), head_major.out.view(torch.int16))
+    with pytest.raises(m.SparseB200Error):
+        m.PreparedTokens(torch.zeros((1, 8, 4, 128), dtype=torch.bfloat16, device="cuda"), k[:1, :1], v[:1, :1],
+                         selected[:1, :1, :8].contiguous(), q_token_major=True)      # Hq/Hkv = 4
