@@ -34,8 +34,10 @@ constexpr int PANEL_BYTES = 128 * 128;
 constexpr int A_STAGES = SB_STC_STAGES;
 constexpr int SCORE_LIMIT = 232448 - 2048 - (A_STAGES + 1) * TILE_BYTES;   // bytes of shared memory left for scores
 constexpr int C_MAX = 192;                 // candidates per list
-constexpr int NUM_THREADS = 256;
-constexpr int TMA_WARP = 4, MMA_WARP = 5;
+constexpr int NUM_THREADS = 512;            // ten warps have a role in the scoring phase; all sixteen re-score
+constexpr int EPI_WARPS = 8;               // two column halves x four TMEM lane quarters
+constexpr int SEL_WARPS = 8;               // warps of the selection phase (one list each at a time)
+constexpr int TMA_WARP = 8, MMA_WARP = 9;
 constexpr float EPS = 6.103515625e-05f;    // 2^-14
 constexpr float SCALE = 0.08838834764831845f;
 
@@ -81,26 +83,50 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
 }
 
 // Exact score contribution of one key descriptor: max over the MP query rows of
-// the fp32 dot product accumulated in feature order (q_s is [128][MP] fp32).
+// the fp32 dot product accumulated in feature order (q_s is [128][MP] fp32, 16-byte
+// aligned). The key row is fetched a quarter (32 features) ahead of the arithmetic.
 template <int MP>
 __device__ __forceinline__ float exact_key_best(const float* q_s, const __nv_bfloat16* krow_g) {
   float acc[MP];
 #pragma unroll
   for (int m = 0; m < MP; ++m) acc[m] = 0.f;
   const uint4* krow = reinterpret_cast<const uint4*>(krow_g);
-#pragma unroll 2
-  for (int c = 0; c < 16; ++c) {
-    const uint4 kv = __ldg(krow + c);
-    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&kv);
+  uint4 cur[4], nxt[4];
 #pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      const float2 kf = __bfloat1622float2(h[e]);
-      const float* q0 = q_s + (c * 8 + 2 * e) * MP;
+  for (int i = 0; i < 4; ++i) cur[i] = __ldg(krow + i);
+#pragma unroll 1
+  for (int part = 0; part < 4; ++part) {
+    if (part < 3) {
 #pragma unroll
-      for (int m = 0; m < MP; ++m) acc[m] = fmaf(q0[m], kf.x, acc[m]);
-#pragma unroll
-      for (int m = 0; m < MP; ++m) acc[m] = fmaf(q0[MP + m], kf.y, acc[m]);
+      for (int i = 0; i < 4; ++i) nxt[i] = __ldg(krow + 4 * (part + 1) + i);
     }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&cur[i]);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 kf = __bfloat1622float2(h[e]);
+        const float4* q0 = reinterpret_cast<const float4*>(q_s + ((part * 4 + i) * 8 + 2 * e) * MP);
+#pragma unroll
+        for (int m = 0; m < MP / 4; ++m) {
+          const float4 qa = q0[m];
+          acc[4 * m + 0] = fmaf(qa.x, kf.x, acc[4 * m + 0]);
+          acc[4 * m + 1] = fmaf(qa.y, kf.x, acc[4 * m + 1]);
+          acc[4 * m + 2] = fmaf(qa.z, kf.x, acc[4 * m + 2]);
+          acc[4 * m + 3] = fmaf(qa.w, kf.x, acc[4 * m + 3]);
+        }
+#pragma unroll
+        for (int m = 0; m < MP / 4; ++m) {
+          const float4 qa = q0[MP / 4 + m];
+          acc[4 * m + 0] = fmaf(qa.x, kf.y, acc[4 * m + 0]);
+          acc[4 * m + 1] = fmaf(qa.y, kf.y, acc[4 * m + 1]);
+          acc[4 * m + 2] = fmaf(qa.z, kf.y, acc[4 * m + 2]);
+          acc[4 * m + 3] = fmaf(qa.w, kf.y, acc[4 * m + 3]);
+        }
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) cur[i] = nxt[i];
   }
   float best = acc[0];
 #pragma unroll
@@ -108,9 +134,71 @@ __device__ __forceinline__ float exact_key_best(const float* q_s, const __nv_bfl
   return best;
 }
 
+// Exact dot products of FOUR key descriptors against MQ query rows (q_s points at the first
+// of them inside the [128][stride] fp32 array): every fp32 sum runs in feature order, as in
+// exact_key_best, but a query value fetched from shared memory feeds four FMAs per lane
+// instead of one (the one-row form is bound by shared-memory loads). best[j] = max over the
+// MQ rows for key j.
+template <int MQ>
+__device__ __forceinline__ void exact_quad_best(const float* q_s, int stride, const uint4* k0, const uint4* k1,
+                                                const uint4* k2, const uint4* k3, float (&best)[4]) {
+  float acc[4][MQ];
+#pragma unroll
+  for (int j = 0; j < 4; ++j)
+#pragma unroll
+    for (int m = 0; m < MQ; ++m) acc[j][m] = 0.f;
+  uint4 cur[4] = {__ldg(k0), __ldg(k1), __ldg(k2), __ldg(k3)};
+#pragma unroll 1
+  for (int c = 0; c < 16; ++c) {
+    uint4 nxt[4];
+    const int cn = c < 15 ? c + 1 : 15;
+    nxt[0] = __ldg(k0 + cn); nxt[1] = __ldg(k1 + cn); nxt[2] = __ldg(k2 + cn); nxt[3] = __ldg(k3 + cn);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      float2 kf[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) kf[j] = __bfloat1622float2(reinterpret_cast<const __nv_bfloat162*>(&cur[j])[e]);
+      const float4* qa = reinterpret_cast<const float4*>(q_s + (c * 8 + 2 * e) * stride);
+      const float4* qb = reinterpret_cast<const float4*>(q_s + (c * 8 + 2 * e + 1) * stride);
+#pragma unroll
+      for (int m = 0; m < MQ / 4; ++m) {
+        const float4 q = qa[m];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          acc[j][4 * m + 0] = fmaf(q.x, kf[j].x, acc[j][4 * m + 0]);
+          acc[j][4 * m + 1] = fmaf(q.y, kf[j].x, acc[j][4 * m + 1]);
+          acc[j][4 * m + 2] = fmaf(q.z, kf[j].x, acc[j][4 * m + 2]);
+          acc[j][4 * m + 3] = fmaf(q.w, kf[j].x, acc[j][4 * m + 3]);
+        }
+      }
+#pragma unroll
+      for (int m = 0; m < MQ / 4; ++m) {
+        const float4 q = qb[m];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          acc[j][4 * m + 0] = fmaf(q.x, kf[j].y, acc[j][4 * m + 0]);
+          acc[j][4 * m + 1] = fmaf(q.y, kf[j].y, acc[j][4 * m + 1]);
+          acc[j][4 * m + 2] = fmaf(q.z, kf[j].y, acc[j][4 * m + 2]);
+          acc[j][4 * m + 3] = fmaf(q.w, kf[j].y, acc[j][4 * m + 3]);
+        }
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) cur[j] = nxt[j];
+  }
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    float bst = acc[j][0];
+#pragma unroll
+    for (int m = 1; m < MQ; ++m) bst = fmaxf(bst, acc[j][m]);
+    best[j] = bst;
+  }
+}
+
 // One CTA: QB query blocks of one (batch, KV head) against every KV block.
-// Warps 0-3 epilogue (TMEM lane quarters), warp 4 TMA, warp 5 MMA issue; all
-// eight warps take part in the selection phase.
+// Warps 0-7 epilogue (warp & 3 = TMEM lane quarter, warp >> 2 = half of the accumulator
+// columns when the columns split on a list boundary), warp 8 TMA, warp 9 MMA issue, the
+// rest wait; the selection phase uses all sixteen.
 template <int GR>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 score_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map, const Params p) {
@@ -126,7 +214,8 @@ score_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant
   volatile int* misc = reinterpret_cast<volatile int*>(aux + 128);   // tmem base, abort, unsafe, l1q
   volatile int* flags = reinterpret_cast<volatile int*>(aux + 144);   // [128] list needs the exact fallback
   float* scratch_f = reinterpret_cast<float*>(aux + 144 + 128 * 4);
-  int* scratch_i = reinterpret_cast<int*>(scratch_f + 10);
+  int* scratch_i = reinterpret_cast<int*>(scratch_f + 20);
+  int* l1_s = scratch_i + 20;                            // [SEL_WARPS] largest L1 norm of a list's query descriptors
   auto bar = [&](int i) { return bar0 + 8u * i; };
   enum { A_FULL = 0, A_EMPTY = A_STAGES, B_FULL = 2 * A_STAGES, ACC_FULL = 2 * A_STAGES + 1, ACC_EMPTY = 2 * A_STAGES + 3 };
 
@@ -139,6 +228,9 @@ score_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant
   const int n_keys = p.nt * p.r;
   const int num_tiles = (n_keys + 127) >> 7;
   const int n_cols = p.qb * GR;                         // MMA N
+  // The column halves must hold whole lists (GR >= 16: a list is GR / 16 chunks of 16
+  // columns; GR < 16: a chunk holds 16 / GR lists), else warps 4-7 sit the tiles out.
+  const bool split = p.qb >= 2 && n_cols >= 32;
   // CTAs of one head walk the key tiles from different starting points, so they do
   // not all ask the L2 for the same tile at the same moment (a max is order-free).
   const int rot = static_cast<int>((static_cast<unsigned>(chunk) * 37u) % static_cast<unsigned>(num_tiles));
@@ -152,7 +244,7 @@ score_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(bar(ACC_FULL + i), 1);
-      mbar_init(bar(ACC_EMPTY + i), 4);
+      mbar_init(bar(ACC_EMPTY + i), split ? 8 : 4);
     }
     mbar_init(bar(B_FULL), 1);
     fence_mbar_init();
@@ -162,6 +254,7 @@ score_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant
     tmem_relinquish();
   }
   for (int j = threadIdx.x; j < p.qb * p.nt; j += NUM_THREADS) scores[j] = static_cast<int>(0x80000000u);
+  if (threadIdx.x < SEL_WARPS) l1_s[threadIdx.x] = 0;
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -220,11 +313,14 @@ score_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant
         tc_commit(bar(ACC_FULL + acc));
       }
     }
-  } else if (warp < 4) {
-    // epilogue: thread = key descriptor row of the tile
-    const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
+  } else if (warp < (split ? EPI_WARPS : 4)) {
+    // epilogue: thread = key descriptor row of the tile, over this warp's share of the columns
+    const int quarter = warp & 3;
+    const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
     const int r_log2 = 31 - __clz(p.r);                  // R is 1, 2 or 4
-    const int n_chunks = n_cols >> 4;
+    const int n_chunks = split ? (n_cols >> 5) : (n_cols >> 4);     // at most 4 either way
+    const int c0 = (warp >> 2) * n_chunks;               // first chunk of this warp
+    const int list0 = GR >= 16 ? (c0 * 16) / GR : c0 * (16 / (GR >= 16 ? 16 : GR));
     bool ok = true;
     for (int t = 0; ok && t < num_tiles; ++t) {
       const int acc = t & 1;
@@ -232,14 +328,14 @@ score_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant
       ok = __all_sync(0xffffffffu, w);
       if (!ok) break;
       tc_fence_after();
-      const int n = ((t + rot) % num_tiles) * 128 + warp * 32 + lane;
+      const int n = ((t + rot) % num_tiles) * 128 + quarter * 32 + lane;
       const bool row_ok = n < n_keys;
       const int blk = n >> r_log2;
-      const uint32_t t_acc = tmem + lane_base + acc * 128;
+      const uint32_t t_acc = tmem + lane_base + acc * 128 + c0 * 16;
       // all columns into registers with one wait, then hand the accumulator back at once
-      uint32_t v[8][16];
+      uint32_t v[4][16];
 #pragma unroll
-      for (int c = 0; c < 8; ++c)
+      for (int c = 0; c < 4; ++c)
         if (c < n_chunks) tmem_ld16(t_acc + c * 16, v[c]);
       tc_wait_ld();
       tc_fence_before();
@@ -249,11 +345,12 @@ score_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant
       // tile, so a plain store suffices.
       auto flush = [&](int tl, float val) {
         for (int d = 1; d < p.r; d <<= 1) val = fmaxf(val, __shfl_xor_sync(0xffffffffu, val, d));
+        tl += list0;
         if (row_ok && (lane & (p.r - 1)) == 0 && qtile0 + tl < p.qt) scores[tl * p.nt + blk] = f2ord(val);
       };
       float cur = -INFINITY;
 #pragma unroll
-      for (int c = 0; c < 8; ++c) {
+      for (int c = 0; c < 4; ++c) {
         if (c < n_chunks) {
           if (GR >= 16) {
             float m5[5];
@@ -289,60 +386,116 @@ score_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant
   }
   if (misc[1]) return;                       // a bounded wait gave up: status word is set
 
-  // ------------------------------------------------------------- selection: one warp per list
-  // The operand buffers are free now: per-warp fp32 query descriptors go to the A
-  // stages, per-warp candidate arrays to the B tile.
+  // ------------------------------------------------------------- selection, SEL_WARPS lists per round
+  // The operand buffers are free now: the fp32 query descriptors of the round's lists go to
+  // the A stages, their candidate arrays to the B tile. Per round:
+  //   1. all threads stage the query descriptors of the round's lists and their L1 norms;
+  //   2. one warp per list finds the C-th largest approximate score and the candidates;
+  //   3. all warps re-score (list, four key rows, up to 16 query rows) items exactly
+  //      (most of the arithmetic; four key rows per lane keep it off the shared-memory pipe);
+  //   4. one warp per list ranks its candidates by counting and proves safety.
   const __nv_bfloat16* kbase = p.kd + static_cast<long long>(bk) * n_keys * 128;
   const float kabs = p.k_absmax[bk];
   const int lists = min(p.qb, p.qt - qtile0);
   const int C = p.cand;
-  {
-    float* q_s = reinterpret_cast<float*>(gbase + OFF_A) + warp * 128 * MP;
-    int32_t* cand_ids = reinterpret_cast<int32_t*>(gbase + OFF_B) + warp * 2 * C_MAX;
-    float* cand_ex = reinterpret_cast<float*>(cand_ids + C_MAX);
+  constexpr int MQ = MP < 8 ? MP : 8;            // query rows of one re-scoring item
+  float* q_all = reinterpret_cast<float*>(gbase + OFF_A);
+  int32_t* cand_all = reinterpret_cast<int32_t*>(gbase + OFF_B);
+  for (int tl0 = 0; tl0 < lists; tl0 += SEL_WARPS) {
+    const int nl = min(SEL_WARPS, lists - tl0);
+    // 1. one descriptor row per thread: the transposing stores of a warp then fall into 32
+    //    different banks (a row per warp would put all of them into one)
+    for (int idx = threadIdx.x; idx < nl * MP; idx += NUM_THREADS) {
+      const int l = idx / MP, m = idx - l * MP;
+      const int mm = m < GR ? m : 0;             // padding repeats descriptor 0: the maximum is unchanged
+      const int g = mm / p.r, rq = mm - g * p.r;
+      const long long qrow = ((static_cast<long long>(b) * p.hq + kvh * group + g) * p.qt + qtile0 + tl0 + l) * p.r + rq;
+      const uint4* src = reinterpret_cast<const uint4*>(p.qd + qrow * 128);
+      float* dst = q_all + l * 128 * MP + m;
+      float sum = 0.f;
+#pragma unroll 4
+      for (int c = 0; c < 16; ++c) {
+        const uint4 raw = __ldg(src + c);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 f = __bfloat1622float2(h[e]);
+          dst[(c * 8 + 2 * e) * MP] = f.x;
+          dst[(c * 8 + 2 * e + 1) * MP] = f.y;
+          sum += fabsf(f.x);
+          sum += fabsf(f.y);
+        }
+      }
+      atomicMax(l1_s + l, __float_as_int(sum));  // non-negative floats order as ints
+    }
+    __syncthreads();
+    const int tl = tl0 + warp;
+    const bool mine = warp < nl;                 // this warp owns list tl of the round
+    int32_t* cand_ids = cand_all + warp * 2 * C_MAX;
+    int* cand_ord = cand_ids + C_MAX;            // exact scores as ordered ints, then as floats
     const unsigned lt_mask = (1u << lane) - 1u;
-    for (int tl = warp; tl < lists; tl += NUM_THREADS / 32) {
-      const int qtile = qtile0 + tl;
+    float delta = 0.f, thr = 0.f;
+    if (mine) {
       const unsigned* keys = reinterpret_cast<const unsigned*>(scores + tl * p.nt);   // ordered ints
-      // query descriptors of the list as fp32 [128][MP], and the largest L1 norm among them
-      for (int m = 0; m < MP; ++m) {        // one descriptor row per step: 256 contiguous bytes
-        const int mm = m < GR ? m : 0;
-        const int g = mm / p.r, rq = mm - g * p.r;
-        const long long qrow = ((static_cast<long long>(b) * p.hq + kvh * group + g) * p.qt + qtile) * p.r + rq;
-        const uint2 raw = __ldg(reinterpret_cast<const uint2*>(p.qd + qrow * 128) + lane);
-        const float2 f0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
-        const float2 f1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
-        q_s[(4 * lane + 0) * MP + m] = f0.x;
-        q_s[(4 * lane + 1) * MP + m] = f0.y;
-        q_s[(4 * lane + 2) * MP + m] = f1.x;
-        q_s[(4 * lane + 3) * MP + m] = f1.y;
-      }
-      __syncwarp();
-      float l1 = 0.f;
-      for (int m = lane; m < MP; m += 32) {
-        float sum = 0.f;
-        for (int d = 0; d < 128; ++d) sum += fabsf(q_s[d * MP + m]);
-        l1 = fmaxf(l1, sum);
-      }
-#pragma unroll
-      for (int d = 16; d > 0; d >>= 1) l1 = fmaxf(l1, __shfl_xor_sync(0xffffffffu, l1, d));
-      const float delta = EPS * (l1 * 1.0001f) * kabs * SCALE;
-      // C-th largest approximate score: bitwise search on the order-preserving keys
+      delta = EPS * (__int_as_float(l1_s[warp]) * 1.0001f) * kabs * SCALE;
+      // C-th largest approximate score T by radix selection on the order-preserving keys,
+      // eight bits per pass: histogram of the digit among the keys that match the digits
+      // found so far, then the largest digit whose suffix count reaches what is still needed.
+      // Afterwards `need` keys equal to T are wanted besides every key above T.
+      int* hist = cand_all + SEL_WARPS * 2 * C_MAX + warp * 256;
       unsigned T = 0;
-      for (int bit = 31; bit >= 0; --bit) {
-        const unsigned trial = T | (1u << bit);
-        int cnt = 0;
-        for (int j = lane; j < p.nt; j += 32) cnt += ((keys[j] ^ 0x80000000u) >= trial) ? 1 : 0;
+      int need = C;
+      for (int pass = 0; pass < 4; ++pass) {
+        const int shift = 24 - 8 * pass;
 #pragma unroll
-        for (int d = 16; d > 0; d >>= 1) cnt += __shfl_xor_sync(0xffffffffu, cnt, d);
-        if (cnt >= C) T = trial;
+        for (int i = 0; i < 8; ++i) hist[lane + 32 * i] = 0;
+        __syncwarp();
+        if (pass == 0) {
+#pragma unroll 4
+          for (int j = lane; j < p.nt; j += 32) atomicAdd(hist + ((keys[j] ^ 0x80000000u) >> 24), 1);
+        } else {
+          const unsigned top = T >> (shift + 8);
+#pragma unroll 4
+          for (int j = lane; j < p.nt; j += 32) {
+            const unsigned u = keys[j] ^ 0x80000000u;
+            if ((u >> (shift + 8)) == top) atomicAdd(hist + ((u >> shift) & 255u), 1);
+          }
+        }
+        __syncwarp();
+        int h[8], lsum = 0;                      // lane l holds digits 8 l .. 8 l + 7
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          h[i] = hist[8 * lane + i];
+          lsum += h[i];
+        }
+        int above = lsum;                        // inclusive suffix sum over lanes >= this one
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+          const int o = __shfl_down_sync(0xffffffffu, above, d);
+          if (lane + d < 32) above += o;
+        }
+        above -= lsum;                           // keys in digits of higher lanes
+        const bool here = above < need && need <= above + lsum;   // exactly one lane
+        int digit = 0, left = 0;
+        if (here) {
+          int run = above;
+#pragma unroll
+          for (int i = 7; i >= 0; --i) {
+            if (run < need && need <= run + h[i]) {
+              digit = 8 * lane + i;
+              left = need - run;
+            }
+            run += h[i];
+          }
+        }
+        const int src = __ffs(__ballot_sync(0xffffffffu, here)) - 1;
+        digit = __shfl_sync(0xffffffffu, digit, src);
+        need = __shfl_sync(0xffffffffu, left, src);
+        T |= static_cast<unsigned>(digit) << shift;
+        __syncwarp();
       }
       // candidates: everything above T, then ties at T in index order, C in total
-      int n_gt = 0;
-      for (int j = lane; j < p.nt; j += 32) n_gt += ((keys[j] ^ 0x80000000u) > T) ? 1 : 0;
-#pragma unroll
-      for (int d = 16; d > 0; d >>= 1) n_gt += __shfl_xor_sync(0xffffffffu, n_gt, d);
-      const int need_eq = C - n_gt;
+      const int need_eq = need;
       int out_run = 0, eq_run = 0;
       for (int base_j = 0; base_j < p.nt; base_j += 32) {
         const int j = base_j + lane;
@@ -356,51 +509,84 @@ score_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant
         out_run += __popc(take_ballot);
         eq_run += __popc(eq_ballot);
       }
-      __syncwarp();
-      const float thr = ord2f(static_cast<int>(T ^ 0x80000000u)) * SCALE;
-      // exact scores of the candidates (R adjacent lanes = the R key representatives of one block)
-      for (int base_i = 0; base_i < C * p.r; base_i += 32) {
+      for (int c = lane; c < C; c += 32) cand_ord[c] = f2ord(-INFINITY);
+      thr = ord2f(static_cast<int>(T ^ 0x80000000u)) * SCALE;
+    }
+    __syncthreads();
+    // 3. items of a list: (quad of key rows, chunk of MQ query rows), chunks fastest: the
+    //    MP / MQ lanes of a quad ask for the same key bytes (one memory transaction), and
+    //    their query values sit in different banks. Key row = candidate * R + representative;
+    //    rows past the end repeat the last one (a maximum does not mind).
+    {
+      const int rows = C * p.r, quads = (rows + 3) >> 2;
+      const int per_list = quads * (MP / MQ), total = nl * per_list;
+      for (int base_i = warp * 32; base_i < total; base_i += NUM_THREADS) {
         const int item = base_i + lane;
-        const bool valid = item < C * p.r;
-        const int c = item / p.r, rk = item - c * p.r;
-        const int blk = valid ? cand_ids[c] : 0;
-        float best = valid ? exact_key_best<MP>(q_s, kbase + (static_cast<long long>(blk) * p.r + rk) * 128) : -INFINITY;
-        for (int d = 1; d < p.r; d <<= 1) best = fmaxf(best, __shfl_xor_sync(0xffffffffu, best, d));
-        if (valid && rk == 0) cand_ex[c] = best * SCALE;
+        if (item < total) {
+          const int l = item / per_list;
+          const int rem = item - l * per_list;
+          const int quad = rem / (MP / MQ), chunk = rem - quad * (MP / MQ);
+          const int32_t* ids_l = cand_all + l * 2 * C_MAX;
+          int* ord_l = cand_all + l * 2 * C_MAX + C_MAX;
+          int cidx[4];
+          const uint4* krow[4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int row = min(quad * 4 + j, rows - 1);
+            cidx[j] = row / p.r;
+            const int rk = row - cidx[j] * p.r;
+            krow[j] = reinterpret_cast<const uint4*>(kbase + (static_cast<long long>(ids_l[cidx[j]]) * p.r + rk) * 128);
+          }
+          float best[4];
+          exact_quad_best<MQ>(q_all + l * 128 * MP + chunk * MQ, MP, krow[0], krow[1], krow[2], krow[3], best);
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            if (best[j] == best[j]) atomicMax(ord_l + cidx[j], f2ord(best[j]));   // a NaN leaves the slot alone
+        }
       }
+    }
+    __syncthreads();
+    if (mine) {
+      // 4. exact top-k of the candidates by (score descending, block id ascending): the rank
+      //    of a candidate is the number of candidates that beat it (ids are distinct)
+      float* cand_ex = reinterpret_cast<float*>(cand_ord);
+      for (int c = lane; c < C; c += 32) cand_ex[c] = ord2f(cand_ord[c]) * SCALE;
       __syncwarp();
-      // exact top-k of the candidates by (score descending, block id ascending)
       constexpr int SLOTS = C_MAX / 32;
       float es[SLOTS];
-      int ei[SLOTS];
+      int ei[SLOTS], rank[SLOTS];
 #pragma unroll
       for (int sidx = 0; sidx < SLOTS; ++sidx) {
         const int c = lane + 32 * sidx;
         es[sidx] = c < C ? cand_ex[c] : -INFINITY;
         ei[sidx] = c < C ? cand_ids[c] : INT_MAX;
+        rank[sidx] = 0;
       }
-      int32_t* out = p.ids + (static_cast<long long>(bk) * p.qt + qtile) * p.topk;
-      float kth = -INFINITY;
-      for (int rank = 0; rank < p.topk; ++rank) {
-        float bs = es[0];
-        int bi = ei[0];
-#pragma unroll
-        for (int sidx = 1; sidx < SLOTS; ++sidx)
-          if (better(es[sidx], ei[sidx], bs, bi)) { bs = es[sidx]; bi = ei[sidx]; }
-#pragma unroll
-        for (int d = 16; d > 0; d >>= 1) {
-          const float os = __shfl_xor_sync(0xffffffffu, bs, d);
-          const int oi = __shfl_xor_sync(0xffffffffu, bi, d);
-          if (better(os, oi, bs, bi)) { bs = os; bi = oi; }
-        }
+#pragma unroll 4
+      for (int j = 0; j < C; ++j) {
+        const float sj = cand_ex[j];
+        const int ij = cand_ids[j];
 #pragma unroll
         for (int sidx = 0; sidx < SLOTS; ++sidx)
-          if (ei[sidx] == bi) { es[sidx] = -INFINITY; ei[sidx] = INT_MAX; }
-        if (lane == 0) out[rank] = bi;
-        kth = bs;
+          if (sidx * 32 < C) rank[sidx] += better(sj, ij, es[sidx], ei[sidx]) ? 1 : 0;
       }
+      int32_t* out = p.ids + (static_cast<long long>(bk) * p.qt + qtile0 + tl) * p.topk;
+      float kth = -INFINITY;
+#pragma unroll
+      for (int sidx = 0; sidx < SLOTS; ++sidx) {
+        const int c = lane + 32 * sidx;
+        if (c < C && rank[sidx] < p.topk) out[rank[sidx]] = ei[sidx];
+        if (c < C && rank[sidx] == p.topk - 1) kth = es[sidx];
+      }
+#pragma unroll
+      for (int d = 16; d > 0; d >>= 1) kth = fmaxf(kth, __shfl_xor_sync(0xffffffffu, kth, d));
       const bool safe = (C >= p.nt) || (kth > thr + delta);
       if (lane == 0) flags[tl] = safe ? 0 : 1;
+    }
+    if (tl0 + SEL_WARPS < lists) {               // another round re-uses the buffers
+      __syncthreads();
+      if (threadIdx.x < SEL_WARPS) l1_s[threadIdx.x] = 0;
+      __syncthreads();
     }
   }
   __syncthreads();
@@ -531,7 +717,7 @@ int launch_summary_select_tc(const void* qd, const void* kd, void* aux, int32_t*
   p.q_chunks = (qt + qb - 1) / qb;
   const int grid = batch * hkv * p.q_chunks;
   const size_t smem = OFF_SCORES + ((static_cast<size_t>(qb) * nt * 4 + 15) & ~static_cast<size_t>(15)) + 144 +
-                      128 * 4 + 10 * 4 + 16 * 4 + 1024;
+                      128 * 4 + 20 * 4 + 20 * 4 + SEL_WARPS * 4 + 1024;
   switch (gr) {
     case 1: return launch_gr<1>(qm, km, p, grid, smem, ctx, 0, stream);
     case 2: return launch_gr<2>(qm, km, p, grid, smem, ctx, 1, stream);
