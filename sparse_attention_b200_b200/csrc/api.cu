@@ -276,7 +276,7 @@ int sparse_b200_indexer_summary(const void* q, const void* k, void* q_desc, void
 
 int64_t sparse_b200_indexer_summary_aux_bytes(int batch, int hkv) {
   if (batch <= 0 || hkv <= 0) return SB_ERR_INVALID;
-  return (static_cast<int64_t>(batch) * hkv + 1) * 4;
+  return (2 * static_cast<int64_t>(batch) * hkv + 1) * 4;
 }
 
 int sparse_b200_indexer_summary_fast(const void* q, const void* k, void* q_desc, void* k_desc, void* aux,
@@ -291,7 +291,7 @@ int sparse_b200_indexer_summary_fast(const void* q, const void* k, void* q_desc,
   if (rc) return rc;
   // small problems: the exact cluster kernel fills the GPU better than the tensor-core pre-filter
   rc = launch_summary_small(q_desc, k_desc, nullptr, block_idx,
-                            static_cast<int32_t*>(aux) + static_cast<long long>(batch) * hkv, batch, hq, hkv,
+                            static_cast<int32_t*>(aux) + 2 * static_cast<long long>(batch) * hkv, batch, hq, hkv,
                             sq / 128, skv / 128, representatives, topk, static_cast<cudaStream_t>(stream));
   if (rc != 1) return rc;
   rc = launch_summary_select_tc(q_desc, k_desc, aux, block_idx, batch, hq, hkv, sq / 128, skv / 128, representatives,

@@ -8,6 +8,7 @@
 #include <cuda_fp8.h>
 #include <cuda_fp16.h>
 #include <cstdint>
+#include "ptx.cuh"
 
 namespace sb {
 
@@ -46,37 +47,6 @@ __device__ __forceinline__ void fp4_stage_rows(uint32_t* rows_i8, float* rows_sc
   }
   for (int e = threadIdx.x; e < 128 * 8; e += blockDim.x)
     rows_sc[e] = fold * e4m3_to_float(scales[(e >> 3) * scale_pitch + (e & 7)]);
-}
-
-// Two fp32 lanes per instruction (round-to-nearest each lane, bit-identical with the scalar forms).
-__device__ __forceinline__ unsigned long long f32x2_pack(float lo, float hi) {
-  unsigned long long r;
-  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
-  return r;
-}
-__device__ __forceinline__ unsigned long long f32x2_pack_bits(int lo, int hi) {
-  unsigned long long r;
-  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo), "r"(hi));
-  return r;
-}
-__device__ __forceinline__ void f32x2_unpack(unsigned long long v, float& lo, float& hi) {
-  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
-}
-__device__ __forceinline__ unsigned long long f32x2_mul(unsigned long long a, unsigned long long b) {
-  unsigned long long r;
-  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
-  return r;
-}
-__device__ __forceinline__ unsigned long long f32x2_sub(unsigned long long a, unsigned long long b) {
-  unsigned long long r;
-  asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
-  return r;
-}
-__device__ __forceinline__ unsigned long long f32x2_fma(unsigned long long a, unsigned long long b,
-                                                        unsigned long long c) {
-  unsigned long long r;
-  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
-  return r;
 }
 
 // Maximum over the 16 x 128 (query, key) scores of one warp: queries 16 * warp .. + 15 of the staged

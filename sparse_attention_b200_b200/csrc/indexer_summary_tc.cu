@@ -34,6 +34,7 @@ constexpr int PANEL_BYTES = 128 * 128;
 constexpr int A_STAGES = SB_STC_STAGES;
 constexpr int SCORE_LIMIT = 232448 - 2048 - (A_STAGES + 1) * TILE_BYTES;   // bytes of shared memory left for scores
 constexpr int C_MAX = 192;                 // candidates per list
+constexpr int LIST_WORDS = 3 * C_MAX;      // per list: block ids, approximate scores, exact scores (ordered ints)
 constexpr int NUM_THREADS = 512;            // ten warps have a role in the scoring phase; all sixteen re-score
 constexpr int EPI_WARPS = 8;               // two column halves x four TMEM lane quarters
 constexpr int SEL_WARPS = 8;               // warps of the selection phase (one list each at a time)
@@ -50,6 +51,7 @@ struct Params {
   const __nv_bfloat16* qd;     // [B, Hq, qt, R, 128]
   const __nv_bfloat16* kd;     // [B, Hkv, nt, R, 128]
   const float* k_absmax;       // [B * Hkv] max |element| of the key descriptors of a head
+  const float* k_norm2;        // [B * Hkv] max squared L2 norm of a key descriptor of the head
   int32_t* ids;                // [B, Hkv, qt, topk]
   int* status;
   int* fallbacks;              // optional counter of lists that took the exact fallback
@@ -142,55 +144,75 @@ __device__ __forceinline__ float exact_key_best(const float* q_s, const __nv_bfl
 template <int MQ>
 __device__ __forceinline__ void exact_quad_best(const float* q_s, int stride, const uint4* k0, const uint4* k1,
                                                 const uint4* k2, const uint4* k3, float (&best)[4]) {
-  float acc[4][MQ];
+  // two query rows per 64-bit accumulator, packed FMAs (each half an ordinary fp32 FMA)
+  unsigned long long acc[4][MQ / 2];
 #pragma unroll
   for (int j = 0; j < 4; ++j)
 #pragma unroll
-    for (int m = 0; m < MQ; ++m) acc[j][m] = 0.f;
-  uint4 cur[4] = {__ldg(k0), __ldg(k1), __ldg(k2), __ldg(k3)};
-#pragma unroll 1
-  for (int c = 0; c < 16; ++c) {
-    uint4 nxt[4];
-    const int cn = c < 15 ? c + 1 : 15;
-    nxt[0] = __ldg(k0 + cn); nxt[1] = __ldg(k1 + cn); nxt[2] = __ldg(k2 + cn); nxt[3] = __ldg(k3 + cn);
+    for (int m = 0; m < MQ / 2; ++m) acc[j][m] = 0ull;
+  // A lane's 128 features are strictly sequential, so a wait for memory inside the loop is
+  // paid in full: the 16-byte pieces of the four rows are requested two steps (16 features)
+  // ahead, through three rotating buffers.
+  const uint4* kr[4] = {k0, k1, k2, k3};
+  auto fetch = [&](uint4 (&buf)[4], int c) {
+    const int cc = c < 15 ? c : 15;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) buf[j] = __ldg(kr[j] + cc);
+  };
+  auto step = [&](const uint4 (&buf)[4], int c) {
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
-      float2 kf[4];
+      unsigned long long kx[4], ky[4];
 #pragma unroll
-      for (int j = 0; j < 4; ++j) kf[j] = __bfloat1622float2(reinterpret_cast<const __nv_bfloat162*>(&cur[j])[e]);
-      const float4* qa = reinterpret_cast<const float4*>(q_s + (c * 8 + 2 * e) * stride);
-      const float4* qb = reinterpret_cast<const float4*>(q_s + (c * 8 + 2 * e + 1) * stride);
+      for (int j = 0; j < 4; ++j) {
+        const float2 kf = __bfloat1622float2(reinterpret_cast<const __nv_bfloat162*>(&buf[j])[e]);
+        kx[j] = f32x2_pack(kf.x, kf.x);
+        ky[j] = f32x2_pack(kf.y, kf.y);
+      }
+      const ulonglong2* qa = reinterpret_cast<const ulonglong2*>(q_s + (c * 8 + 2 * e) * stride);
+      const ulonglong2* qb = reinterpret_cast<const ulonglong2*>(q_s + (c * 8 + 2 * e + 1) * stride);
 #pragma unroll
       for (int m = 0; m < MQ / 4; ++m) {
-        const float4 q = qa[m];
+        const ulonglong2 q = qa[m];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          acc[j][4 * m + 0] = fmaf(q.x, kf[j].x, acc[j][4 * m + 0]);
-          acc[j][4 * m + 1] = fmaf(q.y, kf[j].x, acc[j][4 * m + 1]);
-          acc[j][4 * m + 2] = fmaf(q.z, kf[j].x, acc[j][4 * m + 2]);
-          acc[j][4 * m + 3] = fmaf(q.w, kf[j].x, acc[j][4 * m + 3]);
+          acc[j][2 * m] = f32x2_fma(q.x, kx[j], acc[j][2 * m]);
+          acc[j][2 * m + 1] = f32x2_fma(q.y, kx[j], acc[j][2 * m + 1]);
         }
       }
 #pragma unroll
       for (int m = 0; m < MQ / 4; ++m) {
-        const float4 q = qb[m];
+        const ulonglong2 q = qb[m];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          acc[j][4 * m + 0] = fmaf(q.x, kf[j].y, acc[j][4 * m + 0]);
-          acc[j][4 * m + 1] = fmaf(q.y, kf[j].y, acc[j][4 * m + 1]);
-          acc[j][4 * m + 2] = fmaf(q.z, kf[j].y, acc[j][4 * m + 2]);
-          acc[j][4 * m + 3] = fmaf(q.w, kf[j].y, acc[j][4 * m + 3]);
+          acc[j][2 * m] = f32x2_fma(q.x, ky[j], acc[j][2 * m]);
+          acc[j][2 * m + 1] = f32x2_fma(q.y, ky[j], acc[j][2 * m + 1]);
         }
       }
     }
-#pragma unroll
-    for (int j = 0; j < 4; ++j) cur[j] = nxt[j];
+  };
+  uint4 b0[4], b1[4], b2[4];
+  fetch(b0, 0);
+  fetch(b1, 1);
+#pragma unroll 1
+  for (int c = 0; c < 15; c += 3) {              // on entry b0 = step c, b1 = step c + 1
+    fetch(b2, c + 2);
+    step(b0, c);
+    fetch(b0, c + 3);
+    step(b1, c + 1);
+    fetch(b1, c + 4);
+    step(b2, c + 2);
   }
+  step(b0, 15);
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
-    float bst = acc[j][0];
+    float bst = -INFINITY;
 #pragma unroll
-    for (int m = 1; m < MQ; ++m) bst = fmaxf(bst, acc[j][m]);
+    for (int m = 0; m < MQ / 2; ++m) {
+      float lo, hi;
+      f32x2_unpack(acc[j][m], lo, hi);
+      bst = fmaxf(bst, fmaxf(lo, hi));
+    }
     best[j] = bst;
   }
 }
@@ -215,6 +237,10 @@ score_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant
   volatile int* flags = reinterpret_cast<volatile int*>(aux + 144);   // [128] list needs the exact fallback
   float* scratch_f = reinterpret_cast<float*>(aux + 144 + 128 * 4);
   int* scratch_i = reinterpret_cast<int*>(scratch_f + 20);
+  int* work_cnt = scratch_i + 20 + SEL_WARPS;            // [SEL_WARPS] candidates that need an exact score
+  float* delta_s = reinterpret_cast<float*>(work_cnt + SEL_WARPS);   // [SEL_WARPS] error bound of a list
+  float* kth_s = delta_s + SEL_WARPS;                    // [SEL_WARPS] lower bound of the k-th exact score
+  int* l2_s = reinterpret_cast<int*>(kth_s + SEL_WARPS);  // [SEL_WARPS] largest squared L2 norm of a query descriptor
   int* l1_s = scratch_i + 20;                            // [SEL_WARPS] largest L1 norm of a list's query descriptors
   auto bar = [&](int i) { return bar0 + 8u * i; };
   enum { A_FULL = 0, A_EMPTY = A_STAGES, B_FULL = 2 * A_STAGES, ACC_FULL = 2 * A_STAGES + 1, ACC_EMPTY = 2 * A_STAGES + 3 };
@@ -254,7 +280,7 @@ score_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant
     tmem_relinquish();
   }
   for (int j = threadIdx.x; j < p.qb * p.nt; j += NUM_THREADS) scores[j] = static_cast<int>(0x80000000u);
-  if (threadIdx.x < SEL_WARPS) l1_s[threadIdx.x] = 0;
+  if (threadIdx.x < SEL_WARPS) l1_s[threadIdx.x] = l2_s[threadIdx.x] = 0;
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -391,11 +417,11 @@ score_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant
   // the A stages, their candidate arrays to the B tile. Per round:
   //   1. all threads stage the query descriptors of the round's lists and their L1 norms;
   //   2. one warp per list finds the C-th largest approximate score and the candidates;
-  //   3. all warps re-score (list, four key rows, up to 16 query rows) items exactly
-  //      (most of the arithmetic; four key rows per lane keep it off the shared-memory pipe);
-  //   4. one warp per list ranks its candidates by counting and proves safety.
+  //   3. all threads find the candidates whose order the approximate scores do not settle,
+  //      and re-score those exactly, (four key rows, up to 8 query rows) per lane;
+  //   4. all threads rank the candidates by counting; one thread per list proves safety.
   const __nv_bfloat16* kbase = p.kd + static_cast<long long>(bk) * n_keys * 128;
-  const float kabs = p.k_absmax[bk];
+  const float kabs = p.k_absmax[bk], knorm = sqrtf(p.k_norm2[bk]);
   const int lists = min(p.qb, p.qt - qtile0);
   const int C = p.cand;
   constexpr int MQ = MP < 8 ? MP : 8;            // query rows of one re-scoring item
@@ -412,7 +438,7 @@ score_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant
       const long long qrow = ((static_cast<long long>(b) * p.hq + kvh * group + g) * p.qt + qtile0 + tl0 + l) * p.r + rq;
       const uint4* src = reinterpret_cast<const uint4*>(p.qd + qrow * 128);
       float* dst = q_all + l * 128 * MP + m;
-      float sum = 0.f;
+      float sum = 0.f, squares = 0.f;
 #pragma unroll 4
       for (int c = 0; c < 16; ++c) {
         const uint4 raw = __ldg(src + c);
@@ -424,41 +450,61 @@ score_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant
           dst[(c * 8 + 2 * e + 1) * MP] = f.y;
           sum += fabsf(f.x);
           sum += fabsf(f.y);
+          squares = fmaf(f.x, f.x, squares);
+          squares = fmaf(f.y, f.y, squares);
         }
       }
       atomicMax(l1_s + l, __float_as_int(sum));  // non-negative floats order as ints
+      atomicMax(l2_s + l, __float_as_int(squares));
     }
     __syncthreads();
     const int tl = tl0 + warp;
     const bool mine = warp < nl;                 // this warp owns list tl of the round
-    int32_t* cand_ids = cand_all + warp * 2 * C_MAX;
-    int* cand_ord = cand_ids + C_MAX;            // exact scores as ordered ints, then as floats
+    int32_t* cand_ids = cand_all + warp * LIST_WORDS;
+    float* cand_apx = reinterpret_cast<float*>(cand_ids + C_MAX);
     const unsigned lt_mask = (1u << lane) - 1u;
     float delta = 0.f, thr = 0.f;
     if (mine) {
       const unsigned* keys = reinterpret_cast<const unsigned*>(scores + tl * p.nt);   // ordered ints
-      delta = EPS * (__int_as_float(l1_s[warp]) * 1.0001f) * kabs * SCALE;
-      // C-th largest approximate score T by radix selection on the order-preserving keys,
-      // eight bits per pass: histogram of the digit among the keys that match the digits
-      // found so far, then the largest digit whose suffix count reaches what is still needed.
-      // Afterwards `need` keys equal to T are wanted besides every key above T.
-      int* hist = cand_all + SEL_WARPS * 2 * C_MAX + warp * 256;
-      unsigned T = 0;
+      // sum of |q_d k_d| over the features, bounded by Hoelder (L1 x max) and by Cauchy-Schwarz
+      delta = EPS * 1.0001f * fminf(__int_as_float(l1_s[warp]) * kabs, sqrtf(__int_as_float(l2_s[warp])) * knorm) * SCALE;
+      // C-th largest approximate score T by radix selection, eight bits per pass: histogram
+      // of the digit among the keys that match the digits found so far, then the largest
+      // digit whose suffix count reaches what is still needed. The keys are first moved to
+      // w = (key - smallest key) << (leading zeros of the range): scores of one list share
+      // their exponent bits, and a digit taken from those would send every lane of a warp to
+      // the same histogram bin. Afterwards `need` keys equal to T are wanted besides all above.
+      int* hist = cand_all + SEL_WARPS * LIST_WORDS + warp * 256;
+      unsigned umin = 0xffffffffu, umax = 0u;
+#pragma unroll 8
+      for (int j = lane; j < p.nt; j += 32) {
+        const unsigned u = keys[j] ^ 0x80000000u;
+        umin = min(umin, u);
+        umax = max(umax, u);
+      }
+      umin = __reduce_min_sync(0xffffffffu, umin);
+      umax = __reduce_max_sync(0xffffffffu, umax);
+      const int lz = min(__clz(umax - umin), 31);
+      unsigned W = 0;
       int need = C;
       for (int pass = 0; pass < 4; ++pass) {
         const int shift = 24 - 8 * pass;
+        if (shift + 8 <= lz) break;              // the remaining bits of every w are zero
 #pragma unroll
         for (int i = 0; i < 8; ++i) hist[lane + 32 * i] = 0;
         __syncwarp();
-        if (pass == 0) {
-#pragma unroll 4
-          for (int j = lane; j < p.nt; j += 32) atomicAdd(hist + ((keys[j] ^ 0x80000000u) >> 24), 1);
-        } else {
-          const unsigned top = T >> (shift + 8);
-#pragma unroll 4
-          for (int j = lane; j < p.nt; j += 32) {
-            const unsigned u = keys[j] ^ 0x80000000u;
-            if ((u >> (shift + 8)) == top) atomicAdd(hist + ((u >> shift) & 255u), 1);
+        // keys are fetched eight at a time: a load cannot be moved above an atomic by the
+        // compiler, and one round trip to shared memory per key is what this loop costs otherwise
+        const unsigned top = pass == 0 ? 0u : W >> (shift + 8);
+        for (int j0 = lane; j0 < p.nt; j0 += 256) {
+          unsigned w[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) w[i] = j0 + 32 * i < p.nt ? keys[j0 + 32 * i] : 0u;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const unsigned x = ((w[i] ^ 0x80000000u) - umin) << lz;
+            const bool match = pass == 0 || (x >> (shift + 8)) == top;
+            if (j0 + 32 * i < p.nt && match) atomicAdd(hist + ((x >> shift) & 255u), 1);
           }
         }
         __syncwarp();
@@ -491,50 +537,102 @@ score_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant
         const int src = __ffs(__ballot_sync(0xffffffffu, here)) - 1;
         digit = __shfl_sync(0xffffffffu, digit, src);
         need = __shfl_sync(0xffffffffu, left, src);
-        T |= static_cast<unsigned>(digit) << shift;
+        W |= static_cast<unsigned>(digit) << shift;
         __syncwarp();
       }
+      const unsigned T = (W >> lz) + umin;
       // candidates: everything above T, then ties at T in index order, C in total
       const int need_eq = need;
       int out_run = 0, eq_run = 0;
-      for (int base_j = 0; base_j < p.nt; base_j += 32) {
-        const int j = base_j + lane;
-        const unsigned u = j < p.nt ? (keys[j] ^ 0x80000000u) : 0u;
-        const bool is_gt = j < p.nt && u > T;
-        const bool is_eq = j < p.nt && u == T;
-        const unsigned eq_ballot = __ballot_sync(0xffffffffu, is_eq);
-        const bool take = is_gt || (is_eq && eq_run + __popc(eq_ballot & lt_mask) < need_eq);
-        const unsigned take_ballot = __ballot_sync(0xffffffffu, take);
-        if (take) cand_ids[out_run + __popc(take_ballot & lt_mask)] = j;
-        out_run += __popc(take_ballot);
-        eq_run += __popc(eq_ballot);
+      for (int j0 = 0; j0 < p.nt; j0 += 256) {   // eight groups of 32 keys per step
+        unsigned u[8];
+        bool any_ge = false;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int j = j0 + 32 * i + lane;
+          u[i] = j < p.nt ? (keys[j] ^ 0x80000000u) : 0u;
+          any_ge |= j < p.nt && u[i] >= T;
+        }
+        if (!__any_sync(0xffffffffu, any_ge)) continue;     // most steps hold no candidate
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int j = j0 + 32 * i + lane;
+          const bool is_ge = j < p.nt && u[i] >= T;
+          const bool is_eq = is_ge && u[i] == T;
+          const unsigned eq_ballot = __ballot_sync(0xffffffffu, is_eq);
+          const bool take = is_ge && (!is_eq || eq_run + __popc(eq_ballot & lt_mask) < need_eq);
+          const unsigned take_ballot = __ballot_sync(0xffffffffu, take);
+          if (take) {
+            const int pos = out_run + __popc(take_ballot & lt_mask);
+            cand_ids[pos] = j;
+            cand_apx[pos] = ord2f(static_cast<int>(u[i] ^ 0x80000000u)) * SCALE;
+          }
+          out_run += __popc(take_ballot);
+          eq_run += __popc(eq_ballot);
+        }
       }
-      for (int c = lane; c < C; c += 32) cand_ord[c] = f2ord(-INFINITY);
       thr = ord2f(static_cast<int>(T ^ 0x80000000u)) * SCALE;
+      if (lane == 0) {
+        delta_s[warp] = delta;
+        work_cnt[warp] = 0;
+        kth_s[warp] = -INFINITY;
+      }
     }
     __syncthreads();
-    // 3. items of a list: (quad of key rows, chunk of MQ query rows), chunks fastest: the
-    //    MP / MQ lanes of a quad ask for the same key bytes (one memory transaction), and
-    //    their query values sit in different banks. Key row = candidate * R + representative;
-    //    rows past the end repeat the last one (a maximum does not mind).
+    // 3a. Approximate and exact score of a block differ by at most delta, so two candidates
+    //     whose approximate scores are more than 2 delta apart are ordered by them for certain.
+    //     Only a candidate with another one within 2 delta needs its exact score: those go to
+    //     the work list of their list (the histograms are free by now).
+    int* work = cand_all + SEL_WARPS * LIST_WORDS;            // [SEL_WARPS][C_MAX] candidate slots
+    for (int idx = threadIdx.x; idx < nl * C; idx += NUM_THREADS) {
+      const int l = idx / C, c = idx - l * C;
+      const float* apx = reinterpret_cast<const float*>(cand_all + l * LIST_WORDS + C_MAX);
+      const float a = apx[c], two = 2.f * delta_s[l];
+      int near = 0;
+#pragma unroll 4
+      for (int j = 0; j < C; ++j) near |= static_cast<int>(j != c) & static_cast<int>(!(fabsf(a - apx[j]) > two));
+      int* ord = cand_all + l * LIST_WORDS + 2 * C_MAX;
+      if (near) {
+        ord[c] = f2ord(-INFINITY);
+        work[l * C_MAX + atomicAdd(work_cnt + l, 1)] = c;
+      } else {
+        ord[c] = INT_MIN;                        // "no exact score": below every ordered float
+      }
+    }
+    __syncthreads();
+    // 3b. exact scores of the work lists. Items of a list: (quad of key rows, chunk of MQ query
+    //     rows), chunks fastest: the MP / MQ lanes of a quad ask for the same key bytes (one
+    //     memory transaction), and their query values sit in different banks. Key row = work
+    //     entry * R + representative; rows past the end repeat the last one (a maximum does
+    //     not mind).
     {
-      const int rows = C * p.r, quads = (rows + 3) >> 2;
-      const int per_list = quads * (MP / MQ), total = nl * per_list;
+      int pre[SEL_WARPS + 1];
+      pre[0] = 0;
+#pragma unroll
+      for (int l = 0; l < SEL_WARPS; ++l) {
+        const int rows = l < nl ? work_cnt[l] * p.r : 0;
+        pre[l + 1] = pre[l] + ((rows + 3) >> 2) * (MP / MQ);
+      }
+      const int total = pre[SEL_WARPS];
       for (int base_i = warp * 32; base_i < total; base_i += NUM_THREADS) {
         const int item = base_i + lane;
         if (item < total) {
-          const int l = item / per_list;
-          const int rem = item - l * per_list;
+          int l = 0, first = 0;
+#pragma unroll
+          for (int x = 1; x < SEL_WARPS; ++x)
+            if (item >= pre[x]) { l = x; first = pre[x]; }
+          const int rem = item - first;
           const int quad = rem / (MP / MQ), chunk = rem - quad * (MP / MQ);
-          const int32_t* ids_l = cand_all + l * 2 * C_MAX;
-          int* ord_l = cand_all + l * 2 * C_MAX + C_MAX;
+          const int rows = work_cnt[l] * p.r;
+          const int32_t* ids_l = cand_all + l * LIST_WORDS;
+          int* ord_l = cand_all + l * LIST_WORDS + 2 * C_MAX;
           int cidx[4];
           const uint4* krow[4];
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
             const int row = min(quad * 4 + j, rows - 1);
-            cidx[j] = row / p.r;
-            const int rk = row - cidx[j] * p.r;
+            const int n = row / p.r, rk = row - n * p.r;
+            cidx[j] = work[l * C_MAX + n];
             krow[j] = reinterpret_cast<const uint4*>(kbase + (static_cast<long long>(ids_l[cidx[j]]) * p.r + rk) * 128);
           }
           float best[4];
@@ -546,46 +644,36 @@ score_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant
       }
     }
     __syncthreads();
-    if (mine) {
-      // 4. exact top-k of the candidates by (score descending, block id ascending): the rank
-      //    of a candidate is the number of candidates that beat it (ids are distinct)
-      float* cand_ex = reinterpret_cast<float*>(cand_ord);
-      for (int c = lane; c < C; c += 32) cand_ex[c] = ord2f(cand_ord[c]) * SCALE;
-      __syncwarp();
-      constexpr int SLOTS = C_MAX / 32;
-      float es[SLOTS];
-      int ei[SLOTS], rank[SLOTS];
-#pragma unroll
-      for (int sidx = 0; sidx < SLOTS; ++sidx) {
-        const int c = lane + 32 * sidx;
-        es[sidx] = c < C ? cand_ex[c] : -INFINITY;
-        ei[sidx] = c < C ? cand_ids[c] : INT_MAX;
-        rank[sidx] = 0;
-      }
+    // 4. rank of a candidate = number of candidates that beat it in (exact score descending,
+    //    block id ascending): decided by the approximate scores when they are more than
+    //    2 delta apart, else by the exact scores (both candidates have one then).
+    for (int idx = threadIdx.x; idx < nl * C; idx += NUM_THREADS) {
+      const int l = idx / C, c = idx - l * C;
+      const int32_t* ids_l = cand_all + l * LIST_WORDS;
+      const float* apx = reinterpret_cast<const float*>(ids_l + C_MAX);
+      const int* ord = ids_l + 2 * C_MAX;
+      const float dl = delta_s[l], two = 2.f * dl;
+      const float a = apx[c];
+      const int o = ord[c], id = ids_l[c];
+      const float e = ord2f(o) * SCALE;
+      int rank = 0;
 #pragma unroll 4
       for (int j = 0; j < C; ++j) {
-        const float sj = cand_ex[j];
-        const int ij = cand_ids[j];
-#pragma unroll
-        for (int sidx = 0; sidx < SLOTS; ++sidx)
-          if (sidx * 32 < C) rank[sidx] += better(sj, ij, es[sidx], ei[sidx]) ? 1 : 0;
+        const float d = apx[j] - a, ej = ord2f(ord[j]) * SCALE;
+        const int gt = static_cast<int>(d > two), lt = static_cast<int>(d < -two);
+        const int exact = static_cast<int>(ej > e) | (static_cast<int>(ej == e) & static_cast<int>(ids_l[j] < id));
+        rank += gt | ((gt | lt) ^ 1) & exact;
       }
-      int32_t* out = p.ids + (static_cast<long long>(bk) * p.qt + qtile0 + tl) * p.topk;
-      float kth = -INFINITY;
-#pragma unroll
-      for (int sidx = 0; sidx < SLOTS; ++sidx) {
-        const int c = lane + 32 * sidx;
-        if (c < C && rank[sidx] < p.topk) out[rank[sidx]] = ei[sidx];
-        if (c < C && rank[sidx] == p.topk - 1) kth = es[sidx];
-      }
-#pragma unroll
-      for (int d = 16; d > 0; d >>= 1) kth = fmaxf(kth, __shfl_xor_sync(0xffffffffu, kth, d));
-      const bool safe = (C >= p.nt) || (kth > thr + delta);
-      if (lane == 0) flags[tl] = safe ? 0 : 1;
+      if (rank < p.topk) p.ids[(static_cast<long long>(bk) * p.qt + qtile0 + tl0 + l) * p.topk + rank] = id;
+      // a lower bound of the k-th exact score, for the safety test
+      if (rank == p.topk - 1) kth_s[l] = o != INT_MIN ? e : a - dl;
     }
+    __syncthreads();
+    // safe: no block outside the candidates (exact score <= thr + delta) can reach the top k
+    if (mine && lane == 0) flags[tl] = ((C >= p.nt) || (kth_s[warp] > thr + delta)) ? 0 : 1;
     if (tl0 + SEL_WARPS < lists) {               // another round re-uses the buffers
       __syncthreads();
-      if (threadIdx.x < SEL_WARPS) l1_s[threadIdx.x] = 0;
+      if (threadIdx.x < SEL_WARPS) l1_s[threadIdx.x] = l2_s[threadIdx.x] = 0;
       __syncthreads();
     }
   }
@@ -618,26 +706,41 @@ score_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant
   }
 }
 
-// max |element| of the key descriptors of each (batch, KV head)
+// max |element| and max squared L2 norm of the key descriptors of each (batch, KV head);
+// sixteen adjacent lanes hold one descriptor (per_head is a multiple of 128 elements)
 __global__ void __launch_bounds__(256) absmax_kernel(const __nv_bfloat16* __restrict__ kd, float* __restrict__ out,
-                                                     long long per_head) {
+                                                     float* __restrict__ out_norm2, long long per_head) {
   const int head = blockIdx.y;
   const uint4* src = reinterpret_cast<const uint4*>(kd + static_cast<long long>(head) * per_head);
   const long long n16 = per_head / 8;
-  float m = 0.f;
-  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n16;
-       i += static_cast<long long>(gridDim.x) * blockDim.x) {
-    const uint4 v = __ldg(src + i);
+  float m = 0.f, n2 = 0.f;
+  const int lane = threadIdx.x & 31;
+  for (long long base = static_cast<long long>(blockIdx.x) * blockDim.x + (threadIdx.x - lane); base < n16;
+       base += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long i = base + lane;
+    const uint4 v = i < n16 ? __ldg(src + i) : make_uint4(0u, 0u, 0u, 0u);
     const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+    float sq = 0.f;
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
       const float2 f = __bfloat1622float2(h[e]);
       m = fmaxf(m, fmaxf(fabsf(f.x), fabsf(f.y)));
+      sq = fmaf(f.x, f.x, sq);
+      sq = fmaf(f.y, f.y, sq);
     }
+#pragma unroll
+    for (int d = 8; d > 0; d >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, d);
+    n2 = fmaxf(n2, sq);
   }
 #pragma unroll
-  for (int d = 16; d > 0; d >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, d));
-  if ((threadIdx.x & 31) == 0) atomicMax(reinterpret_cast<int*>(out + head), __float_as_int(m));
+  for (int d = 16; d > 0; d >>= 1) {
+    m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, d));
+    n2 = fmaxf(n2, __shfl_xor_sync(0xffffffffu, n2, d));
+  }
+  if (lane == 0) {
+    atomicMax(reinterpret_cast<int*>(out + head), __float_as_int(m));
+    atomicMax(reinterpret_cast<int*>(out_norm2 + head), __float_as_int(n2));
+  }
 }
 
 template <int GR>
@@ -657,7 +760,8 @@ static int launch_gr(const CUtensorMap& qm, const CUtensorMap& km, const Params&
 
 // Returns SB_OK when the tensor-core path ran, 1 when the problem is not eligible
 // (the caller then runs the exact kernel), negative on error.
-// aux: device floats [B*Hkv] (key abs-max, filled here) + 1 int (fallback counter).
+// aux: device floats [B*Hkv] (key abs-max) + [B*Hkv] (largest squared key norm), both filled
+// here, + 1 int (fallback counter).
 int launch_summary_select_tc(const void* qd, const void* kd, void* aux, int32_t* ids, int batch, int hq, int hkv,
                              int qt, int nt, int r, int topk, cudaStream_t stream) {
   using namespace stc;
@@ -697,19 +801,21 @@ int launch_summary_select_tc(const void* qd, const void* kd, void* aux, int32_t*
       return 1;
   }
   float* absmax = static_cast<float*>(aux);
-  int* fallbacks = reinterpret_cast<int*>(absmax + static_cast<size_t>(batch) * hkv);
-  if (cudaMemsetAsync(aux, 0, (static_cast<size_t>(batch) * hkv + 1) * 4, stream) != cudaSuccess)
+  float* norm2 = absmax + static_cast<size_t>(batch) * hkv;
+  int* fallbacks = reinterpret_cast<int*>(norm2 + static_cast<size_t>(batch) * hkv);
+  if (cudaMemsetAsync(aux, 0, (2 * static_cast<size_t>(batch) * hkv + 1) * 4, stream) != cudaSuccess)
     return set_error(SB_ERR_CUDA, "memset failed");
   const long long per_head = static_cast<long long>(nt) * r * 128;
   int chunks = static_cast<int>((per_head / 8 + 256 * 8 - 1) / (256 * 8));
   if (chunks > 64) chunks = 64;
   if (chunks < 1) chunks = 1;
-  absmax_kernel<<<dim3(chunks, batch * hkv), 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(kd), absmax, per_head);
+  absmax_kernel<<<dim3(chunks, batch * hkv), 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(kd), absmax, norm2, per_head);
 
   Params p{};
   p.qd = static_cast<const __nv_bfloat16*>(qd);
   p.kd = static_cast<const __nv_bfloat16*>(kd);
   p.k_absmax = absmax;
+  p.k_norm2 = norm2;
   p.ids = ids;
   p.status = ctx->status;
   p.fallbacks = fallbacks;
@@ -717,7 +823,7 @@ int launch_summary_select_tc(const void* qd, const void* kd, void* aux, int32_t*
   p.q_chunks = (qt + qb - 1) / qb;
   const int grid = batch * hkv * p.q_chunks;
   const size_t smem = OFF_SCORES + ((static_cast<size_t>(qb) * nt * 4 + 15) & ~static_cast<size_t>(15)) + 144 +
-                      128 * 4 + 20 * 4 + 20 * 4 + SEL_WARPS * 4 + 1024;
+                      128 * 4 + 20 * 4 + 20 * 4 + 5 * SEL_WARPS * 4 + 1024;
   switch (gr) {
     case 1: return launch_gr<1>(qm, km, p, grid, smem, ctx, 0, stream);
     case 2: return launch_gr<2>(qm, km, p, grid, smem, ctx, 1, stream);

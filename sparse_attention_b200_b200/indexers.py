@@ -38,8 +38,9 @@ class SummarySelector:
         self.scores = torch.empty((b, hkv, self.qt, self.nt), dtype=torch.float32, device=q.device) \
             if keep_scores else None
         self.ids = torch.empty((b, hkv, self.qt, topk), dtype=torch.int32, device=q.device)
-        # workspace of the tensor-core path: key abs-max per (batch, KV head) + fallback counter
-        self.aux = torch.zeros(b * hkv + 1, dtype=torch.int32, device=q.device)
+        # workspace of the tensor-core path: key abs-max and largest squared key norm per (batch, KV head)
+        # + fallback counter (sparse_b200_indexer_summary_aux_bytes)
+        self.aux = torch.zeros(2 * b * hkv + 1, dtype=torch.int32, device=q.device)
         self.name = f"mean{r}_bf16"
 
     def prepare(self):
