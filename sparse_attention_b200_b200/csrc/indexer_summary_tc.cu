@@ -416,7 +416,7 @@ score_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant
   // The operand buffers are free now: the fp32 query descriptors of the round's lists go to
   // the A stages, their candidate arrays to the B tile. Per round:
   //   1. all threads stage the query descriptors of the round's lists and their L1 norms;
-  //   2. one warp per list finds the C-th largest approximate score and the candidates;
+  //   2. two to sixteen warps per list find the C-th largest approximate score and the candidates;
   //   3. all threads find the candidates whose order the approximate scores do not settle,
   //      and re-score those exactly, (four key rows, up to 8 query rows) per lane;
   //   4. all threads rank the candidates by counting; one thread per list proves safety.
@@ -458,56 +458,86 @@ score_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant
       atomicMax(l2_s + l, __float_as_int(squares));
     }
     __syncthreads();
-    const int tl = tl0 + warp;
-    const bool mine = warp < nl;                 // this warp owns list tl of the round
-    int32_t* cand_ids = cand_all + warp * LIST_WORDS;
+    // 2. `wpl` warps per list (as many as there are, but no more than one per 1024 keys: with
+    //    short lists the meetings cost more than the shared scan saves); each takes a contiguous
+    //    slice of the list's keys and the warps of a list meet at a named barrier
+    int wpl = nl <= 1 ? 16 : nl <= 2 ? 8 : nl <= 4 ? 4 : 2;
+    while (wpl > 1 && wpl * 1024 > p.nt) wpl >>= 1;
+    const int slot = warp / wpl, sub = warp - slot * wpl;
+    const bool active = slot < nl;
+    const bool mine = active && sub == 0;        // this warp speaks for list tl of the round
+    const int tl = tl0 + slot;
+    int32_t* cand_ids = cand_all + slot * LIST_WORDS;
     float* cand_apx = reinterpret_cast<float*>(cand_ids + C_MAX);
     const unsigned lt_mask = (1u << lane) - 1u;
     float delta = 0.f, thr = 0.f;
-    if (mine) {
+    if (active) {
+      auto group_sync = [&]() {
+        if (wpl > 1) asm volatile("bar.sync %0, %1;" ::"r"(1 + slot), "r"(wpl * 32) : "memory");
+        else __syncwarp();
+      };
       const unsigned* keys = reinterpret_cast<const unsigned*>(scores + tl * p.nt);   // ordered ints
+      int* hist = cand_all + SEL_WARPS * LIST_WORDS + slot * 256;
+      // per list: smallest key, largest key, candidates written, -, ties seen by each warp
+      unsigned* grp = reinterpret_cast<unsigned*>(cand_all + SEL_WARPS * LIST_WORDS + SEL_WARPS * 256 + slot * 24);
+      const int span = (((p.nt + wpl - 1) / wpl) + 31) & ~31;
+      const int lo = sub * span, hi = min(p.nt, lo + span);
       // sum of |q_d k_d| over the features, bounded by Hoelder (L1 x max) and by Cauchy-Schwarz
-      delta = EPS * 1.0001f * fminf(__int_as_float(l1_s[warp]) * kabs, sqrtf(__int_as_float(l2_s[warp])) * knorm) * SCALE;
+      delta = EPS * 1.0001f * fminf(__int_as_float(l1_s[slot]) * kabs, sqrtf(__int_as_float(l2_s[slot])) * knorm) * SCALE;
       // C-th largest approximate score T by radix selection, eight bits per pass: histogram
       // of the digit among the keys that match the digits found so far, then the largest
       // digit whose suffix count reaches what is still needed. The keys are first moved to
       // w = (key - smallest key) << (leading zeros of the range): scores of one list share
       // their exponent bits, and a digit taken from those would send every lane of a warp to
       // the same histogram bin. Afterwards `need` keys equal to T are wanted besides all above.
-      int* hist = cand_all + SEL_WARPS * LIST_WORDS + warp * 256;
+      if (sub == 0 && lane == 0) {
+        grp[0] = 0xffffffffu;
+        grp[1] = 0u;
+        grp[2] = 0u;
+      }
+      group_sync();
       unsigned umin = 0xffffffffu, umax = 0u;
 #pragma unroll 8
-      for (int j = lane; j < p.nt; j += 32) {
+      for (int j = lo + lane; j < hi; j += 32) {
         const unsigned u = keys[j] ^ 0x80000000u;
         umin = min(umin, u);
         umax = max(umax, u);
       }
       umin = __reduce_min_sync(0xffffffffu, umin);
       umax = __reduce_max_sync(0xffffffffu, umax);
+      if (lane == 0 && lo < hi) {
+        atomicMin(grp, umin);
+        atomicMax(grp + 1, umax);
+      }
+      group_sync();
+      umin = grp[0];
+      umax = grp[1];
       const int lz = min(__clz(umax - umin), 31);
       unsigned W = 0;
       int need = C;
       for (int pass = 0; pass < 4; ++pass) {
         const int shift = 24 - 8 * pass;
         if (shift + 8 <= lz) break;              // the remaining bits of every w are zero
-#pragma unroll
-        for (int i = 0; i < 8; ++i) hist[lane + 32 * i] = 0;
-        __syncwarp();
+        for (int i = sub * 32 + lane; i < 256; i += wpl * 32) hist[i] = 0;
+        group_sync();
         // keys are fetched eight at a time: a load cannot be moved above an atomic by the
         // compiler, and one round trip to shared memory per key is what this loop costs otherwise
         const unsigned top = pass == 0 ? 0u : W >> (shift + 8);
-        for (int j0 = lane; j0 < p.nt; j0 += 256) {
-          unsigned w[8];
-#pragma unroll
-          for (int i = 0; i < 8; ++i) w[i] = j0 + 32 * i < p.nt ? keys[j0 + 32 * i] : 0u;
+        for (int j0 = lo + lane; j0 < hi; j0 += 256) {
+          unsigned x[8];
+          bool any = false;
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
-            const unsigned x = ((w[i] ^ 0x80000000u) - umin) << lz;
-            const bool match = pass == 0 || (x >> (shift + 8)) == top;
-            if (j0 + 32 * i < p.nt && match) atomicAdd(hist + ((x >> shift) & 255u), 1);
+            x[i] = j0 + 32 * i < hi ? ((keys[j0 + 32 * i] ^ 0x80000000u) - umin) << lz : 0u;
+            any |= j0 + 32 * i < hi && (pass == 0 || (x[i] >> (shift + 8)) == top);
           }
+          if (!__any_sync(0xffffffffu, any)) continue;      // after the first pass few keys still match
+#pragma unroll
+          for (int i = 0; i < 8; ++i)
+            if (j0 + 32 * i < hi && (pass == 0 || (x[i] >> (shift + 8)) == top))
+              atomicAdd(hist + ((x[i] >> shift) & 255u), 1);
         }
-        __syncwarp();
+        group_sync();
         int h[8], lsum = 0;                      // lane l holds digits 8 l .. 8 l + 7
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
@@ -538,44 +568,62 @@ score_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant
         digit = __shfl_sync(0xffffffffu, digit, src);
         need = __shfl_sync(0xffffffffu, left, src);
         W |= static_cast<unsigned>(digit) << shift;
-        __syncwarp();
+        group_sync();                            // every warp has read the histogram
       }
       const unsigned T = (W >> lz) + umin;
-      // candidates: everything above T, then ties at T in index order, C in total
+      // candidates: everything above T, then ties at T in index order, C in total. First the
+      // ties of each slice are counted, so that a warp knows how many lie before its slice.
       const int need_eq = need;
-      int out_run = 0, eq_run = 0;
-      for (int j0 = 0; j0 < p.nt; j0 += 256) {   // eight groups of 32 keys per step
+      int eq_mine = 0;
+      for (int j0 = lo; j0 < hi; j0 += 256) {
+        int c8 = 0;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int j = j0 + 32 * i + lane;
+          c8 += static_cast<int>(j < hi && (keys[j] ^ 0x80000000u) == T);
+        }
+        eq_mine += c8;
+      }
+      eq_mine = __reduce_add_sync(0xffffffffu, eq_mine);
+      if (lane == 0) grp[4 + sub] = static_cast<unsigned>(eq_mine);
+      group_sync();
+      int eq_run = 0;
+      for (int w = 0; w < sub; ++w) eq_run += static_cast<int>(grp[4 + w]);
+      for (int j0 = lo; j0 < hi; j0 += 256) {    // eight groups of 32 keys per step
         unsigned u[8];
         bool any_ge = false;
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
           const int j = j0 + 32 * i + lane;
-          u[i] = j < p.nt ? (keys[j] ^ 0x80000000u) : 0u;
-          any_ge |= j < p.nt && u[i] >= T;
+          u[i] = j < hi ? (keys[j] ^ 0x80000000u) : 0u;
+          any_ge |= j < hi && u[i] >= T;
         }
         if (!__any_sync(0xffffffffu, any_ge)) continue;     // most steps hold no candidate
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
           const int j = j0 + 32 * i + lane;
-          const bool is_ge = j < p.nt && u[i] >= T;
+          const bool is_ge = j < hi && u[i] >= T;
           const bool is_eq = is_ge && u[i] == T;
           const unsigned eq_ballot = __ballot_sync(0xffffffffu, is_eq);
           const bool take = is_ge && (!is_eq || eq_run + __popc(eq_ballot & lt_mask) < need_eq);
           const unsigned take_ballot = __ballot_sync(0xffffffffu, take);
+          eq_run += __popc(eq_ballot);
+          if (take_ballot == 0u) continue;
+          int first = 0;                         // the order of the candidates in their arrays is free
+          if (lane == 0) first = static_cast<int>(atomicAdd(grp + 2, static_cast<unsigned>(__popc(take_ballot))));
+          first = __shfl_sync(0xffffffffu, first, 0);
           if (take) {
-            const int pos = out_run + __popc(take_ballot & lt_mask);
+            const int pos = first + __popc(take_ballot & lt_mask);
             cand_ids[pos] = j;
             cand_apx[pos] = ord2f(static_cast<int>(u[i] ^ 0x80000000u)) * SCALE;
           }
-          out_run += __popc(take_ballot);
-          eq_run += __popc(eq_ballot);
         }
       }
       thr = ord2f(static_cast<int>(T ^ 0x80000000u)) * SCALE;
-      if (lane == 0) {
-        delta_s[warp] = delta;
-        work_cnt[warp] = 0;
-        kth_s[warp] = -INFINITY;
+      if (mine && lane == 0) {
+        delta_s[slot] = delta;
+        work_cnt[slot] = 0;
+        kth_s[slot] = -INFINITY;
       }
     }
     __syncthreads();
@@ -670,7 +718,7 @@ score_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant
     }
     __syncthreads();
     // safe: no block outside the candidates (exact score <= thr + delta) can reach the top k
-    if (mine && lane == 0) flags[tl] = ((C >= p.nt) || (kth_s[warp] > thr + delta)) ? 0 : 1;
+    if (mine && lane == 0) flags[tl] = ((C >= p.nt) || (kth_s[slot] > thr + delta)) ? 0 : 1;
     if (tl0 + SEL_WARPS < lists) {               // another round re-uses the buffers
       __syncthreads();
       if (threadIdx.x < SEL_WARPS) l1_s[threadIdx.x] = l2_s[threadIdx.x] = 0;
