@@ -6,10 +6,12 @@
 // copies compute every product exactly; only their fp32 accumulation differs from
 // the fixed group-by-group order that defines a score. As in the summary indexer
 // the MMA result is therefore a PRE-FILTER: per query tile the C best pages by
-// approximate tile score are re-scored exactly, the exact top-k of those is the
-// answer when exact k-th score > C-th approximate score + delta
-// (delta = 2^-14 * max_q ||q||_1 * max|k|), and the tile falls back to exact scores
-// of every page otherwise.
+// approximate tile score are the candidates. Approximate and exact score of a page differ
+// by at most delta = 2^-14 * min(max_q ||q||_1 * max|k|, max_q ||q||_2 * max_k ||k||_2),
+// so candidates more than 2 delta apart are ordered by their approximate scores for
+// certain; the others are re-scored exactly. The top-k of the candidates is the answer
+// when a lower bound of the k-th exact score > C-th approximate score + delta, and the
+// tile falls back to exact scores of every page otherwise.
 // Same role as Fp4IndexerStagedMmaSm100 + tile_max_topk16_kernel
 // (indexers/fp4/vendor_minimax_msa/src/sm100/fp4_indexer.py:483-1086,
 // indexers/fp4/tile_topk.cu:38-126).
@@ -37,7 +39,7 @@ constexpr int OFF_SCORES = OFF_B + TILE_BYTES;
 
 struct Params {
   const uint8_t *qp, *qs, *kp, *ks;   // public NVFP4 layout (codes, e4m3 scales)
-  const float* k_absmax;              // [1] max |dequantised key element|
+  const float* k_absmax;              // [0] max |dequantised key element|, [2] largest squared L2 norm of a key
   int32_t* ids;                       // [B, Hidx, Qt, topk]
   int* status;
   int* fallbacks;
@@ -95,23 +97,39 @@ __global__ void __launch_bounds__(256) dequant_kernel(const uint8_t* __restrict_
   *reinterpret_cast<uint4*>(out + row * 128 + w * 8) = o;
 }
 
+// out[0] = max |element|, out[2] = largest squared L2 norm of a row (sixteen adjacent lanes
+// hold one 128-element row); out[1] is the fallback counter of the caller
 __global__ void __launch_bounds__(256) absmax_all_kernel(const __nv_bfloat16* __restrict__ x, float* __restrict__ out,
                                                          long long n16) {
   const uint4* src = reinterpret_cast<const uint4*>(x);
-  float m = 0.f;
-  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n16;
-       i += static_cast<long long>(gridDim.x) * blockDim.x) {
-    const uint4 v = __ldg(src + i);
+  float m = 0.f, n2 = 0.f;
+  const int lane = threadIdx.x & 31;
+  for (long long base = static_cast<long long>(blockIdx.x) * blockDim.x + (threadIdx.x - lane); base < n16;
+       base += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long i = base + lane;
+    const uint4 v = i < n16 ? __ldg(src + i) : make_uint4(0u, 0u, 0u, 0u);
     const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+    float sq = 0.f;
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
       const float2 f = __bfloat1622float2(h[e]);
       m = fmaxf(m, fmaxf(fabsf(f.x), fabsf(f.y)));
+      sq = fmaf(f.x, f.x, sq);
+      sq = fmaf(f.y, f.y, sq);
     }
+#pragma unroll
+    for (int d = 8; d > 0; d >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, d);
+    n2 = fmaxf(n2, sq);
   }
 #pragma unroll
-  for (int d = 16; d > 0; d >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, d));
-  if ((threadIdx.x & 31) == 0) atomicMax(reinterpret_cast<int*>(out), __float_as_int(m));
+  for (int d = 16; d > 0; d >>= 1) {
+    m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, d));
+    n2 = fmaxf(n2, __shfl_xor_sync(0xffffffffu, n2, d));
+  }
+  if (lane == 0) {
+    atomicMax(reinterpret_cast<int*>(out), __float_as_int(m));
+    atomicMax(reinterpret_cast<int*>(out + 2), __float_as_int(n2));
+  }
 }
 
 // One CTA per (batch, index head, query tile): approximate tile scores of every key
@@ -270,27 +288,36 @@ fp4_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
   float* k_sc = q_sc + 128 * 8;
   int32_t* cand_ids = reinterpret_cast<int32_t*>(gbase + OFF_B);
   int* cand_ex = reinterpret_cast<int*>(cand_ids + C_MAX);
+  float* cand_apx = reinterpret_cast<float*>(cand_ex + C_MAX);     // approximate tile scores of the candidates
+  int* near_s = reinterpret_cast<int*>(cand_apx + C_MAX);          // candidate needs its exact score
   const int C = p.cand;
 
   int32_t* out = p.ids + (static_cast<long long>(bh) * qt + qtile) * p.topk;
 
   fp4_stage_rows(q_i8, q_sc, p.qp + (q_row0 * p.hidx + h) * 64, static_cast<long long>(p.hidx) * 64,
                  p.qs + (q_row0 * p.hidx + h) * 8, static_cast<long long>(p.hidx) * 8, 0.25f);
-  if (threadIdx.x == 0) { misc[2] = 0; misc[3] = 0; }
+  if (threadIdx.x == 0) { misc[2] = 0; misc[3] = 0; misc[4] = 0; misc[5] = __float_as_int(-INFINITY); }
   for (int c = threadIdx.x; c < C_MAX; c += NUM_THREADS) cand_ex[c] = static_cast<int>(0x80000000u);
   __syncthreads();
-  if (threadIdx.x < 128) {                 // L1 norm of one dequantised query row
-    float l1 = 0.f;
+  if (threadIdx.x < 128) {                 // L1 norm and squared L2 norm of one dequantised query row
+    float l1 = 0.f, l2 = 0.f;
     for (int g = 0; g < 8; ++g) {
-      int sum = 0;
+      int sum = 0, squares = 0;
       for (int w = 0; w < 4; ++w) {
         const uint32_t word = q_i8[threadIdx.x * FP4_ROW_WORDS + g * 4 + w];
 #pragma unroll
-        for (int e = 0; e < 4; ++e) sum += abs(static_cast<int>(static_cast<int8_t>((word >> (8 * e)) & 0xFFu)));
+        for (int e = 0; e < 4; ++e) {
+          const int v = static_cast<int>(static_cast<int8_t>((word >> (8 * e)) & 0xFFu));
+          sum += abs(v);
+          squares += v * v;
+        }
       }
-      l1 += static_cast<float>(sum) * 2.0f * q_sc[threadIdx.x * 8 + g];
+      const float unit = 2.0f * q_sc[threadIdx.x * 8 + g];      // value of one integer step in this group
+      l1 += static_cast<float>(sum) * unit;
+      l2 += static_cast<float>(squares) * unit * unit;
     }
     atomicMax(const_cast<int*>(misc + 3), __float_as_int(l1 * 1.0001f));
+    atomicMax(const_cast<int*>(misc + 4), __float_as_int(l2 * 1.0001f));
   }
   float thr = 0.f;
   if (warp == 0) {
@@ -320,7 +347,11 @@ fp4_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
       const unsigned eq_ballot = __ballot_sync(0xffffffffu, is_eq);
       const bool take = is_gt || (is_eq && eq_run + __popc(eq_ballot & lt_mask) < need_eq);
       const unsigned take_ballot = __ballot_sync(0xffffffffu, take);
-      if (take) cand_ids[out_run + __popc(take_ballot & lt_mask)] = j;
+      if (take) {
+        const int pos = out_run + __popc(take_ballot & lt_mask);
+        cand_ids[pos] = j;
+        cand_apx[pos] = ord2f(static_cast<int>(u ^ 0x80000000u));
+      }
       out_run += __popc(take_ballot);
       eq_run += __popc(eq_ballot);
     }
@@ -338,44 +369,44 @@ fp4_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
     for (int d = 16; d > 0; d >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, d));
     return m;                              // per-warp maximum; lane 0 publishes it
   };
+  // Approximate and exact tile score differ by at most delta (the sum of |q_d k_d| bounded by
+  // Hoelder and by Cauchy-Schwarz), so candidates more than 2 delta apart are ordered by their
+  // approximate scores for certain: only a candidate with another one within 2 delta is re-scored.
+  const float delta = EPS * fminf(__int_as_float(misc[3]) * p.k_absmax[0],
+                                  sqrtf(__int_as_float(misc[4])) * sqrtf(p.k_absmax[2] * 1.0001f));
+  const float two = 2.f * delta;
+  for (int c = threadIdx.x; c < C; c += NUM_THREADS) {
+    const float a = cand_apx[c];
+    int near = 0;
+#pragma unroll 4
+    for (int j = 0; j < C; ++j) near |= static_cast<int>(j != c) & static_cast<int>(!(fabsf(a - cand_apx[j]) > two));
+    near_s[c] = near;
+  }
+  __syncthreads();
   for (int c = 0; c < C; ++c) {
+    if (!near_s[c]) continue;
     const float m = exact_page(cand_ids[c]);
     if (lane == 0) atomicMax(&cand_ex[c], f2ord(m));
     __syncthreads();
   }
-  if (warp == 0) {
-    constexpr int SLOTS = C_MAX / 32;
-    float es[SLOTS];
-    int ei[SLOTS];
-#pragma unroll
-    for (int sidx = 0; sidx < SLOTS; ++sidx) {
-      const int c = lane + 32 * sidx;
-      es[sidx] = c < C ? ord2f(cand_ex[c]) : -INFINITY;
-      ei[sidx] = c < C ? cand_ids[c] : INT_MAX;
+  // rank of a candidate = number of candidates that beat it in (exact score descending, page
+  // ascending): by the approximate scores when more than 2 delta apart, else by the exact ones
+  for (int c = threadIdx.x; c < C; c += NUM_THREADS) {
+    const float a = cand_apx[c], e = ord2f(cand_ex[c]);
+    const int id = cand_ids[c];
+    int rank = 0;
+#pragma unroll 4
+    for (int j = 0; j < C; ++j) {
+      const float d = cand_apx[j] - a, ej = ord2f(cand_ex[j]);
+      const int gt = static_cast<int>(d > two), lt = static_cast<int>(d < -two);
+      const int exact = static_cast<int>(ej > e) | (static_cast<int>(ej == e) & static_cast<int>(cand_ids[j] < id));
+      rank += gt | (((gt | lt) ^ 1) & exact);
     }
-    float kth = -INFINITY;
-    for (int rank = 0; rank < p.topk; ++rank) {
-      float bs = es[0];
-      int bi = ei[0];
-#pragma unroll
-      for (int sidx = 1; sidx < SLOTS; ++sidx)
-        if (better(es[sidx], ei[sidx], bs, bi)) { bs = es[sidx]; bi = ei[sidx]; }
-#pragma unroll
-      for (int d = 16; d > 0; d >>= 1) {
-        const float os = __shfl_xor_sync(0xffffffffu, bs, d);
-        const int oi = __shfl_xor_sync(0xffffffffu, bi, d);
-        if (better(os, oi, bs, bi)) { bs = os; bi = oi; }
-      }
-#pragma unroll
-      for (int sidx = 0; sidx < SLOTS; ++sidx)
-        if (ei[sidx] == bi) { es[sidx] = -INFINITY; ei[sidx] = INT_MAX; }
-      if (lane == 0) out[rank] = bi;
-      kth = bs;
-    }
-    const float delta = EPS * __int_as_float(misc[3]) * p.k_absmax[0];
-    const bool safe = (C >= p.tiles) || (kth > thr + delta);
-    if (lane == 0) misc[2] = safe ? 0 : 1;
+    if (rank < p.topk) out[rank] = id;
+    if (rank == p.topk - 1) misc[5] = __float_as_int(near_s[c] ? e : a - delta);   // lower bound of the k-th exact score
   }
+  __syncthreads();
+  if (threadIdx.x == 0) misc[2] = ((C >= p.tiles) || (__int_as_float(misc[5]) > thr + delta)) ? 0 : 1;
   __syncthreads();
   if (misc[2]) {
     float* row = reinterpret_cast<float*>(scores);
@@ -399,7 +430,7 @@ fp4_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__
 
 // Returns SB_OK when the tensor-core path ran, 1 when the problem is not eligible.
 // q_deq / k_deq: bf16 workspaces of B*Sq*Hidx*128 and (B*Skv/128)*Hk*128*128 elements;
-// aux: one float (key abs-max) + one int (fallback counter).
+// aux: one float (key abs-max) + one int (fallback counter) + one float (largest squared key norm).
 int launch_fp4_indexer_tc(const void* qp, const void* qs, const void* kp, const void* ks, void* q_deq, void* k_deq,
                           void* aux, int32_t* ids, int batch, int hidx, int hk, int len_q, int len_kv, int topk,
                           cudaStream_t stream) {
@@ -419,7 +450,7 @@ int launch_fp4_indexer_tc(const void* qp, const void* qs, const void* kp, const 
   if (q_rows >= (1LL << 31) || k_rows >= (1LL << 31)) return 1;
   DeviceCtx* ctx = device_ctx();
   if (!ctx) return SB_ERR_CUDA;
-  if (cudaMemsetAsync(aux, 0, 8, stream) != cudaSuccess) return set_error(SB_ERR_CUDA, "memset failed");
+  if (cudaMemsetAsync(aux, 0, 12, stream) != cudaSuccess) return set_error(SB_ERR_CUDA, "memset failed");
   dequant_kernel<<<static_cast<unsigned>((q_rows * 16 + 255) / 256), 256, 0, stream>>>(
       static_cast<const uint8_t*>(qp), static_cast<const uint8_t*>(qs), static_cast<__nv_bfloat16*>(q_deq), q_rows);
   dequant_kernel<<<static_cast<unsigned>((k_rows * 16 + 255) / 256), 256, 0, stream>>>(
