@@ -141,6 +141,31 @@ def test_summary_selector_tensor_core_path_ties_and_constant_inputs():
     m.device_status()
 
 
+@pytest.mark.parametrize("r", [1, 4])
+def test_summary_selector_tensor_core_path_near_ties(r):
+    """A cluster of almost equal blocks at the top of every list (copies of one block, some
+    exact, some with one feature nudged): their approximate scores cannot order them, so the
+    pre-filter must re-score exactly these and still agree with the oracle id for id, while
+    the well separated blocks below them are ordered without exact scores."""
+    m = sp()
+    g = torch.Generator().manual_seed(77)
+    q = (torch.randn((1, 4, 160 * 128, 128), generator=g) + 0.5).to(torch.bfloat16)   # 160 lists: not a small problem
+    k = (0.2 * torch.randn((1, 1, 8192, 128), generator=g)).to(torch.bfloat16)
+    base = (k[:, :, :128].float() + 1.0).to(torch.bfloat16)
+    for blk in range(20):
+        k[:, :, blk * 128:(blk + 1) * 128] = base
+        if blk % 3:                                  # every third copy stays an exact duplicate of block 0
+            k[0, 0, blk * 128:(blk + 1) * 128, blk] = (base[0, 0, :, blk].float() * (1.0 + 0.01 * blk)).to(torch.bfloat16)
+    sel = m.SummarySelector(q.cuda(), k.cuda(), r, topk=32, keep_scores=False)
+    ids = sel.run_fast().cpu()
+    m.device_status()
+    ref = oracle.summary_select(q, k, r, 32)[3]
+    assert torch.equal(ids, ref)
+    assert set(ids[0, 0, 0, :20].tolist()) == set(range(20))
+    assert sel.fallback_lists() <= 8                 # the near ties are settled by re-scoring, not by the fallback
+    print("lists that fell back to exact scoring:", sel.fallback_lists())
+
+
 @pytest.mark.parametrize("b,hkv,g,sq,skv,r,topk", [
     (2, 1, 16, 4096, 16384, 1, 16),      # the reference's selector benchmark shape: 16 query descriptors per list
     (2, 1, 16, 4096, 4096, 4, 16),       # 64 query descriptors, 4 key representatives per block
