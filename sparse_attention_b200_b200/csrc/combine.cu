@@ -110,6 +110,122 @@ __global__ void __launch_bounds__(128) combine_kernel(const T* __restrict__ part
   }
 }
 
+// Eight consecutive features of one partial row.
+template <typename T>
+struct Raw8;
+template <>
+struct Raw8<float> {
+  float4 a, b;
+  __device__ __forceinline__ void load(const float* p) {
+    a = __ldcs(reinterpret_cast<const float4*>(p));
+    b = __ldcs(reinterpret_cast<const float4*>(p) + 1);
+  }
+  __device__ __forceinline__ void clear() { a = b = make_float4(0.f, 0.f, 0.f, 0.f); }
+  __device__ __forceinline__ void unpack(float (&f)[8]) const {
+    f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+  }
+};
+template <>
+struct Raw8<__nv_bfloat16> {
+  uint4 raw;
+  __device__ __forceinline__ void load(const __nv_bfloat16* p) { raw = __ldcs(reinterpret_cast<const uint4*>(p)); }
+  __device__ __forceinline__ void clear() { raw = make_uint4(0u, 0u, 0u, 0u); }
+  __device__ __forceinline__ void unpack(float (&f)[8]) const {
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 x = __bfloat1622float2(h[i]);
+      f[2 * i] = x.x;
+      f[2 * i + 1] = x.y;
+    }
+  }
+};
+
+// Rank counts compiled in (1-4: KV-range segments, KV splits across GPUs; 8 and 16 bf16 ranks:
+// per-token selection lists): the kernel above spends its time issuing instructions there
+// (shuffles for the weights, 64-bit address arithmetic per 8-byte load), not waiting for
+// memory. Here sixteen threads share a row, eight features each, every thread reads the
+// row's R LSEs itself (one broadcast transaction) and computes the weights redundantly: no
+// shuffles, 16-byte loads. U rows per thread keep U R loads of 16 bytes in flight. Same
+// operations in the same order as combine_kernel, so the results are bit-identical.
+template <typename T, int R, int U>
+__global__ void __launch_bounds__(256) combine_few_kernel(const T* __restrict__ partial, const float* __restrict__ lses,
+                                                          __nv_bfloat16* __restrict__ out, float* __restrict__ out_lse,
+                                                          long long rows, long long p_stride_rank, long long p_stride_row,
+                                                          long long l_stride_rank, long long l_stride_row) {
+  const int slot = threadIdx.x >> 4, part = threadIdx.x & 15;
+  const long long row_base = static_cast<long long>(blockIdx.x) * (16 * U) + slot;
+  Raw8<T> val[U][R];
+  float L[U][R];
+#pragma unroll
+  for (int u = 0; u < U; ++u) {
+    const long long row = min(row_base + 16 * u, rows - 1);
+    const T* src = partial + row * p_stride_row + part * 8;
+    const float* lsrc = lses + row * l_stride_row;
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      val[u][r].load(src + r * p_stride_rank);
+      L[u][r] = __ldg(lsrc + r * l_stride_rank);
+    }
+  }
+#pragma unroll
+  for (int u = 0; u < U; ++u) {
+    const long long row = row_base + 16 * u;
+    if (row >= rows) continue;
+    float maximum = L[u][0];
+#pragma unroll
+    for (int r = 1; r < R; ++r) maximum = fmaxf(maximum, L[u][r]);
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    float denom = 0.f;
+    if (maximum > -CUDART_INF_F) {
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        const float w = expf(L[u][r] - maximum);   // exp(-inf) = 0
+        if (!(w > 0.f)) val[u][r].clear();         // a rank of weight 0 is dropped, whatever it holds
+        float f[8];
+        val[u][r].unpack(f);
+        denom += w;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[e] = fmaf(w, f[e], acc[e]);
+      }
+      const float inv = 1.0f / denom;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[e] *= inv;
+    }
+    uint4 packed;
+    __nv_bfloat162 h0 = __floats2bfloat162_rn(acc[0], acc[1]), h1 = __floats2bfloat162_rn(acc[2], acc[3]);
+    __nv_bfloat162 h2 = __floats2bfloat162_rn(acc[4], acc[5]), h3 = __floats2bfloat162_rn(acc[6], acc[7]);
+    packed.x = *reinterpret_cast<uint32_t*>(&h0);
+    packed.y = *reinterpret_cast<uint32_t*>(&h1);
+    packed.z = *reinterpret_cast<uint32_t*>(&h2);
+    packed.w = *reinterpret_cast<uint32_t*>(&h3);
+    *reinterpret_cast<uint4*>(out + row * 128 + part * 8) = packed;
+    if (part == 0 && out_lse) out_lse[row] = (maximum > -CUDART_INF_F) ? maximum + logf(denom) : -CUDART_INF_F;
+  }
+}
+
+template <typename T, int R>
+static void combine_few_launch(const void* partial, const float* lses, void* out, float* out_lse, long long rows,
+                               long long psr, long long psw, long long lsr, long long lsw, cudaStream_t stream) {
+  constexpr int U = R <= 4 ? 2 : 1;
+  combine_few_kernel<T, R, U><<<static_cast<unsigned>((rows + 16 * U - 1) / (16 * U)), 256, 0, stream>>>(
+      static_cast<const T*>(partial), lses, static_cast<__nv_bfloat16*>(out), out_lse, rows, psr, psw, lsr, lsw);
+}
+
+template <typename T>
+static void combine_few_dispatch(int ranks, const void* partial, const float* lses, void* out, float* out_lse,
+                                 long long rows, long long psr, long long psw, long long lsr, long long lsw,
+                                 cudaStream_t stream) {
+  switch (ranks) {
+    case 1: combine_few_launch<T, 1>(partial, lses, out, out_lse, rows, psr, psw, lsr, lsw, stream); break;
+    case 2: combine_few_launch<T, 2>(partial, lses, out, out_lse, rows, psr, psw, lsr, lsw, stream); break;
+    case 3: combine_few_launch<T, 3>(partial, lses, out, out_lse, rows, psr, psw, lsr, lsw, stream); break;
+    case 4: combine_few_launch<T, 4>(partial, lses, out, out_lse, rows, psr, psw, lsr, lsw, stream); break;
+    case 8: combine_few_launch<T, 8>(partial, lses, out, out_lse, rows, psr, psw, lsr, lsw, stream); break;
+    default: combine_few_launch<T, 16>(partial, lses, out, out_lse, rows, psr, psw, lsr, lsw, stream); break;
+  }
+}
+
 template <typename T, int RPW>
 static void combine_launch(const void* partial, const float* lses, void* out, float* out_lse, long long rows, int ranks,
                            long long psr, long long psw, long long lsr, long long lsw, cudaStream_t stream) {
@@ -126,6 +242,17 @@ int launch_combine(const void* partial, int partial_is_f32, const float* lses, v
   DeviceCtx* ctx = device_ctx();
   if (!ctx) return SB_ERR_CUDA;
   if ((rows + 3) / 4 > 0x7fffffffLL) return set_error(SB_ERR_INVALID, "too many rows for one combine launch");
+  // 16-byte accesses of the specialised kernel: every stride must keep them aligned
+  const long long esz = partial_is_f32 ? 4 : 2;
+  const bool aligned = ((reinterpret_cast<uintptr_t>(partial) & 15u) == 0) && ((p_stride_rank * esz) & 15) == 0 &&
+                       ((p_stride_row * esz) & 15) == 0 && ((reinterpret_cast<uintptr_t>(out) & 15u) == 0);
+  const bool compiled_in = (ranks >= 1 && ranks <= 4) || (!partial_is_f32 && (ranks == 8 || ranks == 16));
+  if (compiled_in && aligned) {
+    if (partial_is_f32) combine_few_dispatch<float>(ranks, partial, lses, out, out_lse, rows, p_stride_rank, p_stride_row, l_stride_rank, l_stride_row, stream);
+    else combine_few_dispatch<__nv_bfloat16>(ranks, partial, lses, out, out_lse, rows, p_stride_rank, p_stride_row, l_stride_rank, l_stride_row, stream);
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? SB_OK : set_error(SB_ERR_CUDA, cudaGetErrorString(e));
+  }
   // few ranks: several rows per warp, so that every lane still has 16 loads in flight
   if (partial_is_f32) {
     if (ranks <= 4) combine_launch<float, 4>(partial, lses, out, out_lse, rows, ranks, p_stride_rank, p_stride_row, l_stride_rank, l_stride_row, stream);

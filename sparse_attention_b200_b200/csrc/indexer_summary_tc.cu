@@ -7,16 +7,18 @@
 //      M operand streamed by TMA, the query descriptors of QB query blocks as the
 //      N operand, max over the group's rows and the R key representatives in the
 //      epilogue) stay in shared memory;
-//   2. per query block the C = k + extra best approximate blocks become
-//      candidates and are re-scored with the exact arithmetic (fp32 FMAs in
-//      feature order);
-//   3. the exact top-k of the candidates is the answer if it is provably safe:
-//      exact k-th score > C-th approximate score + delta, where delta bounds
-//      |approximate - exact| for every block of the list
-//      (delta = 2^-14 * max_m ||q_m||_1 * max|k element| * 128^-0.5, an order of
-//      magnitude above the worst case of two 128-term fp32 sums);
-//   4. otherwise (near ties, e.g. constant inputs) the list falls back to exact
-//      scores of all blocks.
+//   2. per query block the C = k + extra best approximate blocks become candidates;
+//      |approximate - exact| <= delta for every block of the list, with
+//      delta = 2^-14 * min(max_m ||q_m||_1 * max|k element|, max_m ||q_m||_2 * max ||k row||_2) * 128^-0.5
+//      (the sum of |q_d k_d| bounded by Hoelder and by Cauchy-Schwarz; 2^-14 is an order
+//      of magnitude above the worst case of two 128-term fp32 sums);
+//   3. two candidates whose approximate scores are more than 2 delta apart are ordered by
+//      them for certain; a candidate with another one within 2 delta is re-scored with the
+//      exact arithmetic (fp32 FMAs in feature order), and such pairs are ordered by
+//      (exact score, block id). The top-k of the candidates is the answer if it is provably
+//      safe: a lower bound of the k-th exact score > C-th approximate score + delta;
+//   4. otherwise (ties that reach beyond the candidates, e.g. constant inputs) the list
+//      falls back to exact scores of all blocks.
 // Replaces descriptor_dot + reduce_topk (indexers/r1_r4/gpu_ops.py:19-49).
 #include "ptx.cuh"
 #include "internal.h"
