@@ -141,6 +141,27 @@ def test_summary_selector_tensor_core_path_ties_and_constant_inputs():
     m.device_status()
 
 
+@pytest.mark.parametrize("shape", [
+    # B, Hq, Hkv, Sq, Skv, R, topk: long lists, where several warps share a list's threshold search
+    (1, 16, 1, 1024, 2176 * 128, 1, 16),      # 8 lists per CTA, 2 warps per list
+    (1, 16, 1, 256, 8320 * 128, 4, 64),       # 2 lists per CTA, 8 warps per list
+    (1, 16, 1, 128, 16512 * 128, 4, 32),      # 1 list per CTA, all 16 warps on it
+    (1, 8, 1, 160 * 128, 2048 * 128, 1, 16),  # 16 lists per CTA: two rounds of 8, 2 warps per list
+])
+def test_summary_selector_tensor_core_path_long_lists(shape):
+    b, hq, hkv, sq, skv, r, topk = shape
+    m = sp()
+    q, k, _ = gen.make_qkv(b, hq, hkv, sq, skv, seed=29, k_block_offset=0.5)
+    sel = m.SummarySelector(q.cuda(), k.cuda(), r, topk=topk, keep_scores=False)
+    ids = sel.run_fast()
+    torch.cuda.synchronize()
+    m.device_status()
+    assert float(sel.aux[:b * hkv].view(torch.float32).min()) > 0     # the key abs-max only the tensor-core path writes
+    ref = oracle.summary_select(q, k, r, topk)[3]
+    assert torch.equal(ids.cpu(), ref)
+    print("lists that fell back to exact scoring:", sel.fallback_lists())
+
+
 @pytest.mark.parametrize("r", [1, 4])
 def test_summary_selector_tensor_core_path_near_ties(r):
     """A cluster of almost equal blocks at the top of every list (copies of one block, some
