@@ -481,9 +481,13 @@ int sparse_b200_indexer_fp4_fast(const void* q_codes, const void* q_scales, cons
                                                 align256(static_cast<size_t>(batch) * len_kv * hk * 256));
   rc = launch_fp4_indexer_tc(q_codes, q_scales, k_codes, k_scales, q_deq, k_deq, aux, block_idx, batch, hidx, hk, len_q,
                              len_kv, topk, static_cast<cudaStream_t>(stream));
-  if (rc == 1) {   // not eligible: exact scorer + top-k, same ids
-    rc = launch_fp4_scores(q_codes, q_scales, k_codes, k_scales, nullptr, tile_scores, batch, hidx, hk, len_q, len_kv,
-                           static_cast<cudaStream_t>(stream));
+  if (rc == 1) {   // not eligible: exact tile scores + top-k, same ids
+    // tensor-core values prune each (query tile, page) pair to the few elements that can hold its maximum
+    rc = launch_fp4_scores_prune(q_codes, q_scales, k_codes, k_scales, q_deq, k_deq, aux, tile_scores, batch, hidx, hk,
+                                 len_q, len_kv, static_cast<cudaStream_t>(stream));
+    if (rc == 1)   // exact scorer that evaluates every element
+      rc = launch_fp4_scores(q_codes, q_scales, k_codes, k_scales, nullptr, tile_scores, batch, hidx, hk, len_q, len_kv,
+                             static_cast<cudaStream_t>(stream));
     if (rc) return rc;
     rc = launch_row_topk(tile_scores, block_idx, static_cast<long long>(batch) * hidx * (len_q / 128), len_kv / 128,
                          topk, static_cast<cudaStream_t>(stream));

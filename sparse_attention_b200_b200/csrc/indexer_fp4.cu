@@ -380,8 +380,28 @@ __global__ void __launch_bounds__(256) row_topk_kernel(const float* __restrict__
   float* scratch_f = scores + tiles;
   int* scratch_i = reinterpret_cast<int*>(scratch_f + 10);
   const long long row = blockIdx.x;
-  for (int t = threadIdx.x; t < tiles; t += blockDim.x) scores[t] = tile_scores[row * tiles + t];
-  __syncthreads();
+  bool has_nan = false;
+  for (int t = threadIdx.x; t < tiles; t += blockDim.x) {
+    const float v = tile_scores[row * tiles + t];
+    scores[t] = v;
+    has_nan |= v != v;
+  }
+  // Short rows without NaN: the rank of a tile is the number of tiles that beat it (score
+  // descending, index ascending), one tile per thread and step; k rounds of block-wide
+  // arg-max cost more than that up to about a thousand tiles.
+  if (!__syncthreads_or(has_nan) && tiles <= 1024) {
+    for (int i = threadIdx.x; i < tiles; i += blockDim.x) {
+      const float si = scores[i];
+      int rank = 0;
+#pragma unroll 4
+      for (int j = 0; j < tiles; ++j) {
+        const float sj = scores[j];
+        rank += static_cast<int>(sj > si) | (static_cast<int>(sj == si) & static_cast<int>(j < i));
+      }
+      if (rank < topk) ids[row * topk + rank] = i;
+    }
+    return;
+  }
   block_topk(scores, tiles, topk, ids + row * topk, scratch_f, scratch_i);
 }
 

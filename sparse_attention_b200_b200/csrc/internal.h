@@ -71,6 +71,9 @@ int launch_kv_token_pipe(const void* q, const void* k, const void* v, const int3
                          int hkv, int sq, int skv, int topk, int q_token_major, cudaStream_t stream);
 int launch_quantize(const void* x, void* packed, void* scales, int batch, int heads_out, int group, int seq,
                     int paged, cudaStream_t stream);
+int launch_fp4_scores_prune(const void* qp, const void* qs, const void* kp, const void* ks, void* q_deq, void* k_deq,
+                            void* aux, float* tile_scores, int batch, int hidx, int hk, int len_q, int len_kv,
+                            cudaStream_t stream);
 int launch_fp4_scores_varlen(const void* qp, const void* qs, const void* kp, const void* ks, const int32_t* cu_q,
                              const int32_t* cu_k, const int32_t* cu_pages, const int32_t* kv_indices,
                              const int32_t* qo_offset, float* out, int batch, int hq, int hk, int total_q,

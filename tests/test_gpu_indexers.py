@@ -340,6 +340,47 @@ def test_fp4_tensor_core_path_bit_exact():
     m.device_status()
 
 
+def _fast_path_tile_scores(ws, b, hidx, hk, lq, lkv):
+    """Tile scores the fast entry left in its workspace: 256 bytes, dequantised q, dequantised k, scores."""
+    def up(n):
+        return (n + 255) // 256 * 256
+    off = 256 + up(b * lq * hidx * 256) + up(b * lkv * hk * 256)
+    n = b * hidx * (lq // 128) * (lkv // 128)
+    return ws[off:off + 4 * n].view(torch.float32).view(b, hidx, lq // 128, lkv // 128)
+
+
+@pytest.mark.parametrize("case", ["random_codes", "shared_key_head", "zero_keys", "one_page"])
+def test_fp4_pruned_tile_scores_bit_exact(case):
+    """Few pages per list: the fast entry computes exact tile scores by pruning each
+    (query tile, page) pair with tensor-core values. Scores must equal those of the scorer that
+    evaluates every element, bit for bit, and the ids those of the oracle."""
+    m = sp()
+    hidx, hk, lq, lkv, topk, seed = {"random_codes": (2, 2, 512, 4096, 16, 11), "shared_key_head": (4, 1, 256, 2048, 8, 12),
+                                     "zero_keys": (1, 1, 256, 1024, 4, 13), "one_page": (1, 1, 128, 128, 1, 14)}[case]
+    b = 2 if case == "random_codes" else 1
+    g = torch.Generator().manual_seed(seed)
+    pages = b * lkv // 128
+    qp = torch.randint(256, (b * lq, hidx, 64), dtype=torch.uint8, generator=g)
+    kp = torch.randint(256, (pages, hk, 128, 64), dtype=torch.uint8, generator=g)
+    if case == "zero_keys":
+        kp.zero_()
+    choices = torch.tensor([0.25, 0.375, 0.5, 0.75, 1.0, 1.5, 2.0])
+    qs = choices[torch.randint(7, (b * lq, hidx, 8), generator=g)].to(torch.float8_e4m3fn)
+    ks = choices[torch.randint(7, (pages, hk, 128, 8), generator=g)].to(torch.float8_e4m3fn)
+    inputs = m.prepare_fp4_inputs(qp.cuda(), kp.cuda(), qs.cuda(), ks.cuda(), batch_size=b, len_q=lq, len_kv=lkv)
+    ids, ws = m.fp4_indexer_fast(inputs, topk=topk)
+    exact_scores = torch.empty((b, hidx, lq // 128, lkv // 128), dtype=torch.float32, device="cuda")
+    exact_ids = m.fp4_indexer(inputs, topk=topk, tile_scores=exact_scores)
+    torch.cuda.synchronize()
+    m.device_status()
+    assert ws[8:12].view(torch.float32).item() > 0 or case == "zero_keys"    # key norm: only the tensor-core kernels write it
+    pruned = _fast_path_tile_scores(ws, b, hidx, hk, lq, lkv)
+    assert torch.equal(pruned.view(torch.int32), exact_scores.view(torch.int32))
+    assert torch.equal(ids, exact_ids)
+    ref = oracle.fp4_select(oracle.fp4_scores(qp, qs, kp, ks, b, lq, lkv), b, lq, topk)
+    assert torch.equal(ids.cpu(), ref)
+
+
 def _varlen_case(seed, hq, hk, q_lens, k_lens, shuffle_pages=True):
     g = torch.Generator().manual_seed(seed)
     total_q = sum(q_lens)
