@@ -615,26 +615,28 @@ fp4_prune_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
   } else {
     // epilogue: thread = key row of the page, this warp's 64-column half of the query tile
     auto meet = [&]() { asm volatile("bar.sync 1, 256;" ::: "memory"); };
-    if (threadIdx.x < 128) {                 // L1 norm and squared L2 norm of one dequantised query row
-      const long long qrow = (q_row0 + threadIdx.x) * p.hidx + h;
-      const uint32_t* qc = reinterpret_cast<const uint32_t*>(p.qp + qrow * 64);
-      const uint8_t* qsc = p.qs + qrow * 8;
+    if (threadIdx.x < 128) {
+      // L1 norm and squared L2 norm of one dequantised query row, from the operand tile the TMA
+      // warp fetched (a row = 128 bytes in each of the two panels; the swizzle only permutes
+      // 16-byte pieces inside them, and the lanes start at different pieces to spare the banks)
       float l1 = 0.f, l2 = 0.f;
-      for (int g = 0; g < 8; ++g) {
-        int sum = 0, squares = 0;
-        for (int w = 0; w < 2; ++w) {
-          uint32_t two_words[2];
-          codes_to_int8(__ldg(qc + 2 * g + w), two_words[0], two_words[1]);
+      if (mbar_wait(bar(B_FULL), 0, guard, 0x5d0)) {
 #pragma unroll
-          for (int e = 0; e < 8; ++e) {
-            const int v = static_cast<int>(static_cast<int8_t>((two_words[e >> 2] >> (8 * (e & 3))) & 0xFFu));
-            sum += abs(v);
-            squares += v * v;
+        for (int panel = 0; panel < 2; ++panel) {
+          const uint4* row = reinterpret_cast<const uint4*>(gbase + OFF_B + panel * PANEL_BYTES + threadIdx.x * 128);
+#pragma unroll
+          for (int c = 0; c < 8; ++c) {
+            const uint4 piece = row[(c + lane) & 7];
+            const __nv_bfloat162* hh = reinterpret_cast<const __nv_bfloat162*>(&piece);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const float2 f = __bfloat1622float2(hh[e]);
+              l1 += fabsf(f.x) + fabsf(f.y);
+              l2 = fmaf(f.x, f.x, l2);
+              l2 = fmaf(f.y, f.y, l2);
+            }
           }
         }
-        const float unit = 0.5f * e4m3_to_float(qsc[g]);          // value of one integer step in this group
-        l1 += static_cast<float>(sum) * unit;
-        l2 += static_cast<float>(squares) * unit * unit;
       }
       atomicMax(const_cast<int*>(misc + 2), __float_as_int(l1 * 1.0001f));
       atomicMax(const_cast<int*>(misc + 3), __float_as_int(l2 * 1.0001f));
