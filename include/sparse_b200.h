@@ -207,11 +207,16 @@ int sparse_b200_indexer_fp4(const void* q_codes, const void* q_scales, const voi
 
 /* Same block ids as sparse_b200_indexer_fp4, bit for bit, with the scoring on the
  * tensor cores: dequantised NVFP4 values are exact in bf16, so tcgen05 bf16 MMAs
- * pre-filter the pages of every query tile, the surviving candidates are re-scored
- * with the exact group-ordered arithmetic, and a tile whose pre-filter cannot be
- * proven safe is scored exactly in full. `workspace` (256-byte aligned device memory
- * of sparse_b200_indexer_fp4_workspace_bytes(...) bytes) holds the dequantised
- * copies; the int at byte offset 4 counts the tiles that took the fallback.
+ * give every dot product within a known bound of its exact value. With many pages
+ * per top-k they pre-filter the pages of every query tile, the candidates whose
+ * order the approximate scores do not settle are re-scored with the exact
+ * group-ordered arithmetic, and a tile whose pre-filter cannot be proven safe is
+ * scored exactly in full; with few pages they prune every (query tile, page) pair
+ * to the few elements that can hold its exact maximum, which are then evaluated
+ * exactly. `workspace` (256-byte aligned device memory of
+ * sparse_b200_indexer_fp4_workspace_bytes(...) bytes) holds the dequantised copies
+ * and the tile scores; the int at byte offset 4 counts the tiles that took the
+ * fallback.
  * Role of fp4_indexer() (indexers/fp4/fp4.py:137-146). */
 int64_t sparse_b200_indexer_fp4_workspace_bytes(int batch, int hidx, int hk, int len_q, int len_kv);
 int sparse_b200_indexer_fp4_fast(const void* q_codes, const void* q_scales, const void* k_codes, const void* k_scales,
