@@ -139,7 +139,7 @@ __global__ void __launch_bounds__(256) dequant_kernel(const uint8_t* __restrict_
 // page on the tensor cores, then candidate selection and exact re-scoring.
 // Warps 0-7 epilogue (lane quarter = warp & 3, column half = warp >> 2), warp 8 TMA,
 // warp 9 MMA issue.
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+__global__ void __launch_bounds__(NUM_THREADS, 2)
 fp4_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map, const Params p) {
   extern __shared__ unsigned char smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
@@ -791,6 +791,7 @@ int launch_fp4_indexer_tc(const void* qp, const void* qs, const void* kp, const 
   const size_t smem = OFF_SCORES + ((static_cast<size_t>(tiles) * 4 + 15) & ~static_cast<size_t>(15)) + 320 + 1024;
   if (!(ctx->tc_attr & (1 << 8))) {
     cudaError_t e = cudaFuncSetAttribute(fp4_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(fp4_tc_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
     if (e != cudaSuccess) return set_error(SB_ERR_CUDA, cudaGetErrorString(e));
     ctx->tc_attr |= (1 << 8);
   }
