@@ -135,7 +135,8 @@ __global__ void __launch_bounds__(256) dequant_kernel(const uint8_t* __restrict_
   }
 }
 
-// One CTA per (batch, index head, query tile): approximate tile scores of every key
+// One CTA per (batch, index head, query tile), two CTAs per SM (the exact re-scoring of one
+// overlaps the tensor-core scoring of the other): approximate tile scores of every key
 // page on the tensor cores, then candidate selection and exact re-scoring.
 // Warps 0-7 epilogue (lane quarter = warp & 3, column half = warp >> 2), warp 8 TMA,
 // warp 9 MMA issue.
