@@ -106,7 +106,11 @@ int sparse_b200_kv_centric(const void* q, const void* k, const void* v, const in
  * block / PV on the tensor cores and scatters normalised partials [B, Hq, Sq, TopK, 128]
  * bf16 and partial_lse [B, Hq, Sq, TopK]; q is [B, Hq, Sq, 128]. Replaces kv11_launch
  * (attention/kv_centric/optimization_round11/tma11_kernel.cu:439-452). Merge with
- * sparse_b200_combine(partial, 0, partial_lse, out, lse, B*Hq*Sq, TopK, rank_major = 0). */
+ * sparse_b200_combine(partial, 0, partial_lse, out, lse, B*Hq*Sq, TopK, rank_major = 0).
+ * An id outside [0, kv_blocks) only raises error_word: its edge is dropped and its
+ * (query, rank) slot of partial / partial_lse is NOT written. A caller that cannot rule
+ * such ids out fills partial_lse with -inf before kv_token_main (Combine ignores -inf
+ * ranks) or reads error_word before merging. */
 int64_t sparse_b200_kv_token_max_tasks(int batch, int hkv, int sq, int topk, int kv_blocks, int group_size);
 int sparse_b200_kv_token_metadata(const int32_t* selected, int32_t* counts, int32_t* cursors, int32_t* row_ptr,
                                   int32_t* query_ids, int32_t* ranks, int32_t* task_ptr, int32_t* tasks,

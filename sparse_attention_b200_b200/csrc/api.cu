@@ -17,11 +17,7 @@ int set_error(int code, const char* message) {
   return code;
 }
 
-#ifdef SB_QC_TRACE
-static const size_t STATUS_BYTES = 64 + 32 * 256 * 8;   // debug builds: room for clock stamps
-#else
 static const size_t STATUS_BYTES = sizeof(int);
-#endif
 static std::mutex g_mutex;
 static DeviceCtx g_ctx[64];
 typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -81,14 +77,6 @@ using namespace sb;
 extern "C" {
 
 const char* sparse_b200_last_error(void) { return g_error; }
-
-#ifdef SB_QC_TRACE
-int sparse_b200_debug_trace(void* host, int bytes) {
-  DeviceCtx* ctx = device_ctx();
-  if (!ctx) return SB_ERR_CUDA;
-  return cudaMemcpy(host, ctx->status + 16, bytes, cudaMemcpyDeviceToHost) == cudaSuccess ? 0 : SB_ERR_CUDA;
-}
-#endif
 
 int sparse_b200_device_status(int reset) {
   DeviceCtx* ctx = device_ctx();
@@ -430,6 +418,7 @@ int sparse_b200_kv_token_main(const void* q, const void* k, const void* v, const
   REQUIRE(sq > 0 && skv >= 128 && skv % 128 == 0 && topk > 0 && topk <= skv / 128,
           "Skv must be a positive multiple of 128 and TopK at most the number of KV blocks");
   REQUIRE(static_cast<long long>(batch) * hkv * skv < (1LL << 31), "flattened KV rows must fit int32");
+  REQUIRE(static_cast<long long>(batch) * hkv * sq * topk < (1LL << 31), "B*Hkv*Sq*TopK must fit int32 (edge offsets)");
   REQUIRE(aligned16(q) && aligned16(k) && aligned16(v) && aligned16(partial) && aligned16(tasks), "misaligned pointer");
   const long long rows = static_cast<long long>(batch) * hkv * (skv / 128);
   return launch_kv_token_main(q, k, v, tasks, task_ptr + rows, query_ids, ranks, partial, partial_lse, batch, hq, hkv,
@@ -448,6 +437,7 @@ int sparse_b200_kv_token_main_tm(const void* q_token_major, const void* k, const
           "Skv must be a positive multiple of 128 and TopK at most the number of KV blocks");
   REQUIRE(static_cast<long long>(batch) * hkv * skv < (1LL << 31) && static_cast<long long>(batch) * sq < (1LL << 31),
           "flattened KV rows and tokens must fit int32");
+  REQUIRE(static_cast<long long>(batch) * hkv * sq * topk < (1LL << 31), "B*Hkv*Sq*TopK must fit int32 (edge offsets)");
   REQUIRE(aligned16(q_token_major) && aligned16(k) && aligned16(v) && aligned16(partial) && aligned16(tasks),
           "misaligned pointer");
   const long long rows = static_cast<long long>(batch) * hkv * (skv / 128);

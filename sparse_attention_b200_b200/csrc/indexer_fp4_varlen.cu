@@ -54,11 +54,16 @@ __global__ void __launch_bounds__(256, 3) fp4_score_varlen_kernel(const VarlenPa
   const int q_begin = p.cu_q[b], q_len = p.cu_q[b + 1] - q_begin;
   const int k_len = p.cu_k[b + 1] - p.cu_k[b];
   if (qtile * 128 >= q_len || k_len <= 0) return;          // block-uniform
-  const int pages = (k_len + 127) >> 7;
+  // Inconsistent arguments must not become out-of-range accesses: the page loop stays inside the
+  // output's page axis (sized from max_seqlen_k on the host) and inside this request's slice of
+  // kv_indices, and the live rows stay inside total_q.
   const int page_begin = p.cu_pages[b];
+  const int pages = min(min((k_len + 127) >> 7, p.tiles_out), p.cu_pages[b + 1] - page_begin);
+  if (q_begin < 0 || page_begin < 0) return;               // block-uniform
   const int offset = p.causal ? (p.qo_offset ? p.qo_offset[b] : k_len - q_len) : 0;
   const int hk_idx = h / (p.hq / p.hk);
-  const int rows_live = min(128, q_len - qtile * 128);
+  const int rows_live = min(min(128, q_len - qtile * 128), p.total_q - q_begin - qtile * 128);
+  if (rows_live <= 0) return;                              // block-uniform
 
   // stage the query tile (rows past the request's end as zeros)
   for (int e = tid; e < 128 * 16; e += 256) {
@@ -149,8 +154,8 @@ __global__ void __launch_bounds__(256, 3) fp4_score_varlen_kernel(const VarlenPa
     }
     if (tig == 0) {
       float* dst = p.out + (static_cast<long long>(h) * p.tiles_out + pg) * p.total_q + q_begin;
-      if (qi0 < q_len) dst[qi0] = r0;
-      if (qi1 < q_len) dst[qi1] = r1;
+      if (qi0 < qtile * 128 + rows_live) dst[qi0] = r0;
+      if (qi1 < qtile * 128 + rows_live) dst[qi1] = r1;
     }
   }
 }

@@ -12,6 +12,7 @@
 // attention/kv_centric/metadata.py:43-72), for any TopK and block count, with its own
 // scans instead of a library call. Edge order inside a row is arbitrary (atomics).
 // error word: bit 1 = an id outside [0, kv_blocks).
+#include <algorithm>
 #include "internal.h"
 
 namespace sb {
@@ -157,17 +158,24 @@ __global__ void __launch_bounds__(256) scatter_edges_kernel(const int32_t* __res
   }
 }
 
-__global__ void __launch_bounds__(128) make_tasks_kernel(const int32_t* __restrict__ row_ptr,
+// One thread per task. The owning row of task t is the last row whose first task is <= t, found
+// by bisection over task_ptr (rows with no edges own no task and are skipped by the search), so a
+// row with thousands of tasks is spread over many CTAs. A task record is (KV-head group, KV
+// block, first edge, edge count).
+__global__ void __launch_bounds__(256) emit_tasks_kernel(const int32_t* __restrict__ row_ptr,
                                                          const int32_t* __restrict__ task_ptr,
-                                                         int32_t* __restrict__ tasks, int rows, int kv_blocks,
-                                                         int capacity) {
-  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
-    const int start = row_ptr[row], end = row_ptr[row + 1];
-    for (int task = task_ptr[row] + threadIdx.x; task < task_ptr[row + 1]; task += blockDim.x) {
-      const int begin = start + (task - task_ptr[row]) * capacity;
-      const int4 value = {row / kv_blocks, row % kv_blocks, begin, min(capacity, end - begin)};
-      *reinterpret_cast<int4*>(tasks + static_cast<long long>(task) * 4) = value;
+                                                         int4* __restrict__ tasks, int rows, int kv_blocks,
+                                                         int edges_per_task) {
+  const int n_tasks = task_ptr[rows];
+  for (int t = blockIdx.x * blockDim.x + threadIdx.x; t < n_tasks; t += gridDim.x * blockDim.x) {
+    int lo = 0, hi = rows;                       // invariant: task_ptr[lo] <= t < task_ptr[hi]
+    while (hi - lo > 1) {
+      const int mid = (lo + hi) >> 1;
+      if (task_ptr[mid] <= t) lo = mid; else hi = mid;
     }
+    const int first_edge = row_ptr[lo] + (t - task_ptr[lo]) * edges_per_task;
+    const int left = row_ptr[lo + 1] - first_edge;
+    tasks[t] = make_int4(lo / kv_blocks, lo % kv_blocks, first_edge, left < edges_per_task ? left : edges_per_task);
   }
 }
 
@@ -200,7 +208,10 @@ int launch_token_metadata(const int32_t* selected, int32_t* counts, int32_t* cur
     scatter_edges_kernel<<<grid, 256, 0, stream>>>(selected, row_ptr, cursors, qids, ranks, edges, group_edges,
                                                    kv_blocks, topk);
   scan_kernel<<<1, 1024, 0, stream>>>(counts, task_ptr, rows, capacity);
-  make_tasks_kernel<<<rows < 4096 ? rows : 4096, 128, 0, stream>>>(row_ptr, task_ptr, tasks, rows, kv_blocks, capacity);
+  const long long task_bound = std::min<long long>((edges + capacity - 1) / capacity + rows, edges);
+  const int task_grid = static_cast<int>(std::min<long long>((task_bound + 255) / 256, 2048));
+  emit_tasks_kernel<<<task_grid > 0 ? task_grid : 1, 256, 0, stream>>>(row_ptr, task_ptr, reinterpret_cast<int4*>(tasks),
+                                                                     rows, kv_blocks, capacity);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? SB_OK : set_error(SB_ERR_CUDA, cudaGetErrorString(e));
 }

@@ -75,14 +75,6 @@ constexpr int OFF_MISC = OFF_BAR + NUM_BARS * 8;   // tmem base (4 B), abort fla
 constexpr int SMEM_BYTES = OFF_MISC + 48 + 1024;   // + slack for manual 1024 alignment
 static_assert(SMEM_BYTES <= 227 * 1024, "shared memory map exceeds the per-CTA limit");
 
-#ifdef SB_QC_TRACE
-// Debug builds only: clock64 stamps of CTA 0 into the words after the status word.
-#define TRACE(slot, idx) do { if (blockIdx.x == 0 && lane == 0 && (idx) < 256) \
-    reinterpret_cast<long long*>(p.status + 16)[(slot) * 256 + (idx)] = clock64(); } while (0)
-#else
-#define TRACE(slot, idx) do { } while (0)
-#endif
-
 struct Params {
   const int32_t* ids;      // [nseg, B, Hkv, Qt, topk]
   const int32_t* counts;   // [nseg, B, Hkv, Qt] or nullptr (= topk everywhere)
@@ -259,7 +251,6 @@ q_centric_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
         bool w = mbar_wait(bar(BAR_KV_EMPTY + slot), (use - 1) & 1, guard, 0x100 + slot);
         if (!__all_sync(0xffffffffu, w)) return false;
       }
-      TRACE(24, static_cast<int>(fills));
       if (lane == 0) {
         const uint32_t dst = base + OFF_RING + slot * TILE_BYTES;
         mbar_expect_tx(bar(BAR_KV_FULL + slot), TILE_BYTES);
@@ -362,9 +353,7 @@ q_centric_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
     bool ok = true;
     auto acquire = [&](uint32_t& slot) -> bool {
       slot = taken % RING;
-      TRACE(22, static_cast<int>(taken));
       bool w = mbar_wait(bar(BAR_KV_FULL + slot), (taken / RING) & 1, guard, 0x200 + slot);
-      TRACE(23, static_cast<int>(taken));
       ++taken;
       tc_fence_after();
       return w;
@@ -375,15 +364,10 @@ q_centric_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
       tc_fence_after();
       return w;
     };
-    int trace_p[2] = {0, 0};
-    (void)trace_p;
     auto wait_p = [&](int q) -> bool {
-      TRACE(20 + q, trace_p[q]);
       bool w = mbar_wait(bar(BAR_P_FULL + q), pphase[q], guard, 0x220 + q);
       pphase[q] ^= 1;
       tc_fence_after();
-      TRACE(16 + q, trace_p[q]);
-      ++trace_p[q];
       return w;
     };
     // S_q = Q_q K^T : 8 MMAs of K = 16 over two 64-column panels.
@@ -552,8 +536,6 @@ q_centric_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
     if (lane == 0) *handed_ptr = 0;
     __syncwarp();
     bool ok = true;
-    int trace_n = 0;
-    (void)trace_n;
     for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x) {
       Stream s[2];
       decode_item(p, item, s);
@@ -579,12 +561,10 @@ q_centric_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
         ok = __all_sync(0xffffffffu, w);
         if (!ok) break;
         tc_fence_after();
-        if ((warp & 3) == 0) TRACE(q * 8 + 0, trace_n);
         uint32_t sv[4][32];
 #pragma unroll
         for (int c = 0; c < 4; ++c) tmem_ld32(t_s + c * 32, sv[c]);
         tc_wait_ld();
-        if ((warp & 3) == 0) TRACE(q * 8 + 1, trace_n);
         // four independent running maxima, three-input max: 64 instructions per row
         float mx[4];
 #pragma unroll
@@ -620,7 +600,6 @@ q_centric_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
             tmem_st32(t_o + c * 32, ov);
           }
         }
-        if ((warp & 3) == 0) TRACE(q * 8 + 2, trace_n);
         // p = 2^(s*scale - max): packed FMAs, exponentials on the special-function unit (moving a
         // share of them to an FMA-pipe polynomial was measured slower: the softmax warps are
         // issue-bound there).
@@ -647,13 +626,10 @@ q_centric_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
           }
         }
         row_sum += (part[0].x + part[0].y) + (part[1].x + part[1].y);
-        if ((warp & 3) == 0) TRACE(q * 8 + 3, trace_n);
         tc_wait_st();
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(bar(BAR_P_FULL + q));
-        if ((warp & 3) == 0) TRACE(q * 8 + 4, trace_n);
-        ++trace_n;
       }
       if (!ok) break;
       // Hand the row statistics to the epilogue warps and go on to the next item. A list of
@@ -697,7 +673,6 @@ q_centric_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
         ok = __all_sync(0xffffffffu, w);
         if (!ok) break;
         tc_fence_after();
-        if (quarter == 0) TRACE(q * 8 + 5, static_cast<int>(done[q]));
         const float inv = stats[q * TILE + quarter * 32 + lane];
         __syncwarp();
         if (lane == 0) mbar_arrive(bar(BAR_STATS_EMPTY + q));
@@ -765,7 +740,6 @@ q_centric_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
             bulk_commit();
           }
         }
-        if (quarter == 0) TRACE(q * 8 + 6, static_cast<int>(done[q]));
       }
     }
     if (lane == 0) bulk_wait_all();      // output stores of this warp have completed

@@ -431,6 +431,49 @@ def test_fp4_scores_ragged_paged_causal(causal):
         assert torch.equal(dense, ragged)
 
 
+def test_fp4_scores_varlen_inconsistent_lengths_stay_in_bounds():
+    """max_seqlen_k smaller than one request's key length, a page table shorter than the key
+    length claims, and cu_seqlens_q that runs past total_q: the kernel must skip what does not fit.
+    The output (sized from max_seqlen_k) sits inside a larger poisoned buffer, so a write outside it,
+    or into another head's rows for pages past the output's page axis, shows up."""
+    m = sp()
+    q_lens, k_lens = [130, 64], [700, 256]
+    qp, qs, kp, ks, cu_q, cu_k, cu_p, kv_idx = _varlen_case(21, 2, 1, q_lens, k_lens)
+    short = 384                                            # 3 pages of output; request 0 has 6 pages of keys
+    hq, total_q = 2, sum(q_lens)
+    tiles = (short + 127) // 128
+    ref_full = oracle.fp4_scores_varlen(qp, qs, kp, ks, cu_q, cu_k, cu_p, kv_idx, max(k_lens))
+    L = m.lib()
+    guard = 4096
+    buf = torch.full((guard + hq * tiles * total_q + guard,), 12345.0, device="cuda")
+    out = buf[guard:guard + hq * tiles * total_q]
+    args = [t.cuda() for t in (qp, qs, kp, ks, cu_q, cu_k, cu_p, kv_idx)]
+    from sparse_attention_b200_b200 import _lib
+    rc = L.sparse_b200_fp4_scores_varlen(*[_lib.ptr(t) for t in args], None, _lib.ptr(out), 2, hq, 1, total_q,
+                                         int(kp.shape[0]), max(q_lens), short, 0, _lib.current_stream())
+    assert rc == 0
+    torch.cuda.synchronize()
+    m.device_status()
+    assert torch.all(buf[:guard] == 12345.0) and torch.all(buf[-guard:] == 12345.0)
+    got = out.view(hq, tiles, total_q).cpu()
+    assert torch.equal(got[:, :, :q_lens[0]], ref_full[:, :tiles, :q_lens[0]])      # the pages that fit are right
+    assert torch.equal(got[:, :2, q_lens[0]:], ref_full[:, :2, q_lens[0]:])
+    # a page table that ends before the key length says, and queries claimed past total_q
+    cu_p_short = cu_p.clone()
+    cu_p_short[1:] -= 2                                    # request 0 now owns 4 pages for 700 keys
+    cu_q_long = cu_q.clone()
+    cu_q_long[-1] += 500
+    buf.fill_(12345.0)
+    rc = L.sparse_b200_fp4_scores_varlen(_lib.ptr(args[0]), _lib.ptr(args[1]), _lib.ptr(args[2]), _lib.ptr(args[3]),
+                                         _lib.ptr(cu_q_long.cuda()), _lib.ptr(args[5]), _lib.ptr(cu_p_short.cuda()),
+                                         _lib.ptr(args[7]), None, _lib.ptr(out), 2, hq, 1, total_q, int(kp.shape[0]),
+                                         max(q_lens) + 500, short, 0, _lib.current_stream())
+    assert rc == 0
+    torch.cuda.synchronize()
+    m.device_status()
+    assert torch.all(buf[:guard] == 12345.0) and torch.all(buf[-guard:] == 12345.0)
+
+
 def test_indexer_then_attention_config1():
     """Configuration 1 end to end: R1 picks top-8 of 32, Q-centric attention,
     against the masked-attention oracle."""

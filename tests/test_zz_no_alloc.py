@@ -69,6 +69,29 @@ def test_noalloc_indexer_matches_regular_entry_twice_in_a_row():
     assert torch.equal(ids.cpu(), oracle.summary_select(q, k, 2, 3)[3])
 
 
+@pytest.mark.gpu
+def test_noalloc_indexer_at_its_limits():
+    """The ends of the built-in array and of the shared score buffer: exactly 32768 descriptors
+    with 4096 KV blocks, group size x R = 16 (the widest padded row block), and R = 2."""
+    g = torch.Generator(device="cuda").manual_seed(901)
+    problems = [
+        (1, 1, 1, 524288, 524288, 4, 64),     # (4096 + 4096) blocks x R4 = 32768 descriptors, nt = 4096
+        (1, 16, 4, 1024, 2048, 4, 7),         # group 4 x R4 = 16
+        (1, 8, 1, 512, 4096, 2, 9),           # group 8 x R2 = 16, R = 2
+        (2, 4, 4, 256, 512, 2, 4),            # R = 2, group 1
+    ]
+    for (b, hq, hkv, sq, skv, r, topk) in problems:
+        q = torch.randn((b, hq, sq, 128), device="cuda", generator=g).to(torch.bfloat16)
+        k = (torch.randn((b, hkv, skv // 128, 128, 128), device="cuda", generator=g)
+             + 0.5 * torch.randn((b, hkv, skv // 128, 1, 128), device="cuda", generator=g)) \
+            .reshape(b, hkv, skv, 128).to(torch.bfloat16)
+        (s_ref, i_ref), (s_new, i_new) = _call_pair(q, k, r, topk)
+        assert torch.equal(i_new, i_ref)
+        assert torch.equal(s_new, s_ref)
+    from sparse_attention_b200_b200 import device_status
+    device_status()
+
+
 def test_noalloc_indexer_rejects_sizes_beyond_its_scratch():
     """Validation happens before any CUDA call, so this runs without a GPU too."""
     L = _lib()
