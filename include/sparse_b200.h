@@ -36,6 +36,22 @@ const char* sparse_b200_last_error(void);
  * device; meant for tests and post-mortems, not for the hot path. */
 int sparse_b200_device_status(int reset);
 
+/* The same check as a return code: synchronises the device, clears the status word and
+ * returns SPARSE_B200_ERR_TIMEOUT (message: the code of the abandoned wait) when a
+ * kernel gave up a bounded wait since the last check, else 0. The reference's waits
+ * have no limit (attention/q_centric/common.cuh:38-52: a protocol error hangs the GPU);
+ * here every wait ends after ~0.8 s at the latest and the outputs of that launch are
+ * incomplete. */
+int sparse_b200_check_status(void);
+
+/* Exercises that give-up path on purpose, harmlessly: one small CTA waits on an
+ * mbarrier nobody arrives on (nothing in flight, no tensor memory held) for at most
+ * limit_cycles (<= 1e8) clock cycles, records code 0x7e57 in the status word, raises
+ * its abort flag, and exits. observed (2 device ints, may be NULL): [0] = 0 when the
+ * wait gave up, [1] = 1 when the CTA's other warp saw the abort flag. No counterpart
+ * in the reference. */
+int sparse_b200_selftest_bounded_wait(int64_t limit_cycles, int32_t* observed, void* stream);
+
 /* Q-centric block-sparse attention forward.
  * Replaces the launch functions behind xomtention_progression::attention_out
  * (attention/q_centric/progression_attention.cpp:11-15, 96-108:

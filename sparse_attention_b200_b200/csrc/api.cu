@@ -88,6 +88,20 @@ int sparse_b200_device_status(int reset) {
   return value;
 }
 
+int sparse_b200_check_status(void) {
+  const int value = sparse_b200_device_status(1);
+  if (value < 0) return value;
+  if (value == 0) return SB_OK;
+  char msg[160];
+  snprintf(msg, sizeof(msg), "a kernel abandoned a bounded wait (code 0x%x); its outputs are incomplete", value);
+  return set_error(SB_ERR_TIMEOUT, msg);
+}
+
+int sparse_b200_selftest_bounded_wait(int64_t limit_cycles, int32_t* observed, void* stream) {
+  REQUIRE(limit_cycles > 0 && limit_cycles <= 100000000LL, "limit must be in (0, 1e8] cycles");
+  return launch_bounded_wait_selftest(limit_cycles, observed, static_cast<cudaStream_t>(stream));
+}
+
 static int check_attention(const void* q, const void* k, const void* v, const int32_t* block_idx,
                            const void* out, int batch, int hq, int hkv, int sq, int skv, int topk, int nseg) {
   REQUIRE(q && k && v && block_idx && out, "q, k, v, block_idx and out must be non-null device pointers");

@@ -83,5 +83,6 @@ int launch_fp4_scores(const void* qp, const void* qs, const void* kp, const void
 int launch_tile_max_topk(const float* query_scores, int32_t* ids, int batch, int heads, int len_q, int tiles, int topk,
                          cudaStream_t stream);
 int launch_row_topk(const float* tile_scores, int32_t* ids, long long rows, int tiles, int topk, cudaStream_t stream);
+int launch_bounded_wait_selftest(long long limit_cycles, int* observed, cudaStream_t stream);
 
 }  // namespace sb

@@ -57,7 +57,8 @@ struct Guard {
 
 // Returns true when the phase with the given parity has completed. On timeout
 // (or when another role already aborted) returns false.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const Guard& g, int code) {
+__device__ __forceinline__ bool mbar_wait_limited(uint32_t bar, uint32_t parity, const Guard& g, int code,
+                                                  long long limit_cycles) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   int spins = 0;
@@ -65,13 +66,16 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const G
     if (mbar_try_wait(bar, parity)) return true;
     if ((++spins & 31) == 0) {
       if (*g.abort_flag) return false;
-      if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
+      if (clock64() - t0 > limit_cycles) {
         *g.abort_flag = 1;
         atomicCAS(g.status, 0, code);
         return false;
       }
     }
   }
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const Guard& g, int code) {
+  return mbar_wait_limited(bar, parity, g, code, WAIT_LIMIT_CYCLES);
 }
 // Quiet bounded wait used while draining after an abort (ignores the flag).
 __device__ __forceinline__ void mbar_wait_drain(uint32_t bar, uint32_t parity) {

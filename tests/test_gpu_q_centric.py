@@ -240,3 +240,25 @@ def test_host_pipeline_matches_device_path():
         pipe.run(hq_, hk_, hv_, hi_, ho, hl).synchronize()
         check(ho, hl, ref_o, ref_l)
     m.device_status()
+    # fewer groups than chunks: a group's heads are split over chunks (K, V and the lists travel with
+    # the first one), staged through caller-owned device buffers; changed inputs on the second call
+    q, k, v = gen.make_qkv(1, 8, 1, 512, 1024, seed=93)
+    ids = gen.make_ids(1, 1, 4, 8, 3, 94)
+    hq_, hk_, hv_, hi_ = (t.clone().pin_memory() for t in (q, k, v, ids))
+    ho = torch.empty(q.shape, dtype=torch.bfloat16).pin_memory()
+    hl = torch.empty(q.shape[:3]).pin_memory()
+    bufs = (torch.empty_like(q, device="cuda"), torch.empty_like(k, device="cuda"), torch.empty_like(v, device="cuda"),
+            torch.empty_like(ids, device="cuda"), torch.empty_like(q, device="cuda"),
+            torch.empty(q.shape[:3], device="cuda"))
+    pipe = m.HostPipeline(1, 8, 1, 512, 1024, 3, "cuda:0", chunks=4, buffers=bufs)
+    assert pipe.chunks == 4
+    for shift in (0, 1):
+        hk_.copy_(k.roll(shift * 128, dims=2))
+        hv_.copy_(v.roll(shift * 128, dims=2))
+        ref_o, ref_l = oracle.gather_attention(q, hk_.clone(), hv_.clone(), ids)
+        ho.fill_(float("nan"))
+        pipe.run(hq_, hk_, hv_, hi_, ho, hl).synchronize()
+        check(ho, hl, ref_o, ref_l)
+    t0 = pipe.run(hq_, hk_, hv_, hi_, ho, hl, copy_only=True)
+    t0.synchronize()
+    m.device_status()
