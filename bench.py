@@ -286,7 +286,11 @@ class Workload:
                 del tile_scores
             ws = sp.fp4_indexer_fast(inputs, ids)[1]
             st["indexer_ms"] = timed(lambda: sp.fp4_indexer_fast(inputs, ids, workspace=ws), steps, warmup, barrier)
+            ws[:32].zero_()                                  # the counters accumulate: one clean call to read them
+            sp.fp4_indexer_fast(inputs, ids, workspace=ws)
             st["indexer_fallback_tiles"] = int(ws[4:8].view(torch.int32).item())
+            st["indexer_bound_violations"] = int(ws[12:16].view(torch.int32).item())
+            st["indexer_max_err_over_bound"] = float(ws[16:20].view(torch.float32).item())
             self.ids = ids
             st["indexer_bytes"] = (ng * n * hidx + ng * n) * 72 + ids.numel() * 4
             st["indexer_bytes_with_quantize"] = st["indexer_bytes"] + (self.q.numel() + self.k.numel()) * 2
@@ -983,6 +987,25 @@ def run_refsel(args):
         except Exception as e:          # Triton missing or unusable on this box
             print(json.dumps({"workload": "refsel", "reference_same_box": f"unavailable: {e}"}), flush=True)
             ref_sel = None
+    # the reference's own NVFP4 indexer (indexers/fp4/fp4.py:122-146): the vendored MiniMax MSA scorer
+    # (CuTe DSL, compiled by nvidia-cutlass-dsl at the first call) + its tile_topk extension, copied
+    # unmodified into baseline/_ref/fp4 and prebuilt by baseline/build_reference_kernels.py
+    ref_fp4, ref_fp4_note = None, None
+    fp4_dir = os.path.join(os.path.dirname(os.path.abspath(__file__)), "baseline", "_ref", "fp4")
+    topk_lib = os.path.join(fp4_dir, "build", "xomtention_tile_topk.so")
+    if os.path.exists(topk_lib):
+        try:
+            import pathlib
+            sys.path.insert(0, os.path.dirname(fp4_dir))
+            import fp4 as ref_fp4_pkg
+            from fp4 import fp4 as ref_fp4
+            torch.ops.load_library(topk_lib)
+            ref_fp4_pkg._load_extension = lambda: torch.ops.xomtention_tile_topk
+            ref_fp4.MSA_CUTE_DIR = pathlib.Path(fp4_dir) / "vendor_minimax_msa"   # the vendored copy of the scorer
+        except Exception as e:
+            ref_fp4, ref_fp4_note = None, f"unavailable: {type(e).__name__}: {e}"
+    else:
+        ref_fp4_note = "unavailable: baseline/_ref/fp4 not built (python baseline/build_reference_kernels.py --ref ...)"
     for Skv in (4096, 8192, 16384):
         gen = torch.Generator(device=dev).manual_seed(29)
         q = torch.randn((B, Hq, Sq, 128), device=dev, generator=gen).to(torch.bfloat16)
@@ -1031,6 +1054,24 @@ def run_refsel(args):
                             "selector_to_attention": round(t_pipe, 2)}
         pub = REFSEL_PUBLISHED[Skv]["FP4"]
         row["reference_published_us"]["FP4"] = {"selector": pub[0], "selector_to_p03": pub[1]}
+        if ref_fp4 is not None:
+            try:
+                rin = ref_fp4.prepare_fp4_inputs(qc, kc, qs, ks, batch_size=B, len_q=Sq, len_kv=Skv)
+                rsel = torch.empty((B, Hkv, Sq // 128, 16), dtype=torch.int32, device=dev)
+                ref_fp4.fp4_indexer(rin, rsel)                      # compiles the scorer
+                torch.cuda.synchronize()
+                t_ref = graph_time_us(lambda: ref_fp4.fp4_indexer(rin, rsel))
+                t_ref_scorer = graph_time_us(lambda: ref_fp4.fp4_block_scores(rin))
+                torch.cuda.synchronize()
+                same = (rsel == ids_fast).all(-1).float().mean().item()
+                row.setdefault("reference_same_box_us", {})["FP4"] = {
+                    "selector": round(t_ref, 2), "scorer_only": round(t_ref_scorer, 2),
+                    "lists_with_identical_ids": round(same, 4)}
+            except Exception as e:                                  # DSL version or compile trouble on this box
+                ref_fp4_note = f"unavailable: {type(e).__name__}: {str(e)[:300]}"
+                ref_fp4 = None
+        if ref_fp4 is None:
+            row.setdefault("reference_same_box_us", {})["FP4"] = ref_fp4_note
         row["us"]["attention_only"] = round(graph_time_us(lambda: sp.attention_out(q, k, v, ids_fast, out)), 2)
         sp.device_status()
         print(json.dumps(row), flush=True)

@@ -225,23 +225,43 @@ int sparse_b200_indexer_fp4(const void* q_codes, const void* q_scales, const voi
                             float* tile_scores, int32_t* block_idx, int batch, int hidx, int hk, int len_q, int len_kv,
                             int topk, void* stream);
 
-/* Same block ids as sparse_b200_indexer_fp4, bit for bit, with the scoring on the
- * tensor cores: dequantised NVFP4 values are exact in bf16, so tcgen05 bf16 MMAs
- * give every dot product within a known bound of its exact value. With many pages
- * per top-k they pre-filter the pages of every query tile, the candidates whose
- * order the approximate scores do not settle are re-scored with the exact
- * group-ordered arithmetic, and a tile whose pre-filter cannot be proven safe is
- * scored exactly in full; with few pages they prune every (query tile, page) pair
- * to the few elements that can hold its exact maximum, which are then evaluated
- * exactly. `workspace` (256-byte aligned device memory of
- * sparse_b200_indexer_fp4_workspace_bytes(...) bytes) holds the dequantised copies
- * and the tile scores; the int at byte offset 4 counts the tiles that took the
- * fallback.
- * Role of fp4_indexer() (indexers/fp4/fp4.py:137-146). */
+/* Same block ids as sparse_b200_indexer_fp4, bit for bit, with the scoring on the NVFP4
+ * tensor cores: tcgen05 block-scaled MMAs (e2m1 codes, ue4m3 scale per 16 features) read
+ * the codes and scales as they are, so every dot product comes within a known bound of
+ * its exact value and nothing is dequantised. With many pages per top-k they pre-filter
+ * the pages of every query tile, the candidates whose order the approximate scores do not
+ * settle are re-scored with the exact group-ordered arithmetic, and a tile whose
+ * pre-filter cannot be proven safe is scored exactly in full; with few pages they prune
+ * every (query tile, page) pair to the few elements that can hold its exact maximum,
+ * which are then evaluated exactly. `workspace` (256-byte aligned device memory of
+ * sparse_b200_indexer_fp4_workspace_bytes(...) bytes) starts with five words that the
+ * owner zeroes ONCE (no call clears them; they accumulate over calls): [0] CTAs of the
+ * tensor-core kernels that ran (int), [1] tiles that took the exact path (int), [2]
+ * unused, [3] scores whose tensor-core value and exact value differed by more than the
+ * bound (int; each sends its tile or pair to the exact path, so ids stay exact),
+ * [4] largest such difference seen, as a fraction of the bound (float); tile scores follow
+ * at byte 256 when the pruning path ran.
+ * Role of fp4_indexer() (indexers/fp4/fp4.py:137-146) with the scorer of
+ * indexers/fp4/vendor_minimax_msa/src/sm100/fp4_indexer.py:201-1108. */
 int64_t sparse_b200_indexer_fp4_workspace_bytes(int batch, int hidx, int hk, int len_q, int len_kv);
 int sparse_b200_indexer_fp4_fast(const void* q_codes, const void* q_scales, const void* k_codes, const void* k_scales,
                                  void* workspace, int64_t workspace_bytes, int32_t* block_idx, int batch, int hidx,
                                  int hk, int len_q, int len_kv, int topk, void* stream);
+
+/* NVFP4 indexer -> attention on one stream with no host synchronisation, the whole of
+ * indexed_attention() (indexers/fp4/pipeline.py:49-65) as one call: [quantise ->] score
+ * on the NVFP4 tensor cores -> top-k -> Q-centric attention. One index head per KV head:
+ * q_codes [B*Sq, Hkv, 64], q_scales [B*Sq, Hkv, 8], k_codes [B*Skv/128, Hkv, 128, 64],
+ * k_scales [B*Skv/128, Hkv, 128, 8]. quantize != 0: the four buffers are OUTPUTS, filled
+ * from q (mean over the Hq/Hkv heads of a group) and k first, the preparation the reference
+ * leaves outside its timing (indexers/fp4/fp4.py:37-119); quantize == 0: they are inputs
+ * prepared earlier. workspace as in sparse_b200_indexer_fp4_fast(B, Hkv, Hkv, Sq, Skv).
+ * block_idx [B, Hkv, Sq/128, TopK] is written and consumed. Nothing is allocated;
+ * capturable in a CUDA graph after one eager call. */
+int sparse_b200_indexed_attention_fp4(const void* q, const void* k, const void* v, void* q_codes, void* q_scales,
+                                      void* k_codes, void* k_scales, void* workspace, int64_t workspace_bytes,
+                                      int32_t* block_idx, void* out, float* lse, int batch, int hq, int hkv, int sq,
+                                      int skv, int topk, int quantize, void* stream);
 
 /* R1 / R4 summary indexer that allocates nothing and takes no workspace: same
  * inputs, outputs, arithmetic and results as sparse_b200_indexer_summary, with

@@ -461,10 +461,8 @@ int sparse_b200_kv_token_main_tm(const void* q_token_major, const void* k, const
 
 int64_t sparse_b200_indexer_fp4_workspace_bytes(int batch, int hidx, int hk, int len_q, int len_kv) {
   if (batch <= 0 || hidx <= 0 || hk <= 0 || len_q <= 0 || len_kv <= 0) return SB_ERR_INVALID;
-  const int64_t q = align256(static_cast<size_t>(batch) * len_q * hidx * 256);
-  const int64_t k = align256(static_cast<size_t>(batch) * len_kv * hk * 256);
   const int64_t tile = align256(static_cast<size_t>(batch) * hidx * (len_q / 128) * (len_kv / 128) * 4);
-  return 256 + q + k + tile;
+  return 256 + tile;
 }
 
 int sparse_b200_indexer_fp4_fast(const void* q_codes, const void* q_scales, const void* k_codes, const void* k_scales,
@@ -479,24 +477,44 @@ int sparse_b200_indexer_fp4_fast(const void* q_codes, const void* q_scales, cons
           "workspace too small (see sparse_b200_indexer_fp4_workspace_bytes)");
   unsigned char* w = static_cast<unsigned char*>(workspace);
   void* aux = w;
-  void* q_deq = w + 256;
-  void* k_deq = w + 256 + align256(static_cast<size_t>(batch) * len_q * hidx * 256);
-  float* tile_scores = reinterpret_cast<float*>(static_cast<unsigned char*>(k_deq) +
-                                                align256(static_cast<size_t>(batch) * len_kv * hk * 256));
-  rc = launch_fp4_indexer_tc(q_codes, q_scales, k_codes, k_scales, q_deq, k_deq, aux, block_idx, batch, hidx, hk, len_q,
-                             len_kv, topk, static_cast<cudaStream_t>(stream));
-  if (rc == 1) {   // not eligible: exact tile scores + top-k, same ids
+  float* tile_scores = reinterpret_cast<float*>(w + 256);
+  rc = launch_fp4_indexer_tc(q_codes, q_scales, k_codes, k_scales, aux, block_idx, batch, hidx, hk, len_q, len_kv, topk,
+                             static_cast<cudaStream_t>(stream));
+  if (rc == 1) {   // few pages per list: exact tile scores + top-k, same ids
     // tensor-core values prune each (query tile, page) pair to the few elements that can hold its maximum
-    rc = launch_fp4_scores_prune(q_codes, q_scales, k_codes, k_scales, q_deq, k_deq, aux, tile_scores, batch, hidx, hk,
-                                 len_q, len_kv, static_cast<cudaStream_t>(stream));
+    rc = launch_fp4_scores_prune(q_codes, q_scales, k_codes, k_scales, aux, tile_scores, batch, hidx, hk, len_q, len_kv,
+                                 static_cast<cudaStream_t>(stream));
+    const bool pruned = rc == SB_OK;
     if (rc == 1)   // exact scorer that evaluates every element
       rc = launch_fp4_scores(q_codes, q_scales, k_codes, k_scales, nullptr, tile_scores, batch, hidx, hk, len_q, len_kv,
                              static_cast<cudaStream_t>(stream));
     if (rc) return rc;
     rc = launch_row_topk(tile_scores, block_idx, static_cast<long long>(batch) * hidx * (len_q / 128), len_kv / 128,
-                         topk, static_cast<cudaStream_t>(stream));
+                         topk, static_cast<cudaStream_t>(stream), pruned);
   }
   return rc;
+}
+
+int sparse_b200_indexed_attention_fp4(const void* q, const void* k, const void* v, void* q_codes, void* q_scales,
+                                      void* k_codes, void* k_scales, void* workspace, int64_t workspace_bytes,
+                                      int32_t* block_idx, void* out, float* lse, int batch, int hq, int hkv, int sq,
+                                      int skv, int topk, int quantize, void* stream) {
+  REQUIRE(q && k && v && q_codes && q_scales && k_codes && k_scales && block_idx && out, "null pointer");
+  REQUIRE(batch > 0 && hkv > 0 && hq >= hkv && hq % hkv == 0, "Hq must be a positive multiple of Hkv");
+  REQUIRE(sq >= 128 && sq % 128 == 0 && skv >= 128 && skv % 128 == 0, "Sq and Skv must be positive multiples of 128");
+  int rc = SB_OK;
+  if (quantize) {
+    // index vector of a (token, KV head) = NVFP4 of the mean of the group's query heads; keys as they are
+    rc = sparse_b200_nvfp4_quantize(q, q_codes, q_scales, batch, hkv, hq / hkv, sq, 0, stream);
+    if (rc) return rc;
+    rc = sparse_b200_nvfp4_quantize(k, k_codes, k_scales, batch, hkv, 1, skv, 1, stream);
+    if (rc) return rc;
+  }
+  rc = sparse_b200_indexer_fp4_fast(q_codes, q_scales, k_codes, k_scales, workspace, workspace_bytes, block_idx, batch,
+                                    hkv, hkv, sq, skv, topk, stream);
+  if (rc) return rc;
+  // same stream: the ids written by the indexer are ready for the attention kernel
+  return sparse_b200_q_centric(q, k, v, block_idx, nullptr, out, lse, batch, hq, hkv, sq, skv, topk, stream);
 }
 
 }  // extern "C"

@@ -381,6 +381,9 @@ __global__ void __launch_bounds__(256) row_topk_kernel(const float* __restrict__
   int* scratch_i = reinterpret_cast<int*>(scratch_f + 10);
   const long long row = blockIdx.x;
   bool has_nan = false;
+  // when launched as a programmatic dependent of the scoring kernel: wait for that grid's results
+  // (returns at once in an ordinary launch)
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   for (int t = threadIdx.x; t < tiles; t += blockDim.x) {
     const float v = tile_scores[row * tiles + t];
     scores[t] = v;
@@ -459,7 +462,10 @@ int launch_tile_max_topk(const float* query_scores, int32_t* ids, int batch, int
   return check_launch();
 }
 
-int launch_row_topk(const float* tile_scores, int32_t* ids, long long rows, int tiles, int topk, cudaStream_t stream) {
+// after_scorer: launch as a programmatic dependent of the kernel launched just before on the stream
+// (which must execute griddepcontrol.launch_dependents), so that launch latency and prologue overlap its tail.
+int launch_row_topk(const float* tile_scores, int32_t* ids, long long rows, int tiles, int topk, cudaStream_t stream,
+                    bool after_scorer) {
   DeviceCtx* ctx = device_ctx();
   if (!ctx) return SB_ERR_CUDA;
   if (topk_smem(tiles) > 200 * 1024) return set_error(SB_ERR_INVALID, "too many KV tiles for the top-k stage");
@@ -467,6 +473,20 @@ int launch_row_topk(const float* tile_scores, int32_t* ids, long long rows, int 
     cudaFuncSetAttribute(tile_max_topk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
     cudaFuncSetAttribute(row_topk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
     ctx->misc_attr[5] = 1;
+  }
+  if (after_scorer) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(static_cast<unsigned>(rows));
+    cfg.blockDim = dim3(256);
+    cfg.dynamicSmemBytes = topk_smem(tiles);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, row_topk_kernel, tile_scores, ids, tiles, topk);
+    return e == cudaSuccess ? SB_OK : set_error(SB_ERR_CUDA, cudaGetErrorString(e));
   }
   row_topk_kernel<<<static_cast<unsigned>(rows), 256, topk_smem(tiles), stream>>>(tile_scores, ids, tiles, topk);
   return check_launch();

@@ -1,0 +1,1004 @@
+// Tensor-core path of the NVFP4 indexer on NVFP4 tensor-core MMAs: the same block ids as the
+// exact scorer followed by tile top-k, bit for bit.
+//
+// tcgen05.mma kind::mxf4nvf4.block_scale multiplies the packed e2m1 codes of a key page
+// (M = 128 rows) and of a query tile (N) straight from shared memory, with the ue4m3 scale of every
+// 16-element group read from tensor memory: no dequantised copy exists anywhere. Operands: 64 bytes
+// of codes per row, TMA-loaded with the 64-byte swizzle; K = 64 per instruction, so two
+// instructions cover the 128 features. The scales of a 128-row tile are re-ordered by the producer
+// warp into the 512-byte "32 x (4 row groups x 4 scales)" chunks the instruction reads
+// (byte (r % 32) * 16 + (r / 32) * 4 + j = scale j of row r) and copied to tensor memory with
+// tcgen05.cp.32x128b.warpx4 by the MMA thread. One 128 x 128 accumulator, two key-scale slots and the
+// query scales take 152 tensor-memory columns (256 allocated), so two CTAs share an SM and the
+// epilogue of one runs under the MMAs of the other. (N = 64 halves of the query tile with three
+// accumulators per CTA were measured slower: an M128 N64 K64 instruction takes nearly as long as
+// an N128 one, both being bound by the shared-memory reads of their operands.)
+//
+// Each product and each 16-element group sum is exact; only the accumulation of the eight scaled
+// group sums is done in the tensor core's own order and precision instead of the fixed group order
+// that defines a score. The MMA result is therefore a PRE-FILTER, as in the summary indexer:
+// approximate and exact score differ by at most delta = 2^-18 * min(max_q ||q||_1 * max|k|,
+// max_q ||q||_2 * max_k ||k||_2) (see EPS below; the pruning kernel, which serves small problems, takes
+// max|k| <= 6 x the largest key scale of its pages instead of a pass over the keys); candidates more
+// than 2 delta apart are ordered by their
+// approximate scores for certain, the others are re-scored exactly, a tile whose pre-filter cannot be
+// proven safe is scored exactly in full. Whenever both values of a score are in hand the kernels
+// also CHECK the bound: a difference above delta sends the tile to the exact path and is counted.
+// Same role as Fp4IndexerStagedMmaSm100 + Fp4IndexerScaleReorderSm100 + tile_max_topk16_kernel
+// (indexers/fp4/vendor_minimax_msa/src/sm100/fp4_indexer.py:83-198, 201-1108,
+// indexers/fp4/tile_topk.cu:38-126).
+#include "ptx.cuh"
+#include "internal.h"
+#include "topk.cuh"
+#include "fp4_exact.cuh"
+
+namespace sb {
+namespace fnv {
+
+constexpr int CODE_BYTES = 128 * 64;              // one operand tile: 128 rows of 64 bytes of codes
+constexpr int SF_BYTES = 1024;                    // its scales: two 512-byte chunks (features 0-63, 64-127)
+constexpr int STAGE_BYTES = CODE_BYTES + SF_BYTES;
+constexpr int A_STAGES = 4;
+constexpr int C_MAX = 192;
+constexpr int NUM_THREADS = 320;
+constexpr int TMA_WARP = 8, MMA_WARP = 9;
+// Bound on |tensor-core dot - canonical dot| relative to B = sum_g |t_g| (t_g = scaled group sum, each
+// exact in fp32): eight terms added by the hardware in an unknown order with at worst a truncating
+// 24-bit datapath give <= 8 * 2^-22 * B, the canonical fp32 sum itself is within 7 * 2^-24 * B of the
+// real value: together < 2^-18 * B, and B <= min(||q||_1 * max|k|, ||q||_2 * ||k||_2). Measured on
+// stress inputs the difference stays below 2^-24 * that bound (the tests print the ratio), and the
+// kernels check it on every score they hold twice.
+constexpr float EPS = 3.814697265625e-06f;        // 2^-18
+constexpr int MAX_TILES = 16384;                  // 64 KiB of scores
+constexpr int ACC_STAGES = 1;                     // accumulators of 128 columns (a whole query tile)
+
+constexpr int OFF_A = 0;
+constexpr int OFF_B = A_STAGES * STAGE_BYTES;     // query tile: codes + scales
+constexpr int OFF_CAND = OFF_B + STAGE_BYTES;     // candidate arrays of the selection phase
+constexpr int OFF_SCORES = OFF_CAND + 4 * C_MAX * 4;
+// the selection phase re-uses [0, OFF_CAND) for int8 rows and fp32 scales of a query tile and a key page
+static_assert(2 * 128 * FP4_ROW_WORDS * 4 + 2 * 128 * 8 * 4 <= OFF_CAND, "staging area of the exact scorer does not fit");
+// tensor memory columns
+constexpr int TM_ACC = 0;
+constexpr int TM_SFA = ACC_STAGES * 128;           // 2 slots x 8 columns (two K halves of 4 columns)
+constexpr int TM_SFB = TM_SFA + 16;               // 8 columns
+constexpr int TM_COLS = 256;
+static_assert(TM_SFB + 8 <= TM_COLS, "tensor memory map");
+
+// barrier indices
+enum { A_FULL = 0, A_EMPTY = A_STAGES, B_FULL = 2 * A_STAGES, ACC_FULL = 2 * A_STAGES + 1,
+       ACC_EMPTY = ACC_FULL + ACC_STAGES, NUM_BARS = ACC_EMPTY + ACC_STAGES };
+
+// kind::mxf4nvf4 instruction descriptor: e2m1 A and B (format 1), ue4m3 scales (0), both K-major,
+// dense, K = 64; N >> 3 in bits 17-22, M >> 4 in bits 24-28.
+__host__ __device__ constexpr uint32_t idesc_nvf4(int m, int n) {
+  return (1u << 7) | (1u << 10) | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
+}
+// K-major operand of 64-byte rows, 64-byte swizzle (layout type 4): 8-row atoms 512 bytes apart.
+__device__ __forceinline__ uint64_t desc_sw64_kmajor(uint32_t addr) {
+  return desc_field(addr) | (desc_field(512) << 32) | (1ULL << 46) | (4ULL << 61);
+}
+// one 512-byte scale chunk: 32 rows of 16 bytes, no swizzle, 8-row groups 128 bytes apart
+__device__ __forceinline__ uint64_t desc_scale_chunk(uint32_t addr) {
+  return desc_field(addr) | (desc_field(128) << 32) | (1ULL << 46);
+}
+__device__ __forceinline__ void mma_nvf4(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t sfa, uint32_t sfb,
+                                         uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.block16 [%0], %1, %2, %3, [%5], [%6], p;\n\t"
+      "}" ::"r"(d),
+      "l"(a), "l"(b), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb)
+      : "memory");
+}
+// 32 rows x 16 bytes of shared memory -> 4 tensor-memory columns of lanes 0-31, repeated for the
+// other three lane quarters
+__device__ __forceinline__ void tmem_cp_scales(uint32_t taddr, uint64_t sdesc) {
+  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+}
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%2, %3, %4}], [%5];" ::"r"(dst),
+      "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ int f2ord(float f) {
+  const int i = __float_as_int(f);
+  return i >= 0 ? i : i ^ 0x7fffffff;
+}
+__device__ __forceinline__ float ord2f(int i) { return __int_as_float(i >= 0 ? i : i ^ 0x7fffffff); }
+
+// Largest |dequantised element| and largest squared L2 norm over all key vectors -> stats[0], stats[1]
+// (zeroed by the caller). Sixteen adjacent threads hold one row.
+__global__ void __launch_bounds__(256) key_stats_kernel(const uint8_t* __restrict__ codes, const uint8_t* __restrict__ scales,
+                                                        long long rows, float* __restrict__ stats) {
+  __shared__ float red_m[8], red_n[8];
+  const long long gid = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const long long row = gid >> 4;
+  const int w = static_cast<int>(gid & 15);
+  float amax = 0.f, squares = 0.f;
+  if (row < rows) {
+    const uint32_t word = __ldg(reinterpret_cast<const uint32_t*>(codes + row * 64 + w * 4));
+    const float sc = 0.5f * e4m3_to_float(scales[row * 8 + (w >> 1)] & 0x7fu);
+    const unsigned long long lut = 0x0C08060403020100ULL;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const uint32_t c = (word >> (4 * e)) & 7u;
+      const float f = static_cast<float>((lut >> (8 * c)) & 0xFFu) * sc;
+      amax = fmaxf(amax, f);
+      squares = fmaf(f, f, squares);
+    }
+  }
+#pragma unroll
+  for (int d = 8; d > 0; d >>= 1) squares += __shfl_xor_sync(0xffffffffu, squares, d);   // the row's 16 threads
+#pragma unroll
+  for (int d = 16; d > 0; d >>= 1) {
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, d));
+    squares = fmaxf(squares, __shfl_xor_sync(0xffffffffu, squares, d));
+  }
+  if ((threadIdx.x & 31) == 0) {
+    red_m[threadIdx.x >> 5] = amax;
+    red_n[threadIdx.x >> 5] = squares;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int i = 1; i < 8; ++i) {
+      amax = fmaxf(amax, red_m[i]);
+      squares = fmaxf(squares, red_n[i]);
+    }
+    atomicMax(reinterpret_cast<int*>(stats), __float_as_int(amax));
+    atomicMax(reinterpret_cast<int*>(stats + 1), __float_as_int(squares));
+  }
+}
+
+// Largest byte of eight packed e4m3 scale words (codes 0x00..0x7e grow with the value; the sign bit,
+// which a valid scale does not carry, is masked off).
+__device__ __forceinline__ uint32_t max_scale_bytes(uint32_t acc, uint32_t w) { return __vmaxu4(acc, w & 0x7f7f7f7fu); }
+__device__ __forceinline__ uint32_t top_byte(uint32_t w) {
+  return max(max(w & 0xffu, (w >> 8) & 0xffu), max((w >> 16) & 0xffu, w >> 24));
+}
+// |dequantised element| <= 6 * scale
+__device__ __forceinline__ float key_bound_from_scale_byte(uint32_t byte) {
+  return 6.0f * e4m3_to_float(static_cast<uint8_t>(byte)) * 1.0001f;
+}
+
+// The eight scales of rows lane, lane + 32, lane + 64, lane + 96 of a 128-row tile (row pitch in bytes).
+struct ScaleRegs { uint2 r[4]; };
+__device__ __forceinline__ ScaleRegs load_scales(const uint8_t* base, long long pitch, int lane) {
+  ScaleRegs s;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) s.r[i] = __ldg(reinterpret_cast<const uint2*>(base + (lane + 32 * i) * pitch));
+  return s;
+}
+// ... written as the two 512-byte chunks the MMA reads: one 16-byte store per lane and chunk.
+__device__ __forceinline__ void store_scale_chunks(unsigned char* dst, const ScaleRegs& s, int lane) {
+  *reinterpret_cast<uint4*>(dst + lane * 16) = make_uint4(s.r[0].x, s.r[1].x, s.r[2].x, s.r[3].x);
+  *reinterpret_cast<uint4*>(dst + 512 + lane * 16) = make_uint4(s.r[0].y, s.r[1].y, s.r[2].y, s.r[3].y);
+}
+
+// Problem geometry shared by the two kernels.
+struct Geometry {
+  const uint8_t *qp, *qs, *kp, *ks;   // public NVFP4 layout (codes, e4m3 scales)
+  int batch, hidx, hk, len_q, tiles;
+};
+
+// ---------------------------------------------------------------- producer and MMA roles
+// Producer warp: query tile once, then key pages page0 + (t + rot) % wrap for t = 0 .. num_tiles - 1.
+__device__ __forceinline__ void producer_role(const Geometry& g, const CUtensorMap* q_map, const CUtensorMap* k_map,
+                                              uint32_t base, unsigned char* gbase, uint32_t bar0, const Guard& guard,
+                                              int b, int h, int hk_idx, long long q_row0, int page0, int num_tiles,
+                                              int rot, int wrap, int lane, int code0, volatile int* key_scale_max) {
+  auto bar = [&](int i) { return bar0 + 8u * i; };
+  auto page_of = [&](int t) { return page0 + (t + rot) % wrap; };
+  auto key_row = [&](int pg) { return ((static_cast<long long>(b) * g.tiles + pg) * g.hk + hk_idx) * 128; };
+  if (lane == 0) {
+    mbar_expect_tx(bar(B_FULL), CODE_BYTES);
+    tma_load_3d(base + OFF_B, q_map, 0, h, static_cast<int>(q_row0), bar(B_FULL));
+  }
+  {
+    const ScaleRegs s = load_scales(g.qs + (q_row0 * g.hidx + h) * 8, static_cast<long long>(g.hidx) * 8, lane);
+    store_scale_chunks(gbase + OFF_B + CODE_BYTES, s, lane);
+    fence_async_smem();
+    __syncwarp();
+    if (lane == 0) mbar_arrive(bar(B_FULL));
+  }
+  // The scales of a page come through registers: requested three pages ahead, so that the producer
+  // never waits a full global-memory latency per page.
+  bool ok = true;
+  uint32_t seen = 0;                 // bytewise maximum of the key scales that went through this warp
+  ScaleRegs ahead[3];
+#pragma unroll
+  for (int i = 0; i < 3; ++i)
+    if (i < num_tiles) ahead[i] = load_scales(g.ks + key_row(page_of(i)) * 8, 8, lane);
+  auto step = [&](int t, ScaleRegs& regs) -> bool {
+    const int s = t % A_STAGES, use = t / A_STAGES;
+    if (use > 0) {
+      bool w = mbar_wait(bar(A_EMPTY + s), (use - 1) & 1, guard, code0 + s);
+      if (!__all_sync(0xffffffffu, w)) return false;
+    }
+    if (lane == 0) {
+      mbar_expect_tx(bar(A_FULL + s), CODE_BYTES);
+      tma_load_2d(base + OFF_A + s * STAGE_BYTES, k_map, 0, static_cast<int>(key_row(page_of(t))), bar(A_FULL + s));
+    }
+    store_scale_chunks(gbase + OFF_A + s * STAGE_BYTES + CODE_BYTES, regs, lane);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) seen = max_scale_bytes(max_scale_bytes(seen, regs.r[i].x), regs.r[i].y);
+    if (t + 3 < num_tiles) regs = load_scales(g.ks + key_row(page_of(t + 3)) * 8, 8, lane);
+    fence_async_smem();
+    __syncwarp();
+    if (lane == 0) mbar_arrive(bar(A_FULL + s));
+    return true;
+  };
+  for (int t = 0; ok && t < num_tiles; t += 3) {
+    ok = step(t, ahead[0]);
+    if (ok && t + 1 < num_tiles) ok = step(t + 1, ahead[1]);
+    if (ok && t + 2 < num_tiles) ok = step(t + 2, ahead[2]);
+  }
+  if (key_scale_max) {
+    uint32_t m = top_byte(seen);
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) m = max(m, __shfl_xor_sync(0xffffffffu, m, d));
+    if (lane == 0) *key_scale_max = static_cast<int>(m);
+  }
+  if (!ok)
+    for (int t = max(0, num_tiles - A_STAGES); t < num_tiles; ++t)
+      mbar_wait_drain(bar(A_FULL + t % A_STAGES), (t / A_STAGES) & 1);
+}
+
+// MMA thread: page t against the whole query tile into accumulator t % ACC_STAGES. The key scales of
+// page t go to slot t & 1, copied as soon as the page has landed: the slot was last read by the MMAs of
+// page t - 2, which had completed (their accumulator had been read out and released) before the MMAs
+// of page t - 1 were issued; this holds for one or two accumulators.
+static_assert(ACC_STAGES <= 2, "the two key-scale slots are protected by the accumulator hand-over only up to two accumulators");
+__device__ __forceinline__ void mma_role(uint32_t base, uint32_t bar0, uint32_t tmem, const Guard& guard, int num_tiles,
+                                         int code0) {
+  auto bar = [&](int i) { return bar0 + 8u * i; };
+  constexpr uint32_t IDESC = idesc_nvf4(128, 128);
+  if (!mbar_wait(bar(B_FULL), 0, guard, code0)) return;
+  tc_fence_after();
+  tmem_cp_scales(tmem + TM_SFB, desc_scale_chunk(base + OFF_B + CODE_BYTES));
+  tmem_cp_scales(tmem + TM_SFB + 4, desc_scale_chunk(base + OFF_B + CODE_BYTES + 512));
+  const uint64_t b0 = desc_sw64_kmajor(base + OFF_B);
+  for (int t = 0; t < num_tiles; ++t) {
+    const int s = t % A_STAGES, st = t % ACC_STAGES;
+    if (!mbar_wait(bar(A_FULL + s), (t / A_STAGES) & 1, guard, code0 + 1 + s)) return;
+    tc_fence_after();
+    // the scale copy does not touch the accumulator: it goes out before the accumulator hand-over is awaited
+    const uint64_t a0 = desc_sw64_kmajor(base + OFF_A + s * STAGE_BYTES);
+    const uint32_t sfa = tmem + TM_SFA + (t & 1) * 8;
+    tmem_cp_scales(sfa, desc_scale_chunk(base + OFF_A + s * STAGE_BYTES + CODE_BYTES));
+    tmem_cp_scales(sfa + 4, desc_scale_chunk(base + OFF_A + s * STAGE_BYTES + CODE_BYTES + 512));
+    if (t >= ACC_STAGES) {
+      if (!mbar_wait(bar(ACC_EMPTY + st), ((t / ACC_STAGES) - 1) & 1, guard, code0 + 8 + st)) return;
+      tc_fence_after();
+    }
+    // second K = 64: 32 bytes further along every row, its scales in the next four columns
+#pragma unroll
+    for (int kh = 0; kh < 2; ++kh)
+      mma_nvf4(tmem + TM_ACC + st * 128, a0 + kh * 2, b0 + kh * 2, IDESC, sfa + kh * 4, tmem + TM_SFB + kh * 4, kh);
+    tc_commit(bar(ACC_FULL + st));
+    tc_commit(bar(A_EMPTY + s));
+  }
+}
+
+// L1 norm and squared L2 norm (both rounded up a little) of dequantised query row `row` of the tile.
+__device__ __forceinline__ void query_row_norms(const Geometry& g, long long q_row0, int h, int row, float& l1, float& l2) {
+  const long long r = (q_row0 + row) * g.hidx + h;
+  const uint4* codes = reinterpret_cast<const uint4*>(g.qp + r * 64);
+  const uint2 sc = __ldg(reinterpret_cast<const uint2*>(g.qs + r * 8));
+  const unsigned long long lut = 0x0C08060403020100ULL;
+  l1 = 0.f;
+  l2 = 0.f;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const uint4 v = __ldg(codes + i);
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int gq = 0; gq < 2; ++gq) {
+      const int grp = i * 2 + gq;
+      const float unit = 0.5f * e4m3_to_float(static_cast<uint8_t>(((grp < 4 ? sc.x : sc.y) >> (8 * (grp & 3))) & 0x7fu));
+      int sum = 0, squares = 0;
+#pragma unroll
+      for (int ww = 0; ww < 2; ++ww)
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const int m = static_cast<int>((lut >> (8 * ((w[gq * 2 + ww] >> (4 * e)) & 7u))) & 0xFFu);
+          sum += m;
+          squares += m * m;
+        }
+      l1 += static_cast<float>(sum) * unit;
+      l2 += static_cast<float>(squares) * unit * unit;
+    }
+  }
+  l1 *= 1.0001f;
+  l2 *= 1.0001f;
+}
+
+struct Params {
+  Geometry g;
+  int* stats;                         // [0] CTAs run (counter), [1] tiles scored exactly in full, [3] bound violations,
+                                      // [4] largest observed |approximate - exact| / delta (float bits); all cumulative
+  const float* key_stats;             // [0] largest |key element|, [1] largest squared key norm (key_stats_kernel)
+  int32_t* ids;                       // [B, Hidx, Qt, topk]
+  int* status;
+  int* fallbacks;                     // tiles scored exactly in full
+  int* violations;                    // re-scored candidates whose two scores differed by more than delta
+  int topk, cand;
+};
+
+// One CTA per (batch, index head, query tile), two CTAs per SM (the exact re-scoring of one
+// overlaps the tensor-core scoring of the other): approximate tile scores of every key
+// page on the tensor cores, then candidate selection and exact re-scoring.
+// Warps 0-7 epilogue (lane quarter = warp & 3, query half = warp >> 2), warp 8 producer,
+// warp 9 MMA issue (one thread).
+__global__ void __launch_bounds__(NUM_THREADS, 2)
+fp4_nv_select_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map, const Params p) {
+  extern __shared__ unsigned char smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  unsigned char* gbase = smem_raw + (base - raw);
+  const Geometry& g = p.g;
+  int* scores = reinterpret_cast<int*>(gbase + OFF_SCORES);
+  const int score_bytes = (g.tiles * 4 + 15) & ~15;
+  unsigned char* aux = gbase + OFF_SCORES + score_bytes;
+  const uint32_t bar0 = base + OFF_SCORES + score_bytes;
+  volatile int* misc = reinterpret_cast<volatile int*>(aux + 128);   // tmem base, abort, unsafe, l1q bits, l2q bits, k-th bound
+  float* scratch_f = reinterpret_cast<float*>(aux + 192);            // [16]
+  int* scratch_i = reinterpret_cast<int*>(aux + 256);                // [16]
+  auto bar = [&](int i) { return bar0 + 8u * i; };
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int qt = g.len_q >> 7;
+  const int qtile = blockIdx.x % qt;
+  const int bh = blockIdx.x / qt;
+  const int h = bh % g.hidx, b = bh / g.hidx;
+  const int hk_idx = g.hk > 1 ? h : 0;
+  const long long q_row0 = static_cast<long long>(b) * g.len_q + static_cast<long long>(qtile) * 128;
+  const int num_tiles = g.tiles;
+  const int rot = static_cast<int>((static_cast<unsigned>(qtile) * 37u) % static_cast<unsigned>(num_tiles));
+  Guard guard{misc + 1, p.status};
+
+  if (threadIdx.x == 0) {
+    misc[1] = 0;
+    for (int i = 0; i < A_STAGES; ++i) {
+      mbar_init(bar(A_FULL + i), 2);      // the TMA transaction of the codes + the producer warp's scale stores
+      mbar_init(bar(A_EMPTY + i), 1);
+    }
+    for (int i = 0; i < ACC_STAGES; ++i) {
+      mbar_init(bar(ACC_FULL + i), 1);
+      mbar_init(bar(ACC_EMPTY + i), 8);
+    }
+    mbar_init(bar(B_FULL), 2);
+    fence_mbar_init();
+  }
+  if (warp == MMA_WARP) {
+    tmem_alloc(smem_u32(const_cast<int*>(misc)), TM_COLS);
+    tmem_relinquish();
+  }
+  for (int j = threadIdx.x; j < g.tiles; j += NUM_THREADS) scores[j] = static_cast<int>(0x80000000u);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = static_cast<uint32_t>(misc[0]);
+
+  if (warp == TMA_WARP) {
+    producer_role(g, &q_map, &k_map, base, gbase, bar0, guard, b, h, hk_idx, q_row0, 0, num_tiles, rot, num_tiles, lane,
+                  0x500, nullptr);
+  } else if (warp == MMA_WARP) {
+    if (lane == 0) mma_role(base, bar0, tmem, guard, num_tiles, 0x510);
+    __syncwarp();
+  } else {
+    // epilogue: thread = key row of the page, this warp's 64-query half of the tile
+    const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const int half = warp >> 2;
+    bool ok = true;
+    for (int t = 0; ok && t < num_tiles; ++t) {
+      const int st = t % ACC_STAGES;
+      bool w = mbar_wait(bar(ACC_FULL + st), (t / ACC_STAGES) & 1, guard, 0x540 + st);
+      ok = __all_sync(0xffffffffu, w);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t t_acc = tmem + lane_base + TM_ACC + st * 128 + half * 64;
+      uint32_t v[4][16];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tmem_ld16(t_acc + c * 16, v[c]);
+      tc_wait_ld();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(ACC_EMPTY + st));
+      float m4[4];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        float m5[5];
+#pragma unroll
+        for (int jj = 0; jj < 5; ++jj)
+          m5[jj] = max3(__uint_as_float(v[c][3 * jj]), __uint_as_float(v[c][3 * jj + 1]), __uint_as_float(v[c][3 * jj + 2]));
+        m4[c] = fmaxf(max3(m5[0], m5[1], m5[2]), max3(m5[3], m5[4], __uint_as_float(v[c][15])));
+      }
+      float m = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+#pragma unroll
+      for (int d = 16; d > 0; d >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, d));
+      if (lane == 0) atomicMax(&scores[(t + rot) % num_tiles], f2ord(m));
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == MMA_WARP) {
+    tc_fence_after();
+    tmem_dealloc(tmem, TM_COLS);
+  }
+  if (misc[1]) return;
+
+  // ------------------------------------------------------------- selection
+  uint32_t* q_i8 = reinterpret_cast<uint32_t*>(gbase + OFF_A);
+  uint32_t* k_i8 = q_i8 + 128 * FP4_ROW_WORDS;
+  float* q_sc = reinterpret_cast<float*>(k_i8 + 128 * FP4_ROW_WORDS);
+  float* k_sc = q_sc + 128 * 8;
+  int32_t* cand_ids = reinterpret_cast<int32_t*>(gbase + OFF_CAND);
+  int* cand_ex = reinterpret_cast<int*>(cand_ids + C_MAX);
+  float* cand_apx = reinterpret_cast<float*>(cand_ex + C_MAX);     // approximate tile scores of the candidates
+  int* near_s = reinterpret_cast<int*>(cand_apx + C_MAX);          // candidate needs its exact score
+  const int C = p.cand;
+
+  int32_t* out = p.ids + (static_cast<long long>(bh) * qt + qtile) * p.topk;
+
+  fp4_stage_rows(q_i8, q_sc, g.qp + (q_row0 * g.hidx + h) * 64, static_cast<long long>(g.hidx) * 64,
+                 g.qs + (q_row0 * g.hidx + h) * 8, static_cast<long long>(g.hidx) * 8, 0.25f);
+  if (threadIdx.x == 0) { misc[2] = 0; misc[3] = 0; misc[4] = 0; misc[5] = __float_as_int(-INFINITY); atomicAdd(p.stats, 1); }
+  for (int c = threadIdx.x; c < C_MAX; c += NUM_THREADS) cand_ex[c] = static_cast<int>(0x80000000u);
+  __syncthreads();
+  if (threadIdx.x < 128) {
+    float l1, l2;
+    query_row_norms(g, q_row0, h, threadIdx.x, l1, l2);
+    atomicMax(const_cast<int*>(misc + 3), __float_as_int(l1));
+    atomicMax(const_cast<int*>(misc + 4), __float_as_int(l2));
+  }
+  float thr = 0.f;
+  if (warp == 0) {
+    // C-th largest approximate score and the candidate set (ties at the threshold in index order)
+    const unsigned* keys = reinterpret_cast<const unsigned*>(scores);
+    const unsigned lt_mask = (1u << lane) - 1u;
+    unsigned T = 0;
+    for (int bit = 31; bit >= 0; --bit) {
+      const unsigned trial = T | (1u << bit);
+      int cnt = 0;
+      for (int j = lane; j < g.tiles; j += 32) cnt += ((keys[j] ^ 0x80000000u) >= trial) ? 1 : 0;
+#pragma unroll
+      for (int d = 16; d > 0; d >>= 1) cnt += __shfl_xor_sync(0xffffffffu, cnt, d);
+      if (cnt >= C) T = trial;
+    }
+    int n_gt = 0;
+    for (int j = lane; j < g.tiles; j += 32) n_gt += ((keys[j] ^ 0x80000000u) > T) ? 1 : 0;
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) n_gt += __shfl_xor_sync(0xffffffffu, n_gt, d);
+    const int need_eq = C - n_gt;
+    int out_run = 0, eq_run = 0;
+    for (int base_j = 0; base_j < g.tiles; base_j += 32) {
+      const int j = base_j + lane;
+      const unsigned u = j < g.tiles ? (keys[j] ^ 0x80000000u) : 0u;
+      const bool is_gt = j < g.tiles && u > T;
+      const bool is_eq = j < g.tiles && u == T;
+      const unsigned eq_ballot = __ballot_sync(0xffffffffu, is_eq);
+      const bool take = is_gt || (is_eq && eq_run + __popc(eq_ballot & lt_mask) < need_eq);
+      const unsigned take_ballot = __ballot_sync(0xffffffffu, take);
+      if (take) {
+        const int pos = out_run + __popc(take_ballot & lt_mask);
+        cand_ids[pos] = j;
+        cand_apx[pos] = ord2f(static_cast<int>(u ^ 0x80000000u));
+      }
+      out_run += __popc(take_ballot);
+      eq_run += __popc(eq_ballot);
+    }
+    thr = ord2f(static_cast<int>(T ^ 0x80000000u));
+  }
+  __syncthreads();
+  // exact tile score of one page: max over the 128 x 128 dots, whole CTA
+  auto exact_page = [&](int pg) -> float {
+    const long long page = (static_cast<long long>(b) * g.tiles + pg) * g.hk + hk_idx;
+    fp4_stage_rows(k_i8, k_sc, g.kp + page * 128 * 64, 64, g.ks + page * 128 * 8, 8, 1.0f);
+    __syncthreads();
+    float m = -INFINITY;
+    if (threadIdx.x < 256) m = fp4_block_max_mma(q_i8, q_sc, k_i8, k_sc, warp, lane);
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, d));
+    return m;                              // per-warp maximum; lane 0 publishes it
+  };
+  // Approximate and exact tile score differ by at most delta (the sum of |q_d k_d| bounded by
+  // Hoelder and by Cauchy-Schwarz), so candidates more than 2 delta apart are ordered by their
+  // approximate scores for certain: only a candidate with another one within 2 delta is re-scored.
+  const float delta = EPS * fminf(__int_as_float(misc[3]) * p.key_stats[0],
+                                  sqrtf(__int_as_float(misc[4])) * sqrtf(p.key_stats[1] * 1.0001f));
+  const float two = 2.f * delta;
+  for (int c = threadIdx.x; c < C; c += NUM_THREADS) {
+    const float a = cand_apx[c];
+    int near = 0;
+#pragma unroll 4
+    for (int j = 0; j < C; ++j) near |= static_cast<int>(j != c) & static_cast<int>(!(fabsf(a - cand_apx[j]) > two));
+    near_s[c] = near;
+  }
+  __syncthreads();
+  for (int c = 0; c < C; ++c) {
+    if (!near_s[c]) continue;
+    const float m = exact_page(cand_ids[c]);
+    if (lane == 0) atomicMax(&cand_ex[c], f2ord(m));
+    __syncthreads();
+  }
+  // The bound checks itself: both scores of a re-scored candidate are in hand. A difference above
+  // delta (the tensor core did not behave as assumed) sends the tile to the exact path below.
+  for (int c = threadIdx.x; c < C; c += NUM_THREADS)
+    if (near_s[c]) {
+      const float diff = fabsf(cand_apx[c] - ord2f(cand_ex[c]));
+      if (delta > 0.f) atomicMax(p.stats + 4, __float_as_int(diff / delta));
+      if (!(diff <= delta)) {
+        misc[2] = 1;
+        atomicAdd(p.violations, 1);
+      }
+    }
+  // rank of a candidate = number of candidates that beat it in (exact score descending, page
+  // ascending): by the approximate scores when more than 2 delta apart, else by the exact ones
+  for (int c = threadIdx.x; c < C; c += NUM_THREADS) {
+    const float a = cand_apx[c], e = ord2f(cand_ex[c]);
+    const int id = cand_ids[c];
+    int rank = 0;
+#pragma unroll 4
+    for (int j = 0; j < C; ++j) {
+      const float d = cand_apx[j] - a, ej = ord2f(cand_ex[j]);
+      const int gt = static_cast<int>(d > two), lt = static_cast<int>(d < -two);
+      const int exact = static_cast<int>(ej > e) | (static_cast<int>(ej == e) & static_cast<int>(cand_ids[j] < id));
+      rank += gt | (((gt | lt) ^ 1) & exact);
+    }
+    if (rank < p.topk) out[rank] = id;
+    if (rank == p.topk - 1) misc[5] = __float_as_int(near_s[c] ? e : a - delta);   // lower bound of the k-th exact score
+  }
+  __syncthreads();
+  if (threadIdx.x == 0 && !misc[2]) misc[2] = ((C >= g.tiles) || (__int_as_float(misc[5]) > thr + delta)) ? 0 : 1;
+  __syncthreads();
+  if (misc[2]) {
+    float* row = reinterpret_cast<float*>(scores);
+    for (int pg = 0; pg < g.tiles; ++pg) {
+      const float m = exact_page(pg);
+      if (lane == 0) scratch_f[warp] = m;
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        float mm = scratch_f[0];
+        for (int w = 1; w < NUM_THREADS / 32; ++w) mm = fmaxf(mm, scratch_f[w]);
+        row[pg] = mm;
+      }
+      __syncthreads();
+    }
+    block_topk(row, g.tiles, p.topk, out, scratch_f, scratch_i);
+    if (threadIdx.x == 0 && p.fallbacks) atomicAdd(p.fallbacks, 1);
+  }
+}
+
+// ---------------------------------------------------------------- exact tile scores by pruning
+// The exact score of a (query tile, key page) pair is the maximum of 128 x 128 exact dots. The
+// tensor cores give every dot within delta of its exact value, so only the elements whose
+// approximate value reaches (largest approximate value - 2 delta) can hold the exact maximum:
+// any other element is below the exact value of the approximate arg-max. Those few elements
+// (usually one) are evaluated with the canonical arithmetic (integer group sums, scaled and
+// added in group order) straight from the codes in global memory. Same scores, bit for bit,
+// as fp4_score_mma_kernel, which evaluates all 16384 elements of a pair exactly. Every
+// evaluated element is also compared with its approximate value: a difference above delta is
+// counted and the pair is re-done by evaluating all of its elements.
+struct PruneParams {
+  Geometry g;
+  int* stats;                         // as in Params
+  float* tile_scores;                 // [B, Hidx, Qt, tiles]
+  int* status;
+  int* violations;
+  int pages_per_cta, chunks;
+};
+
+// Integer dot of one 16-element scale group straight from the e2m1 codes (two words per row):
+// magnitudes 2 |value| through a byte-permute table, the sign of each product from the xor of
+// the code sign bits, products of either sign summed apart with dp4a.
+__device__ __forceinline__ int fp4_group_sum(uint32_t q0, uint32_t q1, uint32_t k0, uint32_t k1) {
+  constexpr uint32_t LUT_LO = 0x03020100u, LUT_HI = 0x0C080604u;      // 2 |value| of codes 0..7
+  int pos = 0, neg = 0;
+#pragma unroll
+  for (int w = 0; w < 2; ++w) {
+    const uint32_t wq = w ? q1 : q0, wk = w ? k1 : k0;
+    const uint32_t sg = ((wq ^ wk) >> 3) & 0x11111111u;               // 1 where the product is negative
+#pragma unroll
+    for (int hh = 0; hh < 2; ++hh) {
+      const uint32_t mq = __byte_perm(LUT_LO, LUT_HI, (wq >> (16 * hh)) & 0x7777u);
+      const uint32_t mk = __byte_perm(LUT_LO, LUT_HI, (wk >> (16 * hh)) & 0x7777u);
+      const uint32_t ng = __byte_perm(0x0000FF00u, 0u, (sg >> (16 * hh)) & 0x1111u);
+      pos = __dp4a(static_cast<int>(mq & ~ng), static_cast<int>(mk), pos);
+      neg = __dp4a(static_cast<int>(mq & ng), static_cast<int>(mk), neg);
+    }
+  }
+  return pos - neg;
+}
+
+// canonical dot of a query row and a key row (16 code words and 8 e4m3 scales each); everything
+// is requested from memory before the first use
+__device__ __forceinline__ float fp4_exact_dot(const uint8_t* __restrict__ q_codes, const uint8_t* __restrict__ q_scales,
+                                               const uint8_t* __restrict__ k_codes, const uint8_t* __restrict__ k_scales) {
+  uint4 qw[4], kw[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    qw[i] = __ldg(reinterpret_cast<const uint4*>(q_codes) + i);
+    kw[i] = __ldg(reinterpret_cast<const uint4*>(k_codes) + i);
+  }
+  const uint2 qs8 = __ldg(reinterpret_cast<const uint2*>(q_scales));
+  const uint2 ks8 = __ldg(reinterpret_cast<const uint2*>(k_scales));
+  const uint32_t* q32 = reinterpret_cast<const uint32_t*>(qw);
+  const uint32_t* k32 = reinterpret_cast<const uint32_t*>(kw);
+  float acc = 0.f;
+#pragma unroll
+  for (int gq = 0; gq < 8; ++gq) {
+    const int sum = fp4_group_sum(q32[2 * gq], q32[2 * gq + 1], k32[2 * gq], k32[2 * gq + 1]);
+    const uint8_t qb = static_cast<uint8_t>(((gq < 4 ? qs8.x : qs8.y) >> (8 * (gq & 3))) & 0xFFu);
+    const uint8_t kb = static_cast<uint8_t>(((gq < 4 ? ks8.x : ks8.y) >> (8 * (gq & 3))) & 0xFFu);
+    const float c = (0.25f * e4m3_to_float(qb)) * e4m3_to_float(kb);
+    acc = fmaf(static_cast<float>(sum), c, acc);
+  }
+  return acc;
+}
+
+constexpr int PR_QCAP = 2048;                // queued elements per CTA
+constexpr int PR_OFF_AUX = OFF_CAND;         // barriers (128 bytes), misc (128 bytes)
+constexpr int PR_OFF_QUEUE = PR_OFF_AUX + 256;            // [PR_QCAP] elements waiting for their exact value
+constexpr int PR_OFF_APX = PR_OFF_QUEUE + PR_QCAP * 4;     // [PR_QCAP] their approximate values
+constexpr int PR_OFF_RES = PR_OFF_APX + PR_QCAP * 4;       // [pages per CTA] exact maxima as ordered ints
+                                                           // then [pages per CTA] flags: pair to be re-done in full
+
+// One CTA per (batch, index head, query tile, chunk of key pages), two CTAs per SM. Warps 0-7 epilogue (lane
+// quarter = warp & 3, query half = warp >> 2), warp 8 producer, warp 9 MMA issue. The epilogue
+// warps meet twice per page at a named barrier (largest approximate value of the page, then
+// largest exact value of the surviving elements); a warp whose bounded wait gave up keeps
+// taking part in those meetings, so nobody is left waiting for it.
+__global__ void __launch_bounds__(NUM_THREADS, 2)
+fp4_nv_prune_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
+                    const PruneParams p) {
+  extern __shared__ unsigned char smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  unsigned char* gbase = smem_raw + (base - raw);
+  const Geometry& g = p.g;
+  unsigned char* aux = gbase + PR_OFF_AUX;
+  const uint32_t bar0 = base + PR_OFF_AUX;
+  // tmem base, abort flag, L1 bits, largest key scale byte, largest approximate value of a page [3 slots], queue length
+  volatile int* misc = reinterpret_cast<volatile int*>(aux + 128);
+  int* queue = reinterpret_cast<int*>(gbase + PR_OFF_QUEUE);
+  float* queue_apx = reinterpret_cast<float*>(gbase + PR_OFF_APX);
+  int* res = reinterpret_cast<int*>(gbase + PR_OFF_RES);
+  int* redo = res + p.pages_per_cta;
+  auto bar = [&](int i) { return bar0 + 8u * i; };
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int qt = g.len_q >> 7;
+  const int chunk = blockIdx.x % p.chunks;
+  const int list = blockIdx.x / p.chunks;            // (batch * Hidx + head) * Qt + query tile
+  const int qtile = list % qt;
+  const int bh = list / qt;
+  const int h = bh % g.hidx, b = bh / g.hidx;
+  const int hk_idx = g.hk > 1 ? h : 0;
+  const long long q_row0 = static_cast<long long>(b) * g.len_q + static_cast<long long>(qtile) * 128;
+  const int page0 = chunk * p.pages_per_cta;
+  const int num_tiles = min(p.pages_per_cta, g.tiles - page0);
+  Guard guard{misc + 1, p.status};
+  // The top-k kernel that follows is launched as a programmatic dependent: its CTAs may be placed as
+  // soon as resources free up; they wait for this whole grid (griddepcontrol.wait) before reading scores.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
+  if (threadIdx.x == 0) {
+    misc[1] = 0;
+    misc[2] = 0;
+    misc[3] = 0;
+    for (int i = 4; i < 7; ++i) misc[i] = INT_MIN;
+    misc[7] = 0;
+    for (int i = 0; i < A_STAGES; ++i) {
+      mbar_init(bar(A_FULL + i), 2);
+      mbar_init(bar(A_EMPTY + i), 1);
+    }
+    for (int i = 0; i < ACC_STAGES; ++i) {
+      mbar_init(bar(ACC_FULL + i), 1);
+      mbar_init(bar(ACC_EMPTY + i), 8);
+    }
+    mbar_init(bar(B_FULL), 2);
+    fence_mbar_init();
+  }
+  if (warp == MMA_WARP) {
+    tmem_alloc(smem_u32(const_cast<int*>(misc)), TM_COLS);
+    tmem_relinquish();
+  }
+  for (int t = threadIdx.x; t < num_tiles; t += NUM_THREADS) {
+    res[t] = INT_MIN;
+    redo[t] = 0;
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = static_cast<uint32_t>(misc[0]);
+
+  if (warp == TMA_WARP) {
+    producer_role(g, &q_map, &k_map, base, gbase, bar0, guard, b, h, hk_idx, q_row0, page0, num_tiles, 0, num_tiles, lane,
+                  0x580, nullptr);
+  } else if (warp == MMA_WARP) {
+    if (lane == 0) mma_role(base, bar0, tmem, guard, num_tiles, 0x590);
+    __syncwarp();
+  } else {
+    // epilogue: thread = key row of the page, this warp's 64-query half of the tile
+    auto meet = [&]() { asm volatile("bar.sync 1, 256;" ::: "memory"); };
+    if (threadIdx.x == 0) atomicAdd(p.stats, 1);
+    if (threadIdx.x < 128) {
+      float l1, l2;
+      query_row_norms(g, q_row0, h, threadIdx.x, l1, l2);
+      atomicMax(const_cast<int*>(misc + 2), __float_as_int(l1));
+    }
+    {
+      // largest scale among this CTA's key pages: 64 threads per page, 16 bytes each
+      uint32_t seen = 0;
+      for (int t = threadIdx.x >> 6; t < num_tiles; t += 4) {
+        const long long page = (static_cast<long long>(b) * g.tiles + page0 + t) * g.hk + hk_idx;
+        const uint4 w = __ldg(reinterpret_cast<const uint4*>(g.ks + page * 1024) + (threadIdx.x & 63));
+        seen = max_scale_bytes(max_scale_bytes(max_scale_bytes(max_scale_bytes(seen, w.x), w.y), w.z), w.w);
+      }
+      uint32_t m = top_byte(seen);
+#pragma unroll
+      for (int d = 16; d > 0; d >>= 1) m = max(m, __shfl_xor_sync(0xffffffffu, m, d));
+      if (lane == 0) atomicMax(const_cast<int*>(misc + 3), static_cast<int>(m));
+    }
+    meet();
+    const float delta = EPS * __int_as_float(misc[2]) * key_bound_from_scale_byte(static_cast<uint32_t>(misc[3]));
+    const float two = 2.f * delta;
+    const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const int half = warp >> 2;
+    const int key_row = (warp & 3) * 32 + lane;
+    // exact value of element (page t of this CTA, key row, query column) into the page's maximum
+    auto evaluate = [&](int t, int krow, int col, float apx) {
+      const long long page = (static_cast<long long>(b) * g.tiles + page0 + t) * g.hk + hk_idx;
+      const long long qrow = (q_row0 + col) * g.hidx + h;
+      const float e = fp4_exact_dot(g.qp + qrow * 64, g.qs + qrow * 8, g.kp + (page * 128 + krow) * 64,
+                                    g.ks + (page * 128 + krow) * 8);
+      if (e == e) atomicMax(res + t, f2ord(e));
+      const float diff = fabsf(apx - e);
+      if (delta > 0.f) atomicMax(p.stats + 4, __float_as_int(diff / delta));
+      if (!(diff <= delta) && e == e) {
+        redo[t] = 1;
+        atomicAdd(p.violations, 1);
+      }
+    };
+    bool ok = true;
+    for (int t = 0; t < num_tiles; ++t) {
+      const int st = t % ACC_STAGES, slot = 4 + t % 3;
+      if (ok) {
+        bool w = mbar_wait(bar(ACC_FULL + st), (t / ACC_STAGES) & 1, guard, 0x5c0 + st);
+        ok = __all_sync(0xffffffffu, w);
+      }
+      uint32_t v[4][16];
+      float mine = -INFINITY;
+      if (ok) {
+        tc_fence_after();
+        const uint32_t t_acc = tmem + lane_base + TM_ACC + st * 128 + half * 64;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) tmem_ld16(t_acc + c * 16, v[c]);
+        tc_wait_ld();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(ACC_EMPTY + st));
+        float m4[4];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          float m5[5];
+#pragma unroll
+          for (int jj = 0; jj < 5; ++jj)
+            m5[jj] = max3(__uint_as_float(v[c][3 * jj]), __uint_as_float(v[c][3 * jj + 1]), __uint_as_float(v[c][3 * jj + 2]));
+          m4[c] = fmaxf(max3(m5[0], m5[1], m5[2]), max3(m5[3], m5[4], __uint_as_float(v[c][15])));
+        }
+        mine = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+        float m = mine;
+#pragma unroll
+        for (int d = 16; d > 0; d >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, d));
+        if (lane == 0) atomicMax(const_cast<int*>(misc + slot), f2ord(m));
+      }
+      meet();
+      // the slot of the page before is free now (everyone read it before this meeting); it is
+      // next written for page t + 2, after the meeting of page t + 1
+      if (threadIdx.x == 0 && t > 0) misc[4 + (t - 1) % 3] = INT_MIN;
+      if (ok) {
+        const float thr = ord2f(misc[slot]) - two;
+        if (!(mine < thr)) {                 // this key row holds at least one element that may be the maximum
+          unsigned long long mask = 0ull;
+#pragma unroll
+          for (int c = 0; c < 4; ++c)
+#pragma unroll
+            for (int jj = 0; jj < 16; ++jj)
+              if (!(__uint_as_float(v[c][jj]) < thr)) mask |= 1ull << (c * 16 + jj);
+          while (mask) {
+            const int bit = __ffsll(static_cast<long long>(mask)) - 1;
+            mask &= mask - 1;
+            const int col = half * 64 + bit;
+            float apx = 0.f;                 // v[bit / 16][bit % 16] without a dynamically indexed register array
+#pragma unroll
+            for (int c = 0; c < 4; ++c)
+#pragma unroll
+              for (int jj = 0; jj < 16; ++jj)
+                if (c * 16 + jj == bit) apx = __uint_as_float(v[c][jj]);
+            const int at = atomicAdd(const_cast<int*>(misc + 7), 1);
+            if (at < PR_QCAP) {
+              queue[at] = (t << 14) | (key_row << 7) | col;
+              queue_apx[at] = apx;
+            } else {
+              evaluate(t, key_row, col, apx);  // queue full (masses of ties): pay for it here
+            }
+          }
+        }
+      }
+    }
+    meet();
+    // the queued elements, one per thread at a time, then the scores of this CTA's pages
+    const int queued = min(misc[7], PR_QCAP);
+    for (int i = threadIdx.x; i < queued; i += 256) {
+      const int e = queue[i];
+      evaluate(e >> 14, (e >> 7) & 127, e & 127, queue_apx[i]);
+    }
+    meet();
+    // a pair whose bound was violated: every one of its 16384 elements, exactly (256 threads)
+    for (int t = 0; t < num_tiles; ++t) {
+      if (!redo[t]) continue;
+      const long long page = (static_cast<long long>(b) * g.tiles + page0 + t) * g.hk + hk_idx;
+      float m = -INFINITY;
+      for (int e = threadIdx.x; e < 128 * 128; e += 256) {
+        const long long qrow = (q_row0 + (e & 127)) * g.hidx + h;
+        m = fmaxf(m, fp4_exact_dot(g.qp + qrow * 64, g.qs + qrow * 8, g.kp + (page * 128 + (e >> 7)) * 64,
+                                   g.ks + (page * 128 + (e >> 7)) * 8));
+      }
+      atomicMax(res + t, f2ord(m));
+    }
+    meet();
+    if (ok)
+      for (int t = threadIdx.x; t < num_tiles; t += 256)
+        p.tile_scores[static_cast<long long>(list) * g.tiles + page0 + t] = ord2f(res[t]);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == MMA_WARP) {
+    tc_fence_after();
+    tmem_dealloc(tmem, TM_COLS);
+  }
+}
+
+// ---------------------------------------------------------------- host side
+static int make_maps(CUtensorMap* qm, CUtensorMap* km, const void* qp, const void* kp, int batch, int hidx, int len_q,
+                     long long k_rows) {
+  {
+    const cuuint64_t dims[3] = {64, static_cast<cuuint64_t>(hidx), static_cast<cuuint64_t>(batch) * len_q};
+    const cuuint64_t strides[2] = {64, static_cast<cuuint64_t>(hidx) * 64};
+    const cuuint32_t box[3] = {64, 1, 128};
+    const cuuint32_t steps[3] = {1, 1, 1};
+    if (encode_tiled(qm, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(qp), dims, strides, box, steps,
+                     CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B))
+      return set_error(SB_ERR_CUDA, "cuTensorMapEncodeTiled failed for the query codes");
+  }
+  {
+    const cuuint64_t dims[2] = {64, static_cast<cuuint64_t>(k_rows)};
+    const cuuint64_t strides[1] = {64};
+    const cuuint32_t box[2] = {64, 128};
+    const cuuint32_t steps[2] = {1, 1};
+    if (encode_tiled(km, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(kp), dims, strides, box, steps,
+                     CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B))
+      return set_error(SB_ERR_CUDA, "cuTensorMapEncodeTiled failed for the key codes");
+  }
+  return SB_OK;
+}
+
+static bool aligned(const void* p, uintptr_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
+
+}  // namespace fnv
+
+// aux (32 bytes, zeroed once by the owner of the workspace; every word accumulates over calls): [0] CTAs of the
+// tensor-core kernels that ran (int), [1] tiles that took the exact path (int), [2] unused, [3] scores whose
+// tensor-core value differed from the exact one by more than delta (int), [4] largest observed
+// |tensor-core value - exact value| / delta (float); [5], [6] scratch of the page pre-filter (largest |key
+// element| and largest squared key norm, rewritten by every call).
+// Returns SB_OK when the tensor-core path ran, 1 when the problem is not eligible.
+int launch_fp4_indexer_tc(const void* qp, const void* qs, const void* kp, const void* ks, void* aux, int32_t* ids,
+                          int batch, int hidx, int hk, int len_q, int len_kv, int topk, cudaStream_t stream) {
+  using namespace fnv;
+  const int tiles = len_kv / 128, qt = len_q / 128;
+  const int extra = topk / 4 > 16 ? topk / 4 : 16;
+  int cand = topk + extra;
+  if (cand > tiles) cand = tiles;
+  if (cand > C_MAX || tiles > MAX_TILES) return 1;
+  // Every candidate is re-scored exactly by one CTA per list, while the pruning scorer spreads
+  // pages over the whole GPU: the pre-filter pays off only when candidates are a small share
+  // of the pages.
+  if (8 * cand > tiles) return 1;
+  const long long q_rows = static_cast<long long>(batch) * len_q * hidx;
+  const long long k_rows = static_cast<long long>(batch) * tiles * hk * 128;
+  if (q_rows >= (1LL << 31) || k_rows >= (1LL << 31)) return 1;
+  if (!aligned(qp, 16) || !aligned(kp, 16) || !aligned(qs, 8) || !aligned(ks, 8)) return 1;
+  DeviceCtx* ctx = device_ctx();
+  if (!ctx) return SB_ERR_CUDA;
+  // key statistics for the error bound: one pass over codes and scales (microseconds next to the scoring)
+  float* key_stats = static_cast<float*>(aux) + 5;
+  if (cudaMemsetAsync(key_stats, 0, 8, stream) != cudaSuccess) return set_error(SB_ERR_CUDA, "memset failed");
+  key_stats_kernel<<<static_cast<unsigned>((k_rows * 16 + 255) / 256), 256, 0, stream>>>(
+      static_cast<const uint8_t*>(kp), static_cast<const uint8_t*>(ks), k_rows, key_stats);
+  CUtensorMap qm, km;
+  int rc = make_maps(&qm, &km, qp, kp, batch, hidx, len_q, k_rows);
+  if (rc) return rc;
+  Params p{};
+  p.key_stats = key_stats;
+  p.g = Geometry{static_cast<const uint8_t*>(qp), static_cast<const uint8_t*>(qs), static_cast<const uint8_t*>(kp),
+                 static_cast<const uint8_t*>(ks), batch, hidx, hk, len_q, tiles};
+  p.stats = static_cast<int*>(aux);
+  p.fallbacks = reinterpret_cast<int*>(aux) + 1;
+  p.violations = reinterpret_cast<int*>(aux) + 3;
+  p.ids = ids;
+  p.status = ctx->status;
+  p.topk = topk; p.cand = cand;
+  const size_t smem = OFF_SCORES + ((static_cast<size_t>(tiles) * 4 + 15) & ~static_cast<size_t>(15)) + 320 + 1024;
+  if (!(ctx->tc_attr & (1 << 8))) {
+    cudaError_t e = cudaFuncSetAttribute(fp4_nv_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(fp4_nv_select_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
+    if (e != cudaSuccess) return set_error(SB_ERR_CUDA, cudaGetErrorString(e));
+    ctx->tc_attr |= (1 << 8);
+  }
+  fp4_nv_select_kernel<<<batch * hidx * qt, NUM_THREADS, smem, stream>>>(qm, km, p);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? SB_OK : set_error(SB_ERR_CUDA, cudaGetErrorString(e));
+}
+
+// Exact tile scores [B, Hidx, Qt, tiles] through fp4_nv_prune_kernel. Returns SB_OK, or 1 when the
+// problem is not eligible (the caller then runs the exact mma.sync scorer). aux as above.
+int launch_fp4_scores_prune(const void* qp, const void* qs, const void* kp, const void* ks, void* aux, float* tile_scores,
+                            int batch, int hidx, int hk, int len_q, int len_kv, cudaStream_t stream) {
+  using namespace fnv;
+  const int tiles = len_kv / 128, qt = len_q / 128;
+  const long long q_rows = static_cast<long long>(batch) * len_q * hidx;
+  const long long k_rows = static_cast<long long>(batch) * tiles * hk * 128;
+  const long long lists = static_cast<long long>(batch) * hidx * qt;
+  if (q_rows >= (1LL << 31) || k_rows >= (1LL << 31) || lists * tiles >= (1LL << 31)) return 1;
+  if (!aligned(qp, 16) || !aligned(kp, 16) || !aligned(qs, 8) || !aligned(ks, 16)) return 1;
+  DeviceCtx* ctx = device_ctx();
+  if (!ctx) return SB_ERR_CUDA;
+  CUtensorMap qm, km;
+  int rc = make_maps(&qm, &km, qp, kp, batch, hidx, len_q, k_rows);
+  if (rc) return rc;
+  PruneParams p{};
+  p.g = Geometry{static_cast<const uint8_t*>(qp), static_cast<const uint8_t*>(qs), static_cast<const uint8_t*>(kp),
+                 static_cast<const uint8_t*>(ks), batch, hidx, hk, len_q, tiles};
+  p.stats = static_cast<int*>(aux);
+  p.violations = reinterpret_cast<int*>(aux) + 3;
+  p.tile_scores = tile_scores;
+  p.status = ctx->status;
+  // Two CTAs fit an SM: while one waits for its accumulator the other uses the tensor pipe. As many
+  // CTAs as fit at once when the lists are few; a CTA keeps its query tile and takes a run of pages.
+  long long chunks = (2LL * ctx->sm_count) / lists;
+  if (chunks > tiles) chunks = tiles;
+  if (chunks < 1) chunks = 1;
+  p.pages_per_cta = static_cast<int>((tiles + chunks - 1) / chunks);
+  p.chunks = (tiles + p.pages_per_cta - 1) / p.pages_per_cta;
+  if (lists * p.chunks >= (1LL << 31)) return 1;
+  if (!(ctx->tc_attr & (1 << 11))) {
+    cudaError_t e = cudaFuncSetAttribute(fp4_nv_prune_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(fp4_nv_prune_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
+    if (e != cudaSuccess) return set_error(SB_ERR_CUDA, cudaGetErrorString(e));
+    ctx->tc_attr |= (1 << 11);
+  }
+  const size_t smem = PR_OFF_RES + static_cast<size_t>(p.pages_per_cta) * 8 + 1024;
+  fp4_nv_prune_kernel<<<static_cast<unsigned>(lists * p.chunks), NUM_THREADS, smem, stream>>>(qm, km, p);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? SB_OK : set_error(SB_ERR_CUDA, cudaGetErrorString(e));
+}
+
+}  // namespace sb

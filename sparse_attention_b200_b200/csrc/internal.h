@@ -57,9 +57,8 @@ int launch_summary_score_topk(const void* qd, const void* kd, float* scores, int
                               int qt, int nt, int r, int topk, cudaStream_t stream);
 int launch_summary_select_tc(const void* qd, const void* kd, void* aux, int32_t* ids, int batch, int hq, int hkv,
                              int qt, int nt, int r, int topk, cudaStream_t stream);
-int launch_fp4_indexer_tc(const void* qp, const void* qs, const void* kp, const void* ks, void* q_deq, void* k_deq,
-                          void* aux, int32_t* ids, int batch, int hidx, int hk, int len_q, int len_kv, int topk,
-                          cudaStream_t stream);
+int launch_fp4_indexer_tc(const void* qp, const void* qs, const void* kp, const void* ks, void* aux, int32_t* ids,
+                          int batch, int hidx, int hk, int len_q, int len_kv, int topk, cudaStream_t stream);
 int launch_token_metadata(const int32_t* selected, int32_t* counts, int32_t* cursors, int32_t* row_ptr,
                           int32_t* qids, int32_t* ranks, int32_t* task_ptr, int32_t* tasks, int32_t* error,
                           int groups, int sq, int topk, int kv_blocks, int group_size, cudaStream_t stream);
@@ -71,9 +70,8 @@ int launch_kv_token_pipe(const void* q, const void* k, const void* v, const int3
                          int hkv, int sq, int skv, int topk, int q_token_major, cudaStream_t stream);
 int launch_quantize(const void* x, void* packed, void* scales, int batch, int heads_out, int group, int seq,
                     int paged, cudaStream_t stream);
-int launch_fp4_scores_prune(const void* qp, const void* qs, const void* kp, const void* ks, void* q_deq, void* k_deq,
-                            void* aux, float* tile_scores, int batch, int hidx, int hk, int len_q, int len_kv,
-                            cudaStream_t stream);
+int launch_fp4_scores_prune(const void* qp, const void* qs, const void* kp, const void* ks, void* aux, float* tile_scores,
+                            int batch, int hidx, int hk, int len_q, int len_kv, cudaStream_t stream);
 int launch_fp4_scores_varlen(const void* qp, const void* qs, const void* kp, const void* ks, const int32_t* cu_q,
                              const int32_t* cu_k, const int32_t* cu_pages, const int32_t* kv_indices,
                              const int32_t* qo_offset, float* out, int batch, int hq, int hk, int total_q,
@@ -82,7 +80,8 @@ int launch_fp4_scores(const void* qp, const void* qs, const void* kp, const void
                       float* tile_scores, int batch, int hidx, int hk, int len_q, int len_kv, cudaStream_t stream);
 int launch_tile_max_topk(const float* query_scores, int32_t* ids, int batch, int heads, int len_q, int tiles, int topk,
                          cudaStream_t stream);
-int launch_row_topk(const float* tile_scores, int32_t* ids, long long rows, int tiles, int topk, cudaStream_t stream);
+int launch_row_topk(const float* tile_scores, int32_t* ids, long long rows, int tiles, int topk, cudaStream_t stream,
+                    bool after_scorer = false);
 int launch_bounded_wait_selftest(long long limit_cycles, int* observed, cudaStream_t stream);
 
 }  // namespace sb

@@ -235,15 +235,16 @@ def fp4_indexer(inputs, selected=None, topk=16, tile_scores=None):
 
 
 def fp4_indexer_fast(inputs, selected=None, topk=16, workspace=None):
-    """Same ids as fp4_indexer through the tensor-core pre-filter + exact re-scoring.
-    Returns (selected, workspace); workspace[1] (int32 view) counts fallback tiles."""
+    """Same ids as fp4_indexer through the NVFP4 tensor-core pre-filter + exact re-scoring.
+    Returns (selected, workspace); the int32 words 1 and 3 of the workspace count the tiles that took
+    the exact path and the violations of the error bound since the workspace was zeroed."""
     b, h, lq, lkv = inputs["batch_size"], inputs["hkv"], inputs["len_q"], inputs["len_kv"]
     dev = inputs["q"].device
     L = _lib.lib()
     L.sparse_b200_indexer_fp4_workspace_bytes.restype = ctypes.c_int64
     need = L.sparse_b200_indexer_fp4_workspace_bytes(b, h, inputs["hk"], lq, lkv)
     if workspace is None:
-        workspace = torch.empty(need, dtype=torch.uint8, device=dev)
+        workspace = torch.zeros(need, dtype=torch.uint8, device=dev)    # its leading counters accumulate over calls
     if selected is None:
         selected = torch.empty((b, h, lq // 128, topk), dtype=torch.int32, device=dev)
     with torch.cuda.device(dev):
@@ -254,12 +255,58 @@ def fp4_indexer_fast(inputs, selected=None, topk=16, workspace=None):
     return selected, workspace
 
 
+class Fp4Pipeline:
+    """quantise -> NVFP4 tensor-core indexer -> top-k -> Q-centric attention as ONE C call on the
+    current stream, every buffer owned here and reused (nothing is allocated per call; capturable
+    in a CUDA graph after one eager call). One index head per KV head: the index vector of a
+    (token, KV head) is the NVFP4 of the mean of the group's query heads.
+    inputs=None: q and k are quantised inside every run(); inputs=<prepare_fp4_inputs bundle>: the
+    prepared codes are used as they are (the reference's timing, indexers/fp4/pipeline.py:49-65)."""
+
+    def __init__(self, q, k, v, topk=16, inputs=None):
+        b, hq, sq, _ = q.shape
+        hkv, skv = k.shape[1:3]
+        dev = q.device
+        self.q, self.k, self.v, self.topk = q, k, v, int(topk)
+        self.dims = (b, hq, hkv, sq, skv)
+        if inputs is None:
+            self.quantize = 1
+            self.qc = torch.empty((b * sq, hkv, 64), dtype=torch.uint8, device=dev)
+            self.qs = torch.empty((b * sq, hkv, 8), dtype=torch.float8_e4m3fn, device=dev)
+            self.kc = torch.empty((b * skv // 128, hkv, 128, 64), dtype=torch.uint8, device=dev)
+            self.ks = torch.empty((b * skv // 128, hkv, 128, 8), dtype=torch.float8_e4m3fn, device=dev)
+        else:
+            if inputs["batch_size"] != b or inputs["hkv"] != hkv or inputs["hk"] != hkv or inputs["len_q"] != sq \
+                    or inputs["len_kv"] != skv:
+                raise ValueError("indexer inputs must match attention shapes (one index head per KV head)")
+            self.quantize = 0
+            self.qc, self.qs, self.kc, self.ks = inputs["q"], inputs["q_scale"], inputs["k"], inputs["k_scale"]
+        L = _lib.lib()
+        L.sparse_b200_indexer_fp4_workspace_bytes.restype = ctypes.c_int64
+        self.ws = torch.zeros(L.sparse_b200_indexer_fp4_workspace_bytes(b, hkv, hkv, sq, skv), dtype=torch.uint8, device=dev)
+        self.ids = torch.empty((b, hkv, sq // 128, self.topk), dtype=torch.int32, device=dev)
+
+    def run(self, out, lse=None):
+        b, hq, hkv, sq, skv = self.dims
+        with torch.cuda.device(self.q.device):
+            _lib.check(_lib.lib().sparse_b200_indexed_attention_fp4(
+                _lib.ptr(self.q), _lib.ptr(self.k), _lib.ptr(self.v), _lib.ptr(self.qc), _lib.ptr(self.qs),
+                _lib.ptr(self.kc), _lib.ptr(self.ks), _lib.ptr(self.ws), ctypes.c_int64(self.ws.numel()),
+                _lib.ptr(self.ids), _lib.ptr(out), _lib.ptr(lse), b, hq, hkv, sq, skv, self.topk, self.quantize,
+                _lib.current_stream()))
+        return out
+
+    def stats(self):
+        """(tiles that took the exact path, bound violations, largest |tensor-core - exact| / bound)
+        of the last run (synchronising)."""
+        w = self.ws[:20].cpu()
+        return int(w[4:8].view(torch.int32)), int(w[12:16].view(torch.int32)), float(w[16:20].view(torch.float32))
+
+
 def indexed_attention(q, k, v, inputs, topk=16):
-    """(O, selected): FP4 indexer then Q-centric attention on the same stream."""
-    from .q_centric import attention
-    b, hq, sq, _ = q.shape
-    if inputs["batch_size"] != b or inputs["hkv"] != k.shape[1] or inputs["len_q"] != sq \
-            or inputs["len_kv"] != k.shape[2]:
-        raise ValueError("indexer inputs must match attention shapes")
-    selected = fp4_indexer(inputs, topk=topk)
-    return attention(q, k, v, selected), selected
+    """(O, selected): NVFP4 tensor-core indexer then Q-centric attention on the same stream, one C call
+    (indexers/fp4/pipeline.py:49-65)."""
+    pipe = Fp4Pipeline(q, k, v, topk=topk, inputs=inputs)
+    out = torch.empty_like(q)
+    pipe.run(out)
+    return out, pipe.ids
