@@ -44,7 +44,9 @@ def copy_sources(ref):
     os.makedirs(SRC, exist_ok=True)
     qc = os.path.join(ref, "attention", "q_centric")
     for f in ("progression_attention.cpp", "01_block_sparse.cu", "02_gqa_block_sparse.cu", "approximations.cuh",
-              "common.cuh", "smem_layout_swizzle128.cuh"):
+              "common.cuh", "smem_layout_swizzle128.cuh",
+              # the reference's own gate (run by tests/test_gpu_reference_gates.py against this library)
+              "progression.py", "progression_validation.py", "checkpoints.py"):
         shutil.copy(os.path.join(qc, f), os.path.join(SRC, f))
     stub = os.path.join(SRC, "p01_stub.cu")
     if not os.path.exists(stub):

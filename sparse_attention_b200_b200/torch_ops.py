@@ -1,0 +1,182 @@
+"""The reference's torch operator names, served by libsparse_b200.so.
+
+`register()` defines the operator libraries the reference's Python loaders look for, so that its
+own modules pick these kernels up unchanged (its loaders build their extension only when the
+operator is not registered yet, attention/q_centric/progression.py:29-36):
+
+  xomtention_progression::attention / attention_out
+      (attention/q_centric/progression_attention.cpp:19-125; `variant` selects nothing here: one kernel)
+  xomtention_tile_topk::tile_topk / tile_topk_out
+      (indexers/fp4/wrapper.cpp:16-80; 16 ids per list as there)
+  xomtention_kvopt11::metadata_temp_bytes / metadata_out / main_out / combine_out
+      (attention/kv_centric/optimization_round11/wrapper11.cpp:29-171): the head-major operator
+      chain. metadata_out serves chunk_size 1 (a task holds at most 128 / group_size queries, the unit
+      the main kernel works on) and main_out the bf16-partial variant (-1). The token-major pair
+      main_tm_out / combine_tm_out is not registered: its partial-output layout [B,Sq,16,Hq,128] is
+      private to the reference's two kernels; `PreparedTokens(q_token_major=True)` is the operator-level
+      replacement.
+
+Each operator validates like the reference (RuntimeError on rejected inputs), runs on the current
+CUDA stream of the tensors' device, allocates only where the reference's does (`attention`,
+`tile_topk`), and is capturable in a CUDA graph. Nothing here is needed by the package itself.
+"""
+import ctypes
+
+import torch
+
+from . import _lib
+from .q_centric import attention as _attention, attention_out as _attention_out
+from .indexers import tile_topk_out as _tile_topk_out
+
+_REGISTERED = {}
+
+
+def _fail(msg):
+    raise _lib.SparseB200Error(msg)
+
+
+def _register_progression():
+    lib = torch.library.Library("xomtention_progression", "DEF")
+    lib.define("attention(Tensor q, Tensor k, Tensor v, Tensor selected_indices, int variant) -> Tensor")
+    lib.define("attention_out(Tensor q, Tensor k, Tensor v, Tensor selected_indices, Tensor(a!) output, int variant) -> ()")
+
+    def attention(q, k, v, selected_indices, variant):
+        return _attention(q, k, v, selected_indices)
+
+    def attention_out(q, k, v, selected_indices, output, variant):
+        _attention_out(q, k, v, selected_indices, output)
+
+    lib.impl("attention", attention, "CUDA")
+    lib.impl("attention_out", attention_out, "CUDA")
+    return lib
+
+
+def _register_tile_topk():
+    lib = torch.library.Library("xomtention_tile_topk", "DEF")
+    lib.define("tile_topk(Tensor scores, int batch_size, int len_q) -> Tensor")
+    lib.define("tile_topk_out(Tensor scores, Tensor(a!) selected, int batch_size, int len_q) -> ()")
+
+    def tile_topk(scores, batch_size, len_q):
+        if scores.dim() != 3 or len_q <= 0 or len_q % 128:
+            _fail("scores must be contiguous [Hkv, KV_tiles, B*Sq]; len_q a positive multiple of 128")
+        selected = torch.empty((batch_size, scores.shape[0], len_q // 128, 16), dtype=torch.int32, device=scores.device)
+        return _tile_topk_out(scores, selected, batch_size=batch_size, len_q=len_q)
+
+    def tile_topk_out(scores, selected, batch_size, len_q):
+        if selected.dim() != 4 or selected.shape[-1] != 16:
+            _fail("selected must have shape [B, Hkv, Sq/128, 16]")
+        if selected.untyped_storage().data_ptr() == scores.untyped_storage().data_ptr():
+            _fail("selected must not alias scores")
+        _tile_topk_out(scores, selected, batch_size=batch_size, len_q=len_q)
+
+    lib.impl("tile_topk", tile_topk, "CUDA")
+    lib.impl("tile_topk_out", tile_topk_out, "CUDA")
+    return lib
+
+
+def _ints(anchor, *tensors):
+    for t in tensors:
+        if not (t.is_cuda and t.device == anchor.device and t.dtype == torch.int32 and t.is_contiguous()) \
+                or t.requires_grad:
+            _fail("same CUDA device, int32 and contiguous layout required")
+
+
+def _register_kvopt11():
+    lib = torch.library.Library("xomtention_kvopt11", "DEF")
+    lib.define("metadata_temp_bytes(int rows) -> int")
+    lib.define("metadata_out(Tensor selected, Tensor(a!) counts, Tensor(b!) row_ptr, Tensor(c!) cursors, "
+               "Tensor(d!) qids, Tensor(e!) ranks, Tensor(f!) chunks, Tensor(g!) task_ptr, Tensor(h!) tasks, "
+               "Tensor(i!) error, Tensor(j!) temp, int kv_blocks, int group_size, int chunk_size) -> ()")
+    lib.define("main_out(Tensor q, Tensor k, Tensor v, Tensor tasks, Tensor qids, Tensor ranks, Tensor(a!) partial, "
+               "Tensor(b!) lses, int variant) -> ()")
+    lib.define("combine_out(Tensor partial, Tensor lses, Tensor(a!) out, Tensor(b!) out_lse) -> ()")
+    # the task count travels from metadata_out to main_out on the device: task_ptr[rows] of the last build
+    state = {}
+
+    def metadata_temp_bytes(rows):
+        if not 0 < rows < 2 ** 31 - 2:
+            _fail("metadata row count")
+        return 16                     # no scratch is used; a token size keeps callers' allocation code unchanged
+
+    def metadata_out(selected, counts, row_ptr, cursors, qids, ranks, chunks, task_ptr, tasks, error, temp,
+                     kv_blocks, group_size, chunk_size):
+        _ints(selected, selected, counts, row_ptr, cursors, qids, ranks, chunks, task_ptr, tasks, error)
+        if selected.dim() != 4:
+            _fail("selected [B,Hkv,Sq,TopK]")
+        if chunk_size != 1:
+            _fail("chunk_size 1 only: a task holds at most 128 / group_size queries")
+        b, hkv, sq, topk = selected.shape
+        rows = b * hkv * kv_blocks
+        for t in (counts, row_ptr, chunks, task_ptr):
+            if t.dim() != 1 or t.numel() != rows + 1:
+                _fail("scan buffers must hold rows + 1 ints")
+        if cursors.numel() < rows or qids.numel() != selected.numel() or ranks.shape != qids.shape or error.numel() != 1:
+            _fail("cursors / edge storage / status shapes")
+        L = _lib.lib()
+        L.sparse_b200_kv_token_max_tasks.restype = ctypes.c_int64
+        bound = L.sparse_b200_kv_token_max_tasks(b, hkv, sq, topk, kv_blocks, group_size)
+        if tasks.dim() != 2 or tasks.shape[1] != 4 or tasks.shape[0] < bound:
+            _fail("bounded tasks: [min(E, ceil(E / (128 / group_size)) + rows), 4]")
+        # counts / cursors are scratch of rows + 1 ints in the C ABI: `chunks` serves as the cursors
+        with torch.cuda.device(selected.device):
+            _lib.check(L.sparse_b200_kv_token_metadata(
+                _lib.ptr(selected), _lib.ptr(counts), _lib.ptr(chunks), _lib.ptr(row_ptr), _lib.ptr(qids), _lib.ptr(ranks),
+                _lib.ptr(task_ptr), _lib.ptr(tasks), _lib.ptr(error), b, hkv, sq, topk, kv_blocks, group_size,
+                _lib.current_stream()))
+        state[tasks.data_ptr()] = task_ptr
+
+    def main_out(q, k, v, tasks, qids, ranks, partial, lses, variant):
+        if variant != -1:
+            _fail("main_out serves the bf16-partial variant (-1)")
+        for t in (q, k, v, partial):
+            if not (t.is_cuda and t.dtype == torch.bfloat16 and t.is_contiguous()) or t.requires_grad:
+                _fail("q, k, v and partial must be contiguous bf16 CUDA tensors (forward only)")
+        _ints(q, tasks, qids, ranks)
+        if q.dim() != 4 or k.dim() != 4 or k.shape != v.shape or q.shape[3] != 128 or k.shape[3] != 128:
+            _fail("QKV rank/shape")
+        b, hq, sq, _ = q.shape
+        hkv, skv = k.shape[1:3]
+        topk = qids.numel() // max(1, b * hkv * sq)
+        if tuple(partial.shape) != (b, hq, sq, topk, 128) or tuple(lses.shape) != (b, hq, sq, topk) \
+                or lses.dtype != torch.float32:
+            _fail("partials must be [B,Hq,Sq,TopK,128] bf16 and [B,Hq,Sq,TopK] fp32")
+        task_ptr = state.get(tasks.data_ptr())
+        if task_ptr is None:
+            _fail("main_out needs the task list of a preceding metadata_out on the same tasks tensor")
+        with torch.cuda.device(q.device):
+            _lib.check(_lib.lib().sparse_b200_kv_token_main(
+                _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(tasks), _lib.ptr(task_ptr), _lib.ptr(qids),
+                _lib.ptr(ranks), _lib.ptr(partial), _lib.ptr(lses), b, hq, hkv, sq, skv, topk, _lib.current_stream()))
+
+    def combine_out(partial, lses, out, out_lse):
+        if partial.dtype not in (torch.float32, torch.bfloat16) or not partial.is_contiguous() or not lses.is_contiguous():
+            _fail("partial dtype / layout")
+        if out.dim() != 4 or out.shape[3] != 128 or tuple(out_lse.shape) != tuple(out.shape[:3]) \
+                or out.dtype != torch.bfloat16 or out_lse.dtype != torch.float32:
+            _fail("output")
+        ranks = partial.shape[-2]
+        if tuple(partial.shape) != (*out.shape[:3], ranks, 128) or tuple(lses.shape) != (*out.shape[:3], ranks):
+            _fail("Combine input")
+        with torch.cuda.device(out.device):
+            _lib.check(_lib.lib().sparse_b200_combine(
+                _lib.ptr(partial), int(partial.dtype == torch.float32), _lib.ptr(lses), _lib.ptr(out), _lib.ptr(out_lse),
+                ctypes.c_int64(out_lse.numel()), ranks, 0, _lib.current_stream()))
+
+    lib.impl("metadata_temp_bytes", metadata_temp_bytes, "CompositeExplicitAutograd")
+    lib.impl("metadata_out", metadata_out, "CUDA")
+    lib.impl("main_out", main_out, "CUDA")
+    lib.impl("combine_out", combine_out, "CUDA")
+    return lib
+
+
+_BUILDERS = {"xomtention_progression": _register_progression, "xomtention_tile_topk": _register_tile_topk,
+             "xomtention_kvopt11": _register_kvopt11}
+
+
+def register(namespaces=tuple(_BUILDERS)):
+    """Defines the operator libraries (once per process). Fails if a namespace is already defined,
+    e.g. by the reference's own extension loaded into the same process."""
+    for name in namespaces:
+        if name not in _REGISTERED:
+            _REGISTERED[name] = _BUILDERS[name]()
+    return {name: getattr(torch.ops, name) for name in namespaces}

@@ -1,0 +1,141 @@
+"""The reference's OWN gate functions, run against this library.
+
+The reference sources are not part of this repository: `python baseline/build_reference_kernels.py
+--ref <checkout>` copies them, unmodified, into the git-ignored baseline/_ref/. Where they are
+present, these tests import the reference's gate modules as they are and point them at this
+library through the operator names / module interface the gates use:
+
+* attention/q_centric/progression_validation.py:78-169 `check_stage_correctness` obtains its
+  kernels from torch.ops.xomtention_progression (progression.py:29-58 only builds the reference
+  extension when that operator is missing); sparse_attention_b200_b200.torch_ops registers the
+  name over libsparse_b200.so first. Ten shape cases + three more for the GQA path, the `_out` form,
+  CUDA-graph replays with changed inputs, seven rejected inputs.
+* attention/kv_centric/validate_gpu.py:131-172 `run_suite` calls `api.attention(..., plan,
+  return_debug)` and `api.load_extension().combine`; a stand-in `api` module routes both to the
+  per-token KV-centric operator. Sixteen cases (sampled partials, analytic cases, reorder,
+  non-default stream, repeat) + the Combine unit with +-1000 LSEs.
+
+Skipped, with the reason, when baseline/_ref/ does not hold the reference files."""
+import os
+import sys
+import types
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+REF = os.path.join(ROOT, "baseline", "_ref")
+
+
+def _need(*paths):
+    missing = [p for p in paths if not os.path.exists(os.path.join(REF, p))]
+    if missing:
+        pytest.skip("reference sources not present under baseline/_ref/: " + ", ".join(missing))
+
+
+@pytest.mark.parametrize("version", ["p02", "p03"])
+def test_reference_q_centric_gate(version):
+    _need("q_centric/progression_validation.py", "q_centric/progression.py", "q_centric/checkpoints.py")
+    from sparse_attention_b200_b200 import torch_ops, device_status
+    torch_ops.register(("xomtention_progression",))
+    sys.path.insert(0, os.path.join(REF, "q_centric"))
+    try:
+        import progression_validation as gate
+        result = gate.check_stage_correctness(version)
+    finally:
+        sys.path.remove(os.path.join(REF, "q_centric"))
+    device_status()
+    assert result["passed"] and len(result["rejected_inputs"]) == 7 and len(result["dynamic_graph_checks"]) == 3
+    print(f"{version}: {len(result['cases'])} cases, persistent two-wave max abs {result['persistent_two_wave_max_abs']:.4g}")
+
+
+def test_reference_kv_centric_gate():
+    _need("kv_centric/validate_gpu.py", "kv_centric/metadata.py", "kv_centric/reference.py")
+    import sparse_attention_b200_b200 as sp
+    import pathlib
+    kv_dir = os.path.join(REF, "kv_centric")
+
+    # stand-in for attention/kv_centric/api.py: same names, same call forms, this library underneath
+    api = types.ModuleType("api")
+    api.ROOT = pathlib.Path(kv_dir)
+
+    class _Ext:
+        @staticmethod
+        def combine(partial, lses):
+            return sp.combine(partial, lses)
+
+    def attention(q, k, v, selected, *, plan=None, return_debug=False):
+        prep = sp.PreparedTokens(q, k, v, selected.to(q.device).contiguous())
+        prep.poison()
+        out, lse = prep.run()
+        if return_debug:
+            return out, lse, prep.partial, prep.lses
+        return out
+    api.attention = attention
+    api.load_extension = lambda: _Ext
+    saved = sys.modules.get("api")
+    sys.modules["api"] = api
+    sys.path.insert(0, kv_dir)
+    try:
+        import validate_gpu
+        report = validate_gpu.run_suite(smoke=False)
+    finally:
+        sys.path.remove(kv_dir)
+        if saved is None:
+            sys.modules.pop("api", None)
+        else:
+            sys.modules["api"] = saved
+    sp.device_status()
+    assert report["passed"] and len(report["cases"]) == 16
+    print(f"kv gate: max output abs {report['max_output_abs']:.4g}, max lse abs {report['max_lse_abs']:.4g}")
+
+
+def test_reference_operator_names_head_major_chain():
+    """xomtention_kvopt11::{metadata_out, main_out, combine_out} and xomtention_tile_topk::* as torch
+    operators: the chain equals the Python mirror bit for bit (no reference sources needed)."""
+    import oracle
+    from oracle import inputs as gen
+    import sparse_attention_b200_b200 as sp
+    from sparse_attention_b200_b200 import torch_ops
+    ops = torch_ops.register(("xomtention_kvopt11", "xomtention_tile_topk"))
+    kv = ops["xomtention_kvopt11"]
+    b, hq, hkv, sq, skv, topk = 2, 16, 2, 200, 4096, 16
+    g = hq // hkv
+    q, k, v = gen.make_qkv(b, hq, hkv, sq, skv, seed=77)
+    gen_ = torch.Generator().manual_seed(78)
+    selected = torch.stack([torch.randperm(skv // 128, generator=gen_)[:topk] for _ in range(b * hkv * sq)]) \
+        .to(torch.int32).reshape(b, hkv, sq, topk)
+    qc, kc, vc, sel = q.cuda(), k.cuda(), v.cuda(), selected.cuda()
+    rows, edges = b * hkv * (skv // 128), selected.numel()
+    ints = lambda n: torch.empty(n, dtype=torch.int32, device="cuda")
+    counts, row_ptr, chunks, task_ptr = ints(rows + 1), ints(rows + 1), ints(rows + 1), ints(rows + 1)
+    cursors, qids, ranks, error = ints(rows), ints(edges), ints(edges), torch.zeros(1, dtype=torch.int32, device="cuda")
+    bound = min(edges, -(-edges // (128 // g)) + rows)
+    tasks = torch.zeros((bound, 4), dtype=torch.int32, device="cuda")
+    temp = torch.empty(kv.metadata_temp_bytes(rows), dtype=torch.uint8, device="cuda")
+    kv.metadata_out(sel, counts, row_ptr, cursors, qids, ranks, chunks, task_ptr, tasks, error, temp, skv // 128, g, 1)
+    partial = torch.full((b, hq, sq, topk, 128), float("nan"), dtype=torch.bfloat16, device="cuda")
+    lses = torch.full((b, hq, sq, topk), float("nan"), device="cuda")
+    kv.main_out(qc, kc, vc, tasks, qids, ranks, partial, lses, -1)
+    out = torch.empty_like(qc)
+    out_lse = torch.empty((b, hq, sq), device="cuda")
+    kv.combine_out(partial, lses, out, out_lse)
+    torch.cuda.synchronize()
+    sp.device_status()
+    assert int(error.item()) == 0
+    prep = sp.PreparedTokens(qc, kc, vc, sel)
+    o2, l2 = prep.run()
+    assert torch.equal(out, o2) and torch.equal(out_lse, l2)
+    with pytest.raises(RuntimeError):
+        kv.metadata_out(sel, counts, row_ptr, cursors, qids, ranks, chunks, task_ptr, tasks, error, temp, skv // 128, g, 8)
+    with pytest.raises(RuntimeError):
+        kv.main_out(qc, kc, vc, tasks, qids, ranks, partial.float(), lses, -2)
+    # tile_topk operators against the Python mirror
+    scores = torch.randn((2, 32, 2 * 256), device="cuda")
+    tk = ops["xomtention_tile_topk"]
+    ids = tk.tile_topk(scores, 2, 256)
+    ids2 = torch.empty_like(ids)
+    tk.tile_topk_out(scores, ids2, 2, 256)
+    assert torch.equal(ids, ids2) and torch.equal(ids, sp.tile_topk(scores, batch_size=2, len_q=256, topk=16))
+    assert torch.equal(ids.cpu(), oracle.fp4_select(scores.cpu(), 2, 256, 16))
