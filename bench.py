@@ -1078,6 +1078,68 @@ def run_refsel(args):
         del q, k, v, out
 
 
+def run_varlen(args):
+    """The ragged / paged / causal NVFP4 scorer (per-query page scores) on a prefill batch and on a decode
+    batch (at most 8 new queries per request, group of 16 heads: the packed form), timed next to the
+    reference's own scorer on the same tensors where baseline/_ref/fp4 holds it
+    (indexers/fp4/vendor_minimax_msa/fp4_indexer_interface.py:745-1056, public scale layout)."""
+    import numpy as np
+    import torch
+    import sparse_attention_b200_b200 as sp
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    vendor = os.path.join(ROOT, "baseline", "_ref", "fp4", "vendor_minimax_msa")
+    ref_fn, ref_note = None, "unavailable: baseline/_ref/fp4 not present"
+    if os.path.isdir(vendor):
+        try:
+            sys.path.insert(0, vendor)
+            from fp4_indexer_interface import fp4_indexer_block_scores as ref_fn
+        except Exception as e:
+            ref_fn, ref_note = None, f"unavailable: {type(e).__name__}: {e}"
+    rng = np.random.default_rng(7)
+    batches = {"prefill": dict(hq=2, hk=1, q_lens=rng.integers(512, 4097, 8).tolist(), k_lens=rng.integers(4096, 16385, 8).tolist()),
+               "decode": dict(hq=16, hk=1, q_lens=rng.integers(1, 9, 64).tolist(), k_lens=rng.integers(8192, 32769, 64).tolist())}
+
+    def barrier():
+        torch.cuda.synchronize()
+    for name, bt in batches.items():
+        hq, hk, q_lens, k_lens = bt["hq"], bt["hk"], bt["q_lens"], bt["k_lens"]
+        pages_per = [(k + 127) // 128 for k in k_lens]
+        total_q, total_pages = sum(q_lens), sum(pages_per)
+        g = torch.Generator(device=dev).manual_seed(11)
+        qp = torch.randint(256, (total_q, hq, 64), dtype=torch.uint8, device=dev, generator=g)
+        kp = torch.randint(256, (total_pages, hk, 128, 64), dtype=torch.uint8, device=dev, generator=g)
+        qs = (torch.rand((total_q, hq, 8), device=dev, generator=g) + 0.5).to(torch.float8_e4m3fn)
+        ks = (torch.rand((total_pages, hk, 128, 8), device=dev, generator=g) + 0.5).to(torch.float8_e4m3fn)
+        cu = lambda xs: torch.tensor([0] + list(np.cumsum(xs)), dtype=torch.int32, device=dev)
+        cu_q, cu_k, cu_p = cu(q_lens), cu(k_lens), cu(pages_per)
+        kv_idx = torch.randperm(total_pages, device=dev, generator=g).to(torch.int32)
+        flop = 2.0 * 128 * hq * sum(q * p_ * 128 for q, p_ in zip(q_lens, pages_per))
+        row = {"workload": "varlen", "batch": name, "requests": len(q_lens), "Hq": hq, "Hk": hk, "total_q": total_q,
+               "total_pages": total_pages, "score_flop": flop, "ms": {}, "reference_same_box_ms": {}}
+        for causal in (False, True):
+            key = "causal" if causal else "full"
+            fn = lambda: sp.fp4_block_scores_varlen(qp, kp, qs, ks, cu_q, cu_k, cu_p, max_seqlen_q=max(q_lens),
+                                                    max_seqlen_k=max(k_lens), kv_indices=kv_idx, causal=causal)
+            row["ms"][key] = timed(fn, args.steps, 3, barrier)
+            if ref_fn is not None:
+                try:
+                    rf = lambda: ref_fn(qp, kp, qs, ks, cu_q, cu_k, cu_p, max_seqlen_q=max(q_lens), max_seqlen_k=max(k_lens),
+                                        kv_indices=kv_idx, fp4_format="nvfp4", causal=causal, scale_layout="public")
+                    theirs = rf()
+                    row["reference_same_box_ms"][key] = timed(rf, args.steps, 3, barrier)
+                    ours = fn()
+                    fin = torch.isfinite(theirs)
+                    row.setdefault("max_abs_diff_vs_reference", {})[key] = (ours[fin] - theirs[fin]).abs().max().item()
+                    row.setdefault("same_inf_pattern", {})[key] = bool(torch.equal(torch.isinf(ours), torch.isinf(theirs)))
+                except Exception as e:
+                    row["reference_same_box_ms"][key] = f"unavailable: {type(e).__name__}: {str(e)[:200]}"
+            else:
+                row["reference_same_box_ms"][key] = ref_note
+        sp.device_status()
+        print(json.dumps(row), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -1087,7 +1149,7 @@ def main():
     ap.add_argument("--kernel-only", action="store_true",
                     help="device-resident timing only (used for profiler captures): no e2e, parity, CPU baseline "
                          "or sub-records")
-    ap.add_argument("--workload", default=HEADLINE, choices=["kvtoken", "refcmp", "refsel"] + sorted(CONFIGS),
+    ap.add_argument("--workload", default=HEADLINE, choices=["kvtoken", "refcmp", "refsel", "varlen"] + sorted(CONFIGS),
                     help=f"{HEADLINE} (default) is the headline workload; c1..c4 run the same way on their own shapes")
     ap.add_argument("--no-configs", action="store_true", help="skip the c1..c4 sub-record of the headline run")
     ap.add_argument("--no-kv-split", action="store_true", help="skip the KV-split sub-record of multi-GPU runs")
@@ -1100,6 +1162,8 @@ def main():
         run_refcmp(args)
     elif args.workload == "refsel":
         run_refsel(args)
+    elif args.workload == "varlen":
+        run_varlen(args)
     elif args.impl == "reference":
         run_reference(args)
     else:

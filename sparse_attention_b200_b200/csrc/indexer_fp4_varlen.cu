@@ -14,6 +14,13 @@
 // src/sm100/fp4_indexer.py:525-529). Arithmetic: the exact one of indexer_fp4.cu (integer group
 // sums on the tensor cores, scaled and added in group order), so scores are bit-identical with
 // the dense scorer wherever both apply.
+//
+// Decode batches (every request has at most 8 new queries) take the PACKED form of the kernel: the
+// 128 rows of a CTA are (head of one KV-head group, query) pairs, 8 query slots for each of up to 16
+// heads, so that one pass over a key page serves the whole group instead of one head with 8 of 128
+// rows alive; the role of Fp4IndexerDecodePackedQSm100
+// (indexers/fp4/vendor_minimax_msa/src/sm100/fp4_indexer.py:1110-1229, taken there when
+// max_seqlen_q <= 8 and Hq / Hk = 16; here for any group size). Same arithmetic, same scores.
 #include <algorithm>
 #include "fp4_exact.cuh"
 #include "internal.h"
@@ -36,10 +43,17 @@ struct VarlenParams {
   const int32_t* qo_offset;     // may be null
   float* out;
   int batch, hq, hk, total_q, total_pages, qt_max, tiles_out, pages_per_cta, causal;
+  int head_blocks;              // packed form: blocks of 16 heads per KV-head group
 };
 
-// blockIdx.x = (request, query tile, query head); blockIdx.y = chunk of logical pages.
-// Warp w owns queries 16 w .. 16 w + 15 of the tile against the 128 keys of a page.
+constexpr int PACK_Q = 8;       // query slots per head in the packed (decode) form
+constexpr int PACK_HEADS = 16;  // heads per CTA in the packed form
+
+// blockIdx.x = (request, query tile, query head), or (request, KV head, block of 16 group heads) in the
+// packed form; blockIdx.y = chunk of logical pages. Warp w owns rows 16 w .. 16 w + 15 of the CTA
+// against the 128 keys of a page. Row r is query qtile * 128 + r of head h, or, packed, query r % 8 of
+// the (r / 8)-th head of the block.
+template <bool PACKED>
 __global__ void __launch_bounds__(256, 3) fp4_score_varlen_kernel(const VarlenParams p) {
   __shared__ uint32_t q_i8[128 * RW];
   __shared__ uint32_t k_i8[128 * RW];
@@ -48,9 +62,22 @@ __global__ void __launch_bounds__(256, 3) fp4_score_varlen_kernel(const VarlenPa
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int gid = lane >> 2, tig = lane & 3, m0 = warp * 16;
-  const int h = blockIdx.x % p.hq;
-  const int rest = blockIdx.x / p.hq;
-  const int qtile = rest % p.qt_max, b = rest / p.qt_max;
+  const int group = p.hq / p.hk;
+  int h, qtile, b, head_block = 0, hk_packed = 0;
+  if (PACKED) {
+    head_block = blockIdx.x % p.head_blocks;
+    const int rest = blockIdx.x / p.head_blocks;
+    hk_packed = rest % p.hk;
+    b = rest / p.hk;
+    qtile = 0;
+    h = hk_packed * group + head_block * PACK_HEADS;       // first head of the block
+  } else {
+    h = blockIdx.x % p.hq;
+    const int rest = blockIdx.x / p.hq;
+    qtile = rest % p.qt_max;
+    b = rest / p.qt_max;
+  }
+  const int heads_here = PACKED ? min(PACK_HEADS, group - head_block * PACK_HEADS) : 1;
   const int q_begin = p.cu_q[b], q_len = p.cu_q[b + 1] - q_begin;
   const int k_len = p.cu_k[b + 1] - p.cu_k[b];
   if (qtile * 128 >= q_len || k_len <= 0) return;          // block-uniform
@@ -61,17 +88,24 @@ __global__ void __launch_bounds__(256, 3) fp4_score_varlen_kernel(const VarlenPa
   const int pages = min(min((k_len + 127) >> 7, p.tiles_out), p.cu_pages[b + 1] - page_begin);
   if (q_begin < 0 || page_begin < 0) return;               // block-uniform
   const int offset = p.causal ? (p.qo_offset ? p.qo_offset[b] : k_len - q_len) : 0;
-  const int hk_idx = h / (p.hq / p.hk);
-  const int rows_live = min(min(128, q_len - qtile * 128), p.total_q - q_begin - qtile * 128);
+  const int hk_idx = PACKED ? hk_packed : h / group;
+  // queries of the request that this CTA serves (the packed form holds at most PACK_Q of them)
+  const int rows_live = min(min(PACKED ? PACK_Q : 128, q_len - qtile * 128), p.total_q - q_begin - qtile * 128);
   if (rows_live <= 0) return;                              // block-uniform
+  // row r of the CTA -> query position inside the request, head, alive?
+  auto row_query = [&](int r) { return PACKED ? (r & (PACK_Q - 1)) : qtile * 128 + r; };
+  auto row_head = [&](int r) { return PACKED ? h + (r >> 3) : h; };
+  auto row_alive = [&](int r) {
+    return PACKED ? ((r >> 3) < heads_here && (r & (PACK_Q - 1)) < rows_live) : r < rows_live;
+  };
 
   // stage the query tile (rows past the request's end as zeros)
   for (int e = tid; e < 128 * 16; e += 256) {
     const int r = e >> 4, w = e & 15;
     uint32_t a = 0, c = 0;
-    if (r < rows_live) {
+    if (row_alive(r)) {
       const uint32_t word = *reinterpret_cast<const uint32_t*>(
-          p.qp + ((static_cast<long long>(q_begin) + qtile * 128 + r) * p.hq + h) * 64 + w * 4);
+          p.qp + ((static_cast<long long>(q_begin) + row_query(r)) * p.hq + row_head(r)) * 64 + w * 4);
       codes_to_int8(word, a, c);
     }
     q_i8[r * RW + 2 * w] = a;
@@ -79,8 +113,8 @@ __global__ void __launch_bounds__(256, 3) fp4_score_varlen_kernel(const VarlenPa
   }
   for (int e = tid; e < 128 * 8; e += 256) {
     const int r = e >> 3;
-    q_sc[e] = r < rows_live
-                  ? 0.25f * e4m3_to_float(p.qs[((static_cast<long long>(q_begin) + qtile * 128 + r) * p.hq + h) * 8 + (e & 7)])
+    q_sc[e] = row_alive(r)
+                  ? 0.25f * e4m3_to_float(p.qs[((static_cast<long long>(q_begin) + row_query(r)) * p.hq + row_head(r)) * 8 + (e & 7)])
                   : 0.f;
   }
 
@@ -88,7 +122,7 @@ __global__ void __launch_bounds__(256, 3) fp4_score_varlen_kernel(const VarlenPa
   const int page0 = blockIdx.y * p.pages_per_cta;
   for (int pg = page0; pg < min(page0 + p.pages_per_cta, pages); ++pg) {
     // nothing of this page is visible to the last live query of the tile: it stays -inf
-    if (p.causal && pg * 128 > qtile * 128 + rows_live - 1 + offset) break;
+    if (p.causal && pg * 128 > (PACKED ? 0 : qtile * 128) + rows_live - 1 + offset) break;
     const int phys = p.kv_indices[page_begin + pg];
     if (phys < 0 || phys >= p.total_pages) continue;       // block-uniform; the page stays -inf
     __syncthreads();
@@ -105,7 +139,8 @@ __global__ void __launch_bounds__(256, 3) fp4_score_varlen_kernel(const VarlenPa
       k_sc[(e & 7) * 128 + (e >> 3)] = e4m3_to_float(p.ks[(page * 128 + (e >> 3)) * 8 + (e & 7)]);
     __syncthreads();
 
-    const int qi0 = qtile * 128 + m0 + gid, qi1 = qi0 + 8;   // this thread's two query positions
+    const int row0 = m0 + gid, row1 = row0 + 8;               // this thread's two rows
+    const int qi0 = row_query(row0), qi1 = row_query(row1);   // and their query positions
     float r0 = -CUDART_INF_F, r1 = -CUDART_INF_F;
 #pragma unroll 1
     for (int half = 0; half < 2; ++half) {
@@ -153,9 +188,10 @@ __global__ void __launch_bounds__(256, 3) fp4_score_varlen_kernel(const VarlenPa
       r1 = fmaxf(r1, __shfl_xor_sync(0xffffffffu, r1, dlt));
     }
     if (tig == 0) {
-      float* dst = p.out + (static_cast<long long>(h) * p.tiles_out + pg) * p.total_q + q_begin;
-      if (qi0 < qtile * 128 + rows_live) dst[qi0] = r0;
-      if (qi1 < qtile * 128 + rows_live) dst[qi1] = r1;
+      if (row_alive(row0))
+        p.out[(static_cast<long long>(row_head(row0)) * p.tiles_out + pg) * p.total_q + q_begin + qi0] = r0;
+      if (row_alive(row1))
+        p.out[(static_cast<long long>(row_head(row1)) * p.tiles_out + pg) * p.total_q + q_begin + qi1] = r1;
     }
   }
 }
@@ -180,14 +216,23 @@ int launch_fp4_scores_varlen(const void* qp, const void* qs, const void* kp, con
   const long long n = static_cast<long long>(hq) * p.tiles_out * total_q;
   const long long fill_blocks = std::min<long long>((n + 255) / 256, 4LL * ctx->sm_count * 8);
   fill_neg_inf_kernel<<<static_cast<unsigned>(fill_blocks > 0 ? fill_blocks : 1), 256, 0, stream>>>(out, n);
-  const long long items = static_cast<long long>(batch) * p.qt_max * hq;
+  // decode batches: every request at most PACK_Q queries -> rows of a CTA = (group head, query) pairs
+  const bool packed = max_seqlen_q <= PACK_Q && hq / hk > 1;
+  p.head_blocks = (hq / hk + PACK_HEADS - 1) / PACK_HEADS;
+  const long long items = packed ? static_cast<long long>(batch) * hk * p.head_blocks
+                                 : static_cast<long long>(batch) * p.qt_max * hq;
   if (items > 0x7fffffffLL) return set_error(SB_ERR_INVALID, "too many (request, query tile, head) items");
   int ppc = 8;
   while (ppc > 1 && ((p.tiles_out + ppc - 1) / ppc) * items < 4LL * ctx->sm_count) ppc >>= 1;
   p.pages_per_cta = ppc;
   const dim3 grid(static_cast<unsigned>(items), static_cast<unsigned>((p.tiles_out + ppc - 1) / ppc));
   if (grid.y > 65535) return set_error(SB_ERR_INVALID, "too many KV pages per request");
-  if (items > 0 && p.tiles_out > 0) fp4_score_varlen_kernel<<<grid, 256, 0, stream>>>(p);
+  if (items > 0 && p.tiles_out > 0) {
+    if (packed)
+      fp4_score_varlen_kernel<true><<<grid, 256, 0, stream>>>(p);
+    else
+      fp4_score_varlen_kernel<false><<<grid, 256, 0, stream>>>(p);
+  }
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? SB_OK : set_error(SB_ERR_CUDA, cudaGetErrorString(e));
 }

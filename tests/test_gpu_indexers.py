@@ -428,6 +428,72 @@ def test_fp4_scores_ragged_paged_causal(causal):
         assert torch.equal(dense, ragged)
 
 
+@pytest.mark.parametrize("heads", [(16, 1), (8, 2), (32, 1), (3, 3)])
+@pytest.mark.parametrize("causal", [False, True])
+def test_fp4_scores_decode_batches(heads, causal):
+    """Decode batches (at most 8 new queries per request): the packed form of the scorer, rows =
+    (group head, query) pairs, for group sizes 16 (the reference's decode case), 4, 32 (two blocks of
+    16 heads) and 1 (not packed). Bit-exact against the oracle, -inf outside."""
+    m = sp()
+    hq, hk = heads
+    q_lens, k_lens = [1, 8, 3, 5], [1000, 517, 128, 2048]
+    qp, qs, kp, ks, cu_q, cu_k, cu_p, kv_idx = _varlen_case(51 + hq, hq, hk, q_lens, k_lens)
+    ref = oracle.fp4_scores_varlen(qp, qs, kp, ks, cu_q, cu_k, cu_p, kv_idx, max(k_lens), causal=causal)
+    out = m.fp4_block_scores_varlen(qp.cuda(), kp.cuda(), qs.cuda(), ks.cuda(), cu_q.cuda(), cu_k.cuda(), cu_p.cuda(),
+                                    max_seqlen_q=max(q_lens), max_seqlen_k=max(k_lens), kv_indices=kv_idx.cuda(),
+                                    causal=causal)
+    torch.cuda.synchronize()
+    m.device_status()
+    assert torch.equal(out.cpu(), ref)
+    # the same requests declared as a prefill batch (max_seqlen_q = 128) take the unpacked form: same scores
+    out2 = m.fp4_block_scores_varlen(qp.cuda(), kp.cuda(), qs.cuda(), ks.cuda(), cu_q.cuda(), cu_k.cuda(), cu_p.cuda(),
+                                     max_seqlen_q=128, max_seqlen_k=max(k_lens), kv_indices=kv_idx.cuda(), causal=causal)
+    assert torch.equal(out2, out)
+
+
+@pytest.mark.parametrize("causal", [False, True])
+def test_fp4_varlen_scores_against_the_reference_scorer(causal):
+    """Pins the ragged / paged / causal contract to the reference's own kernel: the vendored MiniMax
+    MSA scorer (indexers/fp4/vendor_minimax_msa/fp4_indexer_interface.py:745-1056, copied unmodified
+    into the git-ignored baseline/_ref/fp4 by baseline/build_reference_kernels.py) on the same ragged
+    batch, public scale layout. Its scores come from NVFP4 MMAs in the tensor core's own accumulation
+    order, so they are compared with the reference's own gate tolerance (rtol 1e-4, atol 1e-3,
+    benchmarks/ch4_selectors/harness.py:33-42); the -inf pattern must be identical. The CPU oracle is
+    held to the same comparison, which is what pins it."""
+    vendor = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "baseline", "_ref", "fp4",
+                          "vendor_minimax_msa")
+    if not os.path.isdir(vendor):
+        pytest.skip("reference sources not present under baseline/_ref/fp4 (python baseline/build_reference_kernels.py --ref ...)")
+    import sys
+    sys.path.insert(0, vendor)
+    try:
+        from fp4_indexer_interface import fp4_indexer_block_scores
+    except Exception as e:                                  # nvidia-cutlass-dsl missing or unusable here
+        pytest.skip(f"the vendored scorer does not import: {type(e).__name__}: {e}")
+    finally:
+        sys.path.remove(vendor)
+    m = sp()
+    cases = [((4, 1), [200, 128, 300, 77], [1000, 128, 260, 64]),      # prefill-like, ragged
+             ((16, 1), [1, 8, 3, 5], [1000, 517, 128, 2048])]         # decode, group 16 (its packed-Q kernel)
+    for (hq, hk), q_lens, k_lens in cases:
+        qp, qs, kp, ks, cu_q, cu_k, cu_p, kv_idx = _varlen_case(61 + hq, hq, hk, q_lens, k_lens)
+        dev = [t.cuda() for t in (qp, kp, qs, ks, cu_q, cu_k, cu_p)]
+        theirs = fp4_indexer_block_scores(dev[0], dev[1], dev[2], dev[3], dev[4], dev[5], dev[6],
+                                          max_seqlen_q=max(q_lens), max_seqlen_k=max(k_lens), kv_indices=kv_idx.cuda(),
+                                          fp4_format="nvfp4", causal=causal, scale_layout="public")
+        ours = m.fp4_block_scores_varlen(dev[0], dev[1], dev[2], dev[3], dev[4], dev[5], dev[6], max_seqlen_q=max(q_lens),
+                                         max_seqlen_k=max(k_lens), kv_indices=kv_idx.cuda(), causal=causal)
+        torch.cuda.synchronize()
+        ref = oracle.fp4_scores_varlen(qp, qs, kp, ks, cu_q, cu_k, cu_p, kv_idx, max(k_lens), causal=causal)
+        assert theirs.shape == ours.shape == ref.shape
+        for name, mine in (("kernel", ours.cpu()), ("oracle", ref)):
+            t = theirs.cpu()
+            assert torch.equal(torch.isinf(t), torch.isinf(mine)), name
+            fin = torch.isfinite(t)
+            np.testing.assert_allclose(mine[fin].numpy(), t[fin].numpy(), rtol=1e-4, atol=1e-3, err_msg=name)
+    m.device_status()
+
+
 def test_fp4_scores_varlen_inconsistent_lengths_stay_in_bounds():
     """max_seqlen_k smaller than one request's key length, a page table shorter than the key
     length claims, and cu_seqlens_q that runs past total_q: the kernel must skip what does not fit.
