@@ -45,9 +45,10 @@ CONFIGS = {
     "c5": dict(B=1, Hq=64, Hkv=8, N=1048576, topk=64, indexer="r4", op="q_centric", k_offset=0.5),
 }
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the attention kernel, from one
-# Nsight Compute capture per shape (c5: captured at N = 131072 and scaled by the token count,
-# traffic grows in proportion). None = not captured.
-NCU_TRAFFIC_BYTES = {"c2": 1.145e9}
+# Nsight Compute capture per shape. c5: captured at N = 524288 (136.5 GB read + 10.8 GB written for
+# the 8 groups) and doubled: the K + V of a group exceed the L2 at both sizes, so the gathered
+# tiles miss at the same rate and the traffic grows with the token count. None = not captured.
+NCU_TRAFFIC_BYTES = {"c2": 1.145e9, "c5": 2.946e11}
 
 
 def attention_flops(cfg, groups=None):
