@@ -1044,6 +1044,8 @@ def run_refsel(args):
         tile_scores = torch.empty((B, Hkv, Sq // 128, Skv // 128), dtype=torch.float32, device=dev)
         t_sel = graph_time_us(lambda: sp.fp4_indexer_fast(inputs, selected=ids_fast, workspace=ws))
         t_exact = graph_time_us(lambda: sp.fp4_indexer(inputs, selected=ids_exact, tile_scores=tile_scores))
+        sp.fp4_block_scores(inputs, exact=False)             # builds the index tensors once, outside the capture
+        t_scorer = graph_time_us(lambda: sp.fp4_block_scores(inputs, exact=False))
 
         def fp4_pipe():
             sp.fp4_indexer_fast(inputs, selected=ids_fast, workspace=ws)
@@ -1052,7 +1054,7 @@ def run_refsel(args):
         torch.cuda.synchronize()
         assert torch.equal(ids_fast, ids_exact)
         row["us"]["FP4"] = {"selector": round(t_sel, 2), "selector_exact_kernels": round(t_exact, 2),
-                            "selector_to_attention": round(t_pipe, 2)}
+                            "selector_to_attention": round(t_pipe, 2), "scorer_only_per_query_scores": round(t_scorer, 2)}
         pub = REFSEL_PUBLISHED[Skv]["FP4"]
         row["reference_published_us"]["FP4"] = {"selector": pub[0], "selector_to_p03": pub[1]}
         if ref_fp4 is not None:
@@ -1123,6 +1125,14 @@ def run_varlen(args):
             fn = lambda: sp.fp4_block_scores_varlen(qp, kp, qs, ks, cu_q, cu_k, cu_p, max_seqlen_q=max(q_lens),
                                                     max_seqlen_k=max(k_lens), kv_indices=kv_idx, causal=causal)
             row["ms"][key] = timed(fn, args.steps, 3, barrier)
+            fast = lambda: sp.fp4_block_scores_varlen(qp, kp, qs, ks, cu_q, cu_k, cu_p, max_seqlen_q=max(q_lens),
+                                                      max_seqlen_k=max(k_lens), kv_indices=kv_idx, causal=causal, exact=False)
+            row.setdefault("ms_tensor_core", {})[key] = timed(fast, args.steps, 3, barrier)
+            exact_out, fast_out = fn(), fast()
+            fin = torch.isfinite(exact_out)
+            row.setdefault("tensor_core_vs_exact", {})[key] = {
+                "max_abs": (fast_out[fin] - exact_out[fin]).abs().max().item(),
+                "same_inf_pattern": bool(torch.equal(torch.isinf(fast_out), torch.isinf(exact_out)))}
             if ref_fn is not None:
                 try:
                     rf = lambda: ref_fn(qp, kp, qs, ks, cu_q, cu_k, cu_p, max_seqlen_q=max(q_lens), max_seqlen_k=max(k_lens),

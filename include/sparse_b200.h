@@ -217,6 +217,19 @@ int sparse_b200_fp4_scores_varlen(const void* q_codes, const void* q_scales, con
                                   const int32_t* cu_page_offsets, const int32_t* kv_indices, const int32_t* qo_offset,
                                   float* query_scores, int batch, int hq, int hk, int total_q, int total_pages,
                                   int max_seqlen_q, int max_seqlen_k, int causal, void* stream);
+/* Same arguments and output, computed straight off the NVFP4 tensor cores (tcgen05 block-scaled MMAs on the
+ * codes and scales as they are, query tile as the M operand, maximum over the keys of a page along a
+ * tensor-memory lane): what the reference's scorer itself returns
+ * (indexers/fp4/vendor_minimax_msa/src/sm100/fp4_indexer.py:201-1108, decode form :1110-1229). The eight scaled
+ * group sums of a dot are added in the tensor core's own order, so finite scores are within the reference's gate
+ * (rtol 1e-4, atol 1e-3, benchmarks/ch4_selectors/harness.py:33-42) of sparse_b200_fp4_scores_varlen, not bit-equal;
+ * the -inf pattern is identical. Use the exact entry where block ids must be reproducible bit for bit. */
+int sparse_b200_fp4_scores_varlen_fast(const void* q_codes, const void* q_scales, const void* k_codes,
+                                       const void* k_scales, const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k,
+                                       const int32_t* cu_page_offsets, const int32_t* kv_indices,
+                                       const int32_t* qo_offset, float* query_scores, int batch, int hq, int hk,
+                                       int total_q, int total_pages, int max_seqlen_q, int max_seqlen_k, int causal,
+                                       void* stream);
 int sparse_b200_tile_topk(const float* query_scores, int32_t* block_idx, int batch, int heads, int len_q, int kv_tiles,
                           int topk, void* stream);
 int sparse_b200_row_topk(const float* tile_scores, int32_t* block_idx, int64_t rows, int kv_tiles, int topk,

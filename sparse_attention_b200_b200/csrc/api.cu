@@ -363,6 +363,31 @@ int sparse_b200_fp4_scores_varlen(const void* q_codes, const void* q_scales, con
                                   max_seqlen_q, max_seqlen_k, causal, static_cast<cudaStream_t>(stream));
 }
 
+int sparse_b200_fp4_scores_varlen_fast(const void* q_codes, const void* q_scales, const void* k_codes,
+                                       const void* k_scales, const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k,
+                                       const int32_t* cu_page_offsets, const int32_t* kv_indices,
+                                       const int32_t* qo_offset, float* query_scores, int batch, int hq, int hk,
+                                       int total_q, int total_pages, int max_seqlen_q, int max_seqlen_k, int causal,
+                                       void* stream) {
+  REQUIRE(q_codes && q_scales && k_codes && k_scales && cu_seqlens_q && cu_seqlens_k && cu_page_offsets && kv_indices &&
+              query_scores,
+          "null pointer");
+  REQUIRE(batch > 0 && total_q > 0 && total_pages > 0 && max_seqlen_q > 0 && max_seqlen_k > 0,
+          "sizes must be positive");
+  REQUIRE(hq > 0 && hk > 0 && hq % hk == 0, "query heads must be a positive multiple of key heads");
+  REQUIRE(causal || !qo_offset, "qo_offset is only valid with causal masking");
+  REQUIRE((reinterpret_cast<uintptr_t>(q_codes) & 3u) == 0 && (reinterpret_cast<uintptr_t>(k_codes) & 3u) == 0,
+          "packed codes must be 4-byte aligned");
+  int rc = launch_fp4_scores_varlen_nv(q_codes, q_scales, k_codes, k_scales, cu_seqlens_q, cu_seqlens_k, cu_page_offsets,
+                                       kv_indices, qo_offset, query_scores, batch, hq, hk, total_q, total_pages,
+                                       max_seqlen_q, max_seqlen_k, causal, static_cast<cudaStream_t>(stream));
+  if (rc == 1)   // operands not aligned for the TMA path: exact scorer, same contract
+    rc = launch_fp4_scores_varlen(q_codes, q_scales, k_codes, k_scales, cu_seqlens_q, cu_seqlens_k, cu_page_offsets,
+                                  kv_indices, qo_offset, query_scores, batch, hq, hk, total_q, total_pages, max_seqlen_q,
+                                  max_seqlen_k, causal, static_cast<cudaStream_t>(stream));
+  return rc;
+}
+
 int sparse_b200_tile_topk(const float* query_scores, int32_t* block_idx, int batch, int heads, int len_q, int kv_tiles,
                           int topk, void* stream) {
   REQUIRE(query_scores && block_idx, "null pointer");

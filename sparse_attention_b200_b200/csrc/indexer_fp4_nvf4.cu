@@ -31,6 +31,7 @@
 #include "internal.h"
 #include "topk.cuh"
 #include "fp4_exact.cuh"
+#include <algorithm>
 
 namespace sb {
 namespace fnv {
@@ -900,6 +901,265 @@ static int make_maps(CUtensorMap* qm, CUtensorMap* km, const void* qp, const voi
 
 static bool aligned(const void* p, uintptr_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
 
+
+// ---------------------------------------------------------------- per-query page scores (ragged / paged / causal)
+// scores[h, page, query] = max over the visible keys of a page, straight off the NVFP4 MMA: the output the
+// reference's scorer produces (indexers/fp4/vendor_minimax_msa/src/sm100/fp4_indexer.py:201-1108, decode form
+// :1110-1229), values in the tensor core's own accumulation order (within delta of the canonical ones; the
+// reference's gate for this output is rtol 1e-4 / atol 1e-3, benchmarks/ch4_selectors/harness.py:33-42).
+// Here the QUERY tile is the M operand (one tensor-memory lane = one query, so the maximum over the keys of a
+// page is a maximum along a lane) and the key pages stream through as the N operand.
+// One CTA per (request, query tile, head) -- or, packed (decode batches), per (request, KV head, block of 16
+// group heads) with rows = (query, head) pairs -- and chunk of pages. Warps 0-3 epilogue (lane quarter = warp),
+// warp 4 producer, warp 5 MMA issue (one thread). 192 threads, 152 tensor-memory columns: two CTAs per SM.
+struct QueryScoreParams {
+  const uint8_t *qp, *qs, *kp, *ks;
+  const int32_t *cu_q, *cu_k, *cu_pages, *kv_indices, *qo_offset;
+  float* out;                          // [Hq, tiles_out, total_q], pre-filled with -inf
+  int* status;
+  int batch, hq, hk, total_q, total_pages, qt_max, tiles_out, pages_per_cta, causal, head_blocks;
+};
+constexpr int QS_THREADS = 192;
+constexpr int QS_PACK_Q = 8, QS_PACK_HEADS = 16;
+constexpr int QS_OFF_AUX = OFF_CAND;   // barriers (128 bytes), misc (64 bytes)
+
+template <bool PACKED>
+__global__ void __launch_bounds__(QS_THREADS, 2)
+fp4_nv_query_scores_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
+                           const QueryScoreParams p) {
+  extern __shared__ unsigned char smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  unsigned char* gbase = smem_raw + (base - raw);
+  const uint32_t bar0 = base + QS_OFF_AUX;
+  volatile int* misc = reinterpret_cast<volatile int*>(gbase + QS_OFF_AUX + 128);   // tmem base, abort
+  auto bar = [&](int i) { return bar0 + 8u * i; };
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int group = p.hq / p.hk;
+
+  int h0, qtile, b, hk_idx, heads_here = 1;
+  if (PACKED) {
+    const int head_block = blockIdx.x % p.head_blocks;
+    const int rest = blockIdx.x / p.head_blocks;
+    hk_idx = rest % p.hk;
+    b = rest / p.hk;
+    qtile = 0;
+    h0 = hk_idx * group + head_block * QS_PACK_HEADS;
+    heads_here = min(QS_PACK_HEADS, group - head_block * QS_PACK_HEADS);
+  } else {
+    h0 = blockIdx.x % p.hq;
+    const int rest = blockIdx.x / p.hq;
+    qtile = rest % p.qt_max;
+    b = rest / p.qt_max;
+    hk_idx = h0 / group;
+  }
+  const int q_begin = p.cu_q[b], q_len = p.cu_q[b + 1] - q_begin;
+  const int k_len = p.cu_k[b + 1] - p.cu_k[b];
+  if (q_begin < 0 || qtile * 128 >= q_len || k_len <= 0) return;      // block-uniform
+  const int page_begin = p.cu_pages[b];
+  if (page_begin < 0) return;
+  int pages = min(min((k_len + 127) >> 7, p.tiles_out), p.cu_pages[b + 1] - page_begin);
+  const int rows_live = min(min(PACKED ? QS_PACK_Q : 128, q_len - qtile * 128), p.total_q - q_begin - qtile * 128);
+  if (rows_live <= 0) return;
+  const int offset = p.causal ? (p.qo_offset ? p.qo_offset[b] : k_len - q_len) : 0;
+  if (p.causal) {          // pages past the last live query's horizon stay -inf
+    const long long horizon = static_cast<long long>(qtile) * 128 + rows_live - 1 + offset;
+    pages = horizon < 0 ? 0 : min(pages, static_cast<int>(horizon >> 7) + 1);
+  }
+  const int page0 = blockIdx.y * p.pages_per_cta;
+  const int num_tiles = min(p.pages_per_cta, pages - page0);
+  if (num_tiles <= 0) return;
+  // row r of the CTA -> query position inside the request, head, alive?
+  auto row_query = [&](int r) { return PACKED ? (r >> 4) : qtile * 128 + r; };
+  auto row_head = [&](int r) { return PACKED ? h0 + (r & (QS_PACK_HEADS - 1)) : h0; };
+  auto row_alive = [&](int r) {
+    return PACKED ? ((r & (QS_PACK_HEADS - 1)) < heads_here && (r >> 4) < rows_live) : r < rows_live;
+  };
+  Guard guard{misc + 1, p.status};
+
+  if (threadIdx.x == 0) {
+    misc[1] = 0;
+    for (int i = 0; i < A_STAGES; ++i) {
+      mbar_init(bar(A_FULL + i), 2);
+      mbar_init(bar(A_EMPTY + i), 1);
+    }
+    mbar_init(bar(ACC_FULL), 1);
+    mbar_init(bar(ACC_EMPTY), 4);
+    mbar_init(bar(B_FULL), 2);
+    fence_mbar_init();
+  }
+  if (warp == 5) {
+    tmem_alloc(smem_u32(const_cast<int*>(misc)), TM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = static_cast<uint32_t>(misc[0]);
+  // physical page of logical page pg, or -1 when the table entry is out of range (the page stays -inf)
+  auto phys_page = [&](int pg) {
+    const int ph = __ldg(p.kv_indices + page_begin + pg);
+    return (ph < 0 || ph >= p.total_pages) ? -1 : ph;
+  };
+
+  if (warp == 4) {
+    // ----------------------------------------------------------- producer
+    auto bar_ = bar;
+    if (lane == 0) {
+      mbar_expect_tx(bar_(B_FULL), CODE_BYTES);
+      if (PACKED)      // box {64 bytes, 16 heads, 8 queries}: row = query * 16 + head
+        tma_load_3d(base + OFF_B, &q_map, 0, h0, q_begin, bar_(B_FULL));
+      else             // box {64 bytes, 1 head, 128 queries}
+        tma_load_3d(base + OFF_B, &q_map, 0, h0, q_begin + qtile * 128, bar_(B_FULL));
+    }
+    {
+      ScaleRegs s;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int r = lane + 32 * i;
+        s.r[i] = make_uint2(0u, 0u);
+        if (row_alive(r))
+          s.r[i] = __ldg(reinterpret_cast<const uint2*>(
+              p.qs + ((static_cast<long long>(q_begin) + row_query(r)) * p.hq + row_head(r)) * 8));
+      }
+      store_scale_chunks(gbase + OFF_B + CODE_BYTES, s, lane);
+      fence_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_(B_FULL));
+    }
+    auto key_row = [&](int t) {
+      const int ph = phys_page(page0 + t);
+      return (static_cast<long long>(ph < 0 ? 0 : ph) * p.hk + hk_idx) * 128;
+    };
+    bool ok = true;
+    ScaleRegs ahead[3];
+#pragma unroll
+    for (int i = 0; i < 3; ++i)
+      if (i < num_tiles) ahead[i] = load_scales(p.ks + key_row(i) * 8, 8, lane);
+    auto step = [&](int t, ScaleRegs& regs) -> bool {
+      const int s = t % A_STAGES, use = t / A_STAGES;
+      if (use > 0) {
+        bool w = mbar_wait(bar_(A_EMPTY + s), (use - 1) & 1, guard, 0x600 + s);
+        if (!__all_sync(0xffffffffu, w)) return false;
+      }
+      if (lane == 0) {
+        mbar_expect_tx(bar_(A_FULL + s), CODE_BYTES);
+        tma_load_2d(base + OFF_A + s * STAGE_BYTES, &k_map, 0, static_cast<int>(key_row(t)), bar_(A_FULL + s));
+      }
+      store_scale_chunks(gbase + OFF_A + s * STAGE_BYTES + CODE_BYTES, regs, lane);
+      if (t + 3 < num_tiles) regs = load_scales(p.ks + key_row(t + 3) * 8, 8, lane);
+      fence_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_(A_FULL + s));
+      return true;
+    };
+    for (int t = 0; ok && t < num_tiles; t += 3) {
+      ok = step(t, ahead[0]);
+      if (ok && t + 1 < num_tiles) ok = step(t + 1, ahead[1]);
+      if (ok && t + 2 < num_tiles) ok = step(t + 2, ahead[2]);
+    }
+    if (!ok)
+      for (int t = max(0, num_tiles - A_STAGES); t < num_tiles; ++t)
+        mbar_wait_drain(bar_(A_FULL + t % A_STAGES), (t / A_STAGES) & 1);
+  } else if (warp == 5) {
+    // ----------------------------------------------------------- MMA issue (one thread)
+    if (lane == 0) {
+      constexpr uint32_t IDESC = idesc_nvf4(128, 128);
+      bool ok = mbar_wait(bar(B_FULL), 0, guard, 0x610);
+      if (ok) {
+        tc_fence_after();
+        const uint32_t sfq = tmem + TM_SFB;          // query scales: the A operand here
+        tmem_cp_scales(sfq, desc_scale_chunk(base + OFF_B + CODE_BYTES));
+        tmem_cp_scales(sfq + 4, desc_scale_chunk(base + OFF_B + CODE_BYTES + 512));
+        const uint64_t a0 = desc_sw64_kmajor(base + OFF_B);
+        for (int t = 0; ok && t < num_tiles; ++t) {
+          const int s = t % A_STAGES;
+          ok = mbar_wait(bar(A_FULL + s), (t / A_STAGES) & 1, guard, 0x611 + s);
+          if (!ok) break;
+          tc_fence_after();
+          const uint64_t b0 = desc_sw64_kmajor(base + OFF_A + s * STAGE_BYTES);
+          const uint32_t sfk = tmem + TM_SFA + (t & 1) * 8;
+          tmem_cp_scales(sfk, desc_scale_chunk(base + OFF_A + s * STAGE_BYTES + CODE_BYTES));
+          tmem_cp_scales(sfk + 4, desc_scale_chunk(base + OFF_A + s * STAGE_BYTES + CODE_BYTES + 512));
+          if (t >= 1) {
+            ok = mbar_wait(bar(ACC_EMPTY), (t - 1) & 1, guard, 0x618);
+            if (!ok) break;
+            tc_fence_after();
+          }
+#pragma unroll
+          for (int kh = 0; kh < 2; ++kh)
+            mma_nvf4(tmem + TM_ACC, a0 + kh * 2, b0 + kh * 2, IDESC, sfq + kh * 4, sfk + kh * 4, kh);
+          tc_commit(bar(ACC_FULL));
+          tc_commit(bar(A_EMPTY + s));
+        }
+      }
+    }
+    __syncwarp();
+  } else {
+    // ----------------------------------------------------------- epilogue: one lane = one query row
+    const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
+    const int r = warp * 32 + lane;
+    const bool alive = row_alive(r);
+    const int qi = row_query(r);
+    float* dst = p.out + (static_cast<long long>(row_head(r)) * p.tiles_out) * p.total_q + q_begin + qi;
+    // last visible key of this query (inclusive), relative to the request
+    const long long last_key = p.causal ? min(static_cast<long long>(k_len) - 1, static_cast<long long>(qi) + offset)
+                                        : static_cast<long long>(k_len) - 1;
+    bool ok = true;
+    for (int t = 0; ok && t < num_tiles; ++t) {
+      bool w = mbar_wait(bar(ACC_FULL), t & 1, guard, 0x620);
+      ok = __all_sync(0xffffffffu, w);
+      if (!ok) break;
+      tc_fence_after();
+      const int pg = page0 + t;
+      const long long visible = last_key - static_cast<long long>(pg) * 128 + 1;     // visible keys of this page
+      float m = -INFINITY;
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        uint32_t v[4][16];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) tmem_ld16(tmem + lane_base + TM_ACC + half * 64 + c * 16, v[c]);
+        tc_wait_ld();
+        if (half == 1) {
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar(ACC_EMPTY));
+        }
+        if (visible >= (half + 1) * 64) {
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            float m5[5];
+#pragma unroll
+            for (int jj = 0; jj < 5; ++jj)
+              m5[jj] = max3(__uint_as_float(v[c][3 * jj]), __uint_as_float(v[c][3 * jj + 1]), __uint_as_float(v[c][3 * jj + 2]));
+            m = fmaxf(m, fmaxf(max3(m5[0], m5[1], m5[2]), max3(m5[3], m5[4], __uint_as_float(v[c][15]))));
+          }
+        } else if (visible > half * 64) {
+          const int n = static_cast<int>(visible) - half * 64;           // 1 .. 63 visible columns of this half
+#pragma unroll
+          for (int c = 0; c < 4; ++c)
+#pragma unroll
+            for (int jj = 0; jj < 16; ++jj)
+              if (c * 16 + jj < n) m = fmaxf(m, __uint_as_float(v[c][jj]));
+        }
+      }
+      if (alive && phys_page(pg) >= 0) dst[static_cast<long long>(pg) * p.total_q] = m;
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 5) {
+    tc_fence_after();
+    tmem_dealloc(tmem, TM_COLS);
+  }
+}
+
+__global__ void __launch_bounds__(256) fill_neg_inf_kernel(float* out, long long n) {
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
+       i += static_cast<long long>(gridDim.x) * blockDim.x)
+    out[i] = -INFINITY;
+}
+
 }  // namespace fnv
 
 // aux (32 bytes, zeroed once by the owner of the workspace; every word accumulates over calls): [0] CTAs of the
@@ -997,6 +1257,79 @@ int launch_fp4_scores_prune(const void* qp, const void* qs, const void* kp, cons
   }
   const size_t smem = PR_OFF_RES + static_cast<size_t>(p.pages_per_cta) * 8 + 1024;
   fp4_nv_prune_kernel<<<static_cast<unsigned>(lists * p.chunks), NUM_THREADS, smem, stream>>>(qm, km, p);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? SB_OK : set_error(SB_ERR_CUDA, cudaGetErrorString(e));
+}
+
+// Per-query page scores of a ragged batch on the NVFP4 tensor cores. Returns SB_OK, or 1 when the inputs do not
+// meet the alignment the TMA path needs (the caller then runs the exact scorer).
+int launch_fp4_scores_varlen_nv(const void* qp, const void* qs, const void* kp, const void* ks, const int32_t* cu_q,
+                                const int32_t* cu_k, const int32_t* cu_pages, const int32_t* kv_indices,
+                                const int32_t* qo_offset, float* out, int batch, int hq, int hk, int total_q,
+                                int total_pages, int max_seqlen_q, int max_seqlen_k, int causal, cudaStream_t stream) {
+  using namespace fnv;
+  if (!aligned(qp, 16) || !aligned(kp, 16) || !aligned(qs, 8) || !aligned(ks, 8)) return 1;
+  const long long k_rows = static_cast<long long>(total_pages) * hk * 128;
+  if (k_rows >= (1LL << 31) || static_cast<long long>(total_q) >= (1LL << 31)) return 1;
+  DeviceCtx* ctx = device_ctx();
+  if (!ctx) return SB_ERR_CUDA;
+  QueryScoreParams p{};
+  p.qp = static_cast<const uint8_t*>(qp); p.qs = static_cast<const uint8_t*>(qs);
+  p.kp = static_cast<const uint8_t*>(kp); p.ks = static_cast<const uint8_t*>(ks);
+  p.cu_q = cu_q; p.cu_k = cu_k; p.cu_pages = cu_pages; p.kv_indices = kv_indices; p.qo_offset = qo_offset;
+  p.out = out;
+  p.status = ctx->status;
+  p.batch = batch; p.hq = hq; p.hk = hk; p.total_q = total_q; p.total_pages = total_pages;
+  p.qt_max = (max_seqlen_q + 127) / 128;
+  p.tiles_out = (max_seqlen_k + 127) / 128;
+  p.causal = causal;
+  const bool packed = max_seqlen_q <= QS_PACK_Q && hq / hk > 1;
+  p.head_blocks = (hq / hk + QS_PACK_HEADS - 1) / QS_PACK_HEADS;
+  const long long items = packed ? static_cast<long long>(batch) * hk * p.head_blocks
+                                 : static_cast<long long>(batch) * p.qt_max * hq;
+  if (items > 0x7fffffffLL) return set_error(SB_ERR_INVALID, "too many (request, query tile, head) items");
+  const long long n = static_cast<long long>(hq) * p.tiles_out * total_q;
+  const long long fill_blocks = std::min<long long>((n + 255) / 256, 32LL * ctx->sm_count);
+  fill_neg_inf_kernel<<<static_cast<unsigned>(fill_blocks > 0 ? fill_blocks : 1), 256, 0, stream>>>(out, n);
+  if (items == 0 || p.tiles_out == 0) return SB_OK;
+  // enough CTAs to fill the GPU twice over, as long a run of pages per CTA as that allows (the query tile is
+  // loaded once per CTA)
+  int ppc = 64;
+  while (ppc > 2 && ((p.tiles_out + ppc - 1) / ppc) * items < 4LL * ctx->sm_count) ppc >>= 1;
+  p.pages_per_cta = ppc;
+  const dim3 grid(static_cast<unsigned>(items), static_cast<unsigned>((p.tiles_out + ppc - 1) / ppc));
+  if (grid.y > 65535) return set_error(SB_ERR_INVALID, "too many KV pages per request");
+  CUtensorMap qm, km;
+  {
+    const cuuint64_t dims[3] = {64, static_cast<cuuint64_t>(hq), static_cast<cuuint64_t>(total_q)};
+    const cuuint64_t strides[2] = {64, static_cast<cuuint64_t>(hq) * 64};
+    const cuuint32_t box_tile[3] = {64, 1, 128}, box_packed[3] = {64, QS_PACK_HEADS, QS_PACK_Q};
+    const cuuint32_t steps[3] = {1, 1, 1};
+    if (encode_tiled(&qm, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(qp), dims, strides,
+                     packed ? box_packed : box_tile, steps, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B))
+      return set_error(SB_ERR_CUDA, "cuTensorMapEncodeTiled failed for the query codes");
+  }
+  {
+    const cuuint64_t dims[2] = {64, static_cast<cuuint64_t>(k_rows)};
+    const cuuint64_t strides[1] = {64};
+    const cuuint32_t box[2] = {64, 128};
+    const cuuint32_t steps[2] = {1, 1};
+    if (encode_tiled(&km, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(kp), dims, strides, box, steps,
+                     CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B))
+      return set_error(SB_ERR_CUDA, "cuTensorMapEncodeTiled failed for the key codes");
+  }
+  const size_t smem = QS_OFF_AUX + 256 + 1024;
+  if (!(ctx->tc_attr & (1 << 12))) {
+    cudaError_t e = cudaFuncSetAttribute(fp4_nv_query_scores_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 65536);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(fp4_nv_query_scores_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 65536);
+    if (e != cudaSuccess) return set_error(SB_ERR_CUDA, cudaGetErrorString(e));
+    ctx->tc_attr |= (1 << 12);
+  }
+  if (packed)
+    fp4_nv_query_scores_kernel<true><<<grid, QS_THREADS, smem, stream>>>(qm, km, p);
+  else
+    fp4_nv_query_scores_kernel<false><<<grid, QS_THREADS, smem, stream>>>(qm, km, p);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? SB_OK : set_error(SB_ERR_CUDA, cudaGetErrorString(e));
 }

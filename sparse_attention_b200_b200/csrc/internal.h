@@ -76,6 +76,10 @@ int launch_fp4_scores_varlen(const void* qp, const void* qs, const void* kp, con
                              const int32_t* cu_k, const int32_t* cu_pages, const int32_t* kv_indices,
                              const int32_t* qo_offset, float* out, int batch, int hq, int hk, int total_q,
                              int total_pages, int max_seqlen_q, int max_seqlen_k, int causal, cudaStream_t stream);
+int launch_fp4_scores_varlen_nv(const void* qp, const void* qs, const void* kp, const void* ks, const int32_t* cu_q,
+                                const int32_t* cu_k, const int32_t* cu_pages, const int32_t* kv_indices,
+                                const int32_t* qo_offset, float* out, int batch, int hq, int hk, int total_q,
+                                int total_pages, int max_seqlen_q, int max_seqlen_k, int causal, cudaStream_t stream);
 int launch_fp4_scores(const void* qp, const void* qs, const void* kp, const void* ks, float* query_scores,
                       float* tile_scores, int batch, int hidx, int hk, int len_q, int len_kv, cudaStream_t stream);
 int launch_tile_max_topk(const float* query_scores, int32_t* ids, int batch, int heads, int len_q, int tiles, int topk,

@@ -147,9 +147,19 @@ def prepare_fp4_inputs(q_fp4, k_fp4, q_scale, k_scale, *, batch_size, len_q, len
             "hkv": hidx, "hk": k_fp4.shape[1], "len_q": len_q, "len_kv": len_kv}
 
 
-def fp4_block_scores(inputs):
-    """fp32 [Hidx, KV_tiles, B*Sq] scores (max over the keys of each page)."""
+def fp4_block_scores(inputs, exact=True):
+    """fp32 [Hidx, KV_tiles, B*Sq] scores (max over the keys of each page). exact=False: straight off the NVFP4
+    tensor cores (the dense batch handed to the ragged scorer as B equal requests over pages in order)."""
     b, h, lq, lkv = inputs["batch_size"], inputs["hkv"], inputs["len_q"], inputs["len_kv"]
+    if not exact:
+        dev = inputs["q"].device
+        if "cu_q" not in inputs:          # the reference's prepare_fp4_inputs keeps the same index tensors (fp4.py:78-82)
+            req = torch.arange(b + 1, device=dev, dtype=torch.int32)
+            inputs.update(cu_q=req * lq, cu_k=req * lkv, cu_pages=req * (lkv // 128),
+                          page_indices=torch.arange(b * (lkv // 128), device=dev, dtype=torch.int32))
+        return fp4_block_scores_varlen(inputs["q"], inputs["k"], inputs["q_scale"], inputs["k_scale"], inputs["cu_q"],
+                                       inputs["cu_k"], inputs["cu_pages"], max_seqlen_q=lq, max_seqlen_k=lkv,
+                                       kv_indices=inputs["page_indices"], exact=False)
     scores = torch.empty((h, lkv // 128, b * lq), dtype=torch.float32, device=inputs["q"].device)
     with torch.cuda.device(scores.device):
         _lib.check(_lib.lib().sparse_b200_fp4_scores(
@@ -159,10 +169,12 @@ def fp4_block_scores(inputs):
 
 
 def fp4_block_scores_varlen(q_fp4, k_fp4, q_scale, k_scale, cu_seqlens_q, cu_seqlens_k, cu_page_offsets, *,
-                            max_seqlen_q, max_seqlen_k, kv_indices, causal=False, qo_offset=None):
+                            max_seqlen_q, max_seqlen_k, kv_indices, causal=False, qo_offset=None, exact=True):
     """Ragged batch over a paged key cache, optionally causal: fp32 [Hq, ceil(max_seqlen_k/128), total_q]
     (max over the visible keys of each page, -inf where none), the public-layout form of
-    fp4_indexer_block_scores (indexers/fp4/vendor_minimax_msa/fp4_indexer_interface.py:745-811)."""
+    fp4_indexer_block_scores (indexers/fp4/vendor_minimax_msa/fp4_indexer_interface.py:745-811).
+    exact=True: canonical group-ordered arithmetic (bit-reproducible); exact=False: straight off the NVFP4
+    tensor cores, as the reference's scorer (finite scores within its gate tolerance of the exact ones)."""
     if q_fp4.ndim != 3 or q_fp4.shape[2] != 64 or k_fp4.ndim != 4 or tuple(k_fp4.shape[2:]) != (128, 64):
         raise ValueError("q_fp4 must be [total_q,Hq,64] and k_fp4 [total_pages,Hk,128,64]")
     total_q, hq = int(q_fp4.shape[0]), int(q_fp4.shape[1])
@@ -187,8 +199,9 @@ def fp4_block_scores_varlen(q_fp4, k_fp4, q_scale, k_scale, cu_seqlens_q, cu_seq
             raise ValueError(f"{name} must be a contiguous {dtype} CUDA tensor" + (f" of shape {shape}" if shape else ""))
     tiles = (int(max_seqlen_k) + 127) // 128
     scores = torch.empty((hq, tiles, total_q), dtype=torch.float32, device=dev)
+    entry = _lib.lib().sparse_b200_fp4_scores_varlen if exact else _lib.lib().sparse_b200_fp4_scores_varlen_fast
     with torch.cuda.device(dev):
-        _lib.check(_lib.lib().sparse_b200_fp4_scores_varlen(
+        _lib.check(entry(
             _lib.ptr(q_fp4), _lib.ptr(q_scale), _lib.ptr(k_fp4), _lib.ptr(k_scale), _lib.ptr(cu_seqlens_q),
             _lib.ptr(cu_seqlens_k), _lib.ptr(cu_page_offsets), _lib.ptr(kv_indices), _lib.ptr(qo_offset),
             _lib.ptr(scores), batch, hq, hk, total_q, total_pages, int(max_seqlen_q), int(max_seqlen_k),

@@ -451,6 +451,55 @@ def test_fp4_scores_decode_batches(heads, causal):
     assert torch.equal(out2, out)
 
 
+def _assert_within_reference_gate(mine, exact, what):
+    """Finite scores within the reference's own gate (rtol 1e-4, atol 1e-3,
+    benchmarks/ch4_selectors/harness.py:33-42), identical -inf pattern."""
+    assert mine.shape == exact.shape, what
+    assert torch.equal(torch.isinf(mine), torch.isinf(exact)), what
+    fin = torch.isfinite(exact)
+    np.testing.assert_allclose(mine[fin].numpy(), exact[fin].numpy(), rtol=1e-4, atol=1e-3, err_msg=what)
+
+
+@pytest.mark.parametrize("causal", [False, True])
+def test_fp4_scores_on_the_tensor_cores_ragged_decode_dense(causal):
+    """The NVFP4-MMA scorer (per-query page scores straight off tcgen05 block-scaled MMAs, query tile as the M
+    operand) against the exact scorer: ragged prefill batch with explicit causal offsets, decode batches of
+    several group sizes (packed rows), an out-of-range page-table entry, and a dense batch."""
+    m = sp()
+    q_lens, k_lens = [200, 128, 1, 300, 77], [1000, 128, 517, 260, 64]
+    qp, qs, kp, ks, cu_q, cu_k, cu_p, kv_idx = _varlen_case(11, 4, 1, q_lens, k_lens)
+    kv_bad = kv_idx.clone()
+    kv_bad[2] = 10 ** 6                                     # page 2 of request 0 does not exist: stays -inf
+    offsets = [None] + ([torch.tensor([800, 0, 516, -50, 10], dtype=torch.int32)] if causal else [])
+    dev = [t.cuda() for t in (qp, kp, qs, ks, cu_q, cu_k, cu_p)]
+    for table in (kv_idx, kv_bad):
+        for qo in offsets:
+            kw = dict(max_seqlen_q=max(q_lens), max_seqlen_k=max(k_lens), kv_indices=table.cuda(), causal=causal,
+                      qo_offset=None if qo is None else qo.cuda())
+            exact = m.fp4_block_scores_varlen(*dev, **kw)
+            fast = m.fp4_block_scores_varlen(*dev, exact=False, **kw)
+            torch.cuda.synchronize()
+            m.device_status()
+            _assert_within_reference_gate(fast.cpu(), exact.cpu(), f"ragged causal={causal}")
+    for hq, hk in ((16, 1), (8, 2), (32, 1), (3, 3)):
+        q_lens, k_lens = [1, 8, 3, 5], [1000, 517, 128, 2048]
+        qp, qs, kp, ks, cu_q, cu_k, cu_p, kv_idx = _varlen_case(51 + hq, hq, hk, q_lens, k_lens)
+        dev = [t.cuda() for t in (qp, kp, qs, ks, cu_q, cu_k, cu_p)]
+        kw = dict(max_seqlen_q=max(q_lens), max_seqlen_k=max(k_lens), kv_indices=kv_idx.cuda(), causal=causal)
+        exact = m.fp4_block_scores_varlen(*dev, **kw)
+        fast = m.fp4_block_scores_varlen(*dev, exact=False, **kw)
+        torch.cuda.synchronize()
+        m.device_status()
+        _assert_within_reference_gate(fast.cpu(), exact.cpu(), f"decode Hq{hq}/Hk{hk} causal={causal}")
+    if not causal:
+        qp, qs, kp, ks, b, lq, lkv = cases.fp4_case()
+        inputs = m.prepare_fp4_inputs(qp.cuda(), kp.cuda(), qs.cuda(), ks.cuda(), batch_size=b, len_q=lq, len_kv=lkv)
+        _assert_within_reference_gate(m.fp4_block_scores(inputs, exact=False).cpu(), m.fp4_block_scores(inputs).cpu(), "dense")
+        fx = np.load(os.path.join(G, "fp4.npz"))
+        np.testing.assert_allclose(m.fp4_block_scores(inputs, exact=False).cpu().numpy(), fx["scores"], rtol=1e-4, atol=1e-3)
+        m.device_status()
+
+
 @pytest.mark.parametrize("causal", [False, True])
 def test_fp4_varlen_scores_against_the_reference_scorer(causal):
     """Pins the ragged / paged / causal contract to the reference's own kernel: the vendored MiniMax
@@ -484,9 +533,12 @@ def test_fp4_varlen_scores_against_the_reference_scorer(causal):
         ours = m.fp4_block_scores_varlen(dev[0], dev[1], dev[2], dev[3], dev[4], dev[5], dev[6], max_seqlen_q=max(q_lens),
                                          max_seqlen_k=max(k_lens), kv_indices=kv_idx.cuda(), causal=causal)
         torch.cuda.synchronize()
+        fast = m.fp4_block_scores_varlen(dev[0], dev[1], dev[2], dev[3], dev[4], dev[5], dev[6], max_seqlen_q=max(q_lens),
+                                         max_seqlen_k=max(k_lens), kv_indices=kv_idx.cuda(), causal=causal, exact=False)
+        torch.cuda.synchronize()
         ref = oracle.fp4_scores_varlen(qp, qs, kp, ks, cu_q, cu_k, cu_p, kv_idx, max(k_lens), causal=causal)
         assert theirs.shape == ours.shape == ref.shape
-        for name, mine in (("kernel", ours.cpu()), ("oracle", ref)):
+        for name, mine in (("kernel", ours.cpu()), ("tensor-core kernel", fast.cpu()), ("oracle", ref)):
             t = theirs.cpu()
             assert torch.equal(torch.isinf(t), torch.isinf(mine)), name
             fin = torch.isfinite(t)
