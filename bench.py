@@ -266,6 +266,7 @@ class Workload:
             st["indexer_ms"] = timed(sel.run_fast, steps, warmup, barrier)     # pool + tensor-core select
             st["indexer_select_ms"] = st["indexer_ms"] - st["indexer_pool_ms"]
             st["indexer_fallback_lists"] = sel.fallback_lists()
+            st["indexer_bound_violations"], st["indexer_max_err_over_bound"] = sel.bound_stats()
             self.ids = sel.ids
             self.selector = sel
             st["indexer_bytes"] = (self.q.numel() + self.k.numel()) * 2 + self.ids.numel() * 4

@@ -167,9 +167,13 @@ int sparse_b200_indexer_summary(const void* q, const void* k, void* q_desc, void
  * tensor-core pre-filter (tcgen05 MMA on the pooled descriptors) followed by exact
  * re-scoring of the surviving candidates and an exact fallback per list when the
  * pre-filter cannot be proven safe. No scores output. `aux` is a device workspace
- * of sparse_b200_indexer_summary_aux_bytes(B, Hkv) bytes; its last int counts the
- * lists that took the fallback. Shapes the tensor-core path does not cover run the
- * exact kernel. Replaces descriptor_dot + reduce_topk (indexers/r1_r4/gpu_ops.py:19-49). */
+ * of sparse_b200_indexer_summary_aux_bytes(B, Hkv) bytes (layout below). Shapes the
+ * tensor-core path does not cover run the exact kernel. Replaces descriptor_dot +
+ * reduce_topk (indexers/r1_r4/gpu_ops.py:19-49).
+ * aux: 2*B*Hkv floats of key statistics, then three words written by every call: lists that
+ * took the exact fallback (int), re-scored candidates whose tensor-core score differed from
+ * the exact one by more than the error bound (int; such a list takes the fallback, so the ids
+ * stay exact), largest observed difference as a fraction of the bound (float). */
 int64_t sparse_b200_indexer_summary_aux_bytes(int batch, int hkv);
 int sparse_b200_indexer_summary_fast(const void* q, const void* k, void* q_desc, void* k_desc, void* aux,
                                      int32_t* block_idx, int batch, int hq, int hkv, int sq, int skv,

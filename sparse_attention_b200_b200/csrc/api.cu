@@ -278,7 +278,7 @@ int sparse_b200_indexer_summary(const void* q, const void* k, void* q_desc, void
 
 int64_t sparse_b200_indexer_summary_aux_bytes(int batch, int hkv) {
   if (batch <= 0 || hkv <= 0) return SB_ERR_INVALID;
-  return (2 * static_cast<int64_t>(batch) * hkv + 1) * 4;
+  return (2 * static_cast<int64_t>(batch) * hkv + 3) * 4;
 }
 
 int sparse_b200_indexer_summary_fast(const void* q, const void* k, void* q_desc, void* k_desc, void* aux,

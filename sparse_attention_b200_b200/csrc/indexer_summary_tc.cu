@@ -19,6 +19,9 @@
 //      safe: a lower bound of the k-th exact score > C-th approximate score + delta;
 //   4. otherwise (ties that reach beyond the candidates, e.g. constant inputs) the list
 //      falls back to exact scores of all blocks.
+// The bound checks itself: every re-scored candidate has both of its scores in hand; a
+// difference above delta sends the list to the exact fallback and is counted, and the largest
+// observed |approximate - exact| / delta is kept for inspection.
 // Replaces descriptor_dot + reduce_topk (indexers/r1_r4/gpu_ops.py:19-49).
 #include "ptx.cuh"
 #include "internal.h"
@@ -57,6 +60,8 @@ struct Params {
   int32_t* ids;                // [B, Hkv, qt, topk]
   int* status;
   int* fallbacks;              // optional counter of lists that took the exact fallback
+  int* violations;             // re-scored candidates whose two scores differed by more than delta
+  int* max_ratio;              // largest observed |approximate - exact| / delta (float bits)
   int hq, hkv, qt, nt, r, topk, qb, cand;
   int q_chunks;                // ceil(qt / qb)
 };
@@ -243,6 +248,7 @@ score_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant
   float* delta_s = reinterpret_cast<float*>(work_cnt + SEL_WARPS);   // [SEL_WARPS] error bound of a list
   float* kth_s = delta_s + SEL_WARPS;                    // [SEL_WARPS] lower bound of the k-th exact score
   int* l2_s = reinterpret_cast<int*>(kth_s + SEL_WARPS);  // [SEL_WARPS] largest squared L2 norm of a query descriptor
+  volatile int* viol_s = l2_s + SEL_WARPS;                // [SEL_WARPS] a re-scored candidate of the list broke the bound
   int* l1_s = scratch_i + 20;                            // [SEL_WARPS] largest L1 norm of a list's query descriptors
   auto bar = [&](int i) { return bar0 + 8u * i; };
   enum { A_FULL = 0, A_EMPTY = A_STAGES, B_FULL = 2 * A_STAGES, ACC_FULL = 2 * A_STAGES + 1, ACC_EMPTY = 2 * A_STAGES + 3 };
@@ -626,6 +632,7 @@ score_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant
         delta_s[slot] = delta;
         work_cnt[slot] = 0;
         kth_s[slot] = -INFINITY;
+        viol_s[slot] = 0;
       }
     }
     __syncthreads();
@@ -706,6 +713,14 @@ score_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant
       const float a = apx[c];
       const int o = ord[c], id = ids_l[c];
       const float e = ord2f(o) * SCALE;
+      if (o != INT_MIN && e == e) {              // both scores in hand: the bound must hold
+        const float diff = fabsf(a - e);
+        if (dl > 0.f) atomicMax(p.max_ratio, __float_as_int(diff / dl));
+        if (!(diff <= dl)) {
+          viol_s[l] = 1;
+          atomicAdd(p.violations, 1);
+        }
+      }
       int rank = 0;
 #pragma unroll 4
       for (int j = 0; j < C; ++j) {
@@ -720,7 +735,7 @@ score_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant
     }
     __syncthreads();
     // safe: no block outside the candidates (exact score <= thr + delta) can reach the top k
-    if (mine && lane == 0) flags[tl] = ((C >= p.nt) || (kth_s[slot] > thr + delta)) ? 0 : 1;
+    if (mine && lane == 0) flags[tl] = (!viol_s[slot] && ((C >= p.nt) || (kth_s[slot] > thr + delta))) ? 0 : 1;
     if (tl0 + SEL_WARPS < lists) {               // another round re-uses the buffers
       __syncthreads();
       if (threadIdx.x < SEL_WARPS) l1_s[threadIdx.x] = l2_s[threadIdx.x] = 0;
@@ -811,7 +826,8 @@ static int launch_gr(const CUtensorMap& qm, const CUtensorMap& km, const Params&
 // Returns SB_OK when the tensor-core path ran, 1 when the problem is not eligible
 // (the caller then runs the exact kernel), negative on error.
 // aux: device floats [B*Hkv] (key abs-max) + [B*Hkv] (largest squared key norm), both filled
-// here, + 1 int (fallback counter).
+// here, + 3 words: lists that took the exact fallback (int), re-scored candidates that broke the error
+// bound (int), largest observed |approximate - exact| / delta (float).
 int launch_summary_select_tc(const void* qd, const void* kd, void* aux, int32_t* ids, int batch, int hq, int hkv,
                              int qt, int nt, int r, int topk, cudaStream_t stream) {
   using namespace stc;
@@ -853,7 +869,7 @@ int launch_summary_select_tc(const void* qd, const void* kd, void* aux, int32_t*
   float* absmax = static_cast<float*>(aux);
   float* norm2 = absmax + static_cast<size_t>(batch) * hkv;
   int* fallbacks = reinterpret_cast<int*>(norm2 + static_cast<size_t>(batch) * hkv);
-  if (cudaMemsetAsync(aux, 0, (2 * static_cast<size_t>(batch) * hkv + 1) * 4, stream) != cudaSuccess)
+  if (cudaMemsetAsync(aux, 0, (2 * static_cast<size_t>(batch) * hkv + 3) * 4, stream) != cudaSuccess)
     return set_error(SB_ERR_CUDA, "memset failed");
   const long long per_head = static_cast<long long>(nt) * r * 128;
   int chunks = static_cast<int>((per_head / 8 + 256 * 8 - 1) / (256 * 8));
@@ -869,11 +885,13 @@ int launch_summary_select_tc(const void* qd, const void* kd, void* aux, int32_t*
   p.ids = ids;
   p.status = ctx->status;
   p.fallbacks = fallbacks;
+  p.violations = fallbacks + 1;
+  p.max_ratio = fallbacks + 2;
   p.hq = hq; p.hkv = hkv; p.qt = qt; p.nt = nt; p.r = r; p.topk = topk; p.qb = qb; p.cand = cand;
   p.q_chunks = (qt + qb - 1) / qb;
   const int grid = batch * hkv * p.q_chunks;
   const size_t smem = OFF_SCORES + ((static_cast<size_t>(qb) * nt * 4 + 15) & ~static_cast<size_t>(15)) + 144 +
-                      128 * 4 + 20 * 4 + 20 * 4 + 5 * SEL_WARPS * 4 + 1024;
+                      128 * 4 + 20 * 4 + 20 * 4 + 6 * SEL_WARPS * 4 + 1024;
   switch (gr) {
     case 1: return launch_gr<1>(qm, km, p, grid, smem, ctx, 0, stream);
     case 2: return launch_gr<2>(qm, km, p, grid, smem, ctx, 1, stream);

@@ -39,8 +39,8 @@ class SummarySelector:
             if keep_scores else None
         self.ids = torch.empty((b, hkv, self.qt, topk), dtype=torch.int32, device=q.device)
         # workspace of the tensor-core path: key abs-max and largest squared key norm per (batch, KV head)
-        # + fallback counter (sparse_b200_indexer_summary_aux_bytes)
-        self.aux = torch.zeros(2 * b * hkv + 1, dtype=torch.int32, device=q.device)
+        # + fallback counter, bound-violation counter, largest error / bound (sparse_b200_indexer_summary_aux_bytes)
+        self.aux = torch.zeros(2 * b * hkv + 3, dtype=torch.int32, device=q.device)
         self.name = f"mean{r}_bf16"
 
     def prepare(self):
@@ -73,7 +73,13 @@ class SummarySelector:
 
     def fallback_lists(self):
         """Lists of the last run_fast() that needed the exact fallback (synchronising)."""
-        return int(self.aux[-1].item())
+        return int(self.aux[2 * self.b * self.hkv].item())
+
+    def bound_stats(self):
+        """(re-scored candidates whose tensor-core score was further than the error bound from the exact one,
+        largest observed |tensor-core - exact| / bound) of the last run_fast() (synchronising)."""
+        tail = self.aux[2 * self.b * self.hkv + 1:].cpu()
+        return int(tail[0]), float(tail[1:2].view(torch.float32))
 
     def run(self):
         if self.scores is None:

@@ -236,6 +236,50 @@ def test_summary_selector_duplicate_scores_tie_to_lower_id():
     assert pos[2] + 1 == pos[5] and pos[5] + 1 == pos[9]
 
 
+@pytest.mark.parametrize("family", ["row_scales_2^+-12", "cancellation_amplitude_64", "near_subnormal", "gaussian_long"])
+def test_summary_tensor_core_bound_holds_on_stress_inputs(family):
+    """Bit-exact ids of the tensor-core selector rest on |tcgen05 bf16 MMA score - canonical fp32 score| <=
+    delta = 2^-14 * (bound on the sum of |q_d k_d|). Inputs that stress it: token rows scaled by powers of
+    two between 2^-12 and 2^12 (descriptors of wildly different magnitude inside one list), the
+    reference's cancellation_stress family at amplitude 64 (large terms that cancel), values next to
+    the bf16 subnormal range, and long gaussian lists. The kernel compares both scores of every
+    re-scored candidate: no violation may be counted, the largest observed difference must stay under
+    a quarter of the bound, and the ids must equal the exact kernel's."""
+    m = sp()
+    b, hq, hkv, sq, skv, r, topk = 1, 16, 2, 2048, 32768, 4, 32
+    g = torch.Generator().manual_seed(len(family))
+    q = torch.randn((b, hq, sq, 128), generator=g)
+    k = torch.randn((b, hkv, skv, 128), generator=g)
+    if family == "row_scales_2^+-12":
+        q = q * torch.exp2(torch.randint(-12, 13, (b, hq, sq, 1), generator=g).float())
+        k = k * torch.exp2(torch.randint(-12, 13, (b, hkv, skv, 1), generator=g).float())
+    elif family == "cancellation_amplitude_64":
+        # benchmarks/ch4_selectors/reference.py:12-21: a large common component with alternating sign + small noise
+        sign = torch.where(torch.arange(128) % 2 == 0, 1.0, -1.0)
+        q = 64.0 * sign + 0.01 * q
+        k = 64.0 + 0.01 * k
+    elif family == "near_subnormal":
+        q = q * 2.0 ** -60
+        k = k * 2.0 ** -62
+    # every KV block gets an identical twin in the second half of the sequence: all candidates come in exact
+    # ties, so every one of them is re-scored and checked (lists whose ties straddle the candidate cut take
+    # the exact fallback, as they must)
+    k[:, :, skv // 2:] = k[:, :, :skv // 2]
+    q, k = q.to(torch.bfloat16).cuda(), k.to(torch.bfloat16).cuda()
+    fast = m.SummarySelector(q, k, r, topk=topk, keep_scores=False)
+    ids = fast.run_fast().clone()
+    exact = m.SummarySelector(q, k, r, topk=topk, keep_scores=False)
+    exact.prepare()
+    exact.score()
+    torch.cuda.synchronize()
+    m.device_status()
+    violations, ratio = fast.bound_stats()
+    print(f"{family}: fallback lists {fast.fallback_lists()}, violations {violations}, max |approx - exact| / delta {ratio:.3g}")
+    assert torch.equal(ids, exact.ids)
+    assert violations == 0
+    assert ratio <= 0.25
+
+
 def test_fp4_reference_gate_and_bit_exact():
     m = sp()
     fx = np.load(os.path.join(G, "fp4.npz"))
