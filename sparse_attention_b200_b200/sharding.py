@@ -10,7 +10,8 @@ Two ways to shard, both without TMA multicast or any load from a peer's memory:
   selection list to its range, runs the same attention kernel and gets a normalised
   partial (O_r, L_r) for EVERY query; one exchange step then moves the slice of rows
   a rank owns from every peer into local memory (NCCL send/recv), and the local
-  Combine kernel merges them by log-sum-exp (`KVSplit`).
+  Combine kernel merges them by log-sum-exp (`KVSplit`); `KVSplit.run_pipelined` does it in chunks of head
+  pairs, the exchange of one chunk under the attention of the next.
 
 The reference has no multi-GPU path; this module adds the one the 1 Mi-token
 configuration needs.
@@ -137,3 +138,81 @@ class KVSplit:
     def run(self, q, k_local, v_local, ids, kv_blocks, counts=None):
         o_r, l_r = self.partial(q, k_local, v_local, ids, kv_blocks, counts)
         return self.merge(o_r, l_r)
+
+    # ------------------------------------------------------------------ pipelined form
+    def chunks(self, q, heads_per_chunk=2):
+        """(group, first head, heads) chunks of q [B,Hq,Sq,128] seen as [groups, G, Sq, 128] with Hkv = 1 per
+        group (the layout of a rank's problem); chunk c is merged on rank c % R."""
+        groups, g = q.shape[0], q.shape[1]
+        hpc = heads_per_chunk if g % heads_per_chunk == 0 else g
+        return [(grp, h0, hpc) for grp in range(groups) for h0 in range(0, g, hpc)]
+
+    def run_pipelined(self, q, k_local, v_local, ids, kv_blocks, counts=None, heads_per_chunk=2):
+        """Same merge, chunk by chunk: q [groups, G, Sq, 128] with one KV head per group (k_local / v_local
+        [groups, 1, Skv/R, 128], ids [groups, 1, Sq/128, TopK]). The attention of chunk c + 1 runs on the
+        current stream while the partials of chunk c travel to the chunk's owner (rank c % R) on a side
+        stream; the owner merges what it received with its own partial. Returns {chunk index: (O
+        [heads*Sq, 128] bf16, LSE [heads*Sq] fp32)} for the chunks this rank owns; `self.chunks(q)` names them.
+        On CPU tensors (gloo) everything runs in order."""
+        if k_local.shape[1] != 1 or ids.shape[1] != 1:
+            raise ValueError("run_pipelined takes the per-group layout: one KV head per leading index")
+        on_gpu = q.is_cuda
+        ids_r, counts_r = self.filter_fn(ids, counts, kv_blocks, self.ranks, self.rank)
+        plan = self.chunks(q, heads_per_chunk)
+        cur = torch.cuda.current_stream(q.device) if on_gpu else None
+        side = self._side_stream(q.device) if on_gpu else None
+        if on_gpu:
+            side.wait_stream(cur)
+        received, own, sent = {}, {}, []
+        for c, (grp, h0, nh) in enumerate(plan):
+            o_c, l_c = self.attention_fn(q[grp:grp + 1, h0:h0 + nh], k_local[grp:grp + 1], v_local[grp:grp + 1],
+                                         ids_r[grp:grp + 1], counts_r[grp:grp + 1])
+            o_c, l_c = o_c.reshape(-1, 128), l_c.reshape(-1)
+            owner = c % self.ranks
+            ready = None
+            if on_gpu:
+                ready = torch.cuda.Event()
+                ready.record(cur)
+            ctx = torch.cuda.stream(side) if on_gpu else _NullContext()
+            with ctx:
+                if on_gpu:
+                    side.wait_event(ready)
+                ops = []
+                if owner == self.rank:
+                    own[c] = (o_c, l_c)
+                    bufs = []
+                    for peer in range(self.ranks):
+                        if peer == self.rank:
+                            continue
+                        gp = dist.get_global_rank(self.group, peer) if self.group is not None else peer
+                        bo, bl = torch.empty_like(o_c), torch.empty_like(l_c)
+                        ops += [dist.P2POp(dist.irecv, bo, gp, self.group), dist.P2POp(dist.irecv, bl, gp, self.group)]
+                        bufs.append((peer, bo, bl))
+                    received[c] = bufs
+                else:
+                    gp = dist.get_global_rank(self.group, owner) if self.group is not None else owner
+                    ops += [dist.P2POp(dist.isend, o_c, gp, self.group), dist.P2POp(dist.isend, l_c, gp, self.group)]
+                    sent.append((o_c, l_c))            # keep the buffers alive until the transfers have run
+                if ops:
+                    for req in dist.batch_isend_irecv(ops):
+                        req.wait()
+        if on_gpu:
+            cur.wait_stream(side)
+        out = {}
+        for c, (o_c, l_c) in own.items():
+            parts = sorted([(self.rank, o_c, l_c)] + received[c], key=lambda t: t[0])     # fixed rank order
+            out[c] = self.combine_fn(torch.stack([p[1] for p in parts]), torch.stack([p[2] for p in parts]))
+        return out
+
+    def _side_stream(self, device):
+        if getattr(self, "_side", None) is None:
+            self._side = torch.cuda.Stream(device=device)
+        return self._side
+
+
+class _NullContext:
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        return False

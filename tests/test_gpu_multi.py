@@ -48,6 +48,20 @@ def _worker(rank, world, port, result):
         d = (o_slice.float().cpu() - ref_o).abs()
         ok = ok and d.max().item() <= 2e-2 and d.mean().item() <= 2e-3
         ok = ok and bool(torch.all((l_slice.cpu() - ref_l).abs() <= 1e-3 * ref_l.abs().clamp_min(1.0)))
+        # pipelined form: chunks of two heads, the exchange of one under the attention of the next
+        qg, kg, vg, ig, _ = sharding.group_view(q.cuda(), k_local, v_local, ids, 0, 2)
+        merged = split.run_pipelined(qg, kg, vg, ig, 64, heads_per_chunk=2)
+        torch.cuda.synchronize()
+        sp.device_status()
+        plan = split.chunks(qg, 2)
+        ok = ok and sorted(merged) == [c for c in range(len(plan)) if c % world == rank]
+        for c, (oc, lc) in merged.items():
+            grp, h0, nh = plan[c]
+            ref_oc = whole_o[0, grp * 8 + h0:grp * 8 + h0 + nh].reshape(-1, 128)
+            ref_lc = whole_l[0, grp * 8 + h0:grp * 8 + h0 + nh].reshape(-1)
+            dc = (oc.float().cpu() - ref_oc).abs()
+            ok = ok and dc.max().item() <= 2e-2 and dc.mean().item() <= 2e-3
+            ok = ok and bool(torch.all((lc.cpu() - ref_lc).abs() <= 1e-3 * ref_lc.abs().clamp_min(1.0)))
         # head-group sharding: no collective, each rank its own groups
         a, b = sharding.group_range(2, world, rank)
         qv, kv, vv, iv, _ = sharding.group_view(q.cuda(), k.cuda(), v.cuda(), ids, a, b)

@@ -82,6 +82,15 @@ def _worker(rank, world, port, result):
         ref_o = whole_o.reshape(-1, 128)[rank * rows:(rank + 1) * rows]
         ref_l = whole_l.reshape(-1)[rank * rows:(rank + 1) * rows]
         ok = torch.allclose(o_slice, ref_o, atol=2e-6) and torch.allclose(l_slice, ref_l, atol=2e-6)
+        # pipelined form (chunks of head pairs, owner = chunk % ranks): every chunk merged exactly once
+        qg, kg, vg, ig, _ = sharding.group_view(q, k_local, v_local, ids, 0, 2)
+        merged = split.run_pipelined(qg, kg, vg, ig, kv_blocks, heads_per_chunk=1)
+        plan = split.chunks(qg, 1)
+        ok = ok and sorted(merged) == [c for c in range(len(plan)) if c % world == rank]
+        for c, (oc, lc) in merged.items():
+            grp, h0, nh = plan[c]
+            ok = ok and torch.allclose(oc, whole_o[0, grp * 2 + h0:grp * 2 + h0 + nh].reshape(-1, 128), atol=2e-6)
+            ok = ok and torch.allclose(lc, whole_l[0, grp * 2 + h0:grp * 2 + h0 + nh].reshape(-1), atol=2e-6)
         # a rank with an empty filtered list contributed (0, -inf) for that row block
         _, cnt = filter_fn(ids, None, kv_blocks, world, rank)
         if rank == 1:
