@@ -246,7 +246,7 @@ def test_summary_tensor_core_bound_holds_on_stress_inputs(family):
     re-scored candidate: no violation may be counted, the largest observed difference must stay under
     a quarter of the bound, and the ids must equal the exact kernel's."""
     m = sp()
-    b, hq, hkv, sq, skv, r, topk = 1, 16, 2, 2048, 32768, 4, 32
+    b, hq, hkv, sq, skv, r, topk = 1, 8, 1, 160 * 128, 32768, 4, 32      # 160 lists: more than one per SM, so the tensor-core path runs
     g = torch.Generator().manual_seed(len(family))
     q = torch.randn((b, hq, sq, 128), generator=g)
     k = torch.randn((b, hkv, skv, 128), generator=g)
@@ -278,6 +278,8 @@ def test_summary_tensor_core_bound_holds_on_stress_inputs(family):
     assert torch.equal(ids, exact.ids)
     assert violations == 0
     assert ratio <= 0.25
+    if family != "cancellation_amplitude_64":    # there bf16 rounds the noise away: every score is exactly 0 on both paths
+        assert ratio > 0                         # > 0: candidates were re-scored, i.e. the check did run
 
 
 def test_fp4_reference_gate_and_bit_exact():
