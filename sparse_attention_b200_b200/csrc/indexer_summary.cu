@@ -63,7 +63,10 @@ template <int MP>
 __global__ void __launch_bounds__(256) score_topk_kernel(const __nv_bfloat16* __restrict__ qd,
                                                          const __nv_bfloat16* __restrict__ kd,
                                                          float* __restrict__ scores_out, int32_t* __restrict__ ids_out,
-                                                         int hq, int hkv, int qt, int nt, int r, int topk) {
+                                                         int hq, int hkv, int qt, int nt, int r, int topk,
+                                                         int flagged_only) {
+  // second pass after a pre-filter kernel: only lists it marked with -1 as their first id
+  if (flagged_only && ids_out[static_cast<long long>(blockIdx.x) * topk] != -1) return;
   extern __shared__ float smem[];
   float* q_s = smem;                         // [128][MP]
   float* scores = q_s + 128 * MP;            // [nt]
@@ -128,7 +131,8 @@ __global__ void __launch_bounds__(256) score_topk_kernel(const __nv_bfloat16* __
 
 template <int MP>
 int launch_score(const __nv_bfloat16* qd, const __nv_bfloat16* kd, float* scores, int32_t* ids, int batch, int hq,
-                 int hkv, int qt, int nt, int r, int topk, DeviceCtx* ctx, int slot, cudaStream_t stream) {
+                 int hkv, int qt, int nt, int r, int topk, DeviceCtx* ctx, int slot, cudaStream_t stream,
+                 int flagged_only) {
   const size_t smem = (128 * MP + nt + 10) * sizeof(float) + 16 * sizeof(int);
   if (smem > 200 * 1024) return set_error(SB_ERR_INVALID, "too many KV blocks for the summary indexer (shared memory)");
   if (!ctx->misc_attr[slot]) {
@@ -136,7 +140,8 @@ int launch_score(const __nv_bfloat16* qd, const __nv_bfloat16* kd, float* scores
     if (e != cudaSuccess) return set_error(SB_ERR_CUDA, cudaGetErrorString(e));
     ctx->misc_attr[slot] = 1;
   }
-  score_topk_kernel<MP><<<batch * hkv * qt, 256, smem, stream>>>(qd, kd, scores, ids, hq, hkv, qt, nt, r, topk);
+  score_topk_kernel<MP><<<batch * hkv * qt, 256, smem, stream>>>(qd, kd, scores, ids, hq, hkv, qt, nt, r, topk,
+                                                                  flagged_only);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? SB_OK : set_error(SB_ERR_CUDA, cudaGetErrorString(e));
 }
@@ -153,17 +158,17 @@ int launch_pool(const void* x, void* desc, long long num_desc, int tokens_per_de
 }
 
 int launch_summary_score_topk(const void* qd, const void* kd, float* scores, int32_t* ids, int batch, int hq, int hkv,
-                              int qt, int nt, int r, int topk, cudaStream_t stream) {
+                              int qt, int nt, int r, int topk, cudaStream_t stream, int flagged_only) {
   DeviceCtx* ctx = device_ctx();
   if (!ctx) return SB_ERR_CUDA;
   const int m = (hq / hkv) * r;
   const __nv_bfloat16* q = static_cast<const __nv_bfloat16*>(qd);
   const __nv_bfloat16* k = static_cast<const __nv_bfloat16*>(kd);
-  if (m <= 4) return launch_score<4>(q, k, scores, ids, batch, hq, hkv, qt, nt, r, topk, ctx, 0, stream);
-  if (m <= 8) return launch_score<8>(q, k, scores, ids, batch, hq, hkv, qt, nt, r, topk, ctx, 1, stream);
-  if (m <= 16) return launch_score<16>(q, k, scores, ids, batch, hq, hkv, qt, nt, r, topk, ctx, 2, stream);
-  if (m <= 32) return launch_score<32>(q, k, scores, ids, batch, hq, hkv, qt, nt, r, topk, ctx, 3, stream);
-  if (m <= 64) return launch_score<64>(q, k, scores, ids, batch, hq, hkv, qt, nt, r, topk, ctx, 4, stream);
+  if (m <= 4) return launch_score<4>(q, k, scores, ids, batch, hq, hkv, qt, nt, r, topk, ctx, 0, stream, flagged_only);
+  if (m <= 8) return launch_score<8>(q, k, scores, ids, batch, hq, hkv, qt, nt, r, topk, ctx, 1, stream, flagged_only);
+  if (m <= 16) return launch_score<16>(q, k, scores, ids, batch, hq, hkv, qt, nt, r, topk, ctx, 2, stream, flagged_only);
+  if (m <= 32) return launch_score<32>(q, k, scores, ids, batch, hq, hkv, qt, nt, r, topk, ctx, 3, stream, flagged_only);
+  if (m <= 64) return launch_score<64>(q, k, scores, ids, batch, hq, hkv, qt, nt, r, topk, ctx, 4, stream, flagged_only);
   return set_error(SB_ERR_INVALID, "group size x representatives must not exceed 64");
 }
 

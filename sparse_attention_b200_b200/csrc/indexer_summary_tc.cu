@@ -23,10 +23,8 @@
 // difference above delta sends the list to the exact fallback and is counted, and the largest
 // observed |approximate - exact| / delta is kept for inspection.
 // Replaces descriptor_dot + reduce_topk (indexers/r1_r4/gpu_ops.py:19-49).
-#include "ptx.cuh"
-#include "internal.h"
+#include "summary_tc_common.cuh"
 #include "topk.cuh"
-#include <cuda_bf16.h>
 
 namespace sb {
 namespace stc {
@@ -38,58 +36,16 @@ constexpr int PANEL_BYTES = 128 * 128;
 #endif
 constexpr int A_STAGES = SB_STC_STAGES;
 constexpr int SCORE_LIMIT = 232448 - 2048 - (A_STAGES + 1) * TILE_BYTES;   // bytes of shared memory left for scores
-constexpr int C_MAX = 192;                 // candidates per list
 constexpr int LIST_WORDS = 3 * C_MAX;      // per list: block ids, approximate scores, exact scores (ordered ints)
 constexpr int NUM_THREADS = 512;            // ten warps have a role in the scoring phase; all sixteen re-score
 constexpr int EPI_WARPS = 8;               // two column halves x four TMEM lane quarters
 constexpr int SEL_WARPS = 8;               // warps of the selection phase (one list each at a time)
 constexpr int TMA_WARP = 8, MMA_WARP = 9;
-constexpr float EPS = 6.103515625e-05f;    // 2^-14
-constexpr float SCALE = 0.08838834764831845f;
 
 constexpr int OFF_A = 0;
 constexpr int OFF_B = A_STAGES * TILE_BYTES;
 constexpr int OFF_SCORES = OFF_B + TILE_BYTES;
 // after the scores: barriers, candidate arrays, scratch (offsets computed at run time)
-
-struct Params {
-  const __nv_bfloat16* qd;     // [B, Hq, qt, R, 128]
-  const __nv_bfloat16* kd;     // [B, Hkv, nt, R, 128]
-  const float* k_absmax;       // [B * Hkv] max |element| of the key descriptors of a head
-  const float* k_norm2;        // [B * Hkv] max squared L2 norm of a key descriptor of the head
-  int32_t* ids;                // [B, Hkv, qt, topk]
-  int* status;
-  int* fallbacks;              // optional counter of lists that took the exact fallback
-  int* violations;             // re-scored candidates whose two scores differed by more than delta
-  int* max_ratio;              // largest observed |approximate - exact| / delta (float bits)
-  int hq, hkv, qt, nt, r, topk, qb, cand;
-  int q_chunks;                // ceil(qt / qb)
-};
-
-// monotone float <-> int mapping so shared-memory atomicMax works on scores
-__device__ __forceinline__ int f2ord(float f) {
-  const int i = __float_as_int(f);
-  return i >= 0 ? i : i ^ 0x7fffffff;
-}
-__device__ __forceinline__ float ord2f(int i) { return __int_as_float(i >= 0 ? i : i ^ 0x7fffffff); }
-
-__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, int c3,
-                                            uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes "
-      "[%0], [%1, {%2, %3, %4, %5}], [%6];" ::"r"(dst),
-      "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(bar)
-      : "memory");
-}
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-      : "r"(taddr)
-      : "memory");
-}
 
 // Exact score contribution of one key descriptor: max over the MP query rows of
 // the fp32 dot product accumulated in feature order (q_s is [128][MP] fp32, 16-byte
@@ -531,7 +487,10 @@ score_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant
         // keys are fetched eight at a time: a load cannot be moved above an atomic by the
         // compiler, and one round trip to shared memory per key is what this loop costs otherwise
         const unsigned top = pass == 0 ? 0u : W >> (shift + 8);
-        for (int j0 = lo + lane; j0 < hi; j0 += 256) {
+        // the trip count must be the same for every lane (the vote below takes the whole warp): the loop
+        // runs on the slice's first index, the lane offset is added inside
+        for (int jb = lo; jb < hi; jb += 256) {
+          const int j0 = jb + lane;
           unsigned x[8];
           bool any = false;
 #pragma unroll
@@ -837,13 +796,52 @@ int launch_summary_select_tc(const void* qd, const void* kd, void* aux, int32_t*
   int cand = topk + extra;
   if (cand > nt) cand = nt;
   if (cand > C_MAX) return 1;
+  if (static_cast<long long>(batch) * hkv * nt * r >= (1LL << 31) || r > 256 || group > 256) return 1;
+  // the one-CTA-per-unit kernel keeps all scores of its lists in shared memory
   int qb = 128 / gr;
   while (qb > 1 && qb * gr > 16 && (qb / 2) >= qt) qb >>= 1;        // do not cover far more query blocks than exist
   while (static_cast<long long>(qb) * nt * 4 > SCORE_LIMIT && qb * gr > 16) qb >>= 1;
-  if (static_cast<long long>(qb) * nt * 4 > SCORE_LIMIT || qb * gr < 16) return 1;
-  if (static_cast<long long>(batch) * hkv * nt * r >= (1LL << 31) || qb > 256 || r > 256 || group > 256) return 1;
+  const bool unit_form_ok = !(static_cast<long long>(qb) * nt * 4 > SCORE_LIMIT || qb * gr < 16 || qb > 256);
+  // The persistent kernel overlaps the selection of one unit with the scoring of the next; it pays
+  // where scoring dominates (long lists). Short lists are selection-bound and stay with the kernel
+  // whose whole CTA selects.
+  const bool stream_form_ok = gr == 32 && qt >= 256 / gr && r <= 4 &&
+                              (static_cast<long long>(nt) * r >= STREAM_MIN_KEY_ROWS || !unit_form_ok);
+  if (!unit_form_ok && !stream_form_ok) return 1;
   DeviceCtx* ctx = device_ctx();
   if (!ctx) return SB_ERR_CUDA;
+
+  float* absmax = static_cast<float*>(aux);
+  float* norm2 = absmax + static_cast<size_t>(batch) * hkv;
+  int* fallbacks = reinterpret_cast<int*>(norm2 + static_cast<size_t>(batch) * hkv);
+  if (cudaMemsetAsync(aux, 0, (2 * static_cast<size_t>(batch) * hkv + 3) * 4, stream) != cudaSuccess)
+    return set_error(SB_ERR_CUDA, "memset failed");
+  const long long per_head = static_cast<long long>(nt) * r * 128;
+  int chunks = static_cast<int>((per_head / 8 + 256 * 8 - 1) / (256 * 8));
+  if (chunks > 64) chunks = 64;
+  if (chunks < 1) chunks = 1;
+  absmax_kernel<<<dim3(chunks, batch * hkv), 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(kd), absmax, norm2, per_head);
+
+  Params p{};
+  p.qd = static_cast<const __nv_bfloat16*>(qd);
+  p.kd = static_cast<const __nv_bfloat16*>(kd);
+  p.k_absmax = absmax;
+  p.k_norm2 = norm2;
+  p.ids = ids;
+  p.status = ctx->status;
+  p.fallbacks = fallbacks;
+  p.violations = fallbacks + 1;
+  p.max_ratio = fallbacks + 2;
+  p.hq = hq; p.hkv = hkv; p.qt = qt; p.nt = nt; p.r = r; p.topk = topk; p.cand = cand;
+
+  if (stream_form_ok) {
+    // lists it could not prove carry -1 as their first id and are re-done exactly
+    int rc = launch_summary_stream(qd, kd, p, batch, ctx, stream);
+    if (rc == SB_OK)
+      return launch_summary_score_topk(qd, kd, nullptr, ids, batch, hq, hkv, qt, nt, r, topk, stream, 1);
+    if (rc != 1) return rc;
+  }
+  if (!unit_form_ok) return 1;
 
   CUtensorMap qm, km;
   {
@@ -866,28 +864,7 @@ int launch_summary_select_tc(const void* qd, const void* kd, void* aux, int32_t*
                      CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B))
       return 1;
   }
-  float* absmax = static_cast<float*>(aux);
-  float* norm2 = absmax + static_cast<size_t>(batch) * hkv;
-  int* fallbacks = reinterpret_cast<int*>(norm2 + static_cast<size_t>(batch) * hkv);
-  if (cudaMemsetAsync(aux, 0, (2 * static_cast<size_t>(batch) * hkv + 3) * 4, stream) != cudaSuccess)
-    return set_error(SB_ERR_CUDA, "memset failed");
-  const long long per_head = static_cast<long long>(nt) * r * 128;
-  int chunks = static_cast<int>((per_head / 8 + 256 * 8 - 1) / (256 * 8));
-  if (chunks > 64) chunks = 64;
-  if (chunks < 1) chunks = 1;
-  absmax_kernel<<<dim3(chunks, batch * hkv), 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(kd), absmax, norm2, per_head);
-
-  Params p{};
-  p.qd = static_cast<const __nv_bfloat16*>(qd);
-  p.kd = static_cast<const __nv_bfloat16*>(kd);
-  p.k_absmax = absmax;
-  p.k_norm2 = norm2;
-  p.ids = ids;
-  p.status = ctx->status;
-  p.fallbacks = fallbacks;
-  p.violations = fallbacks + 1;
-  p.max_ratio = fallbacks + 2;
-  p.hq = hq; p.hkv = hkv; p.qt = qt; p.nt = nt; p.r = r; p.topk = topk; p.qb = qb; p.cand = cand;
+  p.qb = qb;
   p.q_chunks = (qt + qb - 1) / qb;
   const int grid = batch * hkv * p.q_chunks;
   const size_t smem = OFF_SCORES + ((static_cast<size_t>(qb) * nt * 4 + 15) & ~static_cast<size_t>(15)) + 144 +

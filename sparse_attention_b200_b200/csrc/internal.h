@@ -53,8 +53,9 @@ int launch_pool_small_pair(const void* x, void* desc, long long num_desc, const 
 // returns 1 when the problem is not small; fallback_counter (may be null) is reset to 0
 int launch_summary_small(const void* qd, const void* kd, float* scores, int32_t* ids, int32_t* fallback_counter,
                          int batch, int hq, int hkv, int qt, int nt, int r, int topk, cudaStream_t stream);
+// flagged_only: re-do only the lists whose first id is -1 (second pass after a pre-filter kernel)
 int launch_summary_score_topk(const void* qd, const void* kd, float* scores, int32_t* ids, int batch, int hq, int hkv,
-                              int qt, int nt, int r, int topk, cudaStream_t stream);
+                              int qt, int nt, int r, int topk, cudaStream_t stream, int flagged_only = 0);
 int launch_summary_select_tc(const void* qd, const void* kd, void* aux, int32_t* ids, int batch, int hq, int hkv,
                              int qt, int nt, int r, int topk, cudaStream_t stream);
 int launch_fp4_indexer_tc(const void* qp, const void* qs, const void* kp, const void* ks, void* aux, int32_t* ids,

@@ -162,6 +162,69 @@ def test_summary_selector_tensor_core_path_long_lists(shape):
     print("lists that fell back to exact scoring:", sel.fallback_lists())
 
 
+@pytest.mark.parametrize("shape", [
+    # B, Hq, Hkv, Sq, Skv, R, topk: the persistent form (32 query descriptors per list, at least 8 query
+    # blocks), whose selection warps see a list's scores chunk by chunk, and neighbours of it that stay with
+    # the one-CTA-per-unit kernel (16 / 64 descriptors per list)
+    (2, 16, 2, 44 * 128, 133 * 128, 4, 32),     # 8 lists per unit, last unit half empty, partial last key tile, one chunk
+    (1, 8, 1, 24 * 128, 3000 * 128, 4, 48),     # 94 key tiles: 12 chunks of 8, 3 units
+    (2, 32, 1, 16 * 128, 2100 * 128, 1, 16),    # group 32, R1: a chunk is two key tiles, 9 chunks
+    (1, 16, 1, 160 * 128, 520 * 128, 2, 150),   # group 16, R2, 187 + 16 candidates: more than a chunk holds
+    (3, 8, 1, 56 * 128, 64 * 128, 4, 60),       # all blocks are candidates (64 < 60 + 16)
+    (1, 16, 1, 40 * 128, 2100 * 128, 1, 16),    # 16 descriptors per list: two warps per list, slices of 1056 and 1044
+                                                # blocks (a remainder below 32 once left part of a warp out of a vote)
+    (1, 16, 1, 12 * 128, 2100 * 128, 4, 64),    # 64 descriptors per list
+])
+def test_summary_selector_persistent_form_bit_exact(shape):
+    b, hq, hkv, sq, skv, r, topk = shape
+    m = sp()
+    q, k, _ = gen.make_qkv(b, hq, hkv, sq, skv, seed=31, k_block_offset=0.5)
+    q, k = q.cuda(), k.cuda()
+    fast = m.SummarySelector(q, k, r, topk=topk, keep_scores=False)
+    ids = fast.run_fast().clone()
+    exact = m.SummarySelector(q, k, r, topk=topk, keep_scores=False)
+    exact.prepare()
+    exact.score()
+    torch.cuda.synchronize()
+    m.device_status()
+    assert float(fast.aux[:b * hkv].view(torch.float32).min()) > 0     # the key abs-max only the tensor-core path writes
+    assert torch.equal(ids, exact.ids)
+    violations, ratio = fast.bound_stats()
+    assert violations == 0
+    print("lists that fell back to exact scoring:", fast.fallback_lists(), "max |approx - exact| / delta:", ratio)
+
+
+@pytest.mark.parametrize("order", ["ascending", "descending", "plateaus"])
+def test_summary_selector_persistent_form_adversarial_score_order(order):
+    """Scores that grow with the block index make every chunk beat everything seen before it (the pool of the
+    streaming selection overflows and is cut back again and again); falling scores make the first chunk
+    final; plateaus of exactly equal scores put ties on the threshold. Ids must equal the exact kernel's."""
+    m = sp()
+    b, hq, hkv, sq, skv, r, topk = 1, 8, 1, 24 * 128, 2304 * 128, 4, 32     # more than 2048 blocks: not a small problem
+    nt = skv // 128
+    g = torch.Generator().manual_seed(41)
+    q = (torch.rand((b, hq, sq, 128), generator=g) + 0.5)
+    ramp = torch.arange(nt, dtype=torch.float32) / nt
+    if order == "descending":
+        ramp = 1.0 - ramp
+    if order == "plateaus":
+        ramp = torch.floor(ramp * 16) / 16
+    k = (0.25 + ramp).repeat_interleave(128)[None, None, :, None].expand(b, hkv, skv, 128).clone()
+    if order != "plateaus":
+        k = k + 0.001 * torch.randn((b, hkv, skv, 128), generator=g)
+    q, k = q.to(torch.bfloat16).cuda(), k.to(torch.bfloat16).cuda()
+    fast = m.SummarySelector(q, k, r, topk=topk, keep_scores=False)
+    ids = fast.run_fast().clone()
+    exact = m.SummarySelector(q, k, r, topk=topk, keep_scores=False)
+    exact.prepare()
+    exact.score()
+    torch.cuda.synchronize()
+    m.device_status()
+    assert torch.equal(ids, exact.ids)
+    assert fast.bound_stats()[0] == 0
+    print(order, "lists that fell back to exact scoring:", fast.fallback_lists())
+
+
 @pytest.mark.parametrize("r", [1, 4])
 def test_summary_selector_tensor_core_path_near_ties(r):
     """A cluster of almost equal blocks at the top of every list (copies of one block, some
