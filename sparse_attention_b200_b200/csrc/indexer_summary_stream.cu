@@ -462,23 +462,32 @@ score_stream_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
           // later chunks: only entries above the smallest key kept so far can matter (an entry equal
           // to it is not needed: at least C entries at least as good are in the pool already)
 #pragma unroll 1
-          for (int j0 = 0; j0 < n; j0 += 32) {
-            const int j = j0 + lane;
-            const unsigned u = j < n ? keys[j] ^ 0x80000000u : 0u;     // 0 never passes
-            if (__ballot_sync(0xffffffffu, u > thr_u) == 0u) continue;  // late in a list most groups hold nothing new
-            if (cnt + 32 > CAP) {                // the pool is full: cut it back, raise the threshold
-              __syncwarp();
-              thr_u = warp_compact_pool(pool_ids, pool_keys, cnt, C, lane);
-              __syncwarp();
+          for (int j0 = 0; j0 < n; j0 += 128) {  // four groups of 32 entries per step
+            unsigned u[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const int j = j0 + 32 * i + lane;
+              u[i] = j < n ? keys[j] ^ 0x80000000u : 0u;     // 0 never passes
             }
-            const bool take = u > thr_u;
-            const unsigned ballot = __ballot_sync(0xffffffffu, take);
-            if (take) {
-              const int pos = cnt + __popc(ballot & lt_mask);
-              pool_ids[pos] = block_of(j);
-              pool_keys[pos] = u;
+            const unsigned best = max(max(u[0], u[1]), max(u[2], u[3]));
+            if (!__any_sync(0xffffffffu, best > thr_u)) continue;     // late in a list most steps hold nothing new
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              if (__ballot_sync(0xffffffffu, u[i] > thr_u) == 0u) continue;
+              if (cnt + 32 > CAP) {              // the pool is full: cut it back, raise the threshold
+                __syncwarp();
+                thr_u = warp_compact_pool(pool_ids, pool_keys, cnt, C, lane);
+                __syncwarp();
+              }
+              const bool take = u[i] > thr_u;
+              const unsigned ballot = __ballot_sync(0xffffffffu, take);
+              if (take) {
+                const int pos = cnt + __popc(ballot & lt_mask);
+                pool_ids[pos] = block_of(j0 + 32 * i + lane);
+                pool_keys[pos] = u[i];
+              }
+              cnt += __popc(ballot);
             }
-            cnt += __popc(ballot);
           }
         }
         __syncwarp();
