@@ -2,25 +2,26 @@
 // size x representatives = 32 query descriptors per list (e.g. GQA 8:1 with R4): same block
 // ids as the exact kernel (indexer_summary.cu), bit for bit.
 //
-// One CTA per SM walks work units = (batch, KV head, 256 / GR query blocks). Roles:
+// One CTA per SM walks work units = (batch, KV head, 8 query blocks). Roles:
 //   warp 12       TMA producer: the 256 query descriptors of the unit (B operand, one buffer)
-//                 and the key descriptor tiles (A operand, ring of 32 KiB slots);
+//                 and the key descriptor tiles (A operand, ring of two 32 KiB slots);
 //   warp 13       MMA issuer: tcgen05 M128 N256 K16 x 8 per key tile into one of two 256-column
 //                 TMEM accumulators (N = 256: 167 cycles per instruction against 2 x 116 at N = 128);
 //   warps 0-7     epilogue: lane = key descriptor, warp >> 2 = half of the 256 columns; max over
-//                 a list's GR columns and over the R rows of a KV block -> approximate block
-//                 scores, written to one of two small CHUNK buffers in shared memory;
-//   warps 8-11    selection: a warp owns lists of the unit. It never sees all scores of a list
-//                 at once: per chunk it keeps what can still belong to the C best (first chunk:
-//                 the C-th largest by a bitwise search; later chunks: everything above the
-//                 current C-th value goes to a 256-entry pool that is cut back when it fills).
-//                 After the unit's last chunk the candidates are copied aside and settled as in
-//                 indexer_summary_tc.cu: candidates more than 2 delta apart are ordered by their
-//                 approximate scores, the others are re-scored exactly (fp32 FMAs in feature
-//                 order), ranks by counting, safety test. While it settles the lists of unit u
-//                 the warp keeps taking the chunks of unit u + 1 between re-scoring steps, so the
-//                 chunk buffers (full / empty mbarriers, the only hand-over) never hold up the
-//                 epilogue, and with it the tensor pipe, for long.
+//                 a list's 32 columns and over the R rows of a KV block -> approximate block
+//                 scores, written to one of two CHUNK buffers (16 key tiles) in shared memory;
+//   warps 14, 15  chunk filter: a warp keeps the candidate pools of four lists. It never sees all
+//                 scores of a list at once: per chunk it keeps what can still belong to the C best
+//                 (first chunk: the C-th largest by a bitwise search; later chunks: everything
+//                 above the smallest key kept goes to a 256-entry pool that is cut back when it
+//                 fills). After the unit's last chunk the C .. C + 16 candidates of a list are
+//                 copied to the area of the settle warp that owns the list;
+//   warps 8-11    settle: two lists of the unit each, as in indexer_summary_tc.cu: candidates more
+//                 than 2 delta apart are ordered by their approximate scores, the others are
+//                 re-scored exactly (fp32 FMAs in feature order), ranks by counting, safety test.
+// Chunk buffers (epilogue -> filter) and candidate areas (filter -> settle) are the only hand-overs,
+// each with a full / empty mbarrier pair, so the scoring of unit u + 1, the filtering of its
+// chunks and the settling of unit u run at the same time.
 // A list whose result cannot be proven (ties that reach beyond the candidates, a violated
 // error bound) gets -1 as its first id; the launcher runs the exact kernel on those afterwards.
 // Replaces descriptor_dot + reduce_topk (indexers/r1_r4/gpu_ops.py:19-49).
@@ -49,26 +50,30 @@ constexpr int SLACK = 16;                    // a cut may keep up to C + SLACK e
 constexpr int FIN = C_MAX + SLACK;           // candidates of a list when it is settled
 constexpr int QB_MAX = 8;                    // lists of a unit (GR = 32)
 constexpr int NUM_THREADS = 512;
-// warpgroups: epilogue, epilogue, selection, {TMA, MMA, two idle warps}
-constexpr int EPI_WARPS = 8, SEL_WARP0 = 8, NSEL = 4, TMA_WARP = 12, MMA_WARP = 13;
+// warpgroups: epilogue, epilogue, settle, {TMA, MMA, two chunk-filter warps}
+constexpr int EPI_WARPS = 8, SEL_WARP0 = 8, NSEL = 4, TMA_WARP = 12, MMA_WARP = 13, FLT_WARP0 = 14;
 constexpr int LPW_MAX = QB_MAX / NSEL;       // lists per selection warp
-// registers per thread after the setup barrier (setmaxnreg): 128 * (2 * 104 + 240 + 64) = 65536
-constexpr int EPI_REGS = 104, SEL_REGS = 240, CTRL_REGS = 64;
-// per selection warp: the candidates of its lists while they are settled (ids, approximate scores),
-// exact scores, the list's query descriptors, work list (bytes), filter state
-constexpr int SELW_WORDS = LPW_MAX * 2 * FIN + FIN + 2048 + FIN / 4 + 4 * LPW_MAX;
+// registers per thread after the setup barrier (setmaxnreg): 128 * (2 * 104 + 176 + 128) = 65536; the fourth
+// warpgroup (roles with different code) keeps the 128 it was launched with
+constexpr int EPI_REGS = 104, SEL_REGS = 176;
+// per settle warp: the candidates of its lists (ids, approximate scores; written by a filter warp), exact
+// scores, the list's query descriptors, work list (bytes), candidates per list and smallest key kept
+constexpr int SELW_STATE = LPW_MAX * 2 * FIN + FIN + 2048 + FIN / 4;
+constexpr int SELW_WORDS = SELW_STATE + 2 * LPW_MAX;
 
 constexpr int OFF_A = 0;
 constexpr int OFF_B = OFF_A + A_STAGES * TILE_BYTES;
 constexpr int OFF_SC = OFF_B + B_BYTES;
 constexpr int OFF_POOL = OFF_SC + 2 * SC_WORDS * 4;
 constexpr int OFF_SELW = OFF_POOL + QB_MAX * CAP * 8;
-constexpr int OFF_BARS = OFF_SELW + NSEL * SELW_WORDS * 4;
-constexpr int OFF_MISC = OFF_BARS + 128;
+constexpr int OFF_FST = OFF_SELW + NSEL * SELW_WORDS * 4;   // filter warps: fill and threshold of their pools
+constexpr int OFF_BARS = OFF_FST + 2 * 2 * QB_MAX * 4;
+constexpr int OFF_MISC = OFF_BARS + 192;
 constexpr int SMEM_BYTES = OFF_MISC + 64 + 1024;     // + slack for the 1 KiB alignment
 static_assert(SMEM_BYTES <= 232448, "shared memory");
 
-enum { A_FULL = 0, A_EMPTY = 3, B_FULL = 6, B_EMPTY = 7, ACC_FULL = 8, ACC_EMPTY = 10, SC_FULL = 12, SC_EMPTY = 14 };
+enum { A_FULL = 0, A_EMPTY = 3, B_FULL = 6, B_EMPTY = 7, ACC_FULL = 8, ACC_EMPTY = 10, SC_FULL = 12, SC_EMPTY = 14,
+       FIN_FULL = 16, FIN_EMPTY = 20 };
 
 // Threshold for cutting n <= 512 unsigned keys (arr[j] ^ xorv) down to about C of them, one
 // warp, n >= C >= 1. The keys sit in registers (up to 16 per lane); the value is found bit by
@@ -189,7 +194,11 @@ score_stream_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
       mbar_init(bar(ACC_FULL + i), 1);
       mbar_init(bar(ACC_EMPTY + i), EPI_WARPS);
       mbar_init(bar(SC_FULL + i), EPI_WARPS);
-      mbar_init(bar(SC_EMPTY + i), NSEL);
+      mbar_init(bar(SC_EMPTY + i), 2);
+    }
+    for (int i = 0; i < NSEL; ++i) {
+      mbar_init(bar(FIN_FULL + i), 1);
+      mbar_init(bar(FIN_EMPTY + i), 1);
     }
     fence_mbar_init();
   }
@@ -201,7 +210,6 @@ score_stream_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = static_cast<uint32_t>(misc[0]);
-  if (warp >= TMA_WARP) setmaxnreg_dec<CTRL_REGS>();
   const int my_units = blockIdx.x < units ? (units - 1 - static_cast<int>(blockIdx.x)) / static_cast<int>(gridDim.x) + 1 : 0;
 
   if (warp == TMA_WARP) {
@@ -368,176 +376,141 @@ score_stream_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
     CLK(if (lane == 0 && warp == 0 && (blockIdx.x == 0 || blockIdx.x == 100))
           printf("cta %d epilogue warp 0: total %lld wait ACC_FULL %lld wait SC_EMPTY %lld tiles %d\n", blockIdx.x,
                  clock64() - t_start, w_full, w_sc, g);)
-  } else if (warp >= SEL_WARP0 && warp < SEL_WARP0 + NSEL) {
-    // ------------------------------------------------------------------ selection
-    setmaxnreg_inc<SEL_REGS>();
-    static_assert(GR == 32, "a lane of a selection warp is one query descriptor of a list");
-    constexpr int LPW = QB / NSEL;                 // lists of this warp: sw, sw + NSEL, ...
-    const int sw = warp - SEL_WARP0;
-    int* selw = reinterpret_cast<int*>(gbase + OFF_SELW) + sw * SELW_WORDS;
-    int32_t* fin_ids = selw;                                          // [LPW][FIN] candidates of the lists being settled
-    float* fin_apx = reinterpret_cast<float*>(selw + LPW * FIN);      // [LPW][FIN] their approximate scores
-    int* ord = selw + 2 * LPW * FIN;               // [FIN] exact scores of one list's candidates (ordered ints)
-    uint32_t* qs = reinterpret_cast<uint32_t*>(ord + FIN);            // [64][32] feature pairs of the list's 32 query descriptors
-    unsigned char* work = reinterpret_cast<unsigned char*>(qs + 2048);     // [FIN] candidates that need an exact score
-    int* st_cnt = reinterpret_cast<int*>(qs + 2048) + FIN / 4;        // [LPW] pool fill of the unit being filtered
-    unsigned* st_thr = reinterpret_cast<unsigned*>(st_cnt + LPW);     // [LPW] and its threshold
-    int* st_nc = reinterpret_cast<int*>(st_thr + LPW);                // [LPW] candidates of the unit being settled
-    unsigned* st_thr_fin = reinterpret_cast<unsigned*>(st_nc + LPW);  // [LPW] and their threshold
+  } else if (warp >= FLT_WARP0) {
+    // ------------------------------------------------------------------ chunk filter (warps 14, 15)
+    // Filter warp f keeps the pools of the lists of settle warps 2 f and 2 f + 1 (lists w and w + NSEL
+    // of a unit belong to settle warp w). Per chunk: what can still belong to the C best of a list
+    // goes to its pool; at the end of a unit the pools are cut to C .. C + SLACK candidates and
+    // copied to the settle warps' areas (FIN_EMPTY / FIN_FULL barriers, one pair per settle warp).
+    const int f = warp - FLT_WARP0;
     const unsigned lt_mask = (1u << lane) - 1u;
     const int C = p.cand;
     const int cb = 1 << cb_log2, bpt_mask = (1 << bpt_log2) - 1;
     const int invalid_blocks = (num_tiles << bpt_log2) - p.nt;   // rows past the end of the last key tile
-    bool ok = true;
-    if (lane < LPW) {
-      st_cnt[lane] = 0;
-      st_thr[lane] = 0u;
-    }
+    int* fst = reinterpret_cast<int*>(gbase + OFF_FST) + f * 2 * QB;   // [QB] pool fill, [QB] threshold (own lists only)
+    unsigned* fst_thr = reinterpret_cast<unsigned*>(fst + QB);
+    for (int x = lane; x < 2 * QB; x += 32) fst[x] = 0;
     __syncwarp();
-    CLK(long long t_blocked = 0; long long t_filter = 0; long long t_phase[4] = {0, 0, 0, 0}; int n_poll = 0; int n_hit = 0;
-        const long long t_start = clock64();)
-
-    // The chunks are taken by `pump`: unit fu, chunk fc is the next one. It stops at the end of a
-    // unit until the candidates have been copied aside (`fc` is then reset).
-    int fu = 0, fc = 0, h = 0, f_lists = 0, f_rot = 0;
-    auto pump = [&](bool block) {
-      if (fu >= my_units || fc >= num_chunks) return;
-      CLK(const long long p0 = clock64(); ++n_poll;)
-      bool ready;
-      if (block) ready = mbar_wait(bar(SC_FULL + (h & 1)), (h >> 1) & 1, guard, 0x570 + (h & 1));
-      else ready = mbar_test_wait(bar(SC_FULL + (h & 1)), (h >> 1) & 1);
-      ready = __all_sync(0xffffffffu, ready);
-      if (!ready) {
-        if (block) ok = false;
-        return;
-      }
-      CLK(const long long p1 = clock64(); if (block) t_blocked += p1 - p0; ++n_hit;)
-      if (fc == 0) {                             // first chunk of a unit: its constants
-        const int chunk = (blockIdx.x + fu * gridDim.x) % p.q_chunks;
-        f_lists = min(QB, p.qt - chunk * QB);
-        f_rot = static_cast<int>((static_cast<unsigned>(chunk) * 37u) % static_cast<unsigned>(num_tiles));
-      }
-      const int lists = f_lists, rot = f_rot;
-      const int c = fc;
-      const int tiles_here = min(ch_tiles, num_tiles - c * ch_tiles);
-      const int n = tiles_here << bpt_log2;      // entries of the chunk (rows past the end hold the lowest key)
-      auto block_of = [&](int j) {               // KV block of entry j of this chunk
-        int tt = c * ch_tiles + (j >> bpt_log2) + rot;
-        if (tt >= num_tiles) tt -= num_tiles;
-        return (tt << bpt_log2) + (j & bpt_mask);
-      };
+    bool ok = true;
+    int h = 0;
+    CLK(long long w_sc = 0; long long w_fin = 0; long long t_hand = 0; const long long t_start = clock64();)
+    for (int ui = 0; ok && ui < my_units; ++ui) {
+      const int chunk = (blockIdx.x + ui * gridDim.x) % p.q_chunks;
+      const int lists = min(QB, p.qt - chunk * QB);
+      const int rot = static_cast<int>((static_cast<unsigned>(chunk) * 37u) % static_cast<unsigned>(num_tiles));
+      for (int c = 0; ok && c < num_chunks; ++c, ++h) {
+        CLK(const long long c0 = clock64();)
+        bool w = mbar_wait(bar(SC_FULL + (h & 1)), (h >> 1) & 1, guard, 0x570 + (h & 1));
+        ok = __all_sync(0xffffffffu, w);
+        if (!ok) break;
+        CLK(w_sc += clock64() - c0;)
+        const int tiles_here = min(ch_tiles, num_tiles - c * ch_tiles);
+        const int n = tiles_here << bpt_log2;    // entries of the chunk (rows past the end hold the lowest key)
+        auto block_of = [&](int j) {             // KV block of entry j of this chunk
+          int tt = c * ch_tiles + (j >> bpt_log2) + rot;
+          if (tt >= num_tiles) tt -= num_tiles;
+          return (tt << bpt_log2) + (j & bpt_mask);
+        };
 #pragma unroll 1
-      for (int li = 0; li < LPW; ++li) {
-        const int l = sw + li * NSEL;
-        if (l >= lists) break;
-        const unsigned* keys = reinterpret_cast<const unsigned*>(sc + (h & 1) * SC_WORDS + l * cb);
-        int32_t* pool_ids = reinterpret_cast<int32_t*>(gbase + OFF_POOL) + l * 2 * CAP;
-        unsigned* pool_keys = reinterpret_cast<unsigned*>(pool_ids + CAP);
-        int cnt = st_cnt[li];
-        unsigned thr_u = st_thr[li];
-        if (c == 0 && n - invalid_blocks >= C) {
-          // first chunk with at least C real blocks: its best entries start the pool
-          int need_eq;
-          const unsigned T = warp_select_threshold(keys, 0x80000000u, n, C, lane, need_eq);
-          int out = 0, eq_run = 0;
+        for (int x = 0; x < QB / 2; ++x) {       // own lists: settle warps 2 f, 2 f + 1, their lists w and w + NSEL
+          const int l = 2 * f + (x & 1) + (x >> 1) * NSEL;
+          if (l >= lists) continue;
+          const unsigned* keys = reinterpret_cast<const unsigned*>(sc + (h & 1) * SC_WORDS + l * cb);
+          int32_t* pool_ids = reinterpret_cast<int32_t*>(gbase + OFF_POOL) + l * 2 * CAP;
+          unsigned* pool_keys = reinterpret_cast<unsigned*>(pool_ids + CAP);
+          int cnt = fst[l];
+          unsigned thr_u = fst_thr[l];
+          if (c == 0 && n - invalid_blocks >= C) {
+            // first chunk with at least C real blocks: its best entries start the pool
+            int need_eq;
+            const unsigned T = warp_select_threshold(keys, 0x80000000u, n, C, lane, need_eq);
+            int out = 0, eq_run = 0;
 #pragma unroll 1
-          for (int j0 = 0; j0 < n; j0 += 32) {
-            const int j = j0 + lane;
-            const unsigned u = j < n ? keys[j] ^ 0x80000000u : 0u;
-            const bool ge = j < n && u >= T, eq = ge && u == T;
-            const unsigned eq_ballot = __ballot_sync(0xffffffffu, eq);
-            const bool take = ge && (!eq || eq_run + __popc(eq_ballot & lt_mask) < need_eq);
-            const unsigned take_ballot = __ballot_sync(0xffffffffu, take);
-            eq_run += __popc(eq_ballot);
-            if (take) {
-              const int pos = out + __popc(take_ballot & lt_mask);
-              pool_ids[pos] = block_of(j);
-              pool_keys[pos] = u;
-            }
-            out += __popc(take_ballot);
-          }
-          cnt = out;                             // C .. C + SLACK
-          thr_u = T;
-        } else {
-          // later chunks: only entries above the smallest key kept so far can matter (an entry equal
-          // to it is not needed: at least C entries at least as good are in the pool already)
-#pragma unroll 1
-          for (int j0 = 0; j0 < n; j0 += 128) {  // four groups of 32 entries per step
-            unsigned u[4];
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              const int j = j0 + 32 * i + lane;
-              u[i] = j < n ? keys[j] ^ 0x80000000u : 0u;     // 0 never passes
-            }
-            const unsigned best = max(max(u[0], u[1]), max(u[2], u[3]));
-            if (!__any_sync(0xffffffffu, best > thr_u)) continue;     // late in a list most steps hold nothing new
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              if (__ballot_sync(0xffffffffu, u[i] > thr_u) == 0u) continue;
-              if (cnt + 32 > CAP) {              // the pool is full: cut it back, raise the threshold
-                __syncwarp();
-                thr_u = warp_compact_pool(pool_ids, pool_keys, cnt, C, lane);
-                __syncwarp();
-              }
-              const bool take = u[i] > thr_u;
-              const unsigned ballot = __ballot_sync(0xffffffffu, take);
+            for (int j0 = 0; j0 < n; j0 += 32) {
+              const int j = j0 + lane;
+              const unsigned u = j < n ? keys[j] ^ 0x80000000u : 0u;
+              const bool ge = j < n && u >= T, eq = ge && u == T;
+              const unsigned eq_ballot = __ballot_sync(0xffffffffu, eq);
+              const bool take = ge && (!eq || eq_run + __popc(eq_ballot & lt_mask) < need_eq);
+              const unsigned take_ballot = __ballot_sync(0xffffffffu, take);
+              eq_run += __popc(eq_ballot);
               if (take) {
-                const int pos = cnt + __popc(ballot & lt_mask);
-                pool_ids[pos] = block_of(j0 + 32 * i + lane);
-                pool_keys[pos] = u[i];
+                const int pos = out + __popc(take_ballot & lt_mask);
+                pool_ids[pos] = block_of(j);
+                pool_keys[pos] = u;
               }
-              cnt += __popc(ballot);
+              out += __popc(take_ballot);
+            }
+            cnt = out;                           // C .. C + SLACK
+            thr_u = T;
+          } else {
+            // later chunks: only entries above the smallest key kept so far can matter (an entry equal
+            // to it is not needed: at least C entries at least as good are in the pool already)
+#pragma unroll 1
+            for (int j0 = 0; j0 < n; j0 += 128) {          // four groups of 32 entries per step
+              unsigned u[4];
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                const int j = j0 + 32 * i + lane;
+                u[i] = j < n ? keys[j] ^ 0x80000000u : 0u;   // 0 never passes
+              }
+              const unsigned best = max(max(u[0], u[1]), max(u[2], u[3]));
+              if (!__any_sync(0xffffffffu, best > thr_u)) continue;   // late in a list most steps hold nothing new
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                if (__ballot_sync(0xffffffffu, u[i] > thr_u) == 0u) continue;
+                if (cnt + 32 > CAP) {            // the pool is full: cut it back, raise the threshold
+                  __syncwarp();
+                  thr_u = warp_compact_pool(pool_ids, pool_keys, cnt, C, lane);
+                  __syncwarp();
+                }
+                const bool take = u[i] > thr_u;
+                const unsigned ballot = __ballot_sync(0xffffffffu, take);
+                if (take) {
+                  const int pos = cnt + __popc(ballot & lt_mask);
+                  pool_ids[pos] = block_of(j0 + 32 * i + lane);
+                  pool_keys[pos] = u[i];
+                }
+                cnt += __popc(ballot);
+              }
             }
           }
+          __syncwarp();
+          if (lane == 0) {
+            fst[l] = cnt;
+            fst_thr[l] = thr_u;
+          }
+          __syncwarp();
         }
         __syncwarp();
-        if (lane == 0) {
-          st_cnt[li] = cnt;
-          st_thr[li] = thr_u;
-        }
-        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(SC_EMPTY + (h & 1)));
       }
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar(SC_EMPTY + (h & 1)));
-      ++h;
-      ++fc;
-      CLK(t_filter += clock64() - p1;)
-    };
-
-    // Settling runs in slices (one phase, or two re-scoring steps, per turn of the loop) so that a
-    // chunk of the next unit is taken as soon as it is there.
-    enum { IDLE, PREP, RESCORE, RANK };
-    int phase = IDLE, su = 0, li = 0;            // unit and list being settled
-    int bk = 0, qtile0 = 0, lists = 0, nc = 0, nwork = 0, rows = 0, steps = 0, st = 0;
-    float thr = 0.f, delta = 0.f, kabs = 0.f, knorm = 0.f;
-    long long qrow0 = 0;
-    const __nv_bfloat16* kbase = p.kd;
-    while (ok) {
-      pump(phase == IDLE);
       if (!ok) break;
-      CLK(const long long s0 = clock64(); const int ph0 = phase;)
-      if (phase == IDLE) {
-        if (su >= my_units) break;
-        if (fc < num_chunks) continue;           // unit su is not complete yet
-        // the candidates of this warp's lists move aside; the pools are then free for the next unit
-        const int unit = blockIdx.x + su * gridDim.x;
-        bk = unit / p.q_chunks;
-        const int chunk = unit - bk * p.q_chunks;
-        const int b = bk / p.hkv, kvh = bk - b * p.hkv;
-        qtile0 = chunk * QB;
-        lists = min(QB, p.qt - qtile0);
-        kbase = p.kd + static_cast<long long>(bk) * n_keys * 128;
-        kabs = p.k_absmax[bk];
-        knorm = sqrtf(p.k_norm2[bk]);
-        qrow0 = (static_cast<long long>(b) * p.hq + kvh * group) * p.qt;   // descriptor block of head 0
+      // the unit is complete: hand its candidates to the two settle warps
+      CLK(const long long h0 = clock64(); const long long wf0 = w_fin;)
 #pragma unroll 1
-        for (int x = 0; x < LPW; ++x) {
+      for (int y = 0; ok && y < 2; ++y) {
+        const int sw = 2 * f + y;
+        if (ui > 0) {
+          CLK(const long long c0 = clock64();)
+          bool w = mbar_wait(bar(FIN_EMPTY + sw), (ui - 1) & 1, guard, 0x580 + sw);
+          ok = __all_sync(0xffffffffu, w);
+          if (!ok) break;
+          CLK(w_fin += clock64() - c0;)
+        }
+        int* selw = reinterpret_cast<int*>(gbase + OFF_SELW) + sw * SELW_WORDS;
+        int32_t* fin_ids = selw;
+        float* fin_apx = reinterpret_cast<float*>(selw + LPW_MAX * FIN);
+        int* st_nc = selw + SELW_STATE;
+        unsigned* st_thr_fin = reinterpret_cast<unsigned*>(st_nc + LPW_MAX);
+#pragma unroll 1
+        for (int x = 0; x < QB / NSEL; ++x) {
           const int l = sw + x * NSEL;
           if (l >= lists) break;
           int32_t* pool_ids = reinterpret_cast<int32_t*>(gbase + OFF_POOL) + l * 2 * CAP;
           unsigned* pool_keys = reinterpret_cast<unsigned*>(pool_ids + CAP);
-          int cnt = st_cnt[x];
-          unsigned thr_u = st_thr[x];
+          int cnt = fst[l];
+          unsigned thr_u = fst_thr[l];
           __syncwarp();
           if (cnt > C + SLACK) {
             thr_u = warp_compact_pool(pool_ids, pool_keys, cnt, C, lane);
@@ -551,24 +524,62 @@ score_stream_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
           if (lane == 0) {
             st_nc[x] = cnt;
             st_thr_fin[x] = thr_u;
-            st_cnt[x] = 0;
-            st_thr[x] = 0u;
+            fst[l] = 0;
+            fst_thr[l] = 0u;
           }
         }
         __syncwarp();
-        ++fu;
-        fc = 0;
-        li = 0;
-        if (sw < lists) phase = PREP;
-        else ++su;                               // none of the unit's lists is this warp's
-      } else if (phase == PREP) {
+        if (lane == 0) mbar_arrive(bar(FIN_FULL + sw));
+      }
+      CLK(t_hand += clock64() - h0 - (w_fin - wf0);)
+    }
+    CLK(if (lane == 0 && blockIdx.x == 0)
+          printf("cta 0 filter warp %d: total %lld wait SC_FULL %lld wait FIN_EMPTY %lld hand-over %lld\n", f,
+                 clock64() - t_start, w_sc, w_fin, t_hand);)
+  } else if (warp >= SEL_WARP0 && warp < SEL_WARP0 + NSEL) {
+    // ------------------------------------------------------------------ settle (warps 8-11)
+    setmaxnreg_inc<SEL_REGS>();
+    static_assert(GR == 32, "a lane of a settle warp is one query descriptor of a list");
+    constexpr int LPW = QB / NSEL;                 // lists of this warp: sw, sw + NSEL
+    const int sw = warp - SEL_WARP0;
+    int* selw = reinterpret_cast<int*>(gbase + OFF_SELW) + sw * SELW_WORDS;
+    const int32_t* fin_ids = selw;                                    // [LPW][FIN] candidates of the lists being settled
+    const float* fin_apx = reinterpret_cast<const float*>(selw + LPW_MAX * FIN);   // [LPW][FIN] their approximate scores
+    int* ord = selw + 2 * LPW_MAX * FIN;           // [FIN] exact scores of one list's candidates (ordered ints)
+    uint32_t* qs = reinterpret_cast<uint32_t*>(ord + FIN);            // [64][32] feature pairs of the list's 32 query descriptors
+    unsigned char* work = reinterpret_cast<unsigned char*>(qs + 2048);     // [FIN] candidates that need an exact score
+    const int* st_nc = selw + SELW_STATE;          // [LPW] candidates per list
+    const unsigned* st_thr_fin = reinterpret_cast<const unsigned*>(st_nc + LPW_MAX);   // [LPW] smallest key kept
+    const unsigned lt_mask = (1u << lane) - 1u;
+    bool ok = true;
+    CLK(long long w_full = 0; const long long t_start = clock64();)
+    for (int ui = 0; ok && ui < my_units; ++ui) {
+      {
+        CLK(const long long c0 = clock64();)
+        bool w = mbar_wait(bar(FIN_FULL + sw), ui & 1, guard, 0x590 + sw);
+        ok = __all_sync(0xffffffffu, w);
+        if (!ok) break;
+        CLK(w_full += clock64() - c0;)
+      }
+      const int unit = blockIdx.x + ui * gridDim.x;
+      const int bk = unit / p.q_chunks, chunk = unit - bk * p.q_chunks;
+      const int b = bk / p.hkv, kvh = bk - b * p.hkv;
+      const int qtile0 = chunk * QB;
+      const int lists = min(QB, p.qt - qtile0);
+      const __nv_bfloat16* kbase = p.kd + static_cast<long long>(bk) * n_keys * 128;
+      const float kabs = p.k_absmax[bk], knorm = sqrtf(p.k_norm2[bk]);
+      const long long qrow0 = (static_cast<long long>(b) * p.hq + kvh * group) * p.qt;   // descriptor block of head 0
+#pragma unroll 1
+      for (int li = 0; li < LPW; ++li) {
+        if (sw + li * NSEL >= lists) break;
+        const int qtile = qtile0 + sw + li * NSEL;
+        const int32_t* ids_l = fin_ids + li * FIN;
+        const float* apx = fin_apx + li * FIN;
+        const int nc = st_nc[li];                // C .. C + SLACK (all blocks when the list is shorter than C)
+        const float thr = ord2f(static_cast<int>(st_thr_fin[li] ^ 0x80000000u)) * SCALE;
         // The list's 32 query descriptors go to shared memory (word i of row r at [i][r]: lane r reads
         // its own row without bank conflicts). Their L1 and L2 norms give the error bound of the
         // list: sum of |q_d k_d| bounded by Hoelder (L1 x max) and by Cauchy-Schwarz.
-        const int qtile = qtile0 + sw + li * NSEL;
-        const float* apx = fin_apx + li * FIN;
-        nc = st_nc[li];                          // C .. C + SLACK (all blocks when the list is shorter than C)
-        thr = ord2f(static_cast<int>(st_thr_fin[li] ^ 0x80000000u)) * SCALE;
         {
           const int g = lane >> r_log2, rq = lane & (p.r - 1);     // descriptor = head of the group * R + representative
           const uint4* src = reinterpret_cast<const uint4*>(
@@ -597,10 +608,10 @@ score_stream_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
         float l1 = (s4[0] + s4[1]) + (s4[2] + s4[3]), l2 = (q4[0] + q4[1]) + (q4[2] + q4[3]);
         l1 = __int_as_float(__reduce_max_sync(0xffffffffu, __float_as_int(l1)));   // non-negative floats order as ints
         l2 = __int_as_float(__reduce_max_sync(0xffffffffu, __float_as_int(l2)));
-        delta = EPS * 1.0001f * fminf(l1 * kabs, sqrtf(l2) * knorm) * SCALE;
+        const float delta = EPS * 1.0001f * fminf(l1 * kabs, sqrtf(l2) * knorm) * SCALE;
         const float two = 2.f * delta;
         // candidates whose order the approximate scores do not settle
-        nwork = 0;
+        int nwork = 0;
 #pragma unroll 1
         for (int c0 = 0; c0 < nc; c0 += 32) {
           const int c = c0 + lane;
@@ -616,94 +627,82 @@ score_stream_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
           nwork += __popc(nb);
         }
         __syncwarp();
-        rows = nwork << r_log2;                  // key descriptors to score (R per candidate)
-        steps = (((rows + 3) >> 2) * 4 + 31) >> 5;      // items = quads of key rows x four chunks of query rows
-        st = 0;
-        phase = steps > 0 ? RESCORE : RANK;
-      } else if (phase == RESCORE) {
         // Exact scores: fp32 FMA chains over the features in order, from zero (the arithmetic that
         // defines a score). A lane takes an item = (four key descriptors, eight query descriptors): the
         // key rows come straight from global memory into its registers (16-byte pieces, requested one
-        // piece ahead), the query values from the warp's staging area (the four lanes of a quad read
+        // piece ahead), the query values from the staging area (the four lanes of a quad read
         // different chunks, lanes of different quads the same words), 64 FMAs per 32 bytes loaded
-        // from shared memory. One round of 32 items per turn.
-        {
-          const int item = 32 * st + lane;
-          const int quads = (rows + 3) >> 2;
-          if (item < quads * 4) {
-            const int quad = item >> 2, qc = item & 3;
-            const uint4* krow[4];
-            int cand[4];
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const int row = min(4 * quad + j, rows - 1);     // rows past the end repeat the last one
-              cand[j] = work[row >> r_log2];
-              krow[j] = reinterpret_cast<const uint4*>(
-                  kbase + ((static_cast<long long>(fin_ids[li * FIN + cand[j]]) << r_log2) + (row & (p.r - 1))) * 128);
-            }
-            float acc[4][8];
-#pragma unroll
-            for (int j = 0; j < 4; ++j)
-#pragma unroll
-              for (int m = 0; m < 8; ++m) acc[j][m] = 0.f;
-            uint4 cur[4], nxt[4];
-#pragma unroll
-            for (int j = 0; j < 4; ++j) cur[j] = __ldg(krow[j]);
+        // from shared memory.
+        const int rows = nwork << r_log2;        // key descriptors to score (R per candidate)
+        const int quads = (rows + 3) >> 2;
 #pragma unroll 1
-            for (int pc = 0; pc < 16; ++pc) {
-              const int pn = pc < 15 ? pc + 1 : 15;
+        for (int item = lane; item < quads * 4; item += 32) {
+          const int quad = item >> 2, qc = item & 3;
+          const uint4* krow[4];
+          int cand[4];
 #pragma unroll
-              for (int j = 0; j < 4; ++j) nxt[j] = __ldg(krow[j] + pn);
+          for (int j = 0; j < 4; ++j) {
+            const int row = min(4 * quad + j, rows - 1);       // rows past the end repeat the last one
+            cand[j] = work[row >> r_log2];
+            krow[j] = reinterpret_cast<const uint4*>(
+                kbase + ((static_cast<long long>(ids_l[cand[j]]) << r_log2) + (row & (p.r - 1))) * 128);
+          }
+          float acc[4][8];
 #pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                const uint4* qp = reinterpret_cast<const uint4*>(qs + (4 * pc + e) * 32 + 8 * qc);
-                const uint4 qa = qp[0], qb = qp[1];
-                const uint32_t qw[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
-                float klo[4], khi[4];
+          for (int j = 0; j < 4; ++j)
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                  const uint32_t kw = e == 0 ? cur[j].x : e == 1 ? cur[j].y : e == 2 ? cur[j].z : cur[j].w;
-                  klo[j] = bf_lo(kw);
-                  khi[j] = bf_hi(kw);
-                }
+            for (int m = 0; m < 8; ++m) acc[j][m] = 0.f;
+          uint4 cur[4], nxt[4];
 #pragma unroll
-                for (int m = 0; m < 8; ++m) {
-                  const float x = bf_lo(qw[m]);
+          for (int j = 0; j < 4; ++j) cur[j] = __ldg(krow[j]);
+#pragma unroll 1
+          for (int pc = 0; pc < 16; ++pc) {
+            const int pn = pc < 15 ? pc + 1 : 15;
 #pragma unroll
-                  for (int j = 0; j < 4; ++j) acc[j][m] = fmaf(x, klo[j], acc[j][m]);
-                }
+            for (int j = 0; j < 4; ++j) nxt[j] = __ldg(krow[j] + pn);
 #pragma unroll
-                for (int m = 0; m < 8; ++m) {
-                  const float y = bf_hi(qw[m]);
+            for (int e = 0; e < 4; ++e) {
+              const uint4* qp = reinterpret_cast<const uint4*>(qs + (4 * pc + e) * 32 + 8 * qc);
+              const uint4 qa = qp[0], qb = qp[1];
+              const uint32_t qw[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
+              float klo[4], khi[4];
 #pragma unroll
-                  for (int j = 0; j < 4; ++j) acc[j][m] = fmaf(y, khi[j], acc[j][m]);
-                }
+              for (int j = 0; j < 4; ++j) {
+                const uint32_t kw = e == 0 ? cur[j].x : e == 1 ? cur[j].y : e == 2 ? cur[j].z : cur[j].w;
+                klo[j] = bf_lo(kw);
+                khi[j] = bf_hi(kw);
               }
 #pragma unroll
-              for (int j = 0; j < 4; ++j) cur[j] = nxt[j];
+              for (int m = 0; m < 8; ++m) {
+                const float x = bf_lo(qw[m]);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[j][m] = fmaf(x, klo[j], acc[j][m]);
+              }
+#pragma unroll
+              for (int m = 0; m < 8; ++m) {
+                const float y = bf_hi(qw[m]);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[j][m] = fmaf(y, khi[j], acc[j][m]);
+              }
             }
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              float best = acc[j][0];
-#pragma unroll
-              for (int m = 1; m < 8; ++m) best = fmaxf(best, acc[j][m]);      // fmaxf drops a NaN unless both are
-              if (best == best) atomicMax(ord + cand[j], f2ord(best));       // a NaN leaves the slot alone
-            }
+            for (int j = 0; j < 4; ++j) cur[j] = nxt[j];
           }
-          ++st;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            float best = acc[j][0];
+#pragma unroll
+            for (int m = 1; m < 8; ++m) best = fmaxf(best, acc[j][m]);        // fmaxf drops a NaN unless both are
+            if (best == best) atomicMax(ord + cand[j], f2ord(best));         // a NaN leaves the slot alone
+          }
         }
-        if (st >= steps) phase = RANK;
-      } else {
+        __syncwarp();
         // rank of a candidate = number of candidates that beat it in (exact score descending, block id
         // ascending): decided by the approximate scores when they are more than 2 delta apart, else
         // by the exact scores (both candidates have one then)
-        __syncwarp();
-        const int32_t* ids_l = fin_ids + li * FIN;
-        const float* apx = fin_apx + li * FIN;
-        const float two = 2.f * delta;
         float kth = -INFINITY;
         bool viol = false;
-        int32_t* out_ids = p.ids + (static_cast<long long>(bk) * p.qt + qtile0 + sw + li * NSEL) * p.topk;
+        int32_t* out_ids = p.ids + (static_cast<long long>(bk) * p.qt + qtile) * p.topk;
 #pragma unroll 1
         for (int c0 = 0; c0 < nc; c0 += 32) {
           const int c = c0 + lane;
@@ -741,18 +740,12 @@ score_stream_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
           out_ids[0] = -1;                       // the launcher's exact pass re-does this list
           if (p.fallbacks) atomicAdd(p.fallbacks, 1);
         }
-        ++li;
-        if (sw + li * NSEL < lists && li < LPW) phase = PREP;
-        else {
-          ++su;
-          phase = IDLE;
-        }
       }
-      CLK(t_phase[ph0] += clock64() - s0;)
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(FIN_EMPTY + sw));       // the areas may be overwritten
     }
-    CLK(if (lane == 0 && (sw == 0 || sw == 3) && (blockIdx.x == 0 || blockIdx.x == 100))
-          printf("cta %d selection warp %d: total %lld blocked %lld filter %lld | snapshot %lld prep %lld rescore %lld rank %lld | polls %d hits %d\n",
-                 blockIdx.x, sw, clock64() - t_start, t_blocked, t_filter, t_phase[0], t_phase[1], t_phase[2], t_phase[3], n_poll, n_hit);)
+    CLK(if (lane == 0 && blockIdx.x == 0 && (sw == 0 || sw == 3))
+          printf("cta 0 settle warp %d: total %lld wait FIN_FULL %lld\n", sw, clock64() - t_start, w_full);)
   }
   tc_fence_before();
   __syncthreads();

@@ -1,9 +1,10 @@
 """CPU model of the hand-over protocol of the persistent summary selector
 (csrc/indexer_summary_stream.cu).
 
-Roles of one CTA: TMA producer warp, single-thread MMA issuer, eight epilogue warps, four
-selection warps. They talk through mbarriers only: a ring of two key-tile slots, one
-query-descriptor buffer per work unit, two TMEM accumulators, two score-chunk buffers. Every
+Roles of one CTA: TMA producer warp, single-thread MMA issuer, eight epilogue warps, two chunk
+filter warps, four settle warps. They talk through mbarriers only: a ring of two key-tile slots,
+one query-descriptor buffer per work unit, two TMEM accumulators, two score-chunk buffers, and one
+candidate area per settle warp (filled by the filter warp that keeps its lists). Every
 role derives ring slot, accumulator, chunk buffer and the phase it waits for from its own
 counters (tiles, chunks, units handled so far). The model restates each role's control flow and
 runs the roles under random interleavings with asynchronous TMA completion and an in-order
@@ -14,9 +15,10 @@ tensor pipe, checking at every step that
 * an MMA reads the key tile / query buffer the issuer thinks is there and no TMA load overwrites
   one that an issued MMA has yet to read;
 * an accumulator is not overwritten before all eight epilogue warps have read it, a chunk buffer
-  is neither overwritten while a selection warp still reads it nor read before all eight epilogue
+  is neither overwritten while a filter warp still reads it nor read before all eight epilogue
   warps have written their part;
-* every selection warp sees every chunk of every unit exactly once, in order.
+* every filter warp sees every chunk of every unit exactly once, in order; a settle warp finds
+  the candidates of the unit it expects, and they are not overwritten while it works on them.
 
 Mirrors the kernel by hand: a change of its protocol must be made here too. Same purpose as the
 reference's attention/q_centric/tests/test_schedule.py:6-100 for its own ring schedule.
@@ -25,7 +27,7 @@ import random
 
 import pytest
 
-A_STAGES, EPI, NSEL = 2, 8, 4
+A_STAGES, EPI, NFLT, NSEL = 2, 8, 2, 4
 
 
 class Bar:
@@ -69,7 +71,12 @@ def run_cta(units, num_tiles, ch_tiles, rng, skip=None):
         B["ACC_FULL", i] = Bar(f"ACC_FULL{i}", 1)
         B["ACC_EMPTY", i] = Bar(f"ACC_EMPTY{i}", EPI)
         B["SC_FULL", i] = Bar(f"SC_FULL{i}", EPI)
-        B["SC_EMPTY", i] = Bar(f"SC_EMPTY{i}", NSEL)
+        B["SC_EMPTY", i] = Bar(f"SC_EMPTY{i}", NFLT)
+    for w in range(NSEL):
+        B["FIN_FULL", w] = Bar(f"FIN_FULL{w}", 1)
+        B["FIN_EMPTY", w] = Bar(f"FIN_EMPTY{w}", 1)
+    fin = [None] * NSEL                 # unit whose candidates sit in each settle warp's area
+    fin_busy = [False] * NSEL           # the settle warp is working on them
     ring = [None] * A_STAGES
     ring_readers = [0] * A_STAGES
     qbuf, qbuf_readers = None, 0
@@ -79,7 +86,8 @@ def run_cta(units, num_tiles, ch_tiles, rng, skip=None):
     sc_written = [0, 0]                 # epilogue warps that have finished their part of it
     sc_readers = [0, 0]                 # selection warps still reading
     tma_inflight, pipe = [], []
-    seen = [[] for _ in range(NSEL)]
+    seen = [[] for _ in range(NFLT)]
+    settled = [[] for _ in range(NSEL)]
 
     def wait(bar, phase):
         return ("wait", bar, phase)
@@ -156,25 +164,44 @@ def run_cta(units, num_tiles, ch_tiles, rng, skip=None):
                     h += 1
                 g += 1
 
-    def selection(w):
+    def chunk_filter(f):
         h = 0
         for u in range(units):
             for c in range(num_chunks):
                 buf = h & 1
                 yield wait(B["SC_FULL", buf], h >> 1)
-                assert sc_written[buf] >= EPI, f"selection {w} reads chunk buffer {buf} with {sc_written[buf]} parts written"
+                assert sc_written[buf] >= EPI, f"filter {f} reads chunk buffer {buf} with {sc_written[buf]} parts written"
                 sc_readers[buf] += 1
                 yield ("step",)
-                seen[w].append((u, c))
+                seen[f].append((u, c))
                 sc_readers[buf] -= 1
-                if sc_readers[buf] == 0 and all(len(x) >= len(seen[w]) for x in seen):
+                if sc_readers[buf] == 0 and all(len(x) >= len(seen[f]) for x in seen):
                     sc_written[buf] = 0              # the last reader of this use of the buffer
                 yield ("arrive", B["SC_EMPTY", buf])
                 h += 1
-            for _ in range(rng.randrange(0, 4)):     # settling the unit's lists takes a while
+            for y in range(2):                       # hand the unit's candidates to the two settle warps
+                w = 2 * f + y
+                if u > 0:
+                    yield wait(B["FIN_EMPTY", w], u - 1)
+                assert not fin_busy[w], f"candidate area of settle warp {w} overwritten while it is in use"
+                fin[w] = u
                 yield ("step",)
+                yield ("arrive", B["FIN_FULL", w])
 
-    roles = [producer(), issuer()] + [epilogue(w) for w in range(EPI)] + [selection(w) for w in range(NSEL)]
+    def settle(w):
+        for u in range(units):
+            yield wait(B["FIN_FULL", w], u)
+            assert fin[w] == u, f"settle warp {w} expects unit {u}, its area holds {fin[w]}"
+            fin_busy[w] = True
+            for _ in range(rng.randrange(1, 200)):   # settling a unit's lists takes a while
+                yield ("step",)
+            assert fin[w] == u
+            settled[w].append(u)
+            fin_busy[w] = False
+            yield ("arrive", B["FIN_EMPTY", w])
+
+    roles = [producer(), issuer()] + [epilogue(w) for w in range(EPI)] + [chunk_filter(f) for f in range(NFLT)] \
+        + [settle(w) for w in range(NSEL)]
     pending, alive, steps = [None] * len(roles), [True] * len(roles), 0
     while True:
         choices = []
@@ -221,8 +248,10 @@ def run_cta(units, num_tiles, ch_tiles, rng, skip=None):
     assert not stuck, f"deadlock: roles {stuck} blocked on {[(pending[r][1].name, pending[r][2], pending[r][1].phase) for r in stuck]}"
     assert not tma_inflight and not pipe
     expected = [(u, c) for u in range(units) for c in range(num_chunks)]
+    for f in range(NFLT):
+        assert seen[f] == expected, f"filter warp {f} saw {seen[f][:6]}..."
     for w in range(NSEL):
-        assert seen[w] == expected, f"selection warp {w} saw {seen[w][:6]}..."
+        assert settled[w] == list(range(units))
 
 
 @pytest.mark.parametrize("units", [1, 2, 5])
@@ -233,7 +262,7 @@ def test_roles_agree_on_slots_buffers_and_phases(units, num_tiles, ch_tiles):
         run_cta(units, num_tiles, ch_tiles, rng)
 
 
-@pytest.mark.parametrize("skip", ["SC_EMPTY", "ACC_EMPTY", "A_EMPTY", "B_EMPTY"])
+@pytest.mark.parametrize("skip", ["SC_EMPTY", "ACC_EMPTY", "A_EMPTY", "B_EMPTY", "FIN_EMPTY"])
 def test_model_catches_a_missing_release(skip):
     """The model must be able to fail: ignore one of the release barriers and a hazard, a phase alias
     or a deadlock has to show up."""
