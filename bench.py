@@ -393,10 +393,15 @@ def indexer_roofline(stages, ms, peaks):
     t_hbm = stages["indexer_bytes"] / (peaks["hbm"] * 1e9)
     t_tc = stages["indexer_score_flop"] / (peaks["bf16"] * 1e12)
     bound = "hbm" if t_hbm >= t_tc else "tensor"
-    return {"bound": bound, "hbm_gbs": gbs, "hbm_frac": gbs / peaks["hbm"], "score_tflops": tfs,
-            "tensor_frac": tfs / peaks["bf16"], "frac": (gbs / peaks["hbm"]) if bound == "hbm" else tfs / peaks["bf16"],
-            "algorithmic_bytes": stages["indexer_bytes"], "score_flop": stages["indexer_score_flop"],
-            "peak_hbm_gbs": peaks["hbm"], "peak_bf16_tflops": peaks["bf16"]}
+    rec = {"bound": bound, "hbm_gbs": gbs, "hbm_frac": gbs / peaks["hbm"], "score_tflops": tfs,
+           "tensor_frac": tfs / peaks["bf16"], "frac": (gbs / peaks["hbm"]) if bound == "hbm" else tfs / peaks["bf16"],
+           "algorithmic_bytes": stages["indexer_bytes"], "score_flop": stages["indexer_score_flop"],
+           "peak_hbm_gbs": peaks["hbm"], "peak_bf16_tflops": peaks["bf16"]}
+    if stages.get("indexer_select_ms"):        # the scoring + selection kernel alone (pooling is the HBM-bound part)
+        sel = stages["indexer_score_flop"] / stages["indexer_select_ms"] / 1e9
+        rec["select_score_tflops"] = sel
+        rec["select_tensor_frac"] = sel / peaks["bf16"]
+    return rec
 
 
 def cpu_gather_sample(cfg, q, k, v, ids, budget_s, threads=None):
