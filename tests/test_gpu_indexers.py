@@ -714,12 +714,13 @@ def test_indexer_then_attention_config1():
     assert torch.all((lse.cpu() - ref_l).abs() <= 1e-3 * ref_l.abs().clamp_min(1.0))
 
 
-def test_indexer_attention_pipeline_in_a_cuda_graph():
+@pytest.mark.parametrize("sq", [1024, 80 * 128])      # 16 lists: the small-problem selector; 160 lists: the persistent one
+def test_indexer_attention_pipeline_in_a_cuda_graph(sq):
     """Indexer -> attention as one call, captured once and replayed after the inputs changed:
     new exact ids and a correct output must come out of the replay (the reference's gate,
     benchmarks/ch4_selectors/harness.py:105-111)."""
     m = sp()
-    q, k, v = gen.make_qkv(1, 16, 2, 1024, 8192, seed=61, k_block_offset=0.5)
+    q, k, v = gen.make_qkv(1, 16, 2, sq, 8192, seed=61, k_block_offset=0.5)
     qc, kc, vc = q.cuda(), k.cuda(), v.cuda()
     sel = m.SummarySelector(qc, kc, 4, topk=16, keep_scores=False)
     out = torch.empty_like(qc)
