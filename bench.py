@@ -866,9 +866,18 @@ def run_kv_token(args):
     token_major = {"main_ms": timed(prep_tm.main, args.steps, 3, barrier), "ms": timed(prep_tm.run, args.steps, 3, barrier),
                    "identical_output": bool(torch.equal(prep_tm.out, prep.out))}
     sp.device_status()
+    # q and partials token-major: the reference's own pair (main_tm_out + combine_tm_out)
+    prep_tt = sp.PreparedTokens(prep_tm.q, k, v, selected, q_token_major=True, partial_token_major=True)
+    prep_tt.metadata()
+    token_major["partials_token_major"] = {
+        "main_ms": timed(prep_tt.main, args.steps, 3, barrier), "combine_ms": timed(prep_tt.combine, args.steps, 3, barrier),
+        "ms": timed(prep_tt.run, args.steps, 3, barrier), "identical_output": bool(torch.equal(prep_tt.out, prep.out))}
+    sp.device_status()
+    del prep_tt
     same_box = reference_kv_centric(q, k, v, selected, prep, args.steps, barrier)
     fl = 4.0 * B * Hq * S * (topk * 128) * 128
-    peak_tf, peak_gbs, peak_src = measured_peaks()
+    peaks = measured_peaks()
+    peak_tf, peak_src = peaks["bf16"], peaks["source"]
     value = fl / (ms * 1e-3) / 1e12
     print(json.dumps({"metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": 1, "steps": args.steps,
                       "warmup": 3, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,

@@ -144,6 +144,17 @@ int sparse_b200_kv_token_main_tm(const void* q_token_major, const void* k, const
                                  const int32_t* task_ptr, const int32_t* query_ids, const int32_t* ranks,
                                  void* partial, float* partial_lse, int batch, int hq, int hkv, int sq, int skv,
                                  int topk, void* stream);
+/* The reference's token-major pair as it stands (main_tm_out + combine_tm_out,
+ * attention/kv_centric/optimization_round11/wrapper11.cpp:94-133): q [B, Sq, Hq, 128], partials
+ * token-major too, [B, Sq, TopK, Hq, 128] bf16; partial_lse stays [B, Hq, Sq, TopK] and the merged
+ * output head-major [B, Hq, Sq, 128], as in the reference. Hq / Hkv of 8 or 16; any TopK.
+ * Same arithmetic as the head-major entries: the merged output is bit-identical. */
+int sparse_b200_kv_token_main_tm_partial_tm(const void* q_token_major, const void* k, const void* v,
+                                            const int32_t* tasks, const int32_t* task_ptr, const int32_t* query_ids,
+                                            const int32_t* ranks, void* partial_token_major, float* partial_lse,
+                                            int batch, int hq, int hkv, int sq, int skv, int topk, void* stream);
+int sparse_b200_combine_tm(const void* partial_token_major, int partial_is_f32, const float* partial_lse, void* out,
+                           float* out_lse, int batch, int hq, int sq, int ranks, void* stream);
 
 /* R1 / R4 block-summary indexer (indexers/r1_r4/gpu_ops.py:6-49,
  * indexers/r1_r4/block_selectors.py:9-45), any Hkv, group size x R <= 64, any TopK.

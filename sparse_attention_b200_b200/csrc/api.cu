@@ -464,10 +464,10 @@ int sparse_b200_kv_token_main(const void* q, const void* k, const void* v, const
                               sq, skv, topk, static_cast<cudaStream_t>(stream));
 }
 
-int sparse_b200_kv_token_main_tm(const void* q_token_major, const void* k, const void* v, const int32_t* tasks,
-                                 const int32_t* task_ptr, const int32_t* query_ids, const int32_t* ranks,
-                                 void* partial, float* partial_lse, int batch, int hq, int hkv, int sq, int skv,
-                                 int topk, void* stream) {
+static int kv_token_main_token_major(const void* q_token_major, const void* k, const void* v, const int32_t* tasks,
+                                     const int32_t* task_ptr, const int32_t* query_ids, const int32_t* ranks,
+                                     void* partial, float* partial_lse, int batch, int hq, int hkv, int sq, int skv,
+                                     int topk, int layout, void* stream) {
   REQUIRE(q_token_major && k && v && tasks && task_ptr && query_ids && ranks && partial && partial_lse, "null pointer");
   REQUIRE(batch > 0 && hkv > 0 && hq >= hkv && hq % hkv == 0, "Hq must be a positive multiple of Hkv");
   const int g = hq / hkv;
@@ -481,7 +481,35 @@ int sparse_b200_kv_token_main_tm(const void* q_token_major, const void* k, const
           "misaligned pointer");
   const long long rows = static_cast<long long>(batch) * hkv * (skv / 128);
   return launch_kv_token_pipe(q_token_major, k, v, tasks, task_ptr + rows, query_ids, ranks, partial, partial_lse, batch,
-                              hq, hkv, sq, skv, topk, 1, static_cast<cudaStream_t>(stream));
+                              hq, hkv, sq, skv, topk, layout, static_cast<cudaStream_t>(stream));
+}
+
+int sparse_b200_kv_token_main_tm(const void* q_token_major, const void* k, const void* v, const int32_t* tasks,
+                                 const int32_t* task_ptr, const int32_t* query_ids, const int32_t* ranks,
+                                 void* partial, float* partial_lse, int batch, int hq, int hkv, int sq, int skv,
+                                 int topk, void* stream) {
+  return kv_token_main_token_major(q_token_major, k, v, tasks, task_ptr, query_ids, ranks, partial, partial_lse, batch,
+                                   hq, hkv, sq, skv, topk, 1, stream);
+}
+
+int sparse_b200_kv_token_main_tm_partial_tm(const void* q_token_major, const void* k, const void* v,
+                                            const int32_t* tasks, const int32_t* task_ptr, const int32_t* query_ids,
+                                            const int32_t* ranks, void* partial_token_major, float* partial_lse,
+                                            int batch, int hq, int hkv, int sq, int skv, int topk, void* stream) {
+  return kv_token_main_token_major(q_token_major, k, v, tasks, task_ptr, query_ids, ranks, partial_token_major,
+                                   partial_lse, batch, hq, hkv, sq, skv, topk, 3, stream);
+}
+
+int sparse_b200_combine_tm(const void* partial_token_major, int partial_is_f32, const float* partial_lse, void* out,
+                           float* out_lse, int batch, int hq, int sq, int ranks, void* stream) {
+  REQUIRE(partial_token_major && partial_lse && out, "null pointer");
+  REQUIRE(batch > 0 && hq > 0 && sq > 0 && ranks > 0, "sizes must be positive");
+  REQUIRE(aligned16(partial_token_major) && aligned16(out), "misaligned pointer");
+  const long long rows = static_cast<long long>(batch) * hq * sq;
+  // rows run (batch, head, token) as in the output; the kernel finds a row's partials at
+  // ((b * Sq + s) * ranks * Hq + h) * 128, one rank Hq * 128 elements further
+  return launch_combine(partial_token_major, partial_is_f32, partial_lse, out, out_lse, rows, ranks,
+                        static_cast<long long>(hq) * 128, 128, 1, ranks, static_cast<cudaStream_t>(stream), hq, sq);
 }
 
 int64_t sparse_b200_indexer_fp4_workspace_bytes(int batch, int hidx, int hk, int len_q, int len_kv) {

@@ -42,12 +42,22 @@ struct Raw4<__nv_bfloat16> {
 // needs to approach HBM bandwidth. The raw partial rows are requested first; the LSEs of a row
 // are fetched one rank per lane and reduced with shuffles while those loads fly. A rank of
 // weight 0 is dropped with a select, whatever it holds.
+// Offset of a row's first partial. Rows are (batch, head, token) in that order everywhere; with
+// tm_h > 0 the partials are token-major [B, S, ranks, H, 128] (the caller passes H * 128 as the
+// rank stride), else `row * p_stride_row`.
+__device__ __forceinline__ long long partial_base(long long row, long long p_stride_row, int ranks, int tm_h, int tm_s) {
+  if (tm_h == 0) return row * p_stride_row;
+  const long long bh = row / tm_s;
+  const long long s = row - bh * tm_s, b = bh / tm_h, h = bh - b * tm_h;
+  return ((b * tm_s + s) * ranks * tm_h + h) * 128;
+}
+
 template <typename T, int RPW>
 __global__ void __launch_bounds__(128) combine_kernel(const T* __restrict__ partial, const float* __restrict__ lses,
                                                       __nv_bfloat16* __restrict__ out, float* __restrict__ out_lse,
                                                       long long rows, int ranks, long long p_stride_rank,
                                                       long long p_stride_row, long long l_stride_rank,
-                                                      long long l_stride_row) {
+                                                      long long l_stride_row, int tm_h, int tm_s) {
   constexpr int CB = 16 / RPW;                   // ranks per batch
   const int lane = threadIdx.x & 31;
   const long long row0 = (static_cast<long long>(blockIdx.x) * 4 + (threadIdx.x >> 5)) * RPW;
@@ -58,13 +68,13 @@ __global__ void __launch_bounds__(128) combine_kernel(const T* __restrict__ part
     const long long row = min(row0 + rr, rows - 1);
 #pragma unroll
     for (int j = 0; j < CB; ++j)
-      if (j < ranks) val[rr][j].load(partial + row * p_stride_row + lane * 4 + j * p_stride_rank);
+      if (j < ranks) val[rr][j].load(partial + partial_base(row, p_stride_row, ranks, tm_h, tm_s) + lane * 4 + j * p_stride_rank);
   }
 #pragma unroll
   for (int rr = 0; rr < RPW; ++rr) {
     const bool live = row0 + rr < rows;
     const long long row = live ? row0 + rr : rows - 1;
-    const T* base = partial + row * p_stride_row + lane * 4;
+    const T* base = partial + partial_base(row, p_stride_row, ranks, tm_h, tm_s) + lane * 4;
     const float* lbase = lses + row * l_stride_row;
     // row maximum of the LSEs: lane l takes ranks l, l + 32, ...
     float maximum = -CUDART_INF_F;
@@ -152,7 +162,8 @@ template <typename T, int R, int U>
 __global__ void __launch_bounds__(256) combine_few_kernel(const T* __restrict__ partial, const float* __restrict__ lses,
                                                           __nv_bfloat16* __restrict__ out, float* __restrict__ out_lse,
                                                           long long rows, long long p_stride_rank, long long p_stride_row,
-                                                          long long l_stride_rank, long long l_stride_row) {
+                                                          long long l_stride_rank, long long l_stride_row, int tm_h,
+                                                          int tm_s) {
   const int slot = threadIdx.x >> 4, part = threadIdx.x & 15;
   const long long row_base = static_cast<long long>(blockIdx.x) * (16 * U) + slot;
   Raw8<T> val[U][R];
@@ -160,7 +171,7 @@ __global__ void __launch_bounds__(256) combine_few_kernel(const T* __restrict__ 
 #pragma unroll
   for (int u = 0; u < U; ++u) {
     const long long row = min(row_base + 16 * u, rows - 1);
-    const T* src = partial + row * p_stride_row + part * 8;
+    const T* src = partial + partial_base(row, p_stride_row, R, tm_h, tm_s) + part * 8;
     const float* lsrc = lses + row * l_stride_row;
 #pragma unroll
     for (int r = 0; r < R; ++r) {
@@ -206,39 +217,39 @@ __global__ void __launch_bounds__(256) combine_few_kernel(const T* __restrict__ 
 
 template <typename T, int R>
 static void combine_few_launch(const void* partial, const float* lses, void* out, float* out_lse, long long rows,
-                               long long psr, long long psw, long long lsr, long long lsw, cudaStream_t stream) {
+                               long long psr, long long psw, long long lsr, long long lsw, int tm_h, int tm_s, cudaStream_t stream) {
   constexpr int U = R <= 4 ? 2 : 1;
   combine_few_kernel<T, R, U><<<static_cast<unsigned>((rows + 16 * U - 1) / (16 * U)), 256, 0, stream>>>(
-      static_cast<const T*>(partial), lses, static_cast<__nv_bfloat16*>(out), out_lse, rows, psr, psw, lsr, lsw);
+      static_cast<const T*>(partial), lses, static_cast<__nv_bfloat16*>(out), out_lse, rows, psr, psw, lsr, lsw, tm_h, tm_s);
 }
 
 template <typename T>
 static void combine_few_dispatch(int ranks, const void* partial, const float* lses, void* out, float* out_lse,
                                  long long rows, long long psr, long long psw, long long lsr, long long lsw,
-                                 cudaStream_t stream) {
+                                 int tm_h, int tm_s, cudaStream_t stream) {
   switch (ranks) {
-    case 1: combine_few_launch<T, 1>(partial, lses, out, out_lse, rows, psr, psw, lsr, lsw, stream); break;
-    case 2: combine_few_launch<T, 2>(partial, lses, out, out_lse, rows, psr, psw, lsr, lsw, stream); break;
-    case 3: combine_few_launch<T, 3>(partial, lses, out, out_lse, rows, psr, psw, lsr, lsw, stream); break;
-    case 4: combine_few_launch<T, 4>(partial, lses, out, out_lse, rows, psr, psw, lsr, lsw, stream); break;
-    case 8: combine_few_launch<T, 8>(partial, lses, out, out_lse, rows, psr, psw, lsr, lsw, stream); break;
-    default: combine_few_launch<T, 16>(partial, lses, out, out_lse, rows, psr, psw, lsr, lsw, stream); break;
+    case 1: combine_few_launch<T, 1>(partial, lses, out, out_lse, rows, psr, psw, lsr, lsw, tm_h, tm_s, stream); break;
+    case 2: combine_few_launch<T, 2>(partial, lses, out, out_lse, rows, psr, psw, lsr, lsw, tm_h, tm_s, stream); break;
+    case 3: combine_few_launch<T, 3>(partial, lses, out, out_lse, rows, psr, psw, lsr, lsw, tm_h, tm_s, stream); break;
+    case 4: combine_few_launch<T, 4>(partial, lses, out, out_lse, rows, psr, psw, lsr, lsw, tm_h, tm_s, stream); break;
+    case 8: combine_few_launch<T, 8>(partial, lses, out, out_lse, rows, psr, psw, lsr, lsw, tm_h, tm_s, stream); break;
+    default: combine_few_launch<T, 16>(partial, lses, out, out_lse, rows, psr, psw, lsr, lsw, tm_h, tm_s, stream); break;
   }
 }
 
 template <typename T, int RPW>
 static void combine_launch(const void* partial, const float* lses, void* out, float* out_lse, long long rows, int ranks,
-                           long long psr, long long psw, long long lsr, long long lsw, cudaStream_t stream) {
+                           long long psr, long long psw, long long lsr, long long lsw, int tm_h, int tm_s, cudaStream_t stream) {
   const long long blocks = (rows + 4 * RPW - 1) / (4 * RPW);
   combine_kernel<T, RPW><<<static_cast<unsigned>(blocks), 128, 0, stream>>>(
-      static_cast<const T*>(partial), lses, static_cast<__nv_bfloat16*>(out), out_lse, rows, ranks, psr, psw, lsr, lsw);
+      static_cast<const T*>(partial), lses, static_cast<__nv_bfloat16*>(out), out_lse, rows, ranks, psr, psw, lsr, lsw, tm_h, tm_s);
 }
 
 }  // namespace
 
 int launch_combine(const void* partial, int partial_is_f32, const float* lses, void* out, float* out_lse,
                    long long rows, int ranks, long long p_stride_rank, long long p_stride_row,
-                   long long l_stride_rank, long long l_stride_row, cudaStream_t stream) {
+                   long long l_stride_rank, long long l_stride_row, cudaStream_t stream, int tm_h, int tm_s) {
   DeviceCtx* ctx = device_ctx();
   if (!ctx) return SB_ERR_CUDA;
   if ((rows + 3) / 4 > 0x7fffffffLL) return set_error(SB_ERR_INVALID, "too many rows for one combine launch");
@@ -248,20 +259,20 @@ int launch_combine(const void* partial, int partial_is_f32, const float* lses, v
                        ((p_stride_row * esz) & 15) == 0 && ((reinterpret_cast<uintptr_t>(out) & 15u) == 0);
   const bool compiled_in = (ranks >= 1 && ranks <= 4) || (!partial_is_f32 && (ranks == 8 || ranks == 16));
   if (compiled_in && aligned) {
-    if (partial_is_f32) combine_few_dispatch<float>(ranks, partial, lses, out, out_lse, rows, p_stride_rank, p_stride_row, l_stride_rank, l_stride_row, stream);
-    else combine_few_dispatch<__nv_bfloat16>(ranks, partial, lses, out, out_lse, rows, p_stride_rank, p_stride_row, l_stride_rank, l_stride_row, stream);
+    if (partial_is_f32) combine_few_dispatch<float>(ranks, partial, lses, out, out_lse, rows, p_stride_rank, p_stride_row, l_stride_rank, l_stride_row, tm_h, tm_s, stream);
+    else combine_few_dispatch<__nv_bfloat16>(ranks, partial, lses, out, out_lse, rows, p_stride_rank, p_stride_row, l_stride_rank, l_stride_row, tm_h, tm_s, stream);
     cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? SB_OK : set_error(SB_ERR_CUDA, cudaGetErrorString(e));
   }
   // few ranks: several rows per warp, so that every lane still has 16 loads in flight
   if (partial_is_f32) {
-    if (ranks <= 4) combine_launch<float, 4>(partial, lses, out, out_lse, rows, ranks, p_stride_rank, p_stride_row, l_stride_rank, l_stride_row, stream);
-    else if (ranks <= 8) combine_launch<float, 2>(partial, lses, out, out_lse, rows, ranks, p_stride_rank, p_stride_row, l_stride_rank, l_stride_row, stream);
-    else combine_launch<float, 1>(partial, lses, out, out_lse, rows, ranks, p_stride_rank, p_stride_row, l_stride_rank, l_stride_row, stream);
+    if (ranks <= 4) combine_launch<float, 4>(partial, lses, out, out_lse, rows, ranks, p_stride_rank, p_stride_row, l_stride_rank, l_stride_row, tm_h, tm_s, stream);
+    else if (ranks <= 8) combine_launch<float, 2>(partial, lses, out, out_lse, rows, ranks, p_stride_rank, p_stride_row, l_stride_rank, l_stride_row, tm_h, tm_s, stream);
+    else combine_launch<float, 1>(partial, lses, out, out_lse, rows, ranks, p_stride_rank, p_stride_row, l_stride_rank, l_stride_row, tm_h, tm_s, stream);
   } else {
-    if (ranks <= 4) combine_launch<__nv_bfloat16, 4>(partial, lses, out, out_lse, rows, ranks, p_stride_rank, p_stride_row, l_stride_rank, l_stride_row, stream);
-    else if (ranks <= 8) combine_launch<__nv_bfloat16, 2>(partial, lses, out, out_lse, rows, ranks, p_stride_rank, p_stride_row, l_stride_rank, l_stride_row, stream);
-    else combine_launch<__nv_bfloat16, 1>(partial, lses, out, out_lse, rows, ranks, p_stride_rank, p_stride_row, l_stride_rank, l_stride_row, stream);
+    if (ranks <= 4) combine_launch<__nv_bfloat16, 4>(partial, lses, out, out_lse, rows, ranks, p_stride_rank, p_stride_row, l_stride_rank, l_stride_row, tm_h, tm_s, stream);
+    else if (ranks <= 8) combine_launch<__nv_bfloat16, 2>(partial, lses, out, out_lse, rows, ranks, p_stride_rank, p_stride_row, l_stride_rank, l_stride_row, tm_h, tm_s, stream);
+    else combine_launch<__nv_bfloat16, 1>(partial, lses, out, out_lse, rows, ranks, p_stride_rank, p_stride_row, l_stride_rank, l_stride_row, tm_h, tm_s, stream);
   }
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? SB_OK : set_error(SB_ERR_CUDA, cudaGetErrorString(e));

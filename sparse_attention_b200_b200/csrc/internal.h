@@ -41,7 +41,7 @@ int launch_q_centric(const QCentricArgs& a, cudaStream_t stream);
 
 int launch_combine(const void* partial, int partial_is_f32, const float* lses, void* out, float* out_lse,
                    long long rows, int ranks, long long p_stride_rank, long long p_stride_row,
-                   long long l_stride_rank, long long l_stride_row, cudaStream_t stream);
+                   long long l_stride_rank, long long l_stride_row, cudaStream_t stream, int tm_h = 0, int tm_s = 0);
 int launch_split_segments(const int32_t* ids, const int32_t* counts, int32_t* seg_ids, int32_t* seg_counts,
                           int* error, long long lists, int topk, int kv_blocks, int nseg, cudaStream_t stream);
 int launch_pool(const void* x, void* desc, long long num_desc, int tokens_per_desc, cudaStream_t stream);

@@ -64,6 +64,7 @@ struct Params {
   int batch, hq, hkv, sq, skv, topk, group, group_log2, edges;
   int phases;                   // upper bound on the number of passes over the task list (see Walk)
   int q_token_major;            // q is [B, Sq, Hq, 128]: the G heads of a token are one dense box
+  int partial_token_major;      // partials are [B, Sq, TopK, Hq, 128] (the reference's token-major operators)
   float scale_log2;
 };
 
@@ -443,8 +444,13 @@ kv_token_pipe_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_con
       if (qi >= 0) {
         const int b = k.group / p.hkv, kvh = k.group - b * p.hkv;
         const uint32_t src = stage + lane * G * 128;
-        tma_store_4d(&o_map, 0, rank, qi, b * p.hq + kvh * G, src);
-        tma_store_4d(&o_map, 64, rank, qi, b * p.hq + kvh * G, src + 4096);
+        if (p.partial_token_major) {              // box {64 columns, G heads, 1 rank, 1 token}
+          tma_store_4d(&o_map, 0, kvh * G, rank, b * p.sq + qi, src);
+          tma_store_4d(&o_map, 64, kvh * G, rank, b * p.sq + qi, src + 4096);
+        } else {
+          tma_store_4d(&o_map, 0, rank, qi, b * p.hq + kvh * G, src);
+          tma_store_4d(&o_map, 64, rank, qi, b * p.hq + kvh * G, src + 4096);
+        }
         bulk_commit();
       }
     }
@@ -462,8 +468,9 @@ kv_token_pipe_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_con
 
 }  // namespace kvp
 
-// Pipelined main stage for Hq / Hkv of 8 or 16 (arguments of launch_kv_token_main; q_token_major:
-// q is [B, Sq, Hq, 128] instead of [B, Hq, Sq, 128]).
+// Pipelined main stage for Hq / Hkv of 8 or 16 (arguments of launch_kv_token_main; q_token_major bit 0:
+// q is [B, Sq, Hq, 128] instead of [B, Hq, Sq, 128]; bit 1: the partials are [B, Sq, TopK, Hq, 128]
+// instead of [B, Hq, Sq, TopK, 128]).
 int launch_kv_token_pipe(const void* q, const void* k, const void* v, const int32_t* tasks, const int32_t* task_count,
                          const int32_t* qids, const int32_t* ranks, void* partial, float* lses, int batch, int hq,
                          int hkv, int sq, int skv, int topk, int q_token_major, cudaStream_t stream) {
@@ -480,7 +487,9 @@ int launch_kv_token_pipe(const void* q, const void* k, const void* v, const int3
   while ((1 << p.group_log2) < group) ++p.group_log2;
   p.edges = static_cast<int>(static_cast<long long>(batch) * hkv * sq * topk);
   p.scale_log2 = 1.4426950408889634f / sqrtf(128.0f);
-  p.q_token_major = q_token_major;
+  p.q_token_major = q_token_major & 1;
+  p.partial_token_major = (q_token_major >> 1) & 1;
+  q_token_major &= 1;
   // one segment per 24 MB of Q: the Q rows a segment gathers then stay within L2
   const long long q_bytes = static_cast<long long>(batch) * hq * sq * 256;
   p.phases = static_cast<int>(std::min<long long>(64, (q_bytes + (24LL << 20) - 1) / (24LL << 20)));
@@ -514,12 +523,19 @@ int launch_kv_token_pipe(const void* q, const void* k, const void* v, const int3
       return set_error(SB_ERR_CUDA, "cuTensorMapEncodeTiled failed for q");
   }
   {
-    // partial [B*Hq, Sq, TopK, 128]: one box = the G heads of a KV group at one (token, rank)
-    const cuuint64_t dims[4] = {128, static_cast<cuuint64_t>(topk), static_cast<cuuint64_t>(sq),
-                                static_cast<cuuint64_t>(batch) * hq};
-    const cuuint64_t strides[3] = {256, static_cast<cuuint64_t>(topk) * 256,
-                                   static_cast<cuuint64_t>(sq) * topk * 256};
-    const cuuint32_t box[4] = {64, 1, 1, static_cast<cuuint32_t>(group)};
+    // partial [B*Hq, Sq, TopK, 128]: one box = the G heads of a KV group at one (token, rank);
+    // token-major [B*Sq, TopK, Hq, 128]: the same G rows of 64 columns, heads next to the columns
+    cuuint64_t dims[4] = {128, static_cast<cuuint64_t>(topk), static_cast<cuuint64_t>(sq),
+                          static_cast<cuuint64_t>(batch) * hq};
+    cuuint64_t strides[3] = {256, static_cast<cuuint64_t>(topk) * 256, static_cast<cuuint64_t>(sq) * topk * 256};
+    cuuint32_t box[4] = {64, 1, 1, static_cast<cuuint32_t>(group)};
+    if (p.partial_token_major) {
+      dims[1] = static_cast<cuuint64_t>(hq); dims[2] = static_cast<cuuint64_t>(topk);
+      dims[3] = static_cast<cuuint64_t>(batch) * sq;
+      strides[0] = 256; strides[1] = static_cast<cuuint64_t>(hq) * 256;
+      strides[2] = static_cast<cuuint64_t>(topk) * hq * 256;
+      box[1] = static_cast<cuuint32_t>(group); box[3] = 1;
+    }
     if (encode_tiled(&om, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, partial, dims, strides, box, ones,
                      CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE))
       return set_error(SB_ERR_CUDA, "cuTensorMapEncodeTiled failed for the partial outputs");

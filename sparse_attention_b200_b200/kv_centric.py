@@ -91,11 +91,15 @@ class PreparedTokens:
     q_token_major=True: q is [B,Sq,Hq,128], the layout of the reference's TMA variants (groups of
     8 or 16 heads only); outputs stay head-major."""
 
-    def __init__(self, q, k, v, selected, q_token_major=False):
+    def __init__(self, q, k, v, selected, q_token_major=False, partial_token_major=False):
         import ctypes
         if not (q.is_cuda and q.dtype == torch.bfloat16 and q.is_contiguous() and q.dim() == 4 and q.shape[3] == 128):
             raise _lib.SparseB200Error("q must be contiguous bf16 [B,Hq,Sq,128] (or [B,Sq,Hq,128]) on CUDA")
         self.q_token_major = bool(q_token_major)
+        # partials [B,Sq,TopK,Hq,128] as the reference's main_tm_out writes them (needs q token-major too)
+        self.partial_token_major = bool(partial_token_major)
+        if self.partial_token_major and not self.q_token_major:
+            raise _lib.SparseB200Error("token-major partials go with token-major q")
         q_arg = q
         if self.q_token_major:
             q = q.permute(0, 2, 1, 3)          # a head-major VIEW for the shape checks below; q_arg is what runs
@@ -131,7 +135,8 @@ class PreparedTokens:
         self.qids, self.ranks = ints(self.edges), ints(self.edges)
         self.tasks = torch.zeros((self.max_tasks, 4), device=dev, dtype=torch.int32)
         self.error = ints(1)
-        self.partial = torch.empty((b, hq, sq, self.topk, d), device=dev, dtype=torch.bfloat16)
+        self.partial = torch.empty((b, sq, self.topk, hq, d) if self.partial_token_major else (b, hq, sq, self.topk, d),
+                                   device=dev, dtype=torch.bfloat16)
         self.lses = torch.empty((b, hq, sq, self.topk), device=dev, dtype=torch.float32)
         self.out = torch.empty((b, hq, sq, d), device=dev, dtype=torch.bfloat16)
         self.out_lse = torch.empty((b, hq, sq), device=dev, dtype=torch.float32)
@@ -150,7 +155,9 @@ class PreparedTokens:
 
     def main(self):
         with torch.cuda.device(self.q.device):
-            fn = _lib.lib().sparse_b200_kv_token_main_tm if self.q_token_major else _lib.lib().sparse_b200_kv_token_main
+            L = _lib.lib()
+            fn = L.sparse_b200_kv_token_main_tm_partial_tm if self.partial_token_major else \
+                L.sparse_b200_kv_token_main_tm if self.q_token_major else L.sparse_b200_kv_token_main
             _lib.check(fn(
                 _lib.ptr(self.q), _lib.ptr(self.k), _lib.ptr(self.v), _lib.ptr(self.tasks), _lib.ptr(self.task_ptr),
                 _lib.ptr(self.qids), _lib.ptr(self.ranks), _lib.ptr(self.partial), _lib.ptr(self.lses),
@@ -159,6 +166,11 @@ class PreparedTokens:
     def combine(self):
         import ctypes
         with torch.cuda.device(self.q.device):
+            if self.partial_token_major:
+                _lib.check(_lib.lib().sparse_b200_combine_tm(
+                    _lib.ptr(self.partial), 0, _lib.ptr(self.lses), _lib.ptr(self.out), _lib.ptr(self.out_lse),
+                    self.b, self.hq, self.sq, self.topk, _lib.current_stream()))
+                return
             _lib.check(_lib.lib().sparse_b200_combine(
                 _lib.ptr(self.partial), 0, _lib.ptr(self.lses), _lib.ptr(self.out), _lib.ptr(self.out_lse),
                 ctypes.c_int64(self.out_lse.numel()), self.topk, 0, _lib.current_stream()))

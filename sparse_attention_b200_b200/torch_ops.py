@@ -90,6 +90,9 @@ def _register_kvopt11():
     lib.define("main_out(Tensor q, Tensor k, Tensor v, Tensor tasks, Tensor qids, Tensor ranks, Tensor(a!) partial, "
                "Tensor(b!) lses, int variant) -> ()")
     lib.define("combine_out(Tensor partial, Tensor lses, Tensor(a!) out, Tensor(b!) out_lse) -> ()")
+    lib.define("main_tm_out(Tensor q, Tensor k, Tensor v, Tensor tasks, Tensor qids, Tensor ranks, Tensor(a!) partial, "
+               "Tensor(b!) lses, int variant) -> ()")
+    lib.define("combine_tm_out(Tensor partial, Tensor lses, Tensor(a!) out, Tensor(b!) out_lse) -> ()")
     # the task count travels from metadata_out to main_out on the device: task_ptr[rows] of the last build
     state = {}
 
@@ -162,10 +165,54 @@ def _register_kvopt11():
                 _lib.ptr(partial), int(partial.dtype == torch.float32), _lib.ptr(lses), _lib.ptr(out), _lib.ptr(out_lse),
                 ctypes.c_int64(out_lse.numel()), ranks, 0, _lib.current_stream()))
 
+    def main_tm_out(q, k, v, tasks, qids, ranks, partial, lses, variant):
+        # wrapper11.cpp:94-118: q [B,Sq,Hq,128], partial [B,Sq,TopK,Hq,128], lses [B,Hq,Sq,TopK]; variants 1 and 2
+        # are the bf16-partial ones (0 = fp32 partials is not served)
+        if variant not in (1, 2):
+            _fail("main_tm_out serves the bf16-partial variants (1, 2)")
+        for t in (q, k, v, partial):
+            if not (t.is_cuda and t.dtype == torch.bfloat16 and t.is_contiguous()) or t.requires_grad:
+                _fail("q, k, v and partial must be contiguous bf16 CUDA tensors (forward only)")
+        _ints(q, tasks, qids, ranks)
+        if q.dim() != 4 or k.dim() != 4 or k.shape != v.shape or q.shape[3] != 128 or k.shape[3] != 128:
+            _fail("QKV rank/shape")
+        b, sq, hq, _ = q.shape
+        hkv, skv = k.shape[1:3]
+        if hkv <= 0 or hq % hkv or hq // hkv not in (8, 16):
+            _fail("GQA ratio (the token-major operators serve Hq/Hkv of 8 and 16)")
+        topk = qids.numel() // max(1, b * hkv * sq)
+        if tuple(partial.shape) != (b, sq, topk, hq, 128) or tuple(lses.shape) != (b, hq, sq, topk) \
+                or lses.dtype != torch.float32:
+            _fail("token-major partials")
+        task_ptr = state.get(tasks.data_ptr())
+        if task_ptr is None:
+            _fail("main_tm_out needs the task list of a preceding metadata_out on the same tasks tensor")
+        with torch.cuda.device(q.device):
+            _lib.check(_lib.lib().sparse_b200_kv_token_main_tm_partial_tm(
+                _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(tasks), _lib.ptr(task_ptr), _lib.ptr(qids),
+                _lib.ptr(ranks), _lib.ptr(partial), _lib.ptr(lses), b, hq, hkv, sq, skv, topk, _lib.current_stream()))
+
+    def combine_tm_out(partial, lses, out, out_lse):
+        if partial.dtype not in (torch.float32, torch.bfloat16) or not partial.is_contiguous() or not lses.is_contiguous():
+            _fail("partial dtype / layout")
+        if out.dim() != 4 or out.shape[3] != 128 or tuple(out_lse.shape) != tuple(out.shape[:3]) \
+                or out.dtype != torch.bfloat16 or out_lse.dtype != torch.float32:
+            _fail("output")
+        b, h, s, _ = out.shape
+        ranks = lses.shape[-1]
+        if tuple(partial.shape) != (b, s, ranks, h, 128) or tuple(lses.shape) != (b, h, s, ranks):
+            _fail("token-major Combine input")
+        with torch.cuda.device(out.device):
+            _lib.check(_lib.lib().sparse_b200_combine_tm(
+                _lib.ptr(partial), int(partial.dtype == torch.float32), _lib.ptr(lses), _lib.ptr(out), _lib.ptr(out_lse),
+                b, h, s, ranks, _lib.current_stream()))
+
     lib.impl("metadata_temp_bytes", metadata_temp_bytes, "CompositeExplicitAutograd")
     lib.impl("metadata_out", metadata_out, "CUDA")
     lib.impl("main_out", main_out, "CUDA")
     lib.impl("combine_out", combine_out, "CUDA")
+    lib.impl("main_tm_out", main_tm_out, "CUDA")
+    lib.impl("combine_tm_out", combine_tm_out, "CUDA")
     return lib
 
 

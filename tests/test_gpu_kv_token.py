@@ -186,6 +186,17 @@ def test_token_major_q_gives_identical_results(g):
     assert torch.equal(token_major.partial.view(torch.int16), head_major.partial.view(torch.int16))
     assert torch.equal(token_major.lses, head_major.lses)
     assert torch.equal(token_major.out.view(torch.int16), head_major.out.view(torch.int16))
+    # partials token-major as well ([B,Sq,TopK,Hq,128], what the reference's main_tm_out writes and its
+    # combine_tm_out reads): same partial rows in another place, the same merged output
+    both = m.PreparedTokens(q.permute(0, 2, 1, 3).contiguous(), k, v, selected, q_token_major=True, partial_token_major=True)
+    both.poison()
+    both.run()
+    torch.cuda.synchronize()
+    m.device_status()
+    assert torch.equal(both.partial.permute(0, 3, 1, 2, 4).contiguous().view(torch.int16), head_major.partial.view(torch.int16))
+    assert torch.equal(both.lses, head_major.lses)
+    assert torch.equal(both.out.view(torch.int16), head_major.out.view(torch.int16))
+    assert torch.equal(both.out_lse, head_major.out_lse)
     with pytest.raises(m.SparseB200Error):
         m.PreparedTokens(torch.zeros((1, 8, 4, 128), dtype=torch.bfloat16, device="cuda"), k[:1, :1], v[:1, :1],
                          selected[:1, :1, :8].contiguous(), q_token_major=True)      # Hq/Hkv = 4

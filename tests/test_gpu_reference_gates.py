@@ -92,7 +92,7 @@ def test_reference_kv_centric_gate():
 
 
 def test_reference_operator_names_head_major_chain():
-    """xomtention_kvopt11::{metadata_out, main_out, combine_out} and xomtention_tile_topk::* as torch
+    """xomtention_kvopt11::{metadata_out, main_out, combine_out, main_tm_out, combine_tm_out} and xomtention_tile_topk::* as torch
     operators: the chain equals the Python mirror bit for bit (no reference sources needed)."""
     import oracle
     from oracle import inputs as gen
@@ -131,6 +131,23 @@ def test_reference_operator_names_head_major_chain():
         kv.metadata_out(sel, counts, row_ptr, cursors, qids, ranks, chunks, task_ptr, tasks, error, temp, skv // 128, g, 8)
     with pytest.raises(RuntimeError):
         kv.main_out(qc, kc, vc, tasks, qids, ranks, partial.float(), lses, -2)
+    # the token-major pair (main_tm_out + combine_tm_out, wrapper11.cpp:94-133): q [B,Sq,Hq,128], partials
+    # [B,Sq,TopK,Hq,128]; the merged output is the head-major chain's, bit for bit
+    q_tm = qc.permute(0, 2, 1, 3).contiguous()
+    partial_tm = torch.full((b, sq, topk, hq, 128), float("nan"), dtype=torch.bfloat16, device="cuda")
+    lses_tm = torch.full((b, hq, sq, topk), float("nan"), device="cuda")
+    kv.main_tm_out(q_tm, kc, vc, tasks, qids, ranks, partial_tm, lses_tm, 1)
+    out_tm = torch.full_like(qc, float("nan"))
+    out_lse_tm = torch.full((b, hq, sq), float("nan"), device="cuda")
+    kv.combine_tm_out(partial_tm, lses_tm, out_tm, out_lse_tm)
+    torch.cuda.synchronize()
+    sp.device_status()
+    assert torch.equal(partial_tm.permute(0, 3, 1, 2, 4), partial) and torch.equal(lses_tm, lses)
+    assert torch.equal(out_tm, out) and torch.equal(out_lse_tm, out_lse)
+    with pytest.raises(RuntimeError):
+        kv.main_tm_out(q_tm, kc, vc, tasks, qids, ranks, partial_tm, lses_tm, 0)     # fp32 partials are not served
+    with pytest.raises(RuntimeError):
+        kv.combine_tm_out(partial, lses, out_tm, out_lse_tm)                        # head-major partials
     # tile_topk operators against the Python mirror
     scores = torch.randn((2, 32, 2 * 256), device="cuda")
     tk = ops["xomtention_tile_topk"]
