@@ -95,6 +95,7 @@ def _register_kvopt11():
     lib.define("combine_tm_out(Tensor partial, Tensor lses, Tensor(a!) out, Tensor(b!) out_lse) -> ()")
     # the task count travels from metadata_out to main_out on the device: task_ptr[rows] of the last build
     state = {}
+    private = {}
 
     def metadata_temp_bytes(rows):
         if not 0 < rows < 2 ** 31 - 2:
@@ -106,8 +107,8 @@ def _register_kvopt11():
         _ints(selected, selected, counts, row_ptr, cursors, qids, ranks, chunks, task_ptr, tasks, error)
         if selected.dim() != 4:
             _fail("selected [B,Hkv,Sq,TopK]")
-        if chunk_size != 1:
-            _fail("chunk_size 1 only: a task holds at most 128 / group_size queries")
+        if chunk_size not in (1, 4, 8, 16) or group_size not in (1, 2, 4, 8, 16):
+            _fail("invalid routing geometry")
         b, hkv, sq, topk = selected.shape
         rows = b * hkv * kv_blocks
         for t in (counts, row_ptr, chunks, task_ptr):
@@ -118,15 +119,44 @@ def _register_kvopt11():
         L = _lib.lib()
         L.sparse_b200_kv_token_max_tasks.restype = ctypes.c_int64
         bound = L.sparse_b200_kv_token_max_tasks(b, hkv, sq, topk, kv_blocks, group_size)
-        if tasks.dim() != 2 or tasks.shape[1] != 4 or tasks.shape[0] < bound:
-            _fail("bounded tasks: [min(E, ceil(E / (128 / group_size)) + rows), 4]")
+        cap = 128 // group_size * chunk_size
+        edges = selected.numel()
+        if tasks.dim() != 2 or tasks.shape[1] != 4 or tasks.shape[0] < min(edges, -(-edges // cap) + rows):
+            _fail("bounded tasks: [min(E, ceil(E / (128 / group_size * chunk_size)) + rows), 4]")
+        # The kernels of this library take tasks of at most 128 / group_size queries. With a larger chunk_size
+        # that list lives in storage of the shim (allocated once per geometry), and the caller's tensors get the
+        # grouped list the reference's planner would have written (same edges, tasks of up to chunk_size times as
+        # many queries), which its audit reads.
+        own = chunk_size == 1
+        key = (selected.device, rows, int(bound))
+        if own:
+            run_tasks, run_task_ptr = tasks, task_ptr
+        else:
+            if key not in private:
+                private[key] = (torch.zeros((int(bound), 4), dtype=torch.int32, device=selected.device),
+                                torch.empty(rows + 1, dtype=torch.int32, device=selected.device))
+            run_tasks, run_task_ptr = private[key]
         # counts / cursors are scratch of rows + 1 ints in the C ABI: `chunks` serves as the cursors
         with torch.cuda.device(selected.device):
             _lib.check(L.sparse_b200_kv_token_metadata(
                 _lib.ptr(selected), _lib.ptr(counts), _lib.ptr(chunks), _lib.ptr(row_ptr), _lib.ptr(qids), _lib.ptr(ranks),
-                _lib.ptr(task_ptr), _lib.ptr(tasks), _lib.ptr(error), b, hkv, sq, topk, kv_blocks, group_size,
+                _lib.ptr(run_task_ptr), _lib.ptr(run_tasks), _lib.ptr(error), b, hkv, sq, topk, kv_blocks, group_size,
                 _lib.current_stream()))
-        state[tasks.data_ptr()] = task_ptr
+            if not own:                          # grouped list for the caller, on the device, no synchronisation
+                per_row = row_ptr[1:] - row_ptr[:-1]
+                n_tasks = (per_row + (cap - 1)) // cap
+                ends = torch.cumsum(n_tasks, 0)
+                task_ptr[0] = 0
+                task_ptr[1:] = ends
+                chunks.copy_(task_ptr)
+                t = torch.arange(tasks.shape[0], device=selected.device, dtype=torch.int64)
+                row = torch.searchsorted(ends.to(torch.int64), t, right=True).clamp_(max=rows - 1)
+                local = t - (ends[row].to(torch.int64) - n_tasks[row].to(torch.int64))
+                valid = (t < ends[-1].to(torch.int64)).to(torch.int32)
+                start = row_ptr[row].to(torch.int64) + local * cap
+                count = torch.minimum(per_row[row].to(torch.int64) - local * cap, torch.full_like(local, cap))
+                tasks.copy_(torch.stack([row // kv_blocks, row % kv_blocks, start, count], 1).to(torch.int32) * valid[:, None])
+        state[tasks.data_ptr()] = (run_tasks, run_task_ptr)
 
     def main_out(q, k, v, tasks, qids, ranks, partial, lses, variant):
         if variant != -1:
@@ -143,12 +173,13 @@ def _register_kvopt11():
         if tuple(partial.shape) != (b, hq, sq, topk, 128) or tuple(lses.shape) != (b, hq, sq, topk) \
                 or lses.dtype != torch.float32:
             _fail("partials must be [B,Hq,Sq,TopK,128] bf16 and [B,Hq,Sq,TopK] fp32")
-        task_ptr = state.get(tasks.data_ptr())
-        if task_ptr is None:
+        built = state.get(tasks.data_ptr())
+        if built is None:
             _fail("main_out needs the task list of a preceding metadata_out on the same tasks tensor")
+        run_tasks, task_ptr = built
         with torch.cuda.device(q.device):
             _lib.check(_lib.lib().sparse_b200_kv_token_main(
-                _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(tasks), _lib.ptr(task_ptr), _lib.ptr(qids),
+                _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(run_tasks), _lib.ptr(task_ptr), _lib.ptr(qids),
                 _lib.ptr(ranks), _lib.ptr(partial), _lib.ptr(lses), b, hq, hkv, sq, skv, topk, _lib.current_stream()))
 
     def combine_out(partial, lses, out, out_lse):
@@ -184,12 +215,13 @@ def _register_kvopt11():
         if tuple(partial.shape) != (b, sq, topk, hq, 128) or tuple(lses.shape) != (b, hq, sq, topk) \
                 or lses.dtype != torch.float32:
             _fail("token-major partials")
-        task_ptr = state.get(tasks.data_ptr())
-        if task_ptr is None:
+        built = state.get(tasks.data_ptr())
+        if built is None:
             _fail("main_tm_out needs the task list of a preceding metadata_out on the same tasks tensor")
+        run_tasks, task_ptr = built
         with torch.cuda.device(q.device):
             _lib.check(_lib.lib().sparse_b200_kv_token_main_tm_partial_tm(
-                _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(tasks), _lib.ptr(task_ptr), _lib.ptr(qids),
+                _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(run_tasks), _lib.ptr(task_ptr), _lib.ptr(qids),
                 _lib.ptr(ranks), _lib.ptr(partial), _lib.ptr(lses), b, hq, hkv, sq, skv, topk, _lib.current_stream()))
 
     def combine_tm_out(partial, lses, out, out_lse):

@@ -15,6 +15,11 @@ library through the operator names / module interface the gates use:
   per-token KV-centric operator. Sixteen cases (sampled partials, analytic cases, reorder,
   non-default stream, repeat) + the Combine unit with +-1000 LSEs.
 
+* attention/kv_centric/optimization_round11/api11.py `Prepared`, the reference's host class for its round-11
+  KV-centric operator, used as it is over torch.ops.xomtention_kvopt11 from this library: variants split8_bf16,
+  tma8_bf16 and tma16_bf16 (its planner's chunk sizes 8 and 16, token-major q and partials), its own audit of
+  the task lists.
+
 Skipped, with the reason, when baseline/_ref/ does not hold the reference files."""
 import os
 import sys
@@ -128,7 +133,7 @@ def test_reference_operator_names_head_major_chain():
     o2, l2 = prep.run()
     assert torch.equal(out, o2) and torch.equal(out_lse, l2)
     with pytest.raises(RuntimeError):
-        kv.metadata_out(sel, counts, row_ptr, cursors, qids, ranks, chunks, task_ptr, tasks, error, temp, skv // 128, g, 8)
+        kv.metadata_out(sel, counts, row_ptr, cursors, qids, ranks, chunks, task_ptr, tasks, error, temp, skv // 128, g, 3)
     with pytest.raises(RuntimeError):
         kv.main_out(qc, kc, vc, tasks, qids, ranks, partial.float(), lses, -2)
     # the token-major pair (main_tm_out + combine_tm_out, wrapper11.cpp:94-133): q [B,Sq,Hq,128], partials
@@ -156,3 +161,47 @@ def test_reference_operator_names_head_major_chain():
     tk.tile_topk_out(scores, ids2, 2, 256)
     assert torch.equal(ids, ids2) and torch.equal(ids, sp.tile_topk(scores, batch_size=2, len_q=256, topk=16))
     assert torch.equal(ids.cpu(), oracle.fp4_select(scores.cpu(), 2, 256, 16))
+
+
+def test_reference_round11_prepared_class_runs_on_this_library():
+    """attention/kv_centric/optimization_round11/api11.py `Prepared` (the reference's own host class: GPUPlan with
+    its chunk sizes, main_out / main_tm_out, combine_out / combine_tm_out, partial_view) used as it is, with
+    torch.ops.xomtention_kvopt11 coming from this library instead of the reference's extension: outputs and
+    partials equal this library's Python mirror bit for bit for the bf16-partial variants (split8_bf16, tma8_bf16,
+    tma16_bf16), and the reference's own audit of the task lists (gpu_plan.py:47-73) passes."""
+    _need("kv_centric/optimization_round11/api11.py", "kv_centric/optimization_round4/gpu_plan.py",
+          "kv_centric/optimization_round4/planning.py", "kv_centric/metadata.py")
+    import sparse_attention_b200_b200 as sp
+    from sparse_attention_b200_b200 import torch_ops
+    torch_ops.register(("xomtention_kvopt11",))
+    r11 = os.path.join(REF, "kv_centric", "optimization_round11")
+    sys.path.insert(0, r11)
+    try:
+        import api11
+        api11._OPS = torch.ops.xomtention_kvopt11          # what load_extension() would set after building its own
+        api11.old_plan.load_extension = lambda: api11._OPS
+        gen_ = torch.Generator().manual_seed(5)
+        for b, hkv, g, sq, skv in ((2, 1, 16, 300, 4096), (1, 2, 8, 520, 2048)):
+            hq = hkv * g
+            q_tm = torch.randn((b, sq, hq, 128), generator=gen_).to(torch.bfloat16).cuda()
+            k = torch.randn((b, hkv, skv, 128), generator=gen_).to(torch.bfloat16).cuda()
+            v = torch.randn((b, hkv, skv, 128), generator=gen_).to(torch.bfloat16).cuda()
+            selected = torch.stack([torch.randperm(skv // 128, generator=gen_)[:16] for _ in range(b * hkv * sq)]) \
+                .to(torch.int32).reshape(b, hkv, sq, 16)
+            sel = selected.cuda()
+            ours = sp.PreparedTokens(q_tm.permute(0, 2, 1, 3).contiguous(), k, v, sel)
+            ours.run()
+            for variant in (-1, 1, 2):
+                prep = api11.Prepared(q_tm, k, v, sel, variant=variant)
+                prep.poison()
+                prep.run()
+                torch.cuda.synchronize()
+                sp.device_status()
+                assert torch.equal(prep.out, ours.out) and torch.equal(prep.out_lse, ours.out_lse), variant
+                assert torch.equal(prep.partial_view(), ours.partial) and torch.equal(prep.lses, ours.lses), variant
+                report = prep.plan.audit(selected)
+                assert report["exact_coverage"] and report["gpu_error"] == 0, variant
+            with pytest.raises(RuntimeError):                # fp32 partials are not served
+                api11.Prepared(q_tm, k, v, sel, variant=0).run()
+    finally:
+        sys.path.remove(r11)
