@@ -1,0 +1,98 @@
+"""Seeded random shapes through the indexers' fast paths against their exact kernels on the GPU.
+
+The hand-picked shapes of test_gpu_indexers.py cover the cases each kernel was designed around; a
+defect that depends on a remainder (a slice whose length modulo 256 is below 32 once left part of
+a warp out of a vote) shows only on shapes nobody thought of. Every shape here is drawn from a
+seeded generator, so a failure names a reproducible case. Ids must be bit-identical to the exact
+kernels' (which the other tests pin to the oracle), no bounded wait may run out, no bound may be
+violated."""
+import os
+import random
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+SCALE = int(os.environ.get("SPARSE_B200_RANDOM_SHAPES", "1"))      # multiplies the number of shapes (a longer hunt)
+
+
+def sp():
+    import sparse_attention_b200_b200 as m
+    return m
+
+
+def _summary_shapes(n, seed):
+    rng = random.Random(seed)
+    out = []
+    while len(out) < n:
+        r = rng.choice([1, 2, 4])
+        g = rng.choice([1, 2, 4, 8, 16])
+        if g * r > 64:
+            continue
+        hkv = rng.choice([1, 2, 4])
+        b = rng.choice([1, 2])
+        nt = rng.choice([rng.randint(16, 200), rng.randint(200, 1200), rng.randint(1200, 3000)])
+        topk = rng.choice([4, 8, 16, 32, 64])
+        if topk > nt:
+            continue
+        budget = 120_000_000 // (b * hkv * g * 128 * 128)      # query blocks that keep q under ~240 MB
+        qt = min(rng.choice([rng.randint(1, 12), rng.randint(12, 80), rng.randint(80, 220)]), max(1, budget))
+        out.append((b, hkv * g, hkv, qt * 128, nt * 128, r, topk))
+    return out
+
+
+@pytest.mark.parametrize("shape", _summary_shapes(28 * SCALE, 20250))
+def test_summary_selector_random_shapes(shape):
+    b, hq, hkv, sq, skv, r, topk = shape
+    m = sp()
+    gen = torch.Generator(device="cuda").manual_seed(hash(shape) % (2 ** 31))
+    q = torch.randn((b, hq, sq, 128), device="cuda", generator=gen).to(torch.bfloat16)
+    k = torch.randn((b, hkv, skv, 128), device="cuda", generator=gen)
+    k += 0.5 * torch.randn((b, hkv, skv // 128, 1, 1), device="cuda", generator=gen).expand(-1, -1, -1, 128, 128) \
+        .reshape(b, hkv, skv, 128)
+    k = k.to(torch.bfloat16)
+    fast = m.SummarySelector(q, k, r, topk=topk, keep_scores=False)
+    ids = fast.run_fast().clone()
+    exact = m.SummarySelector(q, k, r, topk=topk, keep_scores=False)
+    exact.prepare()
+    exact.score()
+    torch.cuda.synchronize()
+    m.device_status()
+    assert torch.equal(ids, exact.ids)
+    assert fast.bound_stats()[0] == 0
+
+
+def _fp4_shapes(n, seed):
+    rng = random.Random(seed)
+    out = []
+    while len(out) < n:
+        hidx = rng.choice([1, 2, 4])
+        hk = rng.choice([1, hidx])                   # one shared key head, or one per index head
+        lq = 128 * rng.choice([1, 2, 3, 5, 8, 13, 32])
+        pages = rng.choice([rng.randint(8, 64), rng.randint(64, 300), rng.randint(300, 700)])
+        topk = rng.choice([4, 8, 16, 24, 64])
+        if topk > pages:
+            continue
+        b = rng.choice([1, 2])
+        out.append((b, hidx, hk, lq, pages * 128, topk))
+    return out
+
+
+@pytest.mark.parametrize("shape", _fp4_shapes(20 * SCALE, 777))
+def test_fp4_indexer_random_shapes(shape):
+    b, hidx, hk, lq, lkv, topk = shape
+    m = sp()
+    g = torch.Generator().manual_seed(hash(shape) % (2 ** 31))
+    pages = lkv // 128
+    qp = torch.randint(256, (b * lq, hidx, 64), dtype=torch.uint8, generator=g)
+    kp = torch.randint(256, (b * pages, hk, 128, 64), dtype=torch.uint8, generator=g)
+    choices = torch.tensor([0.25, 0.375, 0.5, 0.75, 1.0, 1.5, 2.0])
+    qs = choices[torch.randint(7, (b * lq, hidx, 8), generator=g)].to(torch.float8_e4m3fn)
+    ks = choices[torch.randint(7, (b * pages, hk, 128, 8), generator=g)].to(torch.float8_e4m3fn)
+    inputs = m.prepare_fp4_inputs(qp.cuda(), kp.cuda(), qs.cuda(), ks.cuda(), batch_size=b, len_q=lq, len_kv=lkv)
+    ids, ws = m.fp4_indexer_fast(inputs, topk=topk)
+    ref = m.fp4_indexer(inputs, topk=topk)
+    torch.cuda.synchronize()
+    m.device_status()
+    assert torch.equal(ids, ref)
+    assert int(ws[12:16].view(torch.int32).item()) == 0          # violations of the tensor-core error bound
