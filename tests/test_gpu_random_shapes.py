@@ -1,4 +1,4 @@
-"""Seeded random shapes through the indexers' fast paths against their exact kernels on the GPU.
+"""Seeded random shapes: the indexers' fast paths against their exact kernels, the attention kernel against the oracle.
 
 The hand-picked shapes of test_gpu_indexers.py cover the cases each kernel was designed around; a
 defect that depends on a remainder (a slice whose length modulo 256 is below 32 once left part of
@@ -96,3 +96,51 @@ def test_fp4_indexer_random_shapes(shape):
     m.device_status()
     assert torch.equal(ids, ref)
     assert int(ws[12:16].view(torch.int32).item()) == 0          # violations of the tensor-core error bound
+
+
+def _attention_shapes(n, seed):
+    rng = random.Random(seed)
+    out = []
+    while len(out) < n:
+        b = rng.choice([1, 2])
+        hkv = rng.choice([1, 2, 3])
+        g = rng.choice([1, 2, 3, 4, 8, 16])
+        qb = rng.randint(1, 9)
+        nb = rng.randint(1, 40)
+        topk = rng.randint(1, min(nb, 12))
+        if b * hkv * g * qb * topk > 1400:          # keeps the CPU oracle to a second or two per case
+            continue
+        out.append((b, hkv * g, hkv, qb * 128, nb * 128, topk, rng.choice(["full", "ragged"]), rng.randrange(1 << 30)))
+    return out
+
+
+@pytest.mark.parametrize("shape", _attention_shapes(16 * SCALE, 4242))
+def test_q_centric_random_shapes(shape):
+    """Random batch / head / group / block counts (odd group sizes, one query block, top-k = all blocks, ragged
+    counts with empty lists) against the CPU oracle, tolerances of test_gpu_q_centric.py."""
+    import oracle
+    from oracle import inputs as gen
+    b, hq, hkv, sq, skv, topk, counts_kind, seed = shape
+    m = sp()
+    q, k, v = gen.make_qkv(b, hq, hkv, sq, skv, seed=seed % 1000, k_block_offset=0.5)
+    g = torch.Generator().manual_seed(seed)
+    qb, nb = sq // 128, skv // 128
+    ids = torch.stack([torch.randperm(nb, generator=g)[:topk] for _ in range(b * hkv * qb)]).to(torch.int32) \
+        .reshape(b, hkv, qb, topk)
+    counts = None
+    if counts_kind == "ragged":
+        counts = torch.randint(0, topk + 1, (b, hkv, qb), generator=g, dtype=torch.int32)
+    ref_o, ref_l = oracle.gather_attention(q, k, v, ids, counts)
+    out = torch.full(q.shape, float("nan"), dtype=torch.bfloat16, device="cuda")
+    lse = torch.full(q.shape[:3], float("nan"), device="cuda")
+    m.attention_out(q.cuda(), k.cuda(), v.cuda(), ids.cuda(), out, None if counts is None else counts.cuda(), lse)
+    torch.cuda.synchronize()
+    m.device_status()
+    o = out.float().cpu()
+    assert torch.isfinite(o).all()
+    d = (o - ref_o).abs()
+    assert d.max().item() <= 2e-2 and d.mean().item() <= 2e-3
+    fin = torch.isfinite(ref_l)
+    l = lse.cpu()
+    assert torch.equal(torch.isinf(l) & (l < 0), ~fin)
+    assert torch.all((l[fin] - ref_l[fin]).abs() <= 1e-3 * ref_l[fin].abs().clamp_min(1.0))
