@@ -221,7 +221,7 @@ score_stream_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
       const int bk = unit / p.q_chunks, chunk = unit - bk * p.q_chunks;
       const int b = bk / p.hkv, kvh = bk - b * p.hkv;
       if (ui > 0) {
-        bool w = mbar_wait(bar(B_EMPTY), (ui - 1) & 1, guard, 0x500);
+        bool w = mbar_wait(bar(B_EMPTY), (ui - 1) & 1, guard, 0x800);
         ok = __all_sync(0xffffffffu, w);
         if (!ok) break;
       }
@@ -236,7 +236,7 @@ score_stream_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
       for (int t = 0; ok && t < num_tiles; ++t, ++fills) {
         const int s = fills % A_STAGES, use = fills / A_STAGES;
         if (use > 0) {
-          bool w = mbar_wait(bar(A_EMPTY + s), (use - 1) & 1, guard, 0x510 + s);
+          bool w = mbar_wait(bar(A_EMPTY + s), (use - 1) & 1, guard, 0x810 + s);
           ok = __all_sync(0xffffffffu, w);
           if (!ok) break;
         }
@@ -263,7 +263,7 @@ score_stream_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
     for (int ui = 0; ok && ui < my_units; ++ui) {
       {
         CLK(const long long c0 = clock64();)
-        bool w = mbar_wait(bar(B_FULL), ui & 1, guard, 0x520);
+        bool w = mbar_wait(bar(B_FULL), ui & 1, guard, 0x820);
         CLK(w_b += clock64() - c0;)
         ok = __all_sync(0xffffffffu, w);
         if (!ok) break;
@@ -272,9 +272,9 @@ score_stream_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
       for (int t = 0; ok && t < num_tiles; ++t, ++g) {
         const int s = g % A_STAGES, acc = g & 1;
         CLK(const long long c0 = clock64();)
-        bool w = mbar_wait(bar(A_FULL + s), (g / A_STAGES) & 1, guard, 0x530 + s);
+        bool w = mbar_wait(bar(A_FULL + s), (g / A_STAGES) & 1, guard, 0x830 + s);
         CLK(const long long c1 = clock64(); w_a += c1 - c0;)
-        if (w && g >= 2) w = mbar_wait(bar(ACC_EMPTY + acc), ((g >> 1) - 1) & 1, guard, 0x540 + acc);
+        if (w && g >= 2) w = mbar_wait(bar(ACC_EMPTY + acc), ((g >> 1) - 1) & 1, guard, 0x840 + acc);
         CLK(w_acc += clock64() - c1;)
         ok = __all_sync(0xffffffffu, w);
         if (!ok) break;
@@ -314,9 +314,9 @@ score_stream_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
         const int acc = g & 1;
         const int slot = t & (ch_tiles - 1);     // tile of the chunk
         CLK(const long long c0 = clock64();)
-        bool w = mbar_wait(bar(ACC_FULL + acc), (g >> 1) & 1, guard, 0x550 + acc);
+        bool w = mbar_wait(bar(ACC_FULL + acc), (g >> 1) & 1, guard, 0x850 + acc);
         CLK(const long long c1 = clock64(); w_full += c1 - c0;)
-        if (w && slot == 0 && h >= 2) w = mbar_wait(bar(SC_EMPTY + (h & 1)), ((h >> 1) - 1) & 1, guard, 0x560 + (h & 1));
+        if (w && slot == 0 && h >= 2) w = mbar_wait(bar(SC_EMPTY + (h & 1)), ((h >> 1) - 1) & 1, guard, 0x860 + (h & 1));
         CLK(w_sc += clock64() - c1;)
         ok = __all_sync(0xffffffffu, w);
         if (!ok) break;
@@ -400,7 +400,7 @@ score_stream_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
       const int rot = static_cast<int>((static_cast<unsigned>(chunk) * 37u) % static_cast<unsigned>(num_tiles));
       for (int c = 0; ok && c < num_chunks; ++c, ++h) {
         CLK(const long long c0 = clock64();)
-        bool w = mbar_wait(bar(SC_FULL + (h & 1)), (h >> 1) & 1, guard, 0x570 + (h & 1));
+        bool w = mbar_wait(bar(SC_FULL + (h & 1)), (h >> 1) & 1, guard, 0x870 + (h & 1));
         ok = __all_sync(0xffffffffu, w);
         if (!ok) break;
         CLK(w_sc += clock64() - c0;)
@@ -493,7 +493,7 @@ score_stream_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
         const int sw = 2 * f + y;
         if (ui > 0) {
           CLK(const long long c0 = clock64();)
-          bool w = mbar_wait(bar(FIN_EMPTY + sw), (ui - 1) & 1, guard, 0x580 + sw);
+          bool w = mbar_wait(bar(FIN_EMPTY + sw), (ui - 1) & 1, guard, 0x880 + sw);
           ok = __all_sync(0xffffffffu, w);
           if (!ok) break;
           CLK(w_fin += clock64() - c0;)
@@ -556,7 +556,7 @@ score_stream_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
     for (int ui = 0; ok && ui < my_units; ++ui) {
       {
         CLK(const long long c0 = clock64();)
-        bool w = mbar_wait(bar(FIN_FULL + sw), ui & 1, guard, 0x590 + sw);
+        bool w = mbar_wait(bar(FIN_FULL + sw), ui & 1, guard, 0x890 + sw);
         ok = __all_sync(0xffffffffu, w);
         if (!ok) break;
         CLK(w_full += clock64() - c0;)

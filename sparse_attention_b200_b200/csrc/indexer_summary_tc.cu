@@ -261,7 +261,7 @@ score_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant
     for (int t = 0; ok && t < num_tiles; ++t) {
       const int s = t % A_STAGES, use = t / A_STAGES;
       if (use > 0) {
-        bool w = mbar_wait(bar(A_EMPTY + s), (use - 1) & 1, guard, 0x400 + s);
+        bool w = mbar_wait(bar(A_EMPTY + s), (use - 1) & 1, guard, 0x900 + s);
         ok = __all_sync(0xffffffffu, w);
         if (!ok) break;
       }
@@ -280,14 +280,14 @@ score_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant
     const uint32_t idesc = idesc_bf16(128, n_cols, false);
     bool ok = true;
     {
-      bool w = mbar_wait(bar(B_FULL), 0, guard, 0x410);
+      bool w = mbar_wait(bar(B_FULL), 0, guard, 0x910);
       ok = __all_sync(0xffffffffu, w);
       tc_fence_after();
     }
     for (int t = 0; ok && t < num_tiles; ++t) {
       const int s = t % A_STAGES, acc = t & 1;
-      bool w = mbar_wait(bar(A_FULL + s), (t / A_STAGES) & 1, guard, 0x420 + s);
-      if (w && t >= 2) w = mbar_wait(bar(ACC_EMPTY + acc), ((t >> 1) - 1) & 1, guard, 0x430 + acc);
+      bool w = mbar_wait(bar(A_FULL + s), (t / A_STAGES) & 1, guard, 0x920 + s);
+      if (w && t >= 2) w = mbar_wait(bar(ACC_EMPTY + acc), ((t >> 1) - 1) & 1, guard, 0x930 + acc);
       ok = __all_sync(0xffffffffu, w);
       if (!ok) break;
       tc_fence_after();
@@ -314,7 +314,7 @@ score_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant
     bool ok = true;
     for (int t = 0; ok && t < num_tiles; ++t) {
       const int acc = t & 1;
-      bool w = mbar_wait(bar(ACC_FULL + acc), (t >> 1) & 1, guard, 0x440 + acc);
+      bool w = mbar_wait(bar(ACC_FULL + acc), (t >> 1) & 1, guard, 0x940 + acc);
       ok = __all_sync(0xffffffffu, w);
       if (!ok) break;
       tc_fence_after();

@@ -129,7 +129,7 @@ kv_token_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant
     if (warp == ISSUE_WARP) {
       bool w = true;
       if (reload) {
-        w = mbar_wait(bar(KV_FULL), kv_phase, guard, 0x600);
+        w = mbar_wait(bar(KV_FULL), kv_phase, guard, 0xa00);
         kv_phase ^= 1;
       }
       ok = __all_sync(0xffffffffu, w);
@@ -145,7 +145,7 @@ kv_token_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant
         tc_commit(bar(S_FULL));
       }
     } else {
-      bool w = mbar_wait(bar(S_FULL), phase, guard, 0x610);
+      bool w = mbar_wait(bar(S_FULL), phase, guard, 0xa10);
       ok = __all_sync(0xffffffffu, w);
       if (ok) {
         // softmax over the single block, P (bf16 pairs) back into the first 64 columns of S
@@ -192,7 +192,7 @@ kv_token_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant
         tc_commit(bar(O_FULL));
       }
     } else if (ok && !misc[1]) {
-      bool w = mbar_wait(bar(O_FULL), phase, guard, 0x620);
+      bool w = mbar_wait(bar(O_FULL), phase, guard, 0xa20);
       ok = __all_sync(0xffffffffu, w);
       if (ok) {
         tc_fence_after();
