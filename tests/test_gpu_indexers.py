@@ -194,6 +194,29 @@ def test_summary_selector_persistent_form_bit_exact(shape):
     print("lists that fell back to exact scoring:", fast.fallback_lists(), "max |approx - exact| / delta:", ratio)
 
 
+@pytest.mark.parametrize("shape", [
+    # B, Hq, Hkv, Sq, KV blocks, R, topk: lists far longer than shared memory could hold as a whole
+    (1, 8, 1, 8 * 128, 32768, 4, 64),        # 4 Mi tokens: 1024 key tiles, 64 chunks per unit
+    (1, 8, 1, 24 * 128, 20001, 4, 128),      # odd block count, 176 candidates
+    (2, 32, 1, 9 * 128, 6000, 1, 16),        # group 32 with R1, last unit holds one list
+])
+def test_summary_selector_persistent_form_very_long_lists(shape):
+    b, hq, hkv, sq, nt, r, topk = shape
+    m = sp()
+    g = torch.Generator(device="cuda").manual_seed(nt)
+    q = torch.randn((b, hq, sq, 128), device="cuda", generator=g).to(torch.bfloat16)
+    k = torch.randn((b, hkv, nt * 128, 128), device="cuda", generator=g).to(torch.bfloat16)
+    fast = m.SummarySelector(q, k, r, topk=topk, keep_scores=False)
+    ids = fast.run_fast().clone()
+    exact = m.SummarySelector(q, k, r, topk=topk, keep_scores=False)
+    exact.prepare()
+    exact.score()
+    torch.cuda.synchronize()
+    m.device_status()
+    assert torch.equal(ids, exact.ids)
+    assert fast.bound_stats()[0] == 0
+
+
 @pytest.mark.parametrize("order", ["ascending", "descending", "plateaus"])
 def test_summary_selector_persistent_form_adversarial_score_order(order):
     """Scores that grow with the block index make every chunk beat everything seen before it (the pool of the
