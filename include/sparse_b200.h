@@ -63,6 +63,20 @@ int sparse_b200_q_centric(const void* q, const void* k, const void* v, const int
                           const int32_t* block_count, void* out, float* lse, int batch, int hq, int hkv,
                           int sq, int skv, int topk, void* stream);
 
+/* sparse_b200_q_centric with a caller-provided scratch buffer (sparse_b200_q_centric_workspace_bytes()
+ * bytes on the current device, 16-byte aligned, private to the call while it runs). With it the kernel
+ * balances its last round of work items: when a launch is a few rounds of (query block, head pair)
+ * items per SM and the last round would keep at most half of the SMs busy, the items of that round are
+ * cut into 2-4 pieces of their lists, the pieces write normalised partials into the workspace and a small
+ * kernel merges them (the log-sum-exp merge of sparse_b200_combine). Results of those rows may differ
+ * from the unbalanced call in the last bf16 bit; everything else is identical. workspace == NULL is
+ * sparse_b200_q_centric. No counterpart in the reference (its kernels take no workspace). */
+int64_t sparse_b200_q_centric_workspace_bytes(void);
+int sparse_b200_q_centric_ws(const void* q, const void* k, const void* v, const int32_t* block_idx,
+                             const int32_t* block_count, void* out, float* lse, void* workspace,
+                             int64_t workspace_bytes, int batch, int hq, int hkv, int sq, int skv, int topk,
+                             void* stream);
+
 /* Same kernel over `nseg` list sets at once, writing normalised partial
  * outputs [nseg, B, Hq, Sq, 128] (bf16, or fp32 when partial_is_f32) and
  * partial LSE [nseg, B, Hq, Sq]. seg_block_idx is [nseg, B, Hkv, Sq/128, TopK],

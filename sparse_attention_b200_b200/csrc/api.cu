@@ -131,6 +131,26 @@ int sparse_b200_q_centric(const void* q, const void* k, const void* v, const int
   return launch_q_centric(a, static_cast<cudaStream_t>(stream));
 }
 
+int64_t sparse_b200_q_centric_workspace_bytes(void) {
+  DeviceCtx* ctx = device_ctx();
+  if (!ctx) return SB_ERR_CUDA;
+  // at most one piece per CTA in the balanced round: two streams of 128 rows, bf16 O + fp32 LSE
+  return static_cast<int64_t>(ctx->sm_count) * 2 * 128 * (128 * 2 + 4) + 512;
+}
+
+int sparse_b200_q_centric_ws(const void* q, const void* k, const void* v, const int32_t* block_idx,
+                             const int32_t* block_count, void* out, float* lse, void* workspace,
+                             int64_t workspace_bytes, int batch, int hq, int hkv, int sq, int skv, int topk,
+                             void* stream) {
+  int rc = check_attention(q, k, v, block_idx, out, batch, hq, hkv, sq, skv, topk, 1);
+  if (rc) return rc;
+  REQUIRE(workspace == nullptr || aligned16(workspace), "misaligned workspace");
+  QCentricArgs a{q, k, v, block_idx, block_count, out, lse, batch, hq, hkv, sq, skv, topk, 1, 0};
+  a.tail_ws = workspace;
+  a.tail_bytes = workspace ? workspace_bytes : 0;
+  return launch_q_centric(a, static_cast<cudaStream_t>(stream));
+}
+
 int sparse_b200_q_centric_partial(const void* q, const void* k, const void* v, const int32_t* seg_block_idx,
                                   const int32_t* seg_block_count, void* partial_out, float* partial_lse,
                                   int nseg, int partial_is_f32, int batch, int hq, int hkv, int sq, int skv,

@@ -36,6 +36,8 @@ struct QCentricArgs {
   void* out;
   float* lse;
   int batch, hq, hkv, sq, skv, topk, nseg, out_f32;
+  void* tail_ws = nullptr;      // optional workspace for balancing the last round of items (q_centric.cu)
+  long long tail_bytes = 0;
 };
 int launch_q_centric(const QCentricArgs& a, cudaStream_t stream);
 

@@ -85,6 +85,12 @@ struct Params {
   int group, qt, pair_mode;
   int items_per_seg, num_items;
   float scale_log2;
+  // Tail balancing (single-segment bf16 launches with a workspace): the items of the last, partly
+  // filled round (index >= tail_first) are cut into tail_parts pieces of their lists; piece v writes a
+  // normalised partial (O, LSE) into the workspace and tail_merge_kernel combines the pieces.
+  // num_virtual = items as the roles see them; without balancing tail_first = num_virtual = num_items.
+  int tail_first, tail_parts, num_virtual;
+  float* tail_lse;         // [pieces * 2 * 128]
 };
 
 struct Stream {
@@ -94,9 +100,17 @@ struct Stream {
   int q_row;           // first row in the 2-D view of Q
   int kv_row;          // first row of its KV head in the 2-D view of K/V
   long long out_row;   // first output row (64-bit: outputs may exceed 2^31 elements)
+  bool tail;           // a piece of a tail item: out_row is a row of the workspace
 };
 
-__device__ __forceinline__ void decode_item(const Params& p, int item, Stream (&s)[2]) {
+__device__ __forceinline__ void decode_item(const Params& p, int virt, Stream (&s)[2]) {
+  int item = virt, part = 0;
+  const bool tail = virt >= p.tail_first;
+  if (tail) {
+    const int t = virt - p.tail_first;
+    item = p.tail_first + t / p.tail_parts;
+    part = t - (t / p.tail_parts) * p.tail_parts;
+  }
   const int seg = item / p.items_per_seg;
   const int local = item - seg * p.items_per_seg;
   if (p.pair_mode) {
@@ -141,12 +155,28 @@ __device__ __forceinline__ void decode_item(const Params& p, int item, Stream (&
   }
   // counts come from the caller: clamp to the list capacity
 #pragma unroll
-  for (int q = 0; q < 2; ++q) s[q].count = min(max(s[q].count, 0), p.topk);
+  for (int q = 0; q < 2; ++q) {
+    s[q].count = min(max(s[q].count, 0), p.topk);
+    s[q].tail = tail;
+    if (tail) {                                  // this piece's share of the list, its rows in the workspace
+      const int lo = part * s[q].count / p.tail_parts, hi = (part + 1) * s[q].count / p.tail_parts;
+      s[q].list += lo;
+      s[q].count = hi - lo;
+      s[q].out_row = (static_cast<long long>(virt - p.tail_first) * 2 + q) * TILE;
+    }
+  }
 }
 
 // Live list lengths of the two streams of an item: all the MMA issuer needs to know
 // (it keeps few registers so that its wait -> issue path stays free of spills).
-__device__ __forceinline__ void item_counts(const Params& p, int item, int (&cnt)[2]) {
+__device__ __forceinline__ void item_counts(const Params& p, int virt, int (&cnt)[2]) {
+  int item = virt, part = 0;
+  const bool tail = virt >= p.tail_first;
+  if (tail) {
+    const int t = virt - p.tail_first;
+    item = p.tail_first + t / p.tail_parts;
+    part = t - (t / p.tail_parts) * p.tail_parts;
+  }
   const int seg = item / p.items_per_seg;
   const int local = item - seg * p.items_per_seg;
   if (p.pair_mode) {
@@ -172,6 +202,10 @@ __device__ __forceinline__ void item_counts(const Params& p, int item, int (&cnt
       cnt[q] = min(max(c, 0), p.topk);
     }
   }
+  if (tail) {
+#pragma unroll
+    for (int q = 0; q < 2; ++q) cnt[q] = (part + 1) * cnt[q] / p.tail_parts - part * cnt[q] / p.tail_parts;
+  }
 }
 
 // One list cursor of the load warp: 32 ids cached across the lanes.
@@ -187,7 +221,7 @@ template <bool OUT_F32>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 q_centric_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
                  const __grid_constant__ CUtensorMap v_map, const __grid_constant__ CUtensorMap o_map,
-                 const Params p) {
+                 const __grid_constant__ CUtensorMap o_tail_map, const Params p) {
   extern __shared__ unsigned char smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
@@ -278,10 +312,10 @@ q_centric_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
     // (and its Q tile) follows that stream's last V tile of the current item, so the
     // next item's first QK can be issued before the current item has drained.
     bool primed[2] = {false, false};
-    for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x) {
+    for (int item = blockIdx.x; ok && item < p.num_virtual; item += gridDim.x) {
       Stream s[2], nx[2];
       decode_item(p, item, s);
-      const bool has_next = item + static_cast<int>(gridDim.x) < p.num_items;
+      const bool has_next = item + static_cast<int>(gridDim.x) < p.num_virtual;
       if (has_next) decode_item(p, item + gridDim.x, nx);
       IdCursor kc[2], vc[2], nc[2];
       kc[0].cached = kc[1].cached = vc[0].cached = vc[1].cached = nc[0].cached = nc[1].cached = 0;
@@ -425,10 +459,10 @@ q_centric_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
 
     bool primed[2] = {false, false};
     int cnt[2] = {0, 0}, ncnt[2] = {0, 0};
-    if (static_cast<int>(blockIdx.x) < p.num_items) item_counts(p, blockIdx.x, ncnt);
-    for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x) {
+    if (static_cast<int>(blockIdx.x) < p.num_virtual) item_counts(p, blockIdx.x, ncnt);
+    for (int item = blockIdx.x; ok && item < p.num_virtual; item += gridDim.x) {
       cnt[0] = ncnt[0]; cnt[1] = ncnt[1];
-      const bool has_next = item + static_cast<int>(gridDim.x) < p.num_items;
+      const bool has_next = item + static_cast<int>(gridDim.x) < p.num_virtual;
       if (has_next) item_counts(p, item + gridDim.x, ncnt);
       uint32_t kslot = 0, vslot = 0;
       if (p.pair_mode) {
@@ -536,14 +570,19 @@ q_centric_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
     if (lane == 0) *handed_ptr = 0;
     __syncwarp();
     bool ok = true;
-    for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x) {
+    for (int item = blockIdx.x; ok && item < p.num_virtual; item += gridDim.x) {
       Stream s[2];
       decode_item(p, item, s);
       const Stream& me = s[q];
       if (!me.valid) continue;
       const long long orow = me.out_row + row_in_tile;
+      float* lse_dst = me.tail ? p.tail_lse : p.lse;
       if (me.count == 0) {
         // empty list: neutral element of the log-sum-exp merge
+        if (me.tail) {                           // an empty piece: only its weight matters to the merge
+          lse_dst[orow] = -INFINITY;
+          continue;
+        }
         if (OUT_F32) {
           float4* dst = reinterpret_cast<float4*>(static_cast<float*>(p.out) + orow * HEAD_DIM);
           for (int c = 0; c < HEAD_DIM / 4; ++c) dst[c] = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -644,7 +683,7 @@ q_centric_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
       __syncwarp();
       if (lane == 0) *handed_ptr = handed + 1;
       stats[q * TILE + row_in_tile] = 1.0f / row_sum;
-      if (p.lse) p.lse[orow] = (row_max + log2f(row_sum)) * 0.6931471805599453f;
+      if (lse_dst) lse_dst[orow] = (row_max + log2f(row_sum)) * 0.6931471805599453f;
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(BAR_STATS_FULL + q));
     }
@@ -659,7 +698,7 @@ q_centric_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
     unsigned char* stage_g = gbase + OFF_STAGE + quarter * STAGE_BYTES;
     uint32_t done[2] = {0, 0};
     bool ok = true;
-    for (int item = blockIdx.x; ok && item < p.num_items; item += gridDim.x) {
+    for (int item = blockIdx.x; ok && item < p.num_virtual; item += gridDim.x) {
       Stream s[2];
       decode_item(p, item, s);
 #pragma unroll 1
@@ -677,6 +716,7 @@ q_centric_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
         __syncwarp();
         if (lane == 0) mbar_arrive(bar(BAR_STATS_EMPTY + q));
         const int out_row32 = static_cast<int>(me.out_row) + quarter * 32;
+        const CUtensorMap* out_map = me.tail ? &o_tail_map : &o_map;
         if (lane == 0) bulk_wait_read0();            // earlier stores have left the staging tile
         __syncwarp();
         if (OUT_F32) {
@@ -707,8 +747,8 @@ q_centric_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
             fence_async_smem();
             __syncwarp();
             if (lane == 0) {
-              tma_store_2d(&o_map, half * 64, out_row32, stage);
-              tma_store_2d(&o_map, half * 64 + 32, out_row32, stage + 4096);
+              tma_store_2d(out_map, half * 64, out_row32, stage);
+              tma_store_2d(out_map, half * 64 + 32, out_row32, stage + 4096);
               bulk_commit();
             }
           }
@@ -735,8 +775,8 @@ q_centric_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
           fence_async_smem();
           __syncwarp();
           if (lane == 0) {
-            tma_store_2d(&o_map, 0, out_row32, stage);
-            tma_store_2d(&o_map, 64, out_row32, stage + 4096);
+            tma_store_2d(out_map, 0, out_row32, stage);
+            tma_store_2d(out_map, 64, out_row32, stage + 4096);
             bulk_commit();
           }
         }
@@ -751,6 +791,61 @@ q_centric_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
   if (warp == MMA_WARP) {
     tc_fence_after();
     tmem_dealloc(tmem, TMEM_COLS);
+  }
+}
+
+// Merge of the pieces of the tail items (see Params::tail_first): one CTA per (tail item, stream, eight
+// query rows), sixteen threads per row (16 bytes each: coalesced). Many small CTAs: a thread makes two
+// dependent round trips to memory (LSEs, then partial rows), so the kernel's time is that latency
+// plus its launch, whatever the row count.
+// out = sum_r exp(L_r - L) O_r / sum_r exp(L_r - L), L = logsumexp_r L_r, pieces in order; a piece with
+// L_r = -inf (empty share of the list) has weight 0 whatever it holds. Launched as a programmatic
+// dependent of the attention kernel: its prologue overlaps that kernel's tail.
+__global__ void __launch_bounds__(128) tail_merge_kernel(const Params p, const __nv_bfloat16* __restrict__ tail_out) {
+  const int t = blockIdx.x >> 5, q = (blockIdx.x >> 4) & 1;
+  Params real = p;
+  real.tail_first = p.num_items;                 // decode the item itself, not a piece of it
+  Stream s[2];
+  decode_item(real, p.tail_first + t, s);
+  asm volatile("griddepcontrol.wait;" ::: "memory");      // the attention kernel's stores are visible from here on
+  if (!s[q].valid) return;
+  const int part16 = threadIdx.x & 15;
+  {
+    const int row = (blockIdx.x & 15) * 8 + (threadIdx.x >> 4);
+    float L[4], maximum = -INFINITY;
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+      L[r] = -INFINITY;
+      if (r < p.tail_parts) L[r] = p.tail_lse[(static_cast<long long>(t * p.tail_parts + r) * 2 + q) * TILE + row];
+      maximum = fmaxf(maximum, L[r]);
+    }
+    float w[4], denom = 0.f;
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+      w[r] = (r < p.tail_parts && L[r] > -INFINITY) ? expf(L[r] - maximum) : 0.f;
+      denom += w[r];
+    }
+    const float inv = denom > 0.f ? 1.f / denom : 0.f;
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+      if (r < p.tail_parts && w[r] > 0.f) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(
+            tail_out + ((static_cast<long long>(t * p.tail_parts + r) * 2 + q) * TILE + row) * HEAD_DIM + part16 * 8);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 f = __bfloat1622float2(h[e]);
+          acc[2 * e] = fmaf(w[r], f.x, acc[2 * e]);
+          acc[2 * e + 1] = fmaf(w[r], f.y, acc[2 * e + 1]);
+        }
+      }
+    }
+    const long long orow = s[q].out_row + row;
+    *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.out) + orow * HEAD_DIM + part16 * 8) =
+        make_uint4(pack_bf16x2(acc[0] * inv, acc[1] * inv), pack_bf16x2(acc[2] * inv, acc[3] * inv),
+                   pack_bf16x2(acc[4] * inv, acc[5] * inv), pack_bf16x2(acc[6] * inv, acc[7] * inv));
+    if (part16 == 0 && p.lse) p.lse[orow] = denom > 0.f ? maximum + logf(denom) : -INFINITY;
   }
 }
 
@@ -796,13 +891,44 @@ int launch_q_centric(const QCentricArgs& a, cudaStream_t stream) {
                                 : a.batch * a.hq * ((p.qt + 1) / 2);
   p.num_items = p.items_per_seg * a.nseg;
   p.scale_log2 = 1.4426950408889634f / sqrtf(static_cast<float>(HEAD_DIM));
+  const int grid = p.num_items < ctx->sm_count ? p.num_items : ctx->sm_count;
 
-  CUtensorMap qm, km, vm, om;
+  // Tail balancing. With few rounds of items per CTA the last, partly filled round costs a whole
+  // round: when at most half of the CTAs would work in it, its items are cut into 2-4 pieces (as
+  // many as idle CTAs allow), so that the round takes a half to a quarter of the time, and a small
+  // kernel merges the pieces. Needs a workspace; single-segment bf16 launches only.
+  p.tail_first = p.num_virtual = p.num_items;
+  p.tail_parts = 1;
+  p.tail_lse = nullptr;
+  __nv_bfloat16* tail_out = nullptr;
+  const int rounds = p.num_items / grid, rem = p.num_items - rounds * grid;
+  if (a.tail_ws && a.nseg == 1 && !a.out_f32 && rem > 0 && 2 * rem <= grid && rounds >= 1 && rounds <= 8 && a.topk >= 8) {
+    int parts = grid / rem;
+    if (parts > 4) parts = 4;
+    if (parts > a.topk / 4) parts = a.topk / 4;  // at least four blocks per piece
+    const long long rows = static_cast<long long>(rem) * parts * 2 * TILE;
+    const long long need = rows * (HEAD_DIM * 2 + 4) + 256;
+    // worth it when the blocks a CTA no longer walks (about 1.7 us each, measured) outweigh the merge
+    // (launch + the partials' round trip through memory: about 4 us + 0.1 us per tail item)
+    const bool pays = parts >= 2 && 1.7f * static_cast<float>(a.topk - a.topk / parts) >= 4.f + 0.1f * static_cast<float>(rem);
+    if (pays && need <= a.tail_bytes && (reinterpret_cast<uintptr_t>(a.tail_ws) & 15u) == 0) {
+      p.tail_first = p.num_items - rem;
+      p.tail_parts = parts;
+      p.num_virtual = p.tail_first + rem * parts;
+      tail_out = static_cast<__nv_bfloat16*>(a.tail_ws);
+      p.tail_lse = reinterpret_cast<float*>(static_cast<unsigned char*>(a.tail_ws) + ((rows * HEAD_DIM * 2 + 255) & ~255LL));
+    }
+  }
+
+  CUtensorMap qm, km, vm, om, omt;
   if (encode_rows_map(&qm, a.q, static_cast<uint64_t>(a.batch) * a.hq * a.sq) ||
       encode_rows_map(&km, a.k, static_cast<uint64_t>(a.batch) * a.hkv * a.skv) ||
       encode_rows_map(&vm, a.v, static_cast<uint64_t>(a.batch) * a.hkv * a.skv) ||
       encode_out_map(&om, a.out, static_cast<uint64_t>(a.nseg) * a.batch * a.hq * a.sq, a.out_f32 != 0))
     return set_error(SB_ERR_CUDA, "cuTensorMapEncodeTiled failed for q/k/v/out");
+  omt = om;
+  if (tail_out && encode_out_map(&omt, tail_out, static_cast<uint64_t>(p.num_virtual - p.tail_first) * 2 * TILE, false))
+    return set_error(SB_ERR_CUDA, "cuTensorMapEncodeTiled failed for the tail workspace");
 
   auto kernel = a.out_f32 ? q_centric_kernel<true> : q_centric_kernel<false>;
   int& configured = a.out_f32 ? ctx->qc_attr_f32 : ctx->qc_attr_bf16;
@@ -811,10 +937,24 @@ int launch_q_centric(const QCentricArgs& a, cudaStream_t stream) {
     if (e != cudaSuccess) return set_error(SB_ERR_CUDA, cudaGetErrorString(e));
     configured = 1;
   }
-  const int grid = p.num_items < ctx->sm_count ? p.num_items : ctx->sm_count;
-  kernel<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(qm, km, vm, om, p);
+  kernel<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(qm, km, vm, om, omt, p);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return set_error(SB_ERR_CUDA, cudaGetErrorString(e));
+  if (tail_out) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((p.num_items - p.tail_first) * 32);
+    cfg.blockDim = dim3(128);
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    const __nv_bfloat16* tail_in = tail_out;
+    e = cudaLaunchKernelEx(&cfg, tail_merge_kernel, p, tail_in);
+    if (e != cudaSuccess) return set_error(SB_ERR_CUDA, cudaGetErrorString(e));
+  }
   return SB_OK;
 }
 

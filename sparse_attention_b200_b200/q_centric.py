@@ -53,15 +53,41 @@ def _validate(q, k, v, ids, out=None, counts=None, lse=None):
         bad("lse must be contiguous float32 [B,Hq,Sq] on q's device")
 
 
-def attention_out(q, k, v, ids, out, counts=None, lse=None):
-    """out <- block-sparse attention; never allocates; runs on the current stream."""
+_WORKSPACES = {}
+
+
+def _workspace(device):
+    """Scratch of the balanced last round, one per (device, stream): allocated at the first call."""
+    key = (device.index, torch.cuda.current_stream(device).cuda_stream)
+    ws = _WORKSPACES.get(key)
+    if ws is None:
+        import ctypes
+        fn = _lib.lib().sparse_b200_q_centric_workspace_bytes
+        fn.restype = ctypes.c_int64
+        with torch.cuda.device(device):
+            ws = torch.empty(int(fn()), dtype=torch.uint8, device=device)
+        _WORKSPACES[key] = ws
+    return ws
+
+
+def attention_out(q, k, v, ids, out, counts=None, lse=None, balance=True):
+    """out <- block-sparse attention on the current stream. balance: let the kernel split the work items of a
+    last, partly filled round (a per-stream scratch buffer is allocated at the first call; no allocation
+    afterwards); False is the plain entry, which never allocates."""
     _validate(q, k, v, ids, out, counts, lse)
     b, hq, sq, _ = q.shape
     hkv, skv = k.shape[1:3]
     with torch.cuda.device(q.device):
-        _lib.check(_lib.lib().sparse_b200_q_centric(
+        if not balance:
+            _lib.check(_lib.lib().sparse_b200_q_centric(
+                _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(ids), _lib.ptr(counts), _lib.ptr(out), _lib.ptr(lse),
+                b, hq, hkv, sq, skv, int(ids.shape[3]), _lib.current_stream()))
+            return
+        import ctypes
+        ws = _workspace(q.device)
+        _lib.check(_lib.lib().sparse_b200_q_centric_ws(
             _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(ids), _lib.ptr(counts), _lib.ptr(out), _lib.ptr(lse),
-            b, hq, hkv, sq, skv, int(ids.shape[3]), _lib.current_stream()))
+            _lib.ptr(ws), ctypes.c_int64(ws.numel()), b, hq, hkv, sq, skv, int(ids.shape[3]), _lib.current_stream()))
 
 
 def attention(q, k, v, ids, counts=None, return_lse=False):

@@ -262,3 +262,42 @@ def test_host_pipeline_matches_device_path():
     t0 = pipe.run(hq_, hk_, hv_, hi_, ho, hl, copy_only=True)
     t0.synchronize()
     m.device_status()
+
+
+@pytest.mark.parametrize("shape,topk,counts_kind", [
+    ((2, 16, 1, 4096, 2048), 16, "full"),      # the reference's shape: 512 items = 3 rounds + 68 -> two pieces each
+    ((1, 8, 2, 40 * 128, 4096), 16, "ragged"),      # 160 items: 1 round + 12 -> four pieces each, ragged counts
+    ((1, 3, 3, 51 * 256, 2048), 8, "full"),    # split mode (group 1): 153 items, 5 left over, two pieces of four blocks
+])
+def test_balanced_last_round_matches_the_plain_call(shape, topk, counts_kind):
+    """With a workspace the kernel cuts the items of a last, partly filled round into pieces and merges their
+    partials: same result as the plain call up to the bf16 rounding of the partials, LSE to fp32 rounding, and
+    inside the oracle tolerance; rows outside the last round are bit-identical."""
+    m = sp()
+    b, hq, hkv, sq, skv = shape
+    q, k, v = gen.make_qkv(b, hq, hkv, sq, skv, seed=11, k_block_offset=0.5)
+    ids = gen.make_ids(b, hkv, sq // 128, skv // 128, topk, 3, "unsorted")
+    counts = None
+    if counts_kind == "ragged":
+        g = torch.Generator().manual_seed(4)
+        counts = torch.randint(0, topk + 1, (b, hkv, sq // 128), generator=g, dtype=torch.int32)
+    qc, kc, vc, ic = q.cuda(), k.cuda(), v.cuda(), ids.cuda()
+    cc = None if counts is None else counts.cuda()
+    plain = torch.full(q.shape, float("nan"), dtype=torch.bfloat16, device="cuda")
+    plain_lse = torch.full(q.shape[:3], float("nan"), device="cuda")
+    m.attention_out(qc, kc, vc, ic, plain, cc, plain_lse, balance=False)
+    bal = torch.full_like(plain, float("nan"))
+    bal_lse = torch.full_like(plain_lse, float("nan"))
+    m.attention_out(qc, kc, vc, ic, bal, cc, bal_lse, balance=True)
+    torch.cuda.synchronize()
+    m.device_status()
+    assert torch.isfinite(bal.float()).all()
+    diff = (bal.float() - plain.float()).abs()
+    changed = (diff > 0).reshape(b, hq, sq // 128, -1).any(-1)    # (head, query block) tiles that went through the merge
+    assert 0 < int(changed.sum()) <= changed.numel() // 2         # the last round only
+    assert diff.max().item() <= 2.0 ** -6 * max(1.0, plain.float().abs().max().item())
+    fin = torch.isfinite(plain_lse)
+    assert torch.equal(torch.isfinite(bal_lse), fin)
+    assert torch.all((bal_lse[fin] - plain_lse[fin]).abs() <= 2e-6 * plain_lse[fin].abs().clamp_min(1.0))
+    ref_o, ref_l = oracle.gather_attention(q, k, v, ids, counts)
+    check(bal, bal_lse, ref_o, ref_l)
