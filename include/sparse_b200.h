@@ -167,6 +167,16 @@ int sparse_b200_kv_token_main_tm_partial_tm(const void* q_token_major, const voi
                                             const int32_t* tasks, const int32_t* task_ptr, const int32_t* query_ids,
                                             const int32_t* ranks, void* partial_token_major, float* partial_lse,
                                             int batch, int hq, int hkv, int sq, int skv, int topk, void* stream);
+/* All layouts of the main stage behind one entry. layout is a mask: bit 0 = q token-major
+ * [B, Sq, Hq, 128], bit 1 = partials token-major [B, Sq, TopK, Hq, 128] (needs bit 0), bit 2 =
+ * fp32 partials instead of bf16. 0, 1 and 3 are the three entries above; 4 and 7 are the
+ * reference's fp32 controls (variants -2 and 0, attention/kv_centric/optimization_round11/
+ * api11.py:22-25, wrapper11.cpp:66-70,97-100), merged by sparse_b200_combine /
+ * sparse_b200_combine_tm with partial_is_f32 = 1. Token-major layouts: Hq / Hkv of 8 or 16. */
+int sparse_b200_kv_token_main_layout(const void* q, const void* k, const void* v, const int32_t* tasks,
+                                     const int32_t* task_ptr, const int32_t* query_ids, const int32_t* ranks,
+                                     void* partial, float* partial_lse, int batch, int hq, int hkv, int sq, int skv,
+                                     int topk, int layout, void* stream);
 int sparse_b200_combine_tm(const void* partial_token_major, int partial_is_f32, const float* partial_lse, void* out,
                            float* out_lse, int batch, int hq, int sq, int ranks, void* stream);
 

@@ -481,7 +481,7 @@ int sparse_b200_kv_token_main(const void* q, const void* k, const void* v, const
   REQUIRE(aligned16(q) && aligned16(k) && aligned16(v) && aligned16(partial) && aligned16(tasks), "misaligned pointer");
   const long long rows = static_cast<long long>(batch) * hkv * (skv / 128);
   return launch_kv_token_main(q, k, v, tasks, task_ptr + rows, query_ids, ranks, partial, partial_lse, batch, hq, hkv,
-                              sq, skv, topk, static_cast<cudaStream_t>(stream));
+                              sq, skv, topk, 0, static_cast<cudaStream_t>(stream));
 }
 
 static int kv_token_main_token_major(const void* q_token_major, const void* k, const void* v, const int32_t* tasks,
@@ -518,6 +518,33 @@ int sparse_b200_kv_token_main_tm_partial_tm(const void* q_token_major, const voi
                                             int batch, int hq, int hkv, int sq, int skv, int topk, void* stream) {
   return kv_token_main_token_major(q_token_major, k, v, tasks, task_ptr, query_ids, ranks, partial_token_major,
                                    partial_lse, batch, hq, hkv, sq, skv, topk, 3, stream);
+}
+
+int sparse_b200_kv_token_main_layout(const void* q, const void* k, const void* v, const int32_t* tasks,
+                                     const int32_t* task_ptr, const int32_t* query_ids, const int32_t* ranks,
+                                     void* partial, float* partial_lse, int batch, int hq, int hkv, int sq, int skv,
+                                     int topk, int layout, void* stream) {
+  REQUIRE(layout >= 0 && layout < 8, "layout is a mask of bits 0 (q token-major), 1 (partials token-major), 2 (fp32)");
+  REQUIRE((layout & 3) != 2, "token-major partials go with token-major q");
+  if (layout & 3)
+    return kv_token_main_token_major(q, k, v, tasks, task_ptr, query_ids, ranks, partial, partial_lse, batch, hq, hkv,
+                                     sq, skv, topk, layout, stream);
+  if (layout == 0)
+    return sparse_b200_kv_token_main(q, k, v, tasks, task_ptr, query_ids, ranks, partial, partial_lse, batch, hq, hkv,
+                                     sq, skv, topk, stream);
+  // head-major fp32 partials: the checks of sparse_b200_kv_token_main, then the fp32 form of the same kernels
+  REQUIRE(q && k && v && tasks && task_ptr && query_ids && ranks && partial && partial_lse, "null pointer");
+  REQUIRE(batch > 0 && hkv > 0 && hq >= hkv && hq % hkv == 0, "Hq must be a positive multiple of Hkv");
+  const int g = hq / hkv;
+  REQUIRE(g == 1 || g == 2 || g == 4 || g == 8 || g == 16, "supported ratios Hq/Hkv are 1, 2, 4, 8, and 16");
+  REQUIRE(sq > 0 && skv >= 128 && skv % 128 == 0 && topk > 0 && topk <= skv / 128,
+          "Skv must be a positive multiple of 128 and TopK at most the number of KV blocks");
+  REQUIRE(static_cast<long long>(batch) * hkv * skv < (1LL << 31), "flattened KV rows must fit int32");
+  REQUIRE(static_cast<long long>(batch) * hkv * sq * topk < (1LL << 31), "B*Hkv*Sq*TopK must fit int32 (edge offsets)");
+  REQUIRE(aligned16(q) && aligned16(k) && aligned16(v) && aligned16(partial) && aligned16(tasks), "misaligned pointer");
+  const long long rows = static_cast<long long>(batch) * hkv * (skv / 128);
+  return launch_kv_token_main(q, k, v, tasks, task_ptr + rows, query_ids, ranks, partial, partial_lse, batch, hq, hkv,
+                              sq, skv, topk, 1, static_cast<cudaStream_t>(stream));
 }
 
 int sparse_b200_combine_tm(const void* partial_token_major, int partial_is_f32, const float* partial_lse, void* out,

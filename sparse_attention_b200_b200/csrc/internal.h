@@ -67,7 +67,7 @@ int launch_token_metadata(const int32_t* selected, int32_t* counts, int32_t* cur
                           int groups, int sq, int topk, int kv_blocks, int group_size, cudaStream_t stream);
 int launch_kv_token_main(const void* q, const void* k, const void* v, const int32_t* tasks, const int32_t* task_count,
                          const int32_t* qids, const int32_t* ranks, void* partial, float* lses, int batch, int hq,
-                         int hkv, int sq, int skv, int topk, cudaStream_t stream);
+                         int hkv, int sq, int skv, int topk, int partial_f32, cudaStream_t stream);
 int launch_kv_token_pipe(const void* q, const void* k, const void* v, const int32_t* tasks, const int32_t* task_count,
                          const int32_t* qids, const int32_t* ranks, void* partial, float* lses, int batch, int hq,
                          int hkv, int sq, int skv, int topk, int q_token_major, cudaStream_t stream);

@@ -38,6 +38,7 @@ struct Params {
   float* lses;                  // [B, Hq, Sq, TopK]
   int* status;
   int batch, hq, hkv, sq, skv, topk, group, group_log2, edges;
+  int partial_f32;              // the partials are fp32 (the reference's fp32 control variants)
   float scale_log2;
 };
 
@@ -200,35 +201,52 @@ kv_token_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant
         unsigned char* stage_g = gbase + OFF_STAGE + warp * 4096;
         const long long my_dst = dst_rows[threadIdx.x];
         if (my_dst >= 0) p.lses[my_dst] = (row_max + log2f(row_sum)) * 0.6931471805599453f;
+        if (p.partial_f32) {
+          // fp32 partials: every thread writes its own row (512 contiguous bytes) straight from tensor memory
+          float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.partial) + (my_dst >= 0 ? my_dst : 0) * 128);
 #pragma unroll 1
-        for (int pass = 0; pass < 2; ++pass) {
-#pragma unroll
-          for (int cc = 0; cc < 2; ++cc) {
+          for (int cc = 0; cc < 4; ++cc) {
             uint32_t ov[32];
-            tmem_ld32(tmem + lane_base + 128 + pass * 64 + cc * 32, ov);
+            tmem_ld32(tmem + lane_base + 128 + cc * 32, ov);
             tc_wait_ld();
+            if (my_dst >= 0) {
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const uint4 val = make_uint4(
-                  pack_bf16x2(__uint_as_float(ov[8 * j]) * inv, __uint_as_float(ov[8 * j + 1]) * inv),
-                  pack_bf16x2(__uint_as_float(ov[8 * j + 2]) * inv, __uint_as_float(ov[8 * j + 3]) * inv),
-                  pack_bf16x2(__uint_as_float(ov[8 * j + 4]) * inv, __uint_as_float(ov[8 * j + 5]) * inv),
-                  pack_bf16x2(__uint_as_float(ov[8 * j + 6]) * inv, __uint_as_float(ov[8 * j + 7]) * inv));
-              *reinterpret_cast<uint4*>(stage_g + lane * 128 + (((cc * 4 + j) ^ (lane & 7)) << 4)) = val;
+              for (int j = 0; j < 8; ++j)
+                dst[cc * 8 + j] = make_float4(__uint_as_float(ov[4 * j]) * inv, __uint_as_float(ov[4 * j + 1]) * inv,
+                                              __uint_as_float(ov[4 * j + 2]) * inv, __uint_as_float(ov[4 * j + 3]) * inv);
             }
           }
-          __syncwarp();
-          // eight lanes write one 128-byte row segment: four destination rows per instruction
+        } else {
+#pragma unroll 1
+          for (int pass = 0; pass < 2; ++pass) {
 #pragma unroll
-          for (int it = 0; it < 8; ++it) {
-            const int rr = it * 4 + (lane >> 3), ch = lane & 7;
-            const long long d = dst_rows[warp * 32 + rr];
-            if (d >= 0) {
-              const uint4 val = *reinterpret_cast<const uint4*>(stage_g + rr * 128 + ((ch ^ (rr & 7)) << 4));
-              *reinterpret_cast<uint4*>(reinterpret_cast<unsigned char*>(p.partial) + d * 256 + pass * 128 + ch * 16) = val;
+            for (int cc = 0; cc < 2; ++cc) {
+              uint32_t ov[32];
+              tmem_ld32(tmem + lane_base + 128 + pass * 64 + cc * 32, ov);
+              tc_wait_ld();
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const uint4 val = make_uint4(
+                    pack_bf16x2(__uint_as_float(ov[8 * j]) * inv, __uint_as_float(ov[8 * j + 1]) * inv),
+                    pack_bf16x2(__uint_as_float(ov[8 * j + 2]) * inv, __uint_as_float(ov[8 * j + 3]) * inv),
+                    pack_bf16x2(__uint_as_float(ov[8 * j + 4]) * inv, __uint_as_float(ov[8 * j + 5]) * inv),
+                    pack_bf16x2(__uint_as_float(ov[8 * j + 6]) * inv, __uint_as_float(ov[8 * j + 7]) * inv));
+                *reinterpret_cast<uint4*>(stage_g + lane * 128 + (((cc * 4 + j) ^ (lane & 7)) << 4)) = val;
+              }
             }
+            __syncwarp();
+            // eight lanes write one 128-byte row segment: four destination rows per instruction
+#pragma unroll
+            for (int it = 0; it < 8; ++it) {
+              const int rr = it * 4 + (lane >> 3), ch = lane & 7;
+              const long long d = dst_rows[warp * 32 + rr];
+              if (d >= 0) {
+                const uint4 val = *reinterpret_cast<const uint4*>(stage_g + rr * 128 + ((ch ^ (rr & 7)) << 4));
+                *reinterpret_cast<uint4*>(reinterpret_cast<unsigned char*>(p.partial) + d * 256 + pass * 128 + ch * 16) = val;
+              }
+            }
+            __syncwarp();
           }
-          __syncwarp();
         }
         tc_fence_before();
       }
@@ -249,20 +267,21 @@ kv_token_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant
 
 int launch_kv_token_main(const void* q, const void* k, const void* v, const int32_t* tasks, const int32_t* task_count,
                          const int32_t* qids, const int32_t* ranks, void* partial, float* lses, int batch, int hq,
-                         int hkv, int sq, int skv, int topk, cudaStream_t stream) {
+                         int hkv, int sq, int skv, int topk, int partial_f32, cudaStream_t stream) {
   using namespace kvt;
   const int group = hq / hkv;
   // groups of 8 or 16 heads take the pipelined kernel (kv_token_pipe.cu); this one serves
   // the smaller groups, whose Q rows cannot be fetched as 1024-byte-aligned TMA boxes
   if (group == 8 || group == 16)
     return launch_kv_token_pipe(q, k, v, tasks, task_count, qids, ranks, partial, lses, batch, hq, hkv, sq, skv, topk,
-                                0, stream);
+                                partial_f32 ? 4 : 0, stream);
   DeviceCtx* ctx = device_ctx();
   if (!ctx) return SB_ERR_CUDA;
   Params p{};
   p.q = static_cast<const __nv_bfloat16*>(q);
   p.tasks = tasks; p.task_count = task_count; p.qids = qids; p.ranks = ranks;
   p.partial = static_cast<__nv_bfloat16*>(partial);
+  p.partial_f32 = partial_f32;
   p.lses = lses;
   p.status = ctx->status;
   p.batch = batch; p.hq = hq; p.hkv = hkv; p.sq = sq; p.skv = skv; p.topk = topk; p.group = group;

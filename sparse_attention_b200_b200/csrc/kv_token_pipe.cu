@@ -65,6 +65,7 @@ struct Params {
   int phases;                   // upper bound on the number of passes over the task list (see Walk)
   int q_token_major;            // q is [B, Sq, Hq, 128]: the G heads of a token are one dense box
   int partial_token_major;      // partials are [B, Sq, TopK, Hq, 128] (the reference's token-major operators)
+  float* partial_f32;           // non-null: fp32 partials (the reference's fp32 controls), written with plain stores
   float scale_log2;
 };
 
@@ -114,6 +115,7 @@ __device__ __forceinline__ void tma_store_4d(const CUtensorMap* map, int x, int 
                : "memory");
 }
 
+template <bool F32>      // fp32 partials (plain stores) instead of bf16 (staged, TMA stores)
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 kv_token_pipe_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
                      const __grid_constant__ CUtensorMap v_map, const __grid_constant__ CUtensorMap o_map,
@@ -417,9 +419,36 @@ kv_token_pipe_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_con
       const float inv = stats[s * 128 + quarter * 32 + lane];
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(STATS_EMPTY + s));
+      const uint32_t t_o = tmem + lane_base + 256 + s * 128;
+      if constexpr (F32) {
+        // fp32 partials: lane = row (query lane / G, head lane % G) writes its 512 bytes from tensor memory
+        const int owner = lane >> p.group_log2, g = lane & (G - 1);
+        const int row_q = __shfl_sync(0xffffffffu, qi, owner), row_rank = __shfl_sync(0xffffffffu, rank, owner);
+        const int b = k.group / p.hkv, head = (k.group - b * p.hkv) * G + g;
+        const long long row =
+            p.partial_token_major
+                ? ((static_cast<long long>(b) * p.sq + row_q) * p.topk + row_rank) * p.hq + head
+                : ((static_cast<long long>(b) * p.hq + head) * p.sq + row_q) * p.topk + row_rank;
+        float4* dst = reinterpret_cast<float4*>(p.partial_f32 + (row_q >= 0 ? row : 0) * 128);
+#pragma unroll 1
+        for (int cc = 0; cc < 8; ++cc) {
+          uint32_t ov[16];
+          tmem_ld16(t_o + cc * 16, ov);
+          tc_wait_ld();
+          if (row_q >= 0) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+              dst[cc * 4 + j] = make_float4(__uint_as_float(ov[4 * j]) * inv, __uint_as_float(ov[4 * j + 1]) * inv,
+                                            __uint_as_float(ov[4 * j + 2]) * inv, __uint_as_float(ov[4 * j + 3]) * inv);
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(O_EMPTY + s));
+        continue;
+      }
       bulk_wait_read0();                             // this lane's earlier stores have left the staging tile
       __syncwarp();
-      const uint32_t t_o = tmem + lane_base + 256 + s * 128;
 #pragma unroll
       for (int cc = 0; cc < 4; ++cc) {
         uint32_t ov[32];
@@ -470,7 +499,7 @@ kv_token_pipe_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_con
 
 // Pipelined main stage for Hq / Hkv of 8 or 16 (arguments of launch_kv_token_main; q_token_major bit 0:
 // q is [B, Sq, Hq, 128] instead of [B, Hq, Sq, 128]; bit 1: the partials are [B, Sq, TopK, Hq, 128]
-// instead of [B, Hq, Sq, TopK, 128]).
+// instead of [B, Hq, Sq, TopK, 128]; bit 2: the partials are fp32 instead of bf16).
 int launch_kv_token_pipe(const void* q, const void* k, const void* v, const int32_t* tasks, const int32_t* task_count,
                          const int32_t* qids, const int32_t* ranks, void* partial, float* lses, int batch, int hq,
                          int hkv, int sq, int skv, int topk, int q_token_major, cudaStream_t stream) {
@@ -489,6 +518,7 @@ int launch_kv_token_pipe(const void* q, const void* k, const void* v, const int3
   p.scale_log2 = 1.4426950408889634f / sqrtf(128.0f);
   p.q_token_major = q_token_major & 1;
   p.partial_token_major = (q_token_major >> 1) & 1;
+  p.partial_f32 = (q_token_major & 4) ? static_cast<float*>(partial) : nullptr;
   q_token_major &= 1;
   // one segment per 24 MB of Q: the Q rows a segment gathers then stay within L2
   const long long q_bytes = static_cast<long long>(batch) * hq * sq * 256;
@@ -536,16 +566,24 @@ int launch_kv_token_pipe(const void* q, const void* k, const void* v, const int3
       strides[2] = static_cast<cuuint64_t>(topk) * hq * 256;
       box[1] = static_cast<cuuint32_t>(group); box[3] = 1;
     }
+    // (fp32 partials are written with plain stores: the map is encoded over the same base and never used)
     if (encode_tiled(&om, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, partial, dims, strides, box, ones,
                      CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE))
       return set_error(SB_ERR_CUDA, "cuTensorMapEncodeTiled failed for the partial outputs");
   }
-  if (!(ctx->tc_attr & (1 << 10))) {
-    cudaError_t e = cudaFuncSetAttribute(kv_token_pipe_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+  const int slot = p.partial_f32 ? 18 : 10;
+  if (!(ctx->tc_attr & (1 << slot))) {
+    cudaError_t e = p.partial_f32 ? cudaFuncSetAttribute(kv_token_pipe_kernel<true>,
+                                                         cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES)
+                                  : cudaFuncSetAttribute(kv_token_pipe_kernel<false>,
+                                                         cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
     if (e != cudaSuccess) return set_error(SB_ERR_CUDA, cudaGetErrorString(e));
-    ctx->tc_attr |= (1 << 10);
+    ctx->tc_attr |= (1 << slot);
   }
-  kv_token_pipe_kernel<<<ctx->sm_count, NUM_THREADS, SMEM_BYTES, stream>>>(qm, km, vm, om, p);
+  if (p.partial_f32)
+    kv_token_pipe_kernel<true><<<ctx->sm_count, NUM_THREADS, SMEM_BYTES, stream>>>(qm, km, vm, om, p);
+  else
+    kv_token_pipe_kernel<false><<<ctx->sm_count, NUM_THREADS, SMEM_BYTES, stream>>>(qm, km, vm, om, p);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? SB_OK : set_error(SB_ERR_CUDA, cudaGetErrorString(e));
 }

@@ -89,15 +89,17 @@ class PreparedTokens:
     metadata() builds the reverse index and the task list on the GPU, main() writes one
     normalised partial per (query, head, rank), combine() merges the TopK partials.
     q_token_major=True: q is [B,Sq,Hq,128], the layout of the reference's TMA variants (groups of
-    8 or 16 heads only); outputs stay head-major."""
+    8 or 16 heads only); outputs stay head-major. partial_f32=True keeps the partials in fp32 (the
+    reference's control variants -2 and 0, api11.py:22-25) instead of bf16."""
 
-    def __init__(self, q, k, v, selected, q_token_major=False, partial_token_major=False):
+    def __init__(self, q, k, v, selected, q_token_major=False, partial_token_major=False, partial_f32=False):
         import ctypes
         if not (q.is_cuda and q.dtype == torch.bfloat16 and q.is_contiguous() and q.dim() == 4 and q.shape[3] == 128):
             raise _lib.SparseB200Error("q must be contiguous bf16 [B,Hq,Sq,128] (or [B,Sq,Hq,128]) on CUDA")
         self.q_token_major = bool(q_token_major)
         # partials [B,Sq,TopK,Hq,128] as the reference's main_tm_out writes them (needs q token-major too)
         self.partial_token_major = bool(partial_token_major)
+        self.partial_f32 = bool(partial_f32)
         if self.partial_token_major and not self.q_token_major:
             raise _lib.SparseB200Error("token-major partials go with token-major q")
         q_arg = q
@@ -136,7 +138,7 @@ class PreparedTokens:
         self.tasks = torch.zeros((self.max_tasks, 4), device=dev, dtype=torch.int32)
         self.error = ints(1)
         self.partial = torch.empty((b, sq, self.topk, hq, d) if self.partial_token_major else (b, hq, sq, self.topk, d),
-                                   device=dev, dtype=torch.bfloat16)
+                                   device=dev, dtype=torch.float32 if self.partial_f32 else torch.bfloat16)
         self.lses = torch.empty((b, hq, sq, self.topk), device=dev, dtype=torch.float32)
         self.out = torch.empty((b, hq, sq, d), device=dev, dtype=torch.bfloat16)
         self.out_lse = torch.empty((b, hq, sq), device=dev, dtype=torch.float32)
@@ -155,25 +157,23 @@ class PreparedTokens:
 
     def main(self):
         with torch.cuda.device(self.q.device):
-            L = _lib.lib()
-            fn = L.sparse_b200_kv_token_main_tm_partial_tm if self.partial_token_major else \
-                L.sparse_b200_kv_token_main_tm if self.q_token_major else L.sparse_b200_kv_token_main
-            _lib.check(fn(
+            layout = int(self.q_token_major) | int(self.partial_token_major) << 1 | int(self.partial_f32) << 2
+            _lib.check(_lib.lib().sparse_b200_kv_token_main_layout(
                 _lib.ptr(self.q), _lib.ptr(self.k), _lib.ptr(self.v), _lib.ptr(self.tasks), _lib.ptr(self.task_ptr),
                 _lib.ptr(self.qids), _lib.ptr(self.ranks), _lib.ptr(self.partial), _lib.ptr(self.lses),
-                self.b, self.hq, self.hkv, self.sq, self.skv, self.topk, _lib.current_stream()))
+                self.b, self.hq, self.hkv, self.sq, self.skv, self.topk, layout, _lib.current_stream()))
 
     def combine(self):
         import ctypes
         with torch.cuda.device(self.q.device):
             if self.partial_token_major:
                 _lib.check(_lib.lib().sparse_b200_combine_tm(
-                    _lib.ptr(self.partial), 0, _lib.ptr(self.lses), _lib.ptr(self.out), _lib.ptr(self.out_lse),
-                    self.b, self.hq, self.sq, self.topk, _lib.current_stream()))
+                    _lib.ptr(self.partial), int(self.partial_f32), _lib.ptr(self.lses), _lib.ptr(self.out),
+                    _lib.ptr(self.out_lse), self.b, self.hq, self.sq, self.topk, _lib.current_stream()))
                 return
             _lib.check(_lib.lib().sparse_b200_combine(
-                _lib.ptr(self.partial), 0, _lib.ptr(self.lses), _lib.ptr(self.out), _lib.ptr(self.out_lse),
-                ctypes.c_int64(self.out_lse.numel()), self.topk, 0, _lib.current_stream()))
+                _lib.ptr(self.partial), int(self.partial_f32), _lib.ptr(self.lses), _lib.ptr(self.out),
+                _lib.ptr(self.out_lse), ctypes.c_int64(self.out_lse.numel()), self.topk, 0, _lib.current_stream()))
 
     def core(self):
         self.main()

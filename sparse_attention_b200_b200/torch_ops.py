@@ -8,13 +8,12 @@ operator is not registered yet, attention/q_centric/progression.py:29-36):
       (attention/q_centric/progression_attention.cpp:19-125; `variant` selects nothing here: one kernel)
   xomtention_tile_topk::tile_topk / tile_topk_out
       (indexers/fp4/wrapper.cpp:16-80; 16 ids per list as there)
-  xomtention_kvopt11::metadata_temp_bytes / metadata_out / main_out / combine_out
-      (attention/kv_centric/optimization_round11/wrapper11.cpp:29-171): the head-major operator
-      chain. metadata_out serves chunk_size 1 (a task holds at most 128 / group_size queries, the unit
-      the main kernel works on) and main_out the bf16-partial variant (-1). The token-major pair
-      main_tm_out / combine_tm_out is not registered: its partial-output layout [B,Sq,16,Hq,128] is
-      private to the reference's two kernels; `PreparedTokens(q_token_major=True)` is the operator-level
-      replacement.
+  xomtention_kvopt11::metadata_temp_bytes / metadata_out / main_out / combine_out / main_tm_out /
+      combine_tm_out (attention/kv_centric/optimization_round11/wrapper11.cpp:29-171): the head-major
+      chain (variants -2 = fp32 partials, -1 = bf16) and the token-major pair (variants 0 = fp32
+      partials, 1 and 2 = bf16; Hq/Hkv of 8 or 16). metadata_out takes the reference's chunk sizes; the
+      main kernels always work on tasks of at most 128 / group_size queries, which metadata_out keeps
+      in storage of its own next to the grouped list it hands back.
 
 Each operator validates like the reference (RuntimeError on rejected inputs), runs on the current
 CUDA stream of the tensors' device, allocates only where the reference's does (`attention`,
@@ -159,11 +158,16 @@ def _register_kvopt11():
         state[tasks.data_ptr()] = (run_tasks, run_task_ptr)
 
     def main_out(q, k, v, tasks, qids, ranks, partial, lses, variant):
-        if variant != -1:
-            _fail("main_out serves the bf16-partial variant (-1)")
-        for t in (q, k, v, partial):
+        # wrapper11.cpp:66-70: -2 = fp32 partials, -1 = bf16 partials
+        if variant not in (-2, -1):
+            _fail("main_out serves the head-major variants (-2, -1); the token-major ones use main_tm_out")
+        f32 = variant == -2
+        for t in (q, k, v):
             if not (t.is_cuda and t.dtype == torch.bfloat16 and t.is_contiguous()) or t.requires_grad:
-                _fail("q, k, v and partial must be contiguous bf16 CUDA tensors (forward only)")
+                _fail("q, k and v must be contiguous bf16 CUDA tensors (forward only)")
+        if not (partial.is_cuda and partial.is_contiguous() and
+                partial.dtype == (torch.float32 if f32 else torch.bfloat16)) or partial.requires_grad:
+            _fail("partial must be a contiguous CUDA tensor of the variant's type (fp32 for -2, bf16 for -1)")
         _ints(q, tasks, qids, ranks)
         if q.dim() != 4 or k.dim() != 4 or k.shape != v.shape or q.shape[3] != 128 or k.shape[3] != 128:
             _fail("QKV rank/shape")
@@ -172,15 +176,16 @@ def _register_kvopt11():
         topk = qids.numel() // max(1, b * hkv * sq)
         if tuple(partial.shape) != (b, hq, sq, topk, 128) or tuple(lses.shape) != (b, hq, sq, topk) \
                 or lses.dtype != torch.float32:
-            _fail("partials must be [B,Hq,Sq,TopK,128] bf16 and [B,Hq,Sq,TopK] fp32")
+            _fail("partials must be [B,Hq,Sq,TopK,128] and [B,Hq,Sq,TopK] fp32")
         built = state.get(tasks.data_ptr())
         if built is None:
             _fail("main_out needs the task list of a preceding metadata_out on the same tasks tensor")
         run_tasks, task_ptr = built
         with torch.cuda.device(q.device):
-            _lib.check(_lib.lib().sparse_b200_kv_token_main(
+            _lib.check(_lib.lib().sparse_b200_kv_token_main_layout(
                 _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(run_tasks), _lib.ptr(task_ptr), _lib.ptr(qids),
-                _lib.ptr(ranks), _lib.ptr(partial), _lib.ptr(lses), b, hq, hkv, sq, skv, topk, _lib.current_stream()))
+                _lib.ptr(ranks), _lib.ptr(partial), _lib.ptr(lses), b, hq, hkv, sq, skv, topk, 4 if f32 else 0,
+                _lib.current_stream()))
 
     def combine_out(partial, lses, out, out_lse):
         if partial.dtype not in (torch.float32, torch.bfloat16) or not partial.is_contiguous() or not lses.is_contiguous():
@@ -197,13 +202,17 @@ def _register_kvopt11():
                 ctypes.c_int64(out_lse.numel()), ranks, 0, _lib.current_stream()))
 
     def main_tm_out(q, k, v, tasks, qids, ranks, partial, lses, variant):
-        # wrapper11.cpp:94-118: q [B,Sq,Hq,128], partial [B,Sq,TopK,Hq,128], lses [B,Hq,Sq,TopK]; variants 1 and 2
-        # are the bf16-partial ones (0 = fp32 partials is not served)
-        if variant not in (1, 2):
-            _fail("main_tm_out serves the bf16-partial variants (1, 2)")
-        for t in (q, k, v, partial):
+        # wrapper11.cpp:94-118: q [B,Sq,Hq,128], partial [B,Sq,TopK,Hq,128], lses [B,Hq,Sq,TopK]; variant 0 has
+        # fp32 partials, 1 and 2 bf16 ones
+        if variant not in (0, 1, 2):
+            _fail("main_tm_out serves the token-major variants (0, 1, 2)")
+        f32 = variant == 0
+        for t in (q, k, v):
             if not (t.is_cuda and t.dtype == torch.bfloat16 and t.is_contiguous()) or t.requires_grad:
-                _fail("q, k, v and partial must be contiguous bf16 CUDA tensors (forward only)")
+                _fail("q, k and v must be contiguous bf16 CUDA tensors (forward only)")
+        if not (partial.is_cuda and partial.is_contiguous() and
+                partial.dtype == (torch.float32 if f32 else torch.bfloat16)) or partial.requires_grad:
+            _fail("partial must be a contiguous CUDA tensor of the variant's type (fp32 for 0, bf16 for 1 and 2)")
         _ints(q, tasks, qids, ranks)
         if q.dim() != 4 or k.dim() != 4 or k.shape != v.shape or q.shape[3] != 128 or k.shape[3] != 128:
             _fail("QKV rank/shape")
@@ -220,9 +229,10 @@ def _register_kvopt11():
             _fail("main_tm_out needs the task list of a preceding metadata_out on the same tasks tensor")
         run_tasks, task_ptr = built
         with torch.cuda.device(q.device):
-            _lib.check(_lib.lib().sparse_b200_kv_token_main_tm_partial_tm(
+            _lib.check(_lib.lib().sparse_b200_kv_token_main_layout(
                 _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(run_tasks), _lib.ptr(task_ptr), _lib.ptr(qids),
-                _lib.ptr(ranks), _lib.ptr(partial), _lib.ptr(lses), b, hq, hkv, sq, skv, topk, _lib.current_stream()))
+                _lib.ptr(ranks), _lib.ptr(partial), _lib.ptr(lses), b, hq, hkv, sq, skv, topk, 7 if f32 else 3,
+                _lib.current_stream()))
 
     def combine_tm_out(partial, lses, out, out_lse):
         if partial.dtype not in (torch.float32, torch.bfloat16) or not partial.is_contiguous() or not lses.is_contiguous():

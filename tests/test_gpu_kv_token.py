@@ -200,3 +200,41 @@ def test_token_major_q_gives_identical_results(g):
     with pytest.raises(m.SparseB200Error):
         m.PreparedTokens(torch.zeros((1, 8, 4, 128), dtype=torch.bfloat16, device="cuda"), k[:1, :1], v[:1, :1],
                          selected[:1, :1, :8].contiguous(), q_token_major=True)      # Hq/Hkv = 4
+
+
+@pytest.mark.parametrize("g,topk,sq", [(1, 16, 130), (2, 5, 77), (4, 16, 257), (8, 16, 300), (16, 7, 129)])
+def test_fp32_partials_round_to_the_bf16_ones(g, topk, sq):
+    """The fp32-partial form of the main stage (the reference's control variants, api11.py:22-25): the same
+    arithmetic with the last rounding left out, so its partials rounded to bf16 are the bf16 partials bit for bit,
+    the LSEs are identical, and the merged output matches the masked-attention reference (every group size: the
+    generic kernel below 8 heads per group, the pipelined one for 8 and 16; token-major for those as well)."""
+    import sparse_attention_b200_b200 as m
+    gen = torch.Generator().manual_seed(17 + g)
+    b, hkv, skv = 2, 2, 2048
+    q = torch.randn((b, hkv * g, sq, 128), generator=gen).to(torch.bfloat16)
+    k = torch.randn((b, hkv, skv, 128), generator=gen).to(torch.bfloat16)
+    v = torch.randn((b, hkv, skv, 128), generator=gen).to(torch.bfloat16)
+    selected = make_selected(b, hkv, sq, skv // 128, topk, "independent", 3)
+    ref_o, ref_l = token_reference(q, k, v, selected)
+    q, k, v, selected = q.cuda(), k.cuda(), v.cuda(), selected.cuda()
+    half = m.PreparedTokens(q, k, v, selected)
+    half.run()
+    full = m.PreparedTokens(q, k, v, selected, partial_f32=True)
+    full.poison()
+    full.run()
+    torch.cuda.synchronize()
+    m.device_status()
+    assert full.partial.dtype == torch.float32 and torch.isfinite(full.partial).all()
+    assert torch.equal(full.partial.to(torch.bfloat16).view(torch.int16), half.partial.view(torch.int16))
+    assert torch.equal(full.lses, half.lses) and torch.equal(full.out_lse, half.out_lse)
+    torch.testing.assert_close(full.out.float().cpu(), ref_o, atol=0.02, rtol=0.02)
+    torch.testing.assert_close(full.out_lse.cpu(), ref_l, atol=0.002, rtol=0.0002)
+    if g in (8, 16):
+        tm = m.PreparedTokens(q.permute(0, 2, 1, 3).contiguous(), k, v, selected, q_token_major=True,
+                              partial_token_major=True, partial_f32=True)
+        tm.poison()
+        tm.run()
+        torch.cuda.synchronize()
+        m.device_status()
+        assert torch.equal(tm.partial.permute(0, 3, 1, 2, 4), full.partial)
+        assert torch.equal(tm.out.view(torch.int16), full.out.view(torch.int16)) and torch.equal(tm.out_lse, full.out_lse)

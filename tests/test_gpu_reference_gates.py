@@ -16,9 +16,9 @@ library through the operator names / module interface the gates use:
   non-default stream, repeat) + the Combine unit with +-1000 LSEs.
 
 * attention/kv_centric/optimization_round11/api11.py `Prepared`, the reference's host class for its round-11
-  KV-centric operator, used as it is over torch.ops.xomtention_kvopt11 from this library: variants split8_bf16,
-  tma8_bf16 and tma16_bf16 (its planner's chunk sizes 8 and 16, token-major q and partials), its own audit of
-  the task lists.
+  KV-centric operator, used as it is over torch.ops.xomtention_kvopt11 from this library: all five variants
+  (split8 and tma8 with fp32 partials, split8_bf16, tma8_bf16 and tma16_bf16; its planner's chunk sizes 8 and 16,
+  token-major q and partials), its own audit of the task lists.
 
 Skipped, with the reason, when baseline/_ref/ does not hold the reference files."""
 import os
@@ -134,8 +134,21 @@ def test_reference_operator_names_head_major_chain():
     assert torch.equal(out, o2) and torch.equal(out_lse, l2)
     with pytest.raises(RuntimeError):
         kv.metadata_out(sel, counts, row_ptr, cursors, qids, ranks, chunks, task_ptr, tasks, error, temp, skv // 128, g, 3)
-    with pytest.raises(RuntimeError):
-        kv.main_out(qc, kc, vc, tasks, qids, ranks, partial.float(), lses, -2)
+    with pytest.raises(RuntimeError):                                  # bf16 variant, fp32 buffer
+        kv.main_out(qc, kc, vc, tasks, qids, ranks, partial.float(), lses, -1)
+    with pytest.raises(RuntimeError):                                  # a token-major variant
+        kv.main_out(qc, kc, vc, tasks, qids, ranks, partial, lses, 1)
+    partial32 = torch.full(partial.shape, float("nan"), device="cuda")
+    lses32 = torch.full_like(lses, float("nan"))
+    kv.main_out(qc, kc, vc, tasks, qids, ranks, partial32, lses32, -2)  # the fp32 control (wrapper11.cpp:66-70)
+    out32 = torch.full_like(out, float("nan"))
+    out_lse32 = torch.full_like(out_lse, float("nan"))
+    kv.combine_out(partial32, lses32, out32, out_lse32)
+    torch.cuda.synchronize()
+    sp.device_status()
+    assert torch.equal(partial32.to(torch.bfloat16), partial) and torch.equal(lses32, lses)
+    assert torch.equal(out_lse32, out_lse)
+    torch.testing.assert_close(out32.float(), out.float(), atol=0.02, rtol=0.02)
     # the token-major pair (main_tm_out + combine_tm_out, wrapper11.cpp:94-133): q [B,Sq,Hq,128], partials
     # [B,Sq,TopK,Hq,128]; the merged output is the head-major chain's, bit for bit
     q_tm = qc.permute(0, 2, 1, 3).contiguous()
@@ -167,8 +180,8 @@ def test_reference_round11_prepared_class_runs_on_this_library():
     """attention/kv_centric/optimization_round11/api11.py `Prepared` (the reference's own host class: GPUPlan with
     its chunk sizes, main_out / main_tm_out, combine_out / combine_tm_out, partial_view) used as it is, with
     torch.ops.xomtention_kvopt11 coming from this library instead of the reference's extension: outputs and
-    partials equal this library's Python mirror bit for bit for the bf16-partial variants (split8_bf16, tma8_bf16,
-    tma16_bf16), and the reference's own audit of the task lists (gpu_plan.py:47-73) passes."""
+    partials equal this library's Python mirror bit for bit for all five variants (split8, split8_bf16, tma8,
+    tma8_bf16, tma16_bf16), and the reference's own audit of the task lists (gpu_plan.py:47-73) passes."""
     _need("kv_centric/optimization_round11/api11.py", "kv_centric/optimization_round4/gpu_plan.py",
           "kv_centric/optimization_round4/planning.py", "kv_centric/metadata.py")
     import sparse_attention_b200_b200 as sp
@@ -201,7 +214,18 @@ def test_reference_round11_prepared_class_runs_on_this_library():
                 assert torch.equal(prep.partial_view(), ours.partial) and torch.equal(prep.lses, ours.lses), variant
                 report = prep.plan.audit(selected)
                 assert report["exact_coverage"] and report["gpu_error"] == 0, variant
-            with pytest.raises(RuntimeError):                # fp32 partials are not served
-                api11.Prepared(q_tm, k, v, sel, variant=0).run()
+            # the fp32 controls (split8 = -2, the class's default, and tma8 = 0): same kernels with fp32 partials
+            ours32 = sp.PreparedTokens(q_tm.permute(0, 2, 1, 3).contiguous(), k, v, sel, partial_f32=True)
+            ours32.run()
+            assert torch.equal(ours32.partial.to(torch.bfloat16), ours.partial) and torch.equal(ours32.lses, ours.lses)
+            for prep in (api11.Prepared(q_tm, k, v, sel), api11.Prepared(q_tm, k, v, sel, variant=0)):
+                assert prep.partial.dtype == torch.float32
+                prep.poison()
+                prep.run()
+                torch.cuda.synchronize()
+                sp.device_status()
+                assert torch.equal(prep.partial_view(), ours32.partial) and torch.equal(prep.lses, ours32.lses)
+                assert torch.equal(prep.out, ours32.out) and torch.equal(prep.out_lse, ours.out_lse)
+                torch.testing.assert_close(prep.out.float(), ours.out.float(), atol=0.02, rtol=0.02)
     finally:
         sys.path.remove(r11)
