@@ -148,6 +148,7 @@ def test_q_centric_random_shapes(shape):
 
 def _token_shapes(n, seed):
     rng = random.Random(seed)
+    layouts = random.Random(seed + 1)        # its own stream: the geometries stay those of the seed
     out = []
     while len(out) < n:
         b = rng.choice([1, 2])
@@ -159,7 +160,7 @@ def _token_shapes(n, seed):
         if b * hkv * g * sq * topk > 160_000:
             continue
         out.append((b, hkv, g, sq, nb * 128, topk, rng.choice(["independent", "hot", "tile_shared", "identical"]),
-                    rng.randrange(1 << 30)))
+                    rng.randrange(1 << 30), layouts.randrange(8)))
     return out
 
 
@@ -167,18 +168,24 @@ def _token_shapes(n, seed):
 def test_token_operator_random_shapes(shape):
     """The per-token KV-centric operator (reverse index, main, Combine) on random geometries: every group size the
     reference serves, token counts with tails, top-k from 1 to all blocks; the reverse index is audited by the CPU
-    validator and the output compared with the masked-attention oracle (the reference's tolerances)."""
+    validator and the output compared with the masked-attention oracle (the reference's tolerances). The last
+    field draws the layout: bit 0 q token-major, bit 1 partials token-major too (both only for 8 or 16 heads per
+    group), bit 2 fp32 partials."""
     import oracle
     from tests.test_gpu_kv_token import make_selected, token_reference
-    b, hkv, g, sq, skv, topk, kind, seed = shape
+    b, hkv, g, sq, skv, topk, kind, seed, layout = shape
     m = sp()
+    q_tm = bool(layout & 1) and g in (8, 16)
+    p_tm, f32 = q_tm and bool(layout & 2), bool(layout & 4)
     gen = torch.Generator().manual_seed(seed)
     q = torch.randn((b, hkv * g, sq, 128), generator=gen).to(torch.bfloat16)
     k = torch.randn((b, hkv, skv, 128), generator=gen).to(torch.bfloat16)
     v = torch.randn((b, hkv, skv, 128), generator=gen).to(torch.bfloat16)
     selected = make_selected(b, hkv, sq, skv // 128, topk, kind, seed % 1000)
     ref_o, ref_l = token_reference(q, k, v, selected)
-    p = m.PreparedTokens(q.cuda(), k.cuda(), v.cuda(), selected.cuda())
+    p = m.PreparedTokens((q.permute(0, 2, 1, 3).contiguous() if q_tm else q).cuda(), k.cuda(), v.cuda(),
+                         selected.cuda(), q_token_major=q_tm, partial_token_major=p_tm, partial_f32=f32)
+    assert p.partial.dtype == (torch.float32 if f32 else torch.bfloat16)
     p.poison()
     out, lse = p.run()
     torch.cuda.synchronize()
