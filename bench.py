@@ -578,6 +578,20 @@ def kv_split_record(sp, sharding, dist, name, cfg, world, rank, dev, barrier, st
     def step_unpipelined():
         res["u"] = split.run(wl.q, k_loc, v_loc, wl.ids, nb)
     ms_plain = timed(step_unpipelined, steps, 2, barrier)
+    # the same merge over peer memory: the Combine kernel reads the other rank's partial rows over NVLink itself
+    peer = {}
+    try:
+        ex = sharding.PeerExchange(wl.q.shape[0] * wl.q.shape[1] * wl.q.shape[2], dev, kv_group)
+    except Exception as e:          # raised on every rank of the pair alike (no IPC / peer access between the GPUs)
+        ex, peer = None, {"unavailable": str(e)[:200]}
+    if ex is not None:
+        def step_peer():
+            res["p"] = split.run_peer(ex, wl.q, k_loc, v_loc, wl.ids, nb)
+        peer["ms_per_step"] = timed(step_peer, steps, 2, barrier)
+        sp.device_status()
+        peer["identical_to_send_recv"] = bool(torch.equal(res["p"][0], res["u"][0]) and torch.equal(res["p"][1], res["u"][1]))
+        res.pop("p", None)
+        ex.close()
     res.pop("u", None)
     ms = timed(step, max(1, steps // 2), 1, barrier)
     sp.device_status()
@@ -599,13 +613,20 @@ def kv_split_record(sp, sharding, dist, name, cfg, world, rank, dev, barrier, st
             par["mean_abs"] = max(par["mean_abs"], d.mean().item())
             par["lse_rel"] = max(par["lse_rel"], ((l - rl[0, 0]).abs() / rl[0, 0].abs().clamp_min(1.0)).max().item())
             par["blocks"] += 1
-    t = torch.tensor([ms, par["max_abs"], par["mean_abs"], par["lse_rel"], ms_plain], device=dev, dtype=torch.float64)
+    t = torch.tensor([ms, par["max_abs"], par["mean_abs"], par["lse_rel"], ms_plain, peer.get("ms_per_step", 0.0),
+                      0.0 if peer.get("identical_to_send_recv", True) else 1.0], device=dev, dtype=torch.float64)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms, mx, mean, lrel, ms_plain = t.tolist()
+    ms, mx, mean, lrel, ms_plain, ms_peer, peer_differs = t.tolist()
     flops = attention_flops(cfg)
+    if "ms_per_step" in peer:
+        peer = {"ms_per_step": ms_peer, "value": flops / (ms_peer * 1e-3) / 1e12, "unit": "TFLOP/s",
+                "identical_to_send_recv": not peer_differs,
+                "how": "partials stay in IPC-mapped exchange memory, ready / done flag words, combine_peer_kernel loads "
+                       "the peer's rows over NVLink (no NCCL call on the data path)"}
     return {"sharding": f"{head_shards} head-group shard(s) x {kvs} KV ranges", "ms_per_step": ms_plain, "steps": steps,
             "value": flops / (ms_plain * 1e-3) / 1e12, "unit": "TFLOP/s",
             "merge": "NCCL send/recv of the owner's rows of (O, LSE) after the attention kernel, then the Combine kernel",
+            "peer_merge": peer,
             "ms_per_step_pipelined": ms,
             "pipelined": "chunks of two heads, a chunk's exchange on a side stream under the attention of the next chunk "
                          "(parity record below is of this form); slower when the persistent attention grid leaves "

@@ -180,6 +180,30 @@ int sparse_b200_kv_token_main_layout(const void* q, const void* k, const void* v
 int sparse_b200_combine_tm(const void* partial_token_major, int partial_is_f32, const float* partial_lse, void* out,
                            float* out_lse, int batch, int hq, int sq, int ranks, void* stream);
 
+/* Cross-GPU merge of the KV-range split over peer memory (one process per GPU, one machine). The
+ * reference has no multi-GPU path; this is the fused form of "exchange the (O, LSE) partials, then
+ * Combine" for the 1 Mi-token configuration: the merge kernel reads the other ranks' partials with
+ * plain loads over NVLink. No multicast, no library kernel on peer memory; every wait on a flag
+ * another GPU writes gives up after wait_ms and records a status code (sparse_b200_device_status).
+ * peer_alloc: `bytes` of zeroed device memory on the current device and a 64-byte handle that
+ * another process turns into a pointer with peer_open (CUDA IPC; the open enables peer access).
+ * peer_signal: after everything earlier on the stream, stores `value` into each of `count` (<= 16)
+ * flag words (host array of device pointers, usually one word in every rank's memory).
+ * peer_wait: a one-thread kernel that returns when each of `count` LOCAL flag words is >= value.
+ * combine_peer: rows [rows, 128] bf16 + LSE [rows] from `ranks` (1, 2, 4, 8) sources given as host
+ * arrays of device pointers (each already at the caller's first row), merged in rank order with the
+ * arithmetic of sparse_b200_combine (bit-identical rows); ready_flags (LOCAL, `ranks` words, or NULL)
+ * are awaited >= value before the first load. */
+int sparse_b200_peer_alloc(int64_t bytes, void** ptr, void* handle64);
+int sparse_b200_peer_open(const void* handle64, void** ptr);
+int sparse_b200_peer_close(void* ptr);
+int sparse_b200_peer_free(void* ptr);
+int sparse_b200_peer_signal(int32_t* const* flags, int count, int value, void* stream);
+int sparse_b200_peer_wait(const int32_t* flags, int count, int value, int wait_ms, void* stream);
+int sparse_b200_combine_peer(const void* const* partials, const float* const* partial_lses, const int32_t* ready_flags,
+                             int value, int wait_ms, void* out, float* out_lse, int64_t rows, int ranks,
+                             void* stream);
+
 /* R1 / R4 block-summary indexer (indexers/r1_r4/gpu_ops.py:6-49,
  * indexers/r1_r4/block_selectors.py:9-45), any Hkv, group size x R <= 64, any TopK.
  * pool_blocks: x [B, H, S, 128] bf16 -> desc [B, H, S/128, R, 128] bf16, the

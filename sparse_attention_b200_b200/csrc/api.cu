@@ -559,6 +559,48 @@ int sparse_b200_combine_tm(const void* partial_token_major, int partial_is_f32, 
                         static_cast<long long>(hq) * 128, 128, 1, ranks, static_cast<cudaStream_t>(stream), hq, sq);
 }
 
+int sparse_b200_peer_alloc(int64_t bytes, void** ptr, void* handle64) {
+  REQUIRE(ptr && handle64 && bytes > 0, "peer_alloc needs a size, a pointer slot and 64 bytes for the handle");
+  if (!device_ctx()) return SB_ERR_CUDA;
+  return peer_alloc(bytes, ptr, handle64);
+}
+
+int sparse_b200_peer_open(const void* handle64, void** ptr) {
+  REQUIRE(ptr && handle64, "null pointer");
+  if (!device_ctx()) return SB_ERR_CUDA;
+  return peer_open(handle64, ptr);
+}
+
+int sparse_b200_peer_close(void* ptr) {
+  REQUIRE(ptr, "null pointer");
+  return peer_close(ptr);
+}
+
+int sparse_b200_peer_free(void* ptr) {
+  REQUIRE(ptr, "null pointer");
+  return peer_free(ptr);
+}
+
+int sparse_b200_peer_signal(int32_t* const* flags, int count, int value, void* stream) {
+  REQUIRE(flags, "null pointer");
+  return launch_peer_signal(flags, count, value, static_cast<cudaStream_t>(stream));
+}
+
+int sparse_b200_peer_wait(const int32_t* flags, int count, int value, int wait_ms, void* stream) {
+  REQUIRE(flags && count > 0, "null pointer");
+  return launch_peer_wait(flags, count, value, wait_ms, static_cast<cudaStream_t>(stream));
+}
+
+int sparse_b200_combine_peer(const void* const* partials, const float* const* partial_lses, const int32_t* ready_flags,
+                             int value, int wait_ms, void* out, float* out_lse, int64_t rows, int ranks,
+                             void* stream) {
+  REQUIRE(partials && partial_lses && out, "null pointer");
+  REQUIRE(rows > 0, "rows must be positive");
+  REQUIRE(aligned16(out), "misaligned pointer");
+  return launch_combine_peer(partials, partial_lses, ready_flags, value, wait_ms, out, out_lse, rows, ranks,
+                             static_cast<cudaStream_t>(stream));
+}
+
 int64_t sparse_b200_indexer_fp4_workspace_bytes(int batch, int hidx, int hk, int len_q, int len_kv) {
   if (batch <= 0 || hidx <= 0 || hk <= 0 || len_q <= 0 || len_kv <= 0) return SB_ERR_INVALID;
   const int64_t tile = align256(static_cast<size_t>(batch) * hidx * (len_q / 128) * (len_kv / 128) * 4);

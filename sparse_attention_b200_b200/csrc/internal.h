@@ -71,6 +71,15 @@ int launch_kv_token_main(const void* q, const void* k, const void* v, const int3
 int launch_kv_token_pipe(const void* q, const void* k, const void* v, const int32_t* tasks, const int32_t* task_count,
                          const int32_t* qids, const int32_t* ranks, void* partial, float* lses, int batch, int hq,
                          int hkv, int sq, int skv, int topk, int q_token_major, cudaStream_t stream);
+// peer_exchange.cu: exchange memory other processes of the machine can map, flag signalling, merge over peer loads
+int peer_alloc(long long bytes, void** ptr, void* handle64);
+int peer_open(const void* handle64, void** ptr);
+int peer_close(void* ptr);
+int peer_free(void* ptr);
+int launch_peer_signal(int32_t* const* flags, int n, int value, cudaStream_t stream);
+int launch_peer_wait(const int32_t* flags, int n, int value, int wait_ms, cudaStream_t stream);
+int launch_combine_peer(const void* const* partials, const float* const* lses, const int32_t* ready, int value,
+                        int wait_ms, void* out, float* out_lse, long long rows, int ranks, cudaStream_t stream);
 int launch_quantize(const void* x, void* packed, void* scales, int batch, int heads_out, int group, int seq,
                     int paged, cudaStream_t stream);
 int launch_fp4_scores_prune(const void* qp, const void* qs, const void* kp, const void* ks, void* aux, float* tile_scores,

@@ -13,6 +13,11 @@ Two ways to shard, both without TMA multicast or any load from a peer's memory:
   Combine kernel merges them by log-sum-exp (`KVSplit`); `KVSplit.run_pipelined` does it in chunks of head
   pairs, the exchange of one chunk under the attention of the next.
 
+`PeerExchange` + `KVSplit.run_peer` are the fused form of that exchange + Combine on one machine: every
+rank keeps its partial in memory the other ranks have mapped (CUDA IPC), flags tell when a partial is
+complete, and the merge kernel reads the peers' rows with plain loads over NVLink (no copy step, no
+NCCL call on the data path, no multicast; every cross-GPU wait is bounded).
+
 The reference has no multi-GPU path; this module adds the one the 1 Mi-token
 configuration needs.
 """
@@ -139,6 +144,20 @@ class KVSplit:
         o_r, l_r = self.partial(q, k_local, v_local, ids, kv_blocks, counts)
         return self.merge(o_r, l_r)
 
+    def run_peer(self, exchange, q, k_local, v_local, ids, kv_blocks, counts=None):
+        """Same result as `run`, bit for bit, without the send/recv step: the attention kernel writes this
+        rank's partial into `exchange` (a PeerExchange of B*Hq*Sq rows made by every rank of the group), and
+        the merge kernel reads this rank's slice of rows from every rank's exchange memory. GPU only."""
+        from .q_centric import attention_out
+        rows = q.shape[0] * q.shape[1] * q.shape[2]
+        if rows != exchange.rows or exchange.ranks != self.ranks or exchange.rank != self.rank:
+            raise ValueError("the exchange was made for another geometry or group")
+        ids_r, counts_r = self.filter_fn(ids, counts, kv_blocks, self.ranks, self.rank)
+        exchange.begin()                                   # every reader of the previous partial has finished
+        attention_out(q, k_local, v_local, ids_r, exchange.o.view(q.shape), counts_r, exchange.lse.view(q.shape[:3]))
+        exchange.publish()                                 # my partial of this step is complete
+        return exchange.merge()
+
     # ------------------------------------------------------------------ pipelined form
     def chunks(self, q, heads_per_chunk=2):
         """(group, first head, heads) chunks of q [B,Hq,Sq,128] seen as [groups, G, Sq, 128] with Hkv = 1 per
@@ -208,6 +227,129 @@ class KVSplit:
         if getattr(self, "_side", None) is None:
             self._side = torch.cuda.Stream(device=device)
         return self._side
+
+
+class PeerExchange:
+    """Exchange memory of one rank for `KVSplit.run_peer`: partial O [rows, 128] bf16, partial LSE [rows] fp32 and
+    two rows of flag words (ready[R], done[R]), allocated by the library, mapped by every other rank of `group`
+    (all ranks of the group must be processes on one machine whose GPUs have peer access). Collective: every rank
+    of the group constructs it at the same point. `wait_ms` bounds every wait on a flag another GPU writes; when it
+    runs out the kernel records a status code (`device_status()` raises) instead of hanging."""
+
+    def __init__(self, rows, device, group=None, wait_ms=4000):
+        import ctypes
+        from . import _lib
+        self.group, self.ranks, self.rank = group, dist.get_world_size(group), dist.get_rank(group)
+        if rows % self.ranks:
+            raise ValueError("B*Hq*Sq must be divisible by the number of KV ranks")
+        if self.ranks not in (1, 2, 4, 8):
+            raise ValueError("the peer merge serves 1, 2, 4 or 8 KV ranks")
+        self.rows, self.per, self.device, self.wait_ms, self.epoch = rows, rows // self.ranks, torch.device(device), wait_ms, 0
+        self.o_bytes = rows * 256
+        self.lse_off = self.o_bytes
+        self.flag_off = (self.lse_off + rows * 4 + 255) // 256 * 256
+        self.bytes = self.flag_off + 256
+        L = _lib.lib()
+        base, handle = ctypes.c_void_p(), ctypes.create_string_buffer(64)
+        with torch.cuda.device(self.device):
+            _lib.check(L.sparse_b200_peer_alloc(ctypes.c_int64(self.bytes), ctypes.byref(base), handle))
+            self.base = base.value
+            handles = [None] * self.ranks
+            dist.all_gather_object(handles, handle.raw, group=group)
+            self.bases, problem = [], None
+            for r, h in enumerate(handles):
+                if r == self.rank:
+                    self.bases.append(self.base)
+                    continue
+                peer = ctypes.c_void_p()
+                rc = L.sparse_b200_peer_open(ctypes.create_string_buffer(h, 64), ctypes.byref(peer))
+                if rc != 0:
+                    problem = f"rank {self.rank} cannot map the memory of rank {r}: {L.sparse_b200_last_error().decode()}"
+                    break
+                self.bases.append(peer.value)
+            problems = [None] * self.ranks
+            dist.all_gather_object(problems, problem, group=group)      # all ranks go on, or none
+            if any(problems):
+                for r, b in enumerate(self.bases):
+                    if r != self.rank:
+                        L.sparse_b200_peer_close(ctypes.c_void_p(b))
+                dist.barrier(group=group)
+                L.sparse_b200_peer_free(ctypes.c_void_p(self.base))
+                self.base = None
+                raise _lib.SparseB200Error("; ".join(p for p in problems if p))
+        self.o = _wrap(self.base, (rows, 128), torch.bfloat16, self.device, self)
+        self.lse = _wrap(self.base + self.lse_off, (rows,), torch.float32, self.device, self)
+        self.flags = _wrap(self.base + self.flag_off, (2, 32), torch.int32, self.device, self)
+        # flag words: ready[j] at flag_off + 4*j, done[j] at flag_off + 128 + 4*j (j = the rank that writes it)
+        arr = ctypes.c_void_p * self.ranks
+        self._ready_targets = arr(*[b + self.flag_off + 4 * self.rank for b in self.bases])
+        self._done_targets = arr(*[b + self.flag_off + 128 + 4 * self.rank for b in self.bases])
+        self._parts = arr(*[b + self.rank * self.per * 256 for b in self.bases])
+        self._lses = arr(*[b + self.lse_off + self.rank * self.per * 4 for b in self.bases])
+        self.out = torch.empty((self.per, 128), dtype=torch.bfloat16, device=self.device)
+        self.out_lse = torch.empty((self.per,), dtype=torch.float32, device=self.device)
+
+    def begin(self):
+        """Opens a step: waits (on the stream) until every rank has finished reading the previous partial."""
+        import ctypes
+        from . import _lib
+        self.epoch += 1
+        if self.epoch > 1:
+            with torch.cuda.device(self.device):
+                _lib.check(_lib.lib().sparse_b200_peer_wait(
+                    ctypes.c_void_p(self.base + self.flag_off + 128), self.ranks, self.epoch - 1, self.wait_ms,
+                    _lib.current_stream()))
+
+    def publish(self):
+        from . import _lib
+        with torch.cuda.device(self.device):
+            _lib.check(_lib.lib().sparse_b200_peer_signal(self._ready_targets, self.ranks, self.epoch,
+                                                          _lib.current_stream()))
+
+    def merge(self):
+        """Merged rows [rank*rows/R, (rank+1)*rows/R) -> (O [rows/R, 128] bf16, LSE [rows/R] fp32); then tells every
+        rank that this rank has finished reading."""
+        import ctypes
+        from . import _lib
+        with torch.cuda.device(self.device):
+            L = _lib.lib()
+            _lib.check(L.sparse_b200_combine_peer(
+                self._parts, self._lses, ctypes.c_void_p(self.base + self.flag_off), self.epoch, self.wait_ms,
+                _lib.ptr(self.out), _lib.ptr(self.out_lse), ctypes.c_int64(self.per), self.ranks, _lib.current_stream()))
+            _lib.check(L.sparse_b200_peer_signal(self._done_targets, self.ranks, self.epoch, _lib.current_stream()))
+        return self.out, self.out_lse
+
+    def close(self):
+        """Collective: all ranks have finished their steps (synchronises, then unmaps and frees)."""
+        from . import _lib
+        import ctypes
+        if self.base is None:
+            return
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group=self.group)
+        L = _lib.lib()
+        with torch.cuda.device(self.device):
+            for r, b in enumerate(self.bases):
+                if r != self.rank:
+                    L.sparse_b200_peer_close(ctypes.c_void_p(b))
+            dist.barrier(group=self.group)
+            self.o = self.lse = self.flags = None
+            L.sparse_b200_peer_free(ctypes.c_void_p(self.base))
+        self.base = None
+
+
+class _Raw:
+    def __init__(self, ptr, shape, typestr, owner):
+        self.owner = owner
+        self.__cuda_array_interface__ = {"shape": tuple(shape), "typestr": typestr, "data": (ptr, False), "version": 2}
+
+
+def _wrap(ptr, shape, dtype, device, owner):
+    """torch tensor over library-owned device memory (no copy; `owner` must outlive it)."""
+    if dtype == torch.bfloat16:         # no typestr for bf16: wrap as int16 and reinterpret
+        return torch.as_tensor(_Raw(ptr, shape, "<i2", owner), device=device).view(torch.bfloat16)
+    typestr = {torch.float32: "<f4", torch.int32: "<i4"}[dtype]
+    return torch.as_tensor(_Raw(ptr, shape, typestr, owner), device=device)
 
 
 class _NullContext:

@@ -1,5 +1,5 @@
-"""Two-GPU run of the KV-range split (NCCL send/recv exchange + Combine kernel) and
-of the head-group sharding. Skipped on a box with fewer than two GPUs."""
+"""Two-GPU run of the KV-range split (NCCL send/recv exchange + Combine kernel, and the merge
+over peer memory) and of the head-group sharding. Skipped on a box with fewer than two GPUs."""
 import os
 import socket
 
@@ -48,6 +48,16 @@ def _worker(rank, world, port, result):
         d = (o_slice.float().cpu() - ref_o).abs()
         ok = ok and d.max().item() <= 2e-2 and d.mean().item() <= 2e-3
         ok = ok and bool(torch.all((l_slice.cpu() - ref_l).abs() <= 1e-3 * ref_l.abs().clamp_min(1.0)))
+        # the same merge over peer memory (IPC-mapped exchange memory, flags, merge kernel loading the peer's
+        # rows): bit-identical to the send/recv form, over several steps of the ready / done hand-shake
+        ex = sharding.PeerExchange(whole_l.numel(), torch.device("cuda", rank))
+        for _ in range(4):
+            o_peer, l_peer = split.run_peer(ex, q.cuda(), k_local, v_local, ids, 64)
+            torch.cuda.synchronize()
+            sp.device_status()
+            ok = ok and torch.equal(o_peer.view(torch.int16), o_slice.view(torch.int16)) and torch.equal(l_peer, l_slice)
+        ok = ok and ex.flags[:, :world].tolist() == [[4] * world, [4] * world]
+        ex.close()
         # pipelined form: chunks of two heads, the exchange of one under the attention of the next
         qg, kg, vg, ig, _ = sharding.group_view(q.cuda(), k_local, v_local, ids, 0, 2)
         merged = split.run_pipelined(qg, kg, vg, ig, 64, heads_per_chunk=2)
