@@ -193,7 +193,15 @@ int sparse_b200_combine_tm(const void* partial_token_major, int partial_is_f32, 
  * combine_peer: rows [rows, 128] bf16 + LSE [rows] from `ranks` (1, 2, 4, 8) sources given as host
  * arrays of device pointers (each already at the caller's first row), merged in rank order with the
  * arithmetic of sparse_b200_combine (bit-identical rows); ready_flags (LOCAL, `ranks` words, or NULL)
- * are awaited >= value before the first load. */
+ * are awaited >= value before the first load.
+ * q_centric_scatter: the attention kernel with its output rows cut into `owners` (1..4) equal slices
+ * of the flattened [B*Hq*Sq] axis (whole 128-row tiles), slice j stored to outs[j] ([rows/owners, 128]
+ * bf16) and lses[j] ([rows/owners] fp32, required) - host arrays of device pointers that may lie in
+ * other GPUs' memory (peer_open): the kernel's TMA stores then carry every finished tile straight to
+ * the rank that merges it, under the remaining computation, and the merge reads local memory only. */
+int sparse_b200_q_centric_scatter(const void* q, const void* k, const void* v, const int32_t* block_idx,
+                                  const int32_t* block_count, void* const* outs, float* const* lses, int owners,
+                                  int batch, int hq, int hkv, int sq, int skv, int topk, void* stream);
 int sparse_b200_peer_alloc(int64_t bytes, void** ptr, void* handle64);
 int sparse_b200_peer_open(const void* handle64, void** ptr);
 int sparse_b200_peer_close(void* ptr);

@@ -151,6 +151,20 @@ int sparse_b200_q_centric_ws(const void* q, const void* k, const void* v, const 
   return launch_q_centric(a, static_cast<cudaStream_t>(stream));
 }
 
+int sparse_b200_q_centric_scatter(const void* q, const void* k, const void* v, const int32_t* block_idx,
+                                  const int32_t* block_count, void* const* outs, float* const* lses, int owners,
+                                  int batch, int hq, int hkv, int sq, int skv, int topk, void* stream) {
+  REQUIRE(outs && lses && owners >= 1 && owners <= 4, "1 to 4 destinations, as host arrays of device pointers");
+  REQUIRE(outs[0] && lses[0], "null destination");
+  int rc = check_attention(q, k, v, block_idx, outs[0], batch, hq, hkv, sq, skv, topk, 1);
+  if (rc) return rc;
+  QCentricArgs a{q, k, v, block_idx, block_count, outs[0], lses[0], batch, hq, hkv, sq, skv, topk, 1, 0};
+  a.owners = owners;
+  a.owner_out = outs;
+  a.owner_lse = lses;
+  return launch_q_centric(a, static_cast<cudaStream_t>(stream));
+}
+
 int sparse_b200_q_centric_partial(const void* q, const void* k, const void* v, const int32_t* seg_block_idx,
                                   const int32_t* seg_block_count, void* partial_out, float* partial_lse,
                                   int nseg, int partial_is_f32, int batch, int hq, int hkv, int sq, int skv,

@@ -38,6 +38,11 @@ struct QCentricArgs {
   int batch, hq, hkv, sq, skv, topk, nseg, out_f32;
   void* tail_ws = nullptr;      // optional workspace for balancing the last round of items (q_centric.cu)
   long long tail_bytes = 0;
+  // scatter launch: the flattened rows are cut into `owners` equal slices; slice 0 goes to (out, lse), slice j to
+  // (owner_out[j], owner_lse[j]) - host arrays of device pointers, possibly in other GPUs' memory
+  int owners = 1;
+  void* const* owner_out = nullptr;
+  float* const* owner_lse = nullptr;
 };
 int launch_q_centric(const QCentricArgs& a, cudaStream_t stream);
 

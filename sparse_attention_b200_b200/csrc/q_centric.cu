@@ -217,11 +217,37 @@ struct IdCursor {
   }
 };
 
-template <bool OUT_F32>
+// Scatter launches (one segment, bf16): the flattened [B*Hq*Sq] rows are cut into `slices` equal runs of
+// slice_tiles 128-row tiles; slice 0 goes to (out, lse) through o_map, slice j > 0 to (out[j-1], lse[j-1]) through
+// m[j-1] - memory that may belong to another GPU and be mapped into this process (the KV-range split across
+// GPUs: every finished tile travels to the rank that merges it while the kernel computes the next ones).
+// A kernel parameter of its own, and an instantiation of its own, so that the ordinary launch keeps its
+// parameter block and register allocation.
+constexpr int MAX_SLICES = 4;
+struct ScatterOn {
+  CUtensorMap m[MAX_SLICES - 1];
+  void* out[MAX_SLICES - 1];
+  float* lse[MAX_SLICES - 1];
+  int slices, slice_tiles;
+};
+struct ScatterOff {};
+
+// slice of the tile that starts at out_row; out_row becomes the row within the slice
+__device__ __forceinline__ int slice_of(const ScatterOn& sc, long long& out_row) {
+  const int tile = static_cast<int>(out_row >> 7);            // 32-bit arithmetic on tile numbers, no division
+  const int d = (tile >= sc.slice_tiles ? 1 : 0) + (tile >= 2 * sc.slice_tiles ? 1 : 0) + (tile >= 3 * sc.slice_tiles ? 1 : 0);
+  out_row = static_cast<long long>(tile - d * sc.slice_tiles) << 7;
+  return d;
+}
+__device__ __forceinline__ int slice_of(const ScatterOff&, long long&) { return 0; }
+
+template <bool OUT_F32, typename Scatter>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 q_centric_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
                  const __grid_constant__ CUtensorMap v_map, const __grid_constant__ CUtensorMap o_map,
-                 const __grid_constant__ CUtensorMap o_tail_map, const Params p) {
+                 const __grid_constant__ CUtensorMap o_tail_map, const Params p,
+                 const __grid_constant__ Scatter sc) {
+  constexpr bool SCATTER = sizeof(Scatter) > 1;
   extern __shared__ unsigned char smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
@@ -575,6 +601,8 @@ q_centric_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
       decode_item(p, item, s);
       const Stream& me = s[q];
       if (!me.valid) continue;
+      // (scatter launches look their destination up where they store, after the loop: nothing more to keep in
+      // registers while the softmax runs)
       const long long orow = me.out_row + row_in_tile;
       float* lse_dst = me.tail ? p.tail_lse : p.lse;
       if (me.count == 0) {
@@ -583,14 +611,26 @@ q_centric_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
           lse_dst[orow] = -INFINITY;
           continue;
         }
+        void* out_base = p.out;
+        long long zrow = orow;
+        float* zlse = p.lse;
+        if constexpr (SCATTER) {
+          long long tile_row = me.out_row;
+          const int slice = slice_of(sc, tile_row);
+          zrow = tile_row + row_in_tile;
+          if (slice) {
+            out_base = sc.out[slice - 1];
+            zlse = sc.lse[slice - 1];
+          }
+        }
         if (OUT_F32) {
-          float4* dst = reinterpret_cast<float4*>(static_cast<float*>(p.out) + orow * HEAD_DIM);
+          float4* dst = reinterpret_cast<float4*>(static_cast<float*>(out_base) + zrow * HEAD_DIM);
           for (int c = 0; c < HEAD_DIM / 4; ++c) dst[c] = make_float4(0.f, 0.f, 0.f, 0.f);
         } else {
-          uint4* dst = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.out) + orow * HEAD_DIM);
+          uint4* dst = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(out_base) + zrow * HEAD_DIM);
           for (int c = 0; c < HEAD_DIM / 8; ++c) dst[c] = make_uint4(0u, 0u, 0u, 0u);
         }
-        if (p.lse) p.lse[orow] = -INFINITY;
+        if (zlse) zlse[zrow] = -INFINITY;
         continue;
       }
       float row_max = 0.f, row_sum = 0.f;
@@ -683,7 +723,14 @@ q_centric_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
       __syncwarp();
       if (lane == 0) *handed_ptr = handed + 1;
       stats[q * TILE + row_in_tile] = 1.0f / row_sum;
-      if (lse_dst) lse_dst[orow] = (row_max + log2f(row_sum)) * 0.6931471805599453f;
+      if constexpr (SCATTER) {
+        long long tile_row = s[q].out_row;
+        const int slice = slice_of(sc, tile_row);
+        float* dst = slice ? sc.lse[slice - 1] : p.lse;
+        dst[tile_row + row_in_tile] = (row_max + log2f(row_sum)) * 0.6931471805599453f;
+      } else {
+        if (lse_dst) lse_dst[orow] = (row_max + log2f(row_sum)) * 0.6931471805599453f;
+      }
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(BAR_STATS_FULL + q));
     }
@@ -715,8 +762,13 @@ q_centric_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constan
         const float inv = stats[q * TILE + quarter * 32 + lane];
         __syncwarp();
         if (lane == 0) mbar_arrive(bar(BAR_STATS_EMPTY + q));
-        const int out_row32 = static_cast<int>(me.out_row) + quarter * 32;
+        long long tile_row = me.out_row;
         const CUtensorMap* out_map = me.tail ? &o_tail_map : &o_map;
+        if constexpr (SCATTER) {
+          const int slice = slice_of(sc, tile_row);
+          if (slice) out_map = &sc.m[slice - 1];
+        }
+        const int out_row32 = static_cast<int>(tile_row) + quarter * 32;
         if (lane == 0) bulk_wait_read0();            // earlier stores have left the staging tile
         __syncwarp();
         if (OUT_F32) {
@@ -902,7 +954,7 @@ int launch_q_centric(const QCentricArgs& a, cudaStream_t stream) {
   p.tail_lse = nullptr;
   __nv_bfloat16* tail_out = nullptr;
   const int rounds = p.num_items / grid, rem = p.num_items - rounds * grid;
-  if (a.tail_ws && a.nseg == 1 && !a.out_f32 && rem > 0 && 2 * rem <= grid && rounds >= 1 && rounds <= 8 && a.topk >= 8) {
+  if (a.tail_ws && a.owners <= 1 && a.nseg == 1 && !a.out_f32 && rem > 0 && 2 * rem <= grid && rounds >= 1 && rounds <= 8 && a.topk >= 8) {
     int parts = grid / rem;
     if (parts > 4) parts = 4;
     if (parts > a.topk / 4) parts = a.topk / 4;  // at least four blocks per piece
@@ -930,14 +982,44 @@ int launch_q_centric(const QCentricArgs& a, cudaStream_t stream) {
   if (tail_out && encode_out_map(&omt, tail_out, static_cast<uint64_t>(p.num_virtual - p.tail_first) * 2 * TILE, false))
     return set_error(SB_ERR_CUDA, "cuTensorMapEncodeTiled failed for the tail workspace");
 
-  auto kernel = a.out_f32 ? q_centric_kernel<true> : q_centric_kernel<false>;
+  if (a.owners > 1) {
+    // scatter launch: slice j of the rows has a destination of its own (a.out / a.lse are slice 0's)
+    const long long rows = static_cast<long long>(a.batch) * a.hq * a.sq;
+    if (a.owners > MAX_SLICES || a.nseg != 1 || a.out_f32 || rows % a.owners || (rows / a.owners) % TILE || !a.lse)
+      return set_error(SB_ERR_INVALID,
+                       "scatter launches: 2 to 4 equal slices of whole 128-row tiles, one segment, bf16, LSE required");
+    ScatterOn sc{};
+    sc.slices = a.owners;
+    sc.slice_tiles = static_cast<int>(rows / a.owners / TILE);
+    if (encode_out_map(&om, a.out, static_cast<uint64_t>(rows / a.owners), false))
+      return set_error(SB_ERR_CUDA, "cuTensorMapEncodeTiled failed for slice 0");
+    for (int j = 1; j < MAX_SLICES; ++j) sc.m[j - 1] = om;
+    for (int j = 1; j < a.owners; ++j) {
+      if (!a.owner_out[j] || !a.owner_lse[j] || (reinterpret_cast<uintptr_t>(a.owner_out[j]) & 15u))
+        return set_error(SB_ERR_INVALID, "every slice needs a 16-byte aligned output and an LSE pointer");
+      sc.out[j - 1] = a.owner_out[j];
+      sc.lse[j - 1] = a.owner_lse[j];
+      if (encode_out_map(&sc.m[j - 1], a.owner_out[j], static_cast<uint64_t>(rows / a.owners), false))
+        return set_error(SB_ERR_CUDA, "cuTensorMapEncodeTiled failed for a slice's destination");
+    }
+    if (!(ctx->tc_attr & (1 << 19))) {
+      cudaError_t e = cudaFuncSetAttribute(q_centric_kernel<false, ScatterOn>,
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+      if (e != cudaSuccess) return set_error(SB_ERR_CUDA, cudaGetErrorString(e));
+      ctx->tc_attr |= (1 << 19);
+    }
+    q_centric_kernel<false, ScatterOn><<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(qm, km, vm, om, om, p, sc);
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? SB_OK : set_error(SB_ERR_CUDA, cudaGetErrorString(e));
+  }
+  auto kernel = a.out_f32 ? q_centric_kernel<true, ScatterOff> : q_centric_kernel<false, ScatterOff>;
   int& configured = a.out_f32 ? ctx->qc_attr_f32 : ctx->qc_attr_bf16;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
     if (e != cudaSuccess) return set_error(SB_ERR_CUDA, cudaGetErrorString(e));
     configured = 1;
   }
-  kernel<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(qm, km, vm, om, omt, p);
+  kernel<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(qm, km, vm, om, omt, p, ScatterOff{});
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return set_error(SB_ERR_CUDA, cudaGetErrorString(e));
   if (tail_out) {

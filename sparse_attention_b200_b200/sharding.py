@@ -158,6 +158,30 @@ class KVSplit:
         exchange.publish()                                 # my partial of this step is complete
         return exchange.merge()
 
+    def run_scatter(self, exchange, q, k_local, v_local, ids, kv_blocks, counts=None):
+        """Same result again, with the transfer inside the attention kernel: every finished 128-row tile of this
+        rank's partial is stored (TMA store, LSE with plain stores) straight into the memory of the rank that
+        merges it, under the remaining computation; the merge then reads local memory only. Up to 4 KV ranks;
+        B*Hq*Sq / ranks must be whole 128-row tiles. GPU only."""
+        import ctypes
+        from . import _lib
+        rows = q.shape[0] * q.shape[1] * q.shape[2]
+        if rows != exchange.rows or exchange.ranks != self.ranks or exchange.rank != self.rank:
+            raise ValueError("the exchange was made for another geometry or group")
+        if self.ranks > 4 or exchange.per % 128:
+            raise ValueError("the scatter form serves up to 4 KV ranks and slices of whole 128-row tiles")
+        ids_r, counts_r = self.filter_fn(ids, counts, kv_blocks, self.ranks, self.rank)
+        b, hq, sq, _ = q.shape
+        hkv, skv = k_local.shape[1:3]
+        exchange.begin()
+        with torch.cuda.device(q.device):
+            _lib.check(_lib.lib().sparse_b200_q_centric_scatter(
+                _lib.ptr(q), _lib.ptr(k_local), _lib.ptr(v_local), _lib.ptr(ids_r), _lib.ptr(counts_r),
+                exchange.slot_out, exchange.slot_lse, self.ranks, b, hq, hkv, sq, skv, int(ids_r.shape[-1]),
+                _lib.current_stream()))
+        exchange.publish()
+        return exchange.merge(slots=True)
+
     # ------------------------------------------------------------------ pipelined form
     def chunks(self, q, heads_per_chunk=2):
         """(group, first head, heads) chunks of q [B,Hq,Sq,128] seen as [groups, G, Sq, 128] with Hkv = 1 per
@@ -286,6 +310,13 @@ class PeerExchange:
         self._done_targets = arr(*[b + self.flag_off + 128 + 4 * self.rank for b in self.bases])
         self._parts = arr(*[b + self.rank * self.per * 256 for b in self.bases])
         self._lses = arr(*[b + self.lse_off + self.rank * self.per * 4 for b in self.bases])
+        # scatter form: the same memory seen as R slots of `per` rows, slot r = what rank r computed for MY rows.
+        # slot_out[j] / slot_lse[j]: where this rank's rows of owner j go (slot `rank` of rank j's memory);
+        # _local_parts / _local_lses: the R slots of my own memory, for the merge
+        self.slot_out = arr(*[b + self.rank * self.per * 256 for b in self.bases])
+        self.slot_lse = arr(*[b + self.lse_off + self.rank * self.per * 4 for b in self.bases])
+        self._local_parts = arr(*[self.base + r * self.per * 256 for r in range(self.ranks)])
+        self._local_lses = arr(*[self.base + self.lse_off + r * self.per * 4 for r in range(self.ranks)])
         self.out = torch.empty((self.per, 128), dtype=torch.bfloat16, device=self.device)
         self.out_lse = torch.empty((self.per,), dtype=torch.float32, device=self.device)
 
@@ -306,15 +337,18 @@ class PeerExchange:
             _lib.check(_lib.lib().sparse_b200_peer_signal(self._ready_targets, self.ranks, self.epoch,
                                                           _lib.current_stream()))
 
-    def merge(self):
+    def merge(self, slots=False):
         """Merged rows [rank*rows/R, (rank+1)*rows/R) -> (O [rows/R, 128] bf16, LSE [rows/R] fp32); then tells every
-        rank that this rank has finished reading."""
+        rank that this rank has finished reading. slots=False: every rank's memory holds its whole partial and the
+        kernel loads this rank's rows from each of them; slots=True (after a scatter launch): the R partials of this
+        rank's rows lie in its own memory."""
         import ctypes
         from . import _lib
         with torch.cuda.device(self.device):
             L = _lib.lib()
             _lib.check(L.sparse_b200_combine_peer(
-                self._parts, self._lses, ctypes.c_void_p(self.base + self.flag_off), self.epoch, self.wait_ms,
+                self._local_parts if slots else self._parts, self._local_lses if slots else self._lses,
+                ctypes.c_void_p(self.base + self.flag_off), self.epoch, self.wait_ms,
                 _lib.ptr(self.out), _lib.ptr(self.out_lse), ctypes.c_int64(self.per), self.ranks, _lib.current_stream()))
             _lib.check(L.sparse_b200_peer_signal(self._done_targets, self.ranks, self.epoch, _lib.current_stream()))
         return self.out, self.out_lse

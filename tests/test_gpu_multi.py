@@ -57,6 +57,12 @@ def _worker(rank, world, port, result):
             sp.device_status()
             ok = ok and torch.equal(o_peer.view(torch.int16), o_slice.view(torch.int16)) and torch.equal(l_peer, l_slice)
         ok = ok and ex.flags[:, :world].tolist() == [[4] * world, [4] * world]
+        # ... and with the transfer inside the attention kernel (tiles stored straight into the merging rank's memory)
+        for _ in range(3):
+            o_sc, l_sc = split.run_scatter(ex, q.cuda(), k_local, v_local, ids, 64)
+            torch.cuda.synchronize()
+            sp.device_status()
+            ok = ok and torch.equal(o_sc.view(torch.int16), o_slice.view(torch.int16)) and torch.equal(l_sc, l_slice)
         ex.close()
         # pipelined form: chunks of two heads, the exchange of one under the attention of the next
         qg, kg, vg, ig, _ = sharding.group_view(q.cuda(), k_local, v_local, ids, 0, 2)

@@ -130,6 +130,58 @@ def test_run_peer_with_one_rank_is_the_attention_itself():
             assert torch.equal(o.view(torch.int16), plain_o.reshape(-1, 128).view(torch.int16))
             assert torch.equal(l, plain_l.reshape(-1))
         assert ex.flags[0, 0].item() == 3 and ex.flags[1, 0].item() == 3
+        o, l = split.run_scatter(ex, qc, kc, vc, ids, 16)          # one slice: the scatter form degenerates too
+        torch.cuda.synchronize()
+        m.device_status()
+        assert torch.equal(o.view(torch.int16), plain_o.reshape(-1, 128).view(torch.int16))
+        assert torch.equal(l, plain_l.reshape(-1))
         ex.close()
     finally:
         dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("owners,shape", [(2, (1, 8, 1, 512, 2048, 6)), (4, (2, 4, 2, 256, 1024, 5)),
+                                          (3, (1, 3, 3, 384, 1024, 4)), (1, (1, 2, 1, 128, 512, 3))])
+def test_scatter_launch_writes_each_slice_of_rows_to_its_destination(owners, shape):
+    """sparse_b200_q_centric_scatter with the destinations in local memory: slice j of the flattened rows lands in
+    buffer j, bit-identical to the plain call (pair mode, split mode, ragged counts with empty lists)."""
+    from sparse_attention_b200_b200 import _lib
+    m = sp()
+    b, hq, hkv, sq, skv, topk = shape
+    g = torch.Generator().manual_seed(sum(shape))
+    q = torch.randn((b, hq, sq, 128), generator=g).to(torch.bfloat16).cuda()
+    k = torch.randn((b, hkv, skv, 128), generator=g).to(torch.bfloat16).cuda()
+    v = torch.randn((b, hkv, skv, 128), generator=g).to(torch.bfloat16).cuda()
+    nb, qb = skv // 128, sq // 128
+    ids = torch.stack([torch.randperm(nb, generator=g)[:topk] for _ in range(b * hkv * qb)]).to(torch.int32) \
+        .reshape(b, hkv, qb, topk).cuda()
+    counts = torch.randint(0, topk + 1, (b, hkv, qb), generator=g, dtype=torch.int32).cuda()
+    ref = torch.empty_like(q)
+    ref_l = torch.empty(q.shape[:3], device="cuda")
+    m.attention_out(q, k, v, ids, ref, counts, ref_l)
+    rows = b * hq * sq
+    per = rows // owners
+    outs = [torch.full((per, 128), float("nan"), dtype=torch.bfloat16, device="cuda") for _ in range(owners)]
+    lses = [torch.full((per,), float("nan"), device="cuda") for _ in range(owners)]
+    arr = ctypes.c_void_p * owners
+    _lib.check(_lib.lib().sparse_b200_q_centric_scatter(
+        _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(ids), _lib.ptr(counts), arr(*[t.data_ptr() for t in outs]),
+        arr(*[t.data_ptr() for t in lses]), owners, b, hq, hkv, sq, skv, topk, _lib.current_stream()))
+    torch.cuda.synchronize()
+    m.device_status()
+    assert torch.equal(torch.cat(outs).view(torch.int16), ref.reshape(-1, 128).view(torch.int16))
+    assert torch.equal(torch.cat(lses).view(torch.int32), ref_l.reshape(-1).view(torch.int32))
+
+
+def test_scatter_launch_rejects_slices_that_cut_a_tile():
+    from sparse_attention_b200_b200 import _lib
+    q = torch.zeros((1, 3, 128, 128), dtype=torch.bfloat16, device="cuda")
+    k = torch.zeros((1, 3, 256, 128), dtype=torch.bfloat16, device="cuda")
+    ids = torch.zeros((1, 3, 1, 1), dtype=torch.int32, device="cuda")
+    outs = [torch.empty((192, 128), dtype=torch.bfloat16, device="cuda") for _ in range(2)]
+    lses = [torch.empty((192,), device="cuda") for _ in range(2)]
+    arr = ctypes.c_void_p * 2
+    rc = _lib.lib().sparse_b200_q_centric_scatter(
+        _lib.ptr(q), _lib.ptr(k), _lib.ptr(k), _lib.ptr(ids), None, arr(*[t.data_ptr() for t in outs]),
+        arr(*[t.data_ptr() for t in lses]), 2, 1, 3, 3, 128, 256, 1, _lib.current_stream())
+    assert rc == _lib.ERR_INVALID                    # 384 rows / 2 = 192: not whole 128-row tiles
