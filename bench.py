@@ -585,19 +585,34 @@ def kv_split_record(sp, sharding, dist, name, cfg, world, rank, dev, barrier, st
         ex = sharding.PeerExchange(wl.q.shape[0] * wl.q.shape[1] * wl.q.shape[2], dev, kv_group)
     except Exception as e:          # raised on every rank of the pair alike (no IPC / peer access between the GPUs)
         ex, peer = None, {"unavailable": str(e)[:200]}
+    def arm_ok():
+        # status word of every rank of the job, read together: either all ranks keep an arm's result or none does
+        code = sp.lib().sparse_b200_device_status(1)
+        t_ = torch.tensor([1 if code != 0 else 0], device=dev, dtype=torch.int32)
+        dist.all_reduce(t_, op=dist.ReduceOp.MAX)
+        return t_.item() == 0, code
     if ex is not None:
         def step_peer():
             res["p"] = split.run_peer(ex, wl.q, k_loc, v_loc, wl.ids, nb)
-        peer["ms_per_step"] = timed(step_peer, steps, 2, barrier)
-        sp.device_status()
-        peer["identical_to_send_recv"] = bool(torch.equal(res["p"][0], res["u"][0]) and torch.equal(res["p"][1], res["u"][1]))
-        res.pop("p", None)
-        # ... and with the transfer inside the attention kernel: tiles stored straight into the merging rank's memory
+
         def step_scatter():
             res["s"] = split.run_scatter(ex, wl.q, k_loc, v_loc, wl.ids, nb)
-        peer["scatter_ms_per_step"] = timed(step_scatter, steps, 2, barrier)
-        sp.device_status()
-        peer["scatter_identical"] = bool(torch.equal(res["s"][0], res["u"][0]) and torch.equal(res["s"][1], res["u"][1]))
+        ms_p = timed(step_peer, steps, 2, barrier)
+        ok_p, code = arm_ok()
+        if ok_p:
+            peer["ms_per_step"] = ms_p
+            peer["identical_to_send_recv"] = bool(torch.equal(res["p"][0], res["u"][0]) and torch.equal(res["p"][1], res["u"][1]))
+            # ... and with the transfer inside the attention kernel: tiles stored straight into the merging rank's memory
+            ms_s = timed(step_scatter, steps, 2, barrier)
+            ok_s, code = arm_ok()
+            if ok_s:
+                peer["scatter_ms_per_step"] = ms_s
+                peer["scatter_identical"] = bool(torch.equal(res["s"][0], res["u"][0]) and torch.equal(res["s"][1], res["u"][1]))
+            else:
+                peer["scatter_failed"] = f"a bounded wait ran out on some rank (status here 0x{code:x})"
+        else:
+            peer = {"unavailable": f"a bounded wait ran out on some rank (status here 0x{code:x})"}
+        res.pop("p", None)
         res.pop("s", None)
         ex.close()
     res.pop("u", None)
@@ -636,12 +651,15 @@ def kv_split_record(sp, sharding, dist, name, cfg, world, rank, dev, barrier, st
                        "the peer's rows over NVLink (no NCCL call on the data path)"}
         if not peer_differs:
             forms["peer_merge"] = ms_peer
-        scatter = {"ms_per_step": ms_scatter, "value": flops / (ms_scatter * 1e-3) / 1e12, "unit": "TFLOP/s",
-                   "identical_to_send_recv": not scatter_differs,
-                   "how": "the attention kernel's TMA stores carry every finished tile into the exchange memory of the "
-                          "rank that merges it (NVLink, under the computation); the merge reads local memory only"}
-        if not scatter_differs:
-            forms["scatter_merge"] = ms_scatter
+        if ms_scatter > 0:
+            scatter = {"ms_per_step": ms_scatter, "value": flops / (ms_scatter * 1e-3) / 1e12, "unit": "TFLOP/s",
+                       "identical_to_send_recv": not scatter_differs,
+                       "how": "the attention kernel's TMA stores carry every finished tile into the exchange memory of "
+                              "the rank that merges it (NVLink, under the computation); the merge reads local memory only"}
+            if not scatter_differs:
+                forms["scatter_merge"] = ms_scatter
+        else:
+            scatter = {"unavailable": "a bounded wait ran out on some rank"}
     best = min(forms, key=forms.get)
     ms_best = forms[best]
     return {"sharding": f"{head_shards} head-group shard(s) x {kvs} KV ranges", "ms_per_step": ms_best, "steps": steps,

@@ -276,12 +276,17 @@ class PeerExchange:
         L = _lib.lib()
         base, handle = ctypes.c_void_p(), ctypes.create_string_buffer(64)
         with torch.cuda.device(self.device):
-            _lib.check(L.sparse_b200_peer_alloc(ctypes.c_int64(self.bytes), ctypes.byref(base), handle))
-            self.base = base.value
+            # every failure below is first told to the whole group, then raised by every rank alike
+            rc = L.sparse_b200_peer_alloc(ctypes.c_int64(self.bytes), ctypes.byref(base), handle)
+            problem = None if rc == 0 else \
+                f"rank {self.rank} cannot allocate exchange memory: {L.sparse_b200_last_error().decode()}"
+            self.base = base.value if rc == 0 else None
             handles = [None] * self.ranks
-            dist.all_gather_object(handles, handle.raw, group=group)
-            self.bases, problem = [], None
+            dist.all_gather_object(handles, handle.raw if rc == 0 else None, group=group)
+            self.bases = []
             for r, h in enumerate(handles):
+                if problem or any(x is None for x in handles):
+                    break
                 if r == self.rank:
                     self.bases.append(self.base)
                     continue
@@ -298,7 +303,8 @@ class PeerExchange:
                     if r != self.rank:
                         L.sparse_b200_peer_close(ctypes.c_void_p(b))
                 dist.barrier(group=group)
-                L.sparse_b200_peer_free(ctypes.c_void_p(self.base))
+                if self.base is not None:
+                    L.sparse_b200_peer_free(ctypes.c_void_p(self.base))
                 self.base = None
                 raise _lib.SparseB200Error("; ".join(p for p in problems if p))
         self.o = _wrap(self.base, (rows, 128), torch.bfloat16, self.device, self)
