@@ -317,12 +317,10 @@ class PeerExchange:
         self._parts = arr(*[b + self.rank * self.per * 256 for b in self.bases])
         self._lses = arr(*[b + self.lse_off + self.rank * self.per * 4 for b in self.bases])
         # scatter form: the same memory seen as R slots of `per` rows, slot r = what rank r computed for MY rows.
-        # slot_out[j] / slot_lse[j]: where this rank's rows of owner j go (slot `rank` of rank j's memory);
-        # _local_parts / _local_lses: the R slots of my own memory, for the merge
+        # slot_out[j] / slot_lse[j]: where this rank's rows of owner j go (slot `rank` of rank j's memory); the R
+        # slots of my own memory are one rank-major [R, per, 128] / [R, per] pair for the merge
         self.slot_out = arr(*[b + self.rank * self.per * 256 for b in self.bases])
         self.slot_lse = arr(*[b + self.lse_off + self.rank * self.per * 4 for b in self.bases])
-        self._local_parts = arr(*[self.base + r * self.per * 256 for r in range(self.ranks)])
-        self._local_lses = arr(*[self.base + self.lse_off + r * self.per * 4 for r in range(self.ranks)])
         self.out = torch.empty((self.per, 128), dtype=torch.bfloat16, device=self.device)
         self.out_lse = torch.empty((self.per,), dtype=torch.float32, device=self.device)
 
@@ -352,8 +350,18 @@ class PeerExchange:
         from . import _lib
         with torch.cuda.device(self.device):
             L = _lib.lib()
+            if slots:
+                # the R partials of my rows are local and rank-major: wait for the ready flags, then the ordinary
+                # Combine kernel (two rows per thread group in flight: it runs at the memory roof)
+                _lib.check(L.sparse_b200_peer_wait(ctypes.c_void_p(self.base + self.flag_off), self.ranks, self.epoch,
+                                                   self.wait_ms, _lib.current_stream()))
+                _lib.check(L.sparse_b200_combine(
+                    ctypes.c_void_p(self.base), 0, ctypes.c_void_p(self.base + self.lse_off), _lib.ptr(self.out),
+                    _lib.ptr(self.out_lse), ctypes.c_int64(self.per), self.ranks, 1, _lib.current_stream()))
+                _lib.check(L.sparse_b200_peer_signal(self._done_targets, self.ranks, self.epoch, _lib.current_stream()))
+                return self.out, self.out_lse
             _lib.check(L.sparse_b200_combine_peer(
-                self._local_parts if slots else self._parts, self._local_lses if slots else self._lses,
+                self._parts, self._lses,
                 ctypes.c_void_p(self.base + self.flag_off), self.epoch, self.wait_ms,
                 _lib.ptr(self.out), _lib.ptr(self.out_lse), ctypes.c_int64(self.per), self.ranks, _lib.current_stream()))
             _lib.check(L.sparse_b200_peer_signal(self._done_targets, self.ranks, self.epoch, _lib.current_stream()))
