@@ -899,6 +899,53 @@ def reference_kv_centric(q, k, v, selected, ours, steps, barrier):
             "stages": stages, "max_abs_diff_out": diff, "max_abs_diff_lse": lse_diff}
 
 
+def run_peermerge(args):
+    """One GPU's share of the peer-memory merge, with the "peers" in local memory: combine_peer_kernel over R = 2
+    separate partial buffers (the kernel of KVSplit.run_peer; over NVLink its remote half is bound by the link) next
+    to the Combine kernel on one rank-major buffer (the local merge of KVSplit.run_scatter). 1 Mi rows by default
+    (--n overrides)."""
+    import ctypes
+    import torch
+    import sparse_attention_b200_b200 as sp
+    from sparse_attention_b200_b200 import _lib
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    rows, ranks = args.n or (1 << 20), 2
+    gen = torch.Generator(device=dev).manual_seed(3)
+    part = torch.randn((ranks, rows, 128), device=dev, generator=gen).to(torch.bfloat16)
+    lses = torch.randn((ranks, rows), device=dev, generator=gen)
+    out = torch.empty((rows, 128), dtype=torch.bfloat16, device=dev)
+    out_lse = torch.empty((rows,), device=dev)
+    ref = torch.empty_like(out)
+    ref_lse = torch.empty_like(out_lse)
+    L = sp.lib()
+    arr = ctypes.c_void_p * ranks
+    parts, ls = arr(*[part[r].data_ptr() for r in range(ranks)]), arr(*[lses[r].data_ptr() for r in range(ranks)])
+
+    def peer():
+        _lib.check(L.sparse_b200_combine_peer(parts, ls, None, 0, 1000, _lib.ptr(out), _lib.ptr(out_lse),
+                                              ctypes.c_int64(rows), ranks, _lib.current_stream()))
+
+    def plain():
+        _lib.check(L.sparse_b200_combine(_lib.ptr(part), 0, _lib.ptr(lses), _lib.ptr(ref), _lib.ptr(ref_lse),
+                                         ctypes.c_int64(rows), ranks, 1, _lib.current_stream()))
+    sync = torch.cuda.synchronize
+    steps = max(args.steps, 5)
+    ms_peer = timed(peer, steps, 3, sync)
+    ms_plain = timed(plain, steps, 3, sync)
+    sp.device_status()
+    peaks = measured_peaks()
+    byts = rows * (ranks * 256 + ranks * 4 + 260)
+    print(json.dumps({
+        "metric": "merge of 2 partial (O, LSE) per row, bf16", "unit": "GB/s", "n_gpus": 1, "steps": steps,
+        "config": {"workload": "peermerge", "rows": rows, "ranks": ranks,
+                   "l2": f"{byts / 1e9:.2f} GB per launch exceed the 126 MB L2"},
+        "combine_peer_kernel": {"ms": ms_peer, "gbs": byts / ms_peer / 1e6, "frac_hbm": byts / ms_peer / 1e6 / peaks["hbm"]},
+        "combine_few_kernel": {"ms": ms_plain, "gbs": byts / ms_plain / 1e6, "frac_hbm": byts / ms_plain / 1e6 / peaks["hbm"]},
+        "identical": bool(torch.equal(out, ref) and torch.equal(out_lse, ref_lse)),
+        "algorithmic_bytes": byts}))
+
+
 def run_kv_token(args):
     """The reference's own KV-centric benchmark shape (B8, Hq16, Hkv1, Sq = Skv = 4096, TopK 16,
     per-TOKEN independent lists; benchmarks/ch5_kv_centric/round11_final/RESULTS_RU.md:9-13)
@@ -1250,7 +1297,7 @@ def main():
     ap.add_argument("--kernel-only", action="store_true",
                     help="device-resident timing only (used for profiler captures): no e2e, parity, CPU baseline "
                          "or sub-records")
-    ap.add_argument("--workload", default=HEADLINE, choices=["kvtoken", "refcmp", "refsel", "varlen"] + sorted(CONFIGS),
+    ap.add_argument("--workload", default=HEADLINE, choices=["kvtoken", "refcmp", "refsel", "varlen", "peermerge"] + sorted(CONFIGS),
                     help=f"{HEADLINE} (default) is the headline workload; c1..c4 run the same way on their own shapes")
     ap.add_argument("--no-configs", action="store_true", help="skip the c1..c4 sub-record of the headline run")
     ap.add_argument("--no-kv-split", action="store_true", help="skip the KV-split sub-record of multi-GPU runs")
@@ -1265,6 +1312,8 @@ def main():
         run_refsel(args)
     elif args.workload == "varlen":
         run_varlen(args)
+    elif args.workload == "peermerge":
+        run_peermerge(args)
     elif args.impl == "reference":
         run_reference(args)
     else:
