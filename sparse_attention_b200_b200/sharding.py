@@ -162,7 +162,9 @@ class KVSplit:
         """Same result again, with the transfer inside the attention kernel: every finished 128-row tile of this
         rank's partial is stored (TMA store, LSE with plain stores) straight into the memory of the rank that
         merges it, under the remaining computation; the merge then reads local memory only. Up to 4 KV ranks;
-        B*Hq*Sq / ranks must be whole 128-row tiles. GPU only."""
+        B*Hq*Sq / ranks must be whole 128-row tiles. GPU only. (A scatter launch never cuts the items of a short
+        last round into pieces as `attention_out(balance=True)` may on launches of a few rounds; where that
+        applies the rows of that round can differ from `run` in the last bf16 bit.)"""
         import ctypes
         from . import _lib
         rows = q.shape[0] * q.shape[1] * q.shape[2]

@@ -144,6 +144,28 @@ def test_q_centric_random_shapes(shape):
     l = lse.cpu()
     assert torch.equal(torch.isinf(l) & (l < 0), ~fin)
     assert torch.all((l[fin] - ref_l[fin]).abs() <= 1e-3 * ref_l[fin].abs().clamp_min(1.0))
+    # the scatter launch (rows cut into 2-4 slices with destinations of their own) must write the same bits
+    import ctypes
+    from sparse_attention_b200_b200 import _lib
+    tiles = b * hq * qb
+    qc, kc, vc, idc = q.cuda(), k.cuda(), v.cuda(), ids.cuda()
+    cc = None if counts is None else counts.cuda()
+    plain, plain_l = torch.empty_like(out), torch.empty_like(lse)
+    m.attention_out(qc, kc, vc, idc, plain, cc, plain_l, balance=False)      # (scatter launches never balance a last round)
+    for owners in (2, 3, 4):
+        if tiles % owners:
+            continue
+        per = tiles // owners * 128
+        outs = [torch.full((per, 128), float("nan"), dtype=torch.bfloat16, device="cuda") for _ in range(owners)]
+        lses = [torch.full((per,), float("nan"), device="cuda") for _ in range(owners)]
+        arr = ctypes.c_void_p * owners
+        _lib.check(_lib.lib().sparse_b200_q_centric_scatter(
+            _lib.ptr(qc), _lib.ptr(kc), _lib.ptr(vc), _lib.ptr(idc), _lib.ptr(cc), arr(*[t.data_ptr() for t in outs]),
+            arr(*[t.data_ptr() for t in lses]), owners, b, hq, hkv, sq, skv, topk, _lib.current_stream()))
+        torch.cuda.synchronize()
+        m.device_status()
+        assert torch.equal(torch.cat(outs).view(torch.int16), plain.reshape(-1, 128).view(torch.int16)), owners
+        assert torch.equal(torch.cat(lses).view(torch.int32), plain_l.reshape(-1).view(torch.int32)), owners
 
 
 def _token_shapes(n, seed):
