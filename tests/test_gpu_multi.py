@@ -80,19 +80,20 @@ def _worker(rank, world, port, result):
             ok = ok and bool(torch.all((lc.cpu() - ref_lc).abs() <= 1e-3 * ref_lc.abs().clamp_min(1.0)))
         # head-group sharding: no collective, each rank its own groups
         a, b = sharding.group_range(2, world, rank)
-        qv, kv, vv, iv, _ = sharding.group_view(q.cuda(), k.cuda(), v.cuda(), ids, a, b)
-        og = sp.attention(qv, kv, vv, iv)
-        dg = (og.float().cpu().reshape(-1, 512, 128) - whole_o[0, a * 8:b * 8]).abs()
-        ok = ok and dg.max().item() <= 2e-2
+        if b > a:                                  # with more ranks than groups some ranks hold none
+            qv, kv, vv, iv, _ = sharding.group_view(q.cuda(), k.cuda(), v.cuda(), ids, a, b)
+            og = sp.attention(qv, kv, vv, iv)
+            dg = (og.float().cpu().reshape(-1, 512, 128) - whole_o[0, a * 8:b * 8]).abs()
+            ok = ok and dg.max().item() <= 2e-2
         result[rank] = bool(ok)
     finally:
         dist.destroy_process_group()
 
 
-def test_kv_split_and_group_sharding_two_gpus():
-    if torch.cuda.device_count() < 2:
-        pytest.skip("needs two GPUs")
-    world = 2
+@pytest.mark.parametrize("world", [2, 4])
+def test_kv_split_and_group_sharding(world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
     port = _free_port()
     ctx = mp.get_context("spawn")
     result = ctx.Manager().dict()
@@ -102,4 +103,4 @@ def test_kv_split_and_group_sharding_two_gpus():
     for p in procs:
         p.join(timeout=300)
         assert p.exitcode == 0
-    assert dict(result) == {0: True, 1: True}
+    assert dict(result) == {r: True for r in range(world)}
