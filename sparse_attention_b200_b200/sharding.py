@@ -1,6 +1,7 @@
 """Multi-GPU sharding of the hot path: one process per GPU, torch.distributed for the plumbing.
 
-Two ways to shard, both without TMA multicast or any load from a peer's memory:
+Two ways to shard (no TMA multicast anywhere; a peer's memory is touched only by this package's own kernels,
+with plain loads and stores, in the `PeerExchange` forms below):
 
 * by (batch, KV-head group): groups are independent in the indexer, in the
   attention kernel and in Combine, so ranks need no data-path collective
@@ -16,7 +17,9 @@ Two ways to shard, both without TMA multicast or any load from a peer's memory:
 `PeerExchange` + `KVSplit.run_peer` are the fused form of that exchange + Combine on one machine: every
 rank keeps its partial in memory the other ranks have mapped (CUDA IPC), flags tell when a partial is
 complete, and the merge kernel reads the peers' rows with plain loads over NVLink (no copy step, no
-NCCL call on the data path, no multicast; every cross-GPU wait is bounded).
+NCCL call on the data path, no multicast; every cross-GPU wait is bounded). `KVSplit.run_scatter` goes one
+step further: the attention kernel itself stores every finished tile into the exchange memory of the rank
+that merges it, so the transfer runs under the computation and the merge is local.
 
 The reference has no multi-GPU path; this module adds the one the 1 Mi-token
 configuration needs.
